@@ -1,0 +1,39 @@
+// Library-wide pieces of the C ABI: error strings, version, device check.
+#include "sp24_common.cuh"
+
+namespace sp24 {
+
+int check_device() {
+    // The answer is cached per device ordinal; the cache is written once per device and only ever
+    // with the same value, so concurrent first calls are harmless.
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return SP24_ERR_CUDA;
+    if (dev >= 0 && dev < 64 && cached[dev]) return cached[dev] == 1 ? SP24_OK : SP24_ERR_DEVICE;
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return SP24_ERR_CUDA;
+    const int ok = major == 10;
+    if (dev >= 0 && dev < 64) cached[dev] = ok ? 1 : 2;
+    return ok ? SP24_OK : SP24_ERR_DEVICE;
+}
+
+int launch_status() { return cudaGetLastError() == cudaSuccess ? SP24_OK : SP24_ERR_CUDA; }
+
+}  // namespace sp24
+
+extern "C" const char *sp24_strerror(int code) {
+    switch (code) {
+        case SP24_OK: return "ok";
+        case SP24_ERR_SHAPE: return "unsupported shape: a dimension is not a positive multiple of the required block size";
+        case SP24_ERR_STRIDE: return "unsupported leading dimension: too small or not a multiple of 16 bytes";
+        case SP24_ERR_DTYPE: return "unsupported element type combination";
+        case SP24_ERR_ALIGN: return "pointer is not 16-byte aligned";
+        case SP24_ERR_ARG: return "invalid argument: null pointer, contradictory flags or value out of range";
+        case SP24_ERR_CUDA: return "the CUDA runtime reported an error";
+        case SP24_ERR_DEVICE: return "the current device is not a compute capability 10.x GPU";
+        case SP24_ERR_TOO_LARGE: return "size exceeds a fixed capacity of this entry point";
+        default: return "unknown sparse24_b200 error code";
+    }
+}
+
+extern "C" int sp24_abi_version(void) { return 1; }

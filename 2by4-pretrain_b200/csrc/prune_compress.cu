@@ -1,0 +1,334 @@
+// Dense -> 2:4 compressed conversion: fused prune (magnitude / supplied mask / MVUE) + value
+// compaction + metadata packing, for row-major and column-major storage of the logical matrix.
+//
+// Both kernels are HBM-bound streaming kernels.  Values leave through 16-byte coalesced stores;
+// metadata words are first placed in shared memory at their position inside the destination run
+// (the reordered layout keeps every aligned group of 32 rows x 2 metadata columns contiguous) and
+// then written with 16-byte stores, so no partial sector is ever written.
+#include "sp24_common.cuh"
+
+namespace sp24 {
+namespace {
+
+struct PcParams {
+    const void *dense;
+    void *packed;
+    void *meta;
+    const uint8_t *mask;
+    const float *uniforms;
+    int64_t m, k, ld_dense, ld_packed, ld_mask, ld_u;
+    uint64_t seed, offset;
+};
+
+template <typename T, int N> __device__ __forceinline__ void load_elems(const T *p, T (&out)[N]) {
+    constexpr int PER = (sizeof(T) * N >= 16) ? 16 / sizeof(T) : N;
+#pragma unroll
+    for (int i = 0; i < N / PER; ++i) {
+        Vec<T, PER> v = load_vec<T, PER>(p + i * PER);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) out[i * PER + j] = v.v[j];
+    }
+}
+template <typename T, int N> __device__ __forceinline__ void store_elems(T *p, const T (&in)[N]) {
+    constexpr int PER = (sizeof(T) * N >= 16) ? 16 / sizeof(T) : N;
+#pragma unroll
+    for (int i = 0; i < N / PER; ++i) {
+        Vec<T, PER> v;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) v.v[j] = in[i * PER + j];
+        store_vec<T, PER>(p + i * PER, v);
+    }
+}
+
+// One group of four: decide the keep mask, emit the two stored values and the 4-bit code.
+template <typename TIn, typename TOut, int MODE>
+__device__ __forceinline__ uint32_t do_group(const TIn (&in)[4], uint32_t given_mask, float u0, float u1, TOut &o0,
+                                             TOut &o1) {
+    uint32_t keep;
+    if constexpr (MODE == SP24_PRUNE_MVUE) {
+        float x[4] = {Elem<TIn>::to_f32(in[0]), Elem<TIn>::to_f32(in[1]), Elem<TIn>::to_f32(in[2]),
+                      Elem<TIn>::to_f32(in[3])};
+        keep = mvue24_group(x, u0, u1);
+        const uint32_t nib = encode_nibble(keep);
+        o0 = Elem<TOut>::from_f32(pick4(nib & 3u, x[0], x[1], x[2], x[3]));
+        o1 = Elem<TOut>::from_f32(pick4(nib >> 2, x[0], x[1], x[2], x[3]));
+        return nib;
+    } else {
+        if constexpr (MODE == SP24_PRUNE_MASK) {
+            keep = given_mask;
+        } else {
+            keep = magnitude_mask4(Elem<TIn>::to_f32(in[0]), Elem<TIn>::to_f32(in[1]), Elem<TIn>::to_f32(in[2]),
+                                   Elem<TIn>::to_f32(in[3]));
+        }
+        const uint32_t nib = encode_nibble(keep);
+        o0 = convert<TOut>(pick4(nib & 3u, in[0], in[1], in[2], in[3]));
+        o1 = convert<TOut>(pick4(nib >> 2, in[0], in[1], in[2], in[3]));
+        return nib;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// row-major storage: groups of four run along the contiguous axis.
+// Tile = 32 rows x 32 metadata columns; 8 warps, lane = metadata column, warp w owns rows 4w..4w+3.
+// ---------------------------------------------------------------------------------------------
+template <typename TIn, typename TOut, int MODE, bool HAS_U>
+__global__ void __launch_bounds__(256) pc_row_kernel(PcParams P) {
+    constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;  // dense elements per metadata word
+    constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;    // bytes per metadata word
+    constexpr int GROUP = MB == 2 ? 32 : 16;
+    using MetaT = typename VecBytes<MB>::type;
+    constexpr int RPI = (CH * sizeof(TIn) >= 128) ? 1 : (CH * sizeof(TIn) >= 64 ? 2 : 4);  // rows in flight
+
+    __shared__ __align__(16) MetaT smeta[16][64];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t ncols = P.k / CH;
+    const int64_t c = (int64_t)blockIdx.x * 32 + lane;
+    const int64_t r0 = (int64_t)blockIdx.y * 32;
+    const TIn *dense = static_cast<const TIn *>(P.dense);
+    TOut *packed = static_cast<TOut *>(P.packed);
+
+    if (c < ncols) {
+#pragma unroll
+        for (int it = 0; it < 4 / RPI; ++it) {
+            TIn in[RPI][CH];
+            uint8_t mk[RPI][CH];
+#pragma unroll
+            for (int j = 0; j < RPI; ++j) {
+                const int64_t r = r0 + warp * 4 + it * RPI + j;
+                load_elems<TIn, CH>(dense + r * P.ld_dense + c * CH, in[j]);
+                if constexpr (MODE == SP24_PRUNE_MASK) load_elems<uint8_t, CH>(P.mask + r * P.ld_mask + c * CH, mk[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < RPI; ++j) {
+                const int rr = warp * 4 + it * RPI + j;
+                const int64_t r = r0 + rr;
+                TOut out[CH / 2];
+                uint32_t word = 0;
+#pragma unroll
+                for (int g2 = 0; g2 < CH / 8; ++g2) {
+                    float u[4] = {0.f, 0.f, 0.f, 0.f};
+                    if constexpr (MODE == SP24_PRUNE_MVUE) {
+                        if constexpr (HAS_U) {
+                            const float *up = P.uniforms + r * P.ld_u + c * CH + g2 * 8;
+                            const float2 ua = *reinterpret_cast<const float2 *>(up);
+                            const float2 ub = *reinterpret_cast<const float2 *>(up + 4);
+                            u[0] = ua.x; u[1] = ua.y; u[2] = ub.x; u[3] = ub.y;
+                        } else {
+                            const uint64_t gi = (uint64_t)r * (uint64_t)(P.k / 4) + (uint64_t)(c * (CH / 4) + g2 * 2);
+                            mvue_uniform_pairs(gi >> 1, P.seed, P.offset, u[0], u[1], u[2], u[3]);
+                        }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int g = g2 * 2 + h;
+                        const TIn grp[4] = {in[j][4 * g], in[j][4 * g + 1], in[j][4 * g + 2], in[j][4 * g + 3]};
+                        uint32_t given = 0;
+                        if constexpr (MODE == SP24_PRUNE_MASK) {
+                            given = (mk[j][4 * g] != 0) | ((mk[j][4 * g + 1] != 0) << 1) | ((mk[j][4 * g + 2] != 0) << 2) |
+                                    ((mk[j][4 * g + 3] != 0) << 3);
+                        }
+                        const uint32_t nib =
+                            do_group<TIn, TOut, MODE>(grp, given, u[2 * h], u[2 * h + 1], out[2 * g], out[2 * g + 1]);
+                        word |= nib << (4 * g);
+                    }
+                }
+                store_elems<TOut, CH / 2>(packed + r * P.ld_packed + c * (CH / 2), out);
+                smeta[lane >> 1][(rr / GROUP) * 2 * GROUP + meta_run_pos<MB>(rr % GROUP, lane & 1)] = (MetaT)word;
+            }
+        }
+    }
+    __syncthreads();
+    // 16 column pairs x 64 words, written as 16-byte pieces
+    constexpr int PIECES = 64 * MB / 16;
+    for (int i = threadIdx.x; i < 16 * PIECES; i += 256) {
+        const int pair = i / PIECES, piece = i % PIECES;
+        const int64_t cp = (int64_t)blockIdx.x * 16 + pair;
+        if (cp * 2 < ncols) {
+            char *dst = static_cast<char *>(P.meta) + (cp * 2 * P.m + 2 * r0) * MB + piece * 16;
+            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(
+                reinterpret_cast<const char *>(&smeta[pair][0]) + piece * 16);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// column-major storage: element (r, c) at c*ld + r, groups of four run along the strided axis.
+// Everything is element-wise across r, so loads and stores are naturally coalesced along r.
+// Thread = V consecutive rows x one metadata column; warp = 32*V rows; 8 warps = 8 metadata columns.
+// ---------------------------------------------------------------------------------------------
+template <typename TIn, typename TOut, int MODE, bool HAS_U>
+__global__ void __launch_bounds__(256) pc_col_kernel(PcParams P) {
+    constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;
+    constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;
+    constexpr int GROUP = MB == 2 ? 32 : 16;
+    constexpr int V = 16 / sizeof(TIn);
+    constexpr int RT = 32 * V;  // rows per block
+    using MetaT = typename VecBytes<MB>::type;
+
+    __shared__ __align__(16) MetaT smeta[4][2 * RT];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t ncols = P.k / CH;
+    const int64_t r0 = (int64_t)blockIdx.x * RT;
+    const int64_t r = r0 + lane * V;
+    const int64_t c = (int64_t)blockIdx.y * 8 + warp;
+    const TIn *dense = static_cast<const TIn *>(P.dense);
+    TOut *packed = static_cast<TOut *>(P.packed);
+
+    if (r < P.m && c < ncols) {
+        uint32_t word[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) word[v] = 0;
+#pragma unroll
+        for (int half = 0; half < CH / 16; ++half) {
+            TIn in[16][V];
+            uint8_t mk[16][V];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int64_t kk = c * CH + half * 16 + j;
+                load_elems<TIn, V>(dense + kk * P.ld_dense + r, in[j]);
+                if constexpr (MODE == SP24_PRUNE_MASK) load_elems<uint8_t, V>(P.mask + kk * P.ld_mask + r, mk[j]);
+            }
+#pragma unroll
+            for (int g2 = 0; g2 < 2; ++g2) {
+                float u[V][4];
+                if constexpr (MODE == SP24_PRUNE_MVUE) {
+                    const int64_t gcol = c * (CH / 4) + half * 4 + g2 * 2;  // first of the two groups
+                    if constexpr (HAS_U) {
+                        float t0[V], t1[V], t2[V], t3[V];
+                        load_elems<float, V>(P.uniforms + (gcol * 4 + 0) * P.ld_u + r, t0);
+                        load_elems<float, V>(P.uniforms + (gcol * 4 + 1) * P.ld_u + r, t1);
+                        load_elems<float, V>(P.uniforms + (gcol * 4 + 4) * P.ld_u + r, t2);
+                        load_elems<float, V>(P.uniforms + (gcol * 4 + 5) * P.ld_u + r, t3);
+#pragma unroll
+                        for (int v = 0; v < V; ++v) { u[v][0] = t0[v]; u[v][1] = t1[v]; u[v][2] = t2[v]; u[v][3] = t3[v]; }
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < V; ++v) {
+                            const uint64_t gi = (uint64_t)(r + v) * (uint64_t)(P.k / 4) + (uint64_t)gcol;
+                            mvue_uniform_pairs(gi >> 1, P.seed, P.offset, u[v][0], u[v][1], u[v][2], u[v][3]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int g = g2 * 2 + h;  // group inside this half (0..3)
+                    TOut o0[V], o1[V];
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        const TIn grp[4] = {in[4 * g][v], in[4 * g + 1][v], in[4 * g + 2][v], in[4 * g + 3][v]};
+                        uint32_t given = 0;
+                        if constexpr (MODE == SP24_PRUNE_MASK) {
+                            given = (mk[4 * g][v] != 0) | ((mk[4 * g + 1][v] != 0) << 1) | ((mk[4 * g + 2][v] != 0) << 2) |
+                                    ((mk[4 * g + 3][v] != 0) << 3);
+                        }
+                        float ua = 0.f, ub = 0.f;
+                        if constexpr (MODE == SP24_PRUNE_MVUE) { ua = u[v][2 * h]; ub = u[v][2 * h + 1]; }
+                        const uint32_t nib = do_group<TIn, TOut, MODE>(grp, given, ua, ub, o0[v], o1[v]);
+                        word[v] |= nib << (4 * (half * 4 + g));
+                    }
+                    const int64_t prow = c * (CH / 2) + (half * 4 + g) * 2;
+                    store_elems<TOut, V>(packed + prow * P.ld_packed + r, o0);
+                    store_elems<TOut, V>(packed + (prow + 1) * P.ld_packed + r, o1);
+                }
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const int rr = lane * V + v;
+            smeta[warp >> 1][(rr / GROUP) * 2 * GROUP + meta_run_pos<MB>(rr % GROUP, warp & 1)] = (MetaT)word[v];
+        }
+    }
+    __syncthreads();
+    const int64_t rows_here = (P.m - r0 < RT) ? (P.m - r0) : RT;
+    const int pieces = (int)(rows_here * 2 * MB / 16);
+    for (int i = threadIdx.x; i < 4 * (2 * RT * MB / 16); i += 256) {
+        const int pair = i / (2 * RT * MB / 16), piece = i % (2 * RT * MB / 16);
+        const int64_t cp = (int64_t)blockIdx.y * 4 + pair;
+        if (piece < pieces && cp * 2 < ncols) {
+            char *dst = static_cast<char *>(P.meta) + (cp * 2 * P.m + 2 * r0) * MB + piece * 16;
+            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(
+                reinterpret_cast<const char *>(&smeta[pair][0]) + piece * 16);
+        }
+    }
+}
+
+template <typename TIn, typename TOut, int MODE, bool HAS_U>
+int launch(const PcParams &P, int col_major, cudaStream_t st) {
+    constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;
+    if (!col_major) {
+        dim3 grid((unsigned)((P.k / CH + 31) / 32), (unsigned)(P.m / 32));
+        pc_row_kernel<TIn, TOut, MODE, HAS_U><<<grid, 256, 0, st>>>(P);
+    } else {
+        constexpr int RT = 32 * (16 / (int)sizeof(TIn));
+        dim3 grid((unsigned)((P.m + RT - 1) / RT), (unsigned)((P.k / CH + 7) / 8));
+        pc_col_kernel<TIn, TOut, MODE, HAS_U><<<grid, 256, 0, st>>>(P);
+    }
+    return launch_status();
+}
+
+template <typename TIn, typename TOut> int dispatch_mode(const PcParams &P, int mode, int col_major, cudaStream_t st) {
+    switch (mode) {
+        case SP24_PRUNE_MSE: return launch<TIn, TOut, SP24_PRUNE_MSE, false>(P, col_major, st);
+        case SP24_PRUNE_MASK: return launch<TIn, TOut, SP24_PRUNE_MASK, false>(P, col_major, st);
+        case SP24_PRUNE_MVUE:
+            if constexpr (std::is_same<TIn, int8_t>::value) {
+                return SP24_ERR_DTYPE;
+            } else {
+                return P.uniforms ? launch<TIn, TOut, SP24_PRUNE_MVUE, true>(P, col_major, st)
+                                  : launch<TIn, TOut, SP24_PRUNE_MVUE, false>(P, col_major, st);
+            }
+        default: return SP24_ERR_ARG;
+    }
+}
+
+template <typename TIn> int dispatch_out(const PcParams &P, int packed_dtype, int mode, int col_major, cudaStream_t st) {
+    switch (packed_dtype) {
+        case SP24_F16: return dispatch_mode<TIn, __half>(P, mode, col_major, st);
+        case SP24_BF16: return dispatch_mode<TIn, __nv_bfloat16>(P, mode, col_major, st);
+        case SP24_E4M3: return dispatch_mode<TIn, e4m3_t>(P, mode, col_major, st);
+        case SP24_E5M2: return dispatch_mode<TIn, e5m2_t>(P, mode, col_major, st);
+        default: return SP24_ERR_DTYPE;
+    }
+}
+
+}  // namespace
+}  // namespace sp24
+
+extern "C" int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
+                                   int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
+                                   int mode, const void *mask, int64_t ld_mask, const float *uniforms,
+                                   int64_t ld_uniforms, uint64_t seed, uint64_t offset, void *stream) {
+    using namespace sp24;
+    if (!dense || !packed || !meta) return SP24_ERR_ARG;
+    const int so = dtype_size(packed_dtype), si = dtype_size(dense_dtype);
+    if (so == 0 || si == 0 || packed_dtype == SP24_F32) return SP24_ERR_DTYPE;
+    if (dense_dtype == SP24_E4M3 || dense_dtype == SP24_E5M2) return SP24_ERR_DTYPE;
+    if ((dense_dtype == SP24_I8) != (packed_dtype == SP24_I8)) return SP24_ERR_DTYPE;
+    const int64_t kmult = so == 2 ? 64 : 128;
+    if (m <= 0 || k <= 0 || m % 32 || k % kmult) return SP24_ERR_SHAPE;
+    if (mode == SP24_PRUNE_MASK && !mask) return SP24_ERR_ARG;
+    if (mode != SP24_PRUNE_MASK && mask) return SP24_ERR_ARG;
+    if (mode != SP24_PRUNE_MVUE && uniforms) return SP24_ERR_ARG;
+    if (mode < SP24_PRUNE_MSE || mode > SP24_PRUNE_MVUE) return SP24_ERR_ARG;
+    const int64_t inner = col_major ? m : k, inner_p = col_major ? m : k / 2;
+    if (ld_dense < inner || (ld_dense * si) % 16) return SP24_ERR_STRIDE;
+    if (ld_packed < inner_p || (ld_packed * so) % 16) return SP24_ERR_STRIDE;
+    if (mask && (ld_mask < inner || ld_mask % 16)) return SP24_ERR_STRIDE;
+    if (uniforms && (ld_uniforms < inner || ld_uniforms % 4)) return SP24_ERR_STRIDE;
+    if (!aligned16(dense) || !aligned16(packed) || !aligned16(meta) || (mask && !aligned16(mask)) ||
+        (uniforms && !aligned16(uniforms)))
+        return SP24_ERR_ALIGN;
+    if (int rc = check_device()) return rc;
+    PcParams P{dense, packed, meta, static_cast<const uint8_t *>(mask), uniforms, m, k, ld_dense, ld_packed, ld_mask,
+               ld_uniforms, seed, offset};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dense_dtype) {
+        case SP24_F32: return dispatch_out<float>(P, packed_dtype, mode, col_major, st);
+        case SP24_F16: return dispatch_out<__half>(P, packed_dtype, mode, col_major, st);
+        case SP24_BF16: return dispatch_out<__nv_bfloat16>(P, packed_dtype, mode, col_major, st);
+        case SP24_I8: return dispatch_mode<int8_t, int8_t>(P, mode, col_major, st);
+        default: return SP24_ERR_DTYPE;
+    }
+}

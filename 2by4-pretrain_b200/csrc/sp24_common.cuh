@@ -1,0 +1,238 @@
+// Shared device helpers of the sm_100a kernels: element conversion, the 2:4 selection
+// and encoding rules, the metadata placement formula, MVUE arithmetic and the Philox stream.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <type_traits>
+
+#include "../../include/sparse24_b200.h"
+
+namespace sp24 {
+
+// ---------------------------------------------------------------------------------------------
+// element types
+// ---------------------------------------------------------------------------------------------
+struct e4m3_t { uint8_t b; };
+struct e5m2_t { uint8_t b; };
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static constexpr int code = SP24_F32;
+    __device__ static float to_f32(float v) { return v; }
+    __device__ static float from_f32(float v) { return v; }
+};
+template <> struct Elem<__half> {
+    static constexpr int code = SP24_F16;
+    __device__ static float to_f32(__half v) { return __half2float(v); }
+    __device__ static __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr int code = SP24_BF16;
+    __device__ static float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ static __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct Elem<e4m3_t> {
+    static constexpr int code = SP24_E4M3;
+    __device__ static float to_f32(e4m3_t v) {
+        return __half2float(__half(__nv_cvt_fp8_to_halfraw(v.b, __NV_E4M3)));
+    }
+    __device__ static e4m3_t from_f32(float v) {
+        return e4m3_t{(uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3)};
+    }
+};
+template <> struct Elem<e5m2_t> {
+    static constexpr int code = SP24_E5M2;
+    __device__ static float to_f32(e5m2_t v) {
+        return __half2float(__half(__nv_cvt_fp8_to_halfraw(v.b, __NV_E5M2)));
+    }
+    __device__ static e5m2_t from_f32(float v) {
+        return e5m2_t{(uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2)};
+    }
+};
+template <> struct Elem<int8_t> {
+    static constexpr int code = SP24_I8;
+    __device__ static float to_f32(int8_t v) { return (float)v; }
+    __device__ static int8_t from_f32(float v) { return (int8_t)v; }
+};
+
+// value as stored in TIn -> value stored in TOut (one rounding from the source precision)
+template <typename TOut, typename TIn> __device__ __forceinline__ TOut convert(TIn v) {
+    return Elem<TOut>::from_f32(Elem<TIn>::to_f32(v));
+}
+
+// ---------------------------------------------------------------------------------------------
+// vector access (16-byte, or narrower when the element count demands)
+// ---------------------------------------------------------------------------------------------
+template <int BYTES> struct VecBytes;
+template <> struct VecBytes<16> { using type = uint4; };
+template <> struct VecBytes<8> { using type = uint2; };
+template <> struct VecBytes<4> { using type = uint32_t; };
+template <> struct VecBytes<2> { using type = uint16_t; };
+template <> struct VecBytes<1> { using type = uint8_t; };
+
+template <typename T, int N> struct alignas(sizeof(T) * N) Vec {
+    T v[N];
+};
+
+template <typename T, int N> __device__ __forceinline__ Vec<T, N> load_vec(const T *p) {
+    using R = typename VecBytes<sizeof(T) * N>::type;
+    Vec<T, N> out;
+    *reinterpret_cast<R *>(&out) = *reinterpret_cast<const R *>(p);
+    return out;
+}
+template <typename T, int N> __device__ __forceinline__ void store_vec(T *p, const Vec<T, N> &val) {
+    using R = typename VecBytes<sizeof(T) * N>::type;
+    *reinterpret_cast<R *>(p) = *reinterpret_cast<const R *>(&val);
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2:4 selection by magnitude: six strict comparisons, ties keep the higher index.
+// Returns the keep mask as bits 0..3.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t magnitude_mask4(float a0, float a1, float a2, float a3) {
+    a0 = fabsf(a0); a1 = fabsf(a1); a2 = fabsf(a2); a3 = fabsf(a3);
+    const bool x1 = a0 > a1, x2 = a0 > a2, x3 = a0 > a3, x4 = a1 > a2, x5 = a1 > a3, x6 = a2 > a3;
+    const bool m0 = (x2 && x3) || (x1 && x2) || (x1 && x3);
+    const bool m1 = (!x1 && x5) || (x4 && x5) || (!x1 && x4);
+    const bool m2 = (!x2 && !x4) || (!x2 && x6) || (!x4 && x6);
+    const bool m3 = (!x3 && !x5) || (!x3 && !x6) || (!x5 && !x6);
+    return (uint32_t)m0 | ((uint32_t)m1 << 1) | ((uint32_t)m2 << 2) | ((uint32_t)m3 << 3);
+}
+
+// Encoding of a keep mask (bits 0..3) into the 4-bit metadata code idx0 | idx1 << 2.  The same
+// boolean formulas serve masks with fewer or more than two bits (fall-back encodings).
+__device__ __forceinline__ uint32_t encode_nibble(uint32_t mask) {
+    const uint32_t m0 = mask & 1u, m1 = (mask >> 1) & 1u, m2 = (mask >> 2) & 1u;
+    const uint32_t bit0 = (m0 ^ 1u) & m1;
+    const uint32_t bit1 = (m0 ^ 1u) & (m1 ^ 1u);
+    const uint32_t bit2 = bit1 | (m2 ^ 1u);
+    const uint32_t bit3 = bit0 | (m1 ^ 1u) | m2;
+    return bit0 | (bit1 << 1) | (bit2 << 2) | (bit3 << 3);
+}
+
+template <typename T> __device__ __forceinline__ T pick4(uint32_t idx, T v0, T v1, T v2, T v3) {
+    const T lo = (idx & 1u) ? v1 : v0;
+    const T hi = (idx & 1u) ? v3 : v2;
+    return (idx & 2u) ? hi : lo;
+}
+
+// ---------------------------------------------------------------------------------------------
+// metadata placement: logical element (r, c) of the (m, ncols) metadata matrix -> flat offset in the
+// reordered buffer.  GROUP/INTER = 32/4 for 16-bit metadata words, 16/2 for 32-bit words.
+// ---------------------------------------------------------------------------------------------
+template <int META_BYTES> __device__ __forceinline__ int64_t meta_offset(int64_t r, int64_t c, int64_t m) {
+    constexpr int GROUP = META_BYTES == 2 ? 32 : 16;
+    constexpr int INTER = META_BYTES == 2 ? 4 : 2;
+    int64_t dr = r / GROUP * GROUP + (r % 8) * INTER + (r % GROUP) / 8;
+    int64_t dc = c;
+    const bool r_odd = dr & 1, c_odd = dc & 1;
+    if (!r_odd && c_odd) { dr += 1; dc -= 1; }
+    else if (r_odd && !c_odd) { dr -= 1; dc += 1; }
+    return (dc >> 1) * (2 * m) + dr * 2 + (dc & 1);
+}
+
+// Inside one aligned group of GROUP rows and one column pair the destination is a contiguous run of
+// 2*GROUP words.  Position (0 .. 2*GROUP-1) of (row-in-group rr, column parity cp) inside that run.
+template <int META_BYTES> __device__ __forceinline__ int meta_run_pos(int rr, int cp) {
+    constexpr int GROUP = META_BYTES == 2 ? 32 : 16;
+    constexpr int INTER = META_BYTES == 2 ? 4 : 2;
+    int dr = (rr % 8) * INTER + (rr % GROUP) / 8;
+    int dc = cp;
+    if (!(dr & 1) && dc) { dr += 1; dc = 0; }
+    else if ((dr & 1) && !dc) { dr -= 1; dc = 1; }
+    return dr * 2 + dc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Philox4x32-10 and the uniform pair of a group
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+    constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        const uint32_t hi0 = __umulhi(M0, c.x), lo0 = M0 * c.x;
+        const uint32_t hi1 = __umulhi(M1, c.z), lo1 = M1 * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+        k.x += W0;
+        k.y += W1;
+    }
+    return c;
+}
+
+__device__ __forceinline__ float u32_to_uniform(uint32_t x) { return (float)(x >> 8) * 5.9604644775390625e-08f; }
+
+// Uniform pairs of the two groups 2*pair and 2*pair+1 (linear group index over the logical matrix).
+__device__ __forceinline__ void mvue_uniform_pairs(uint64_t pair, uint64_t seed, uint64_t offset, float &u0a,
+                                                   float &u1a, float &u0b, float &u1b) {
+    const uint4 r = philox4x32_10(make_uint4((uint32_t)pair, (uint32_t)(pair >> 32), (uint32_t)offset,
+                                             (uint32_t)(offset >> 32)),
+                                  make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+    u0a = u32_to_uniform(r.x); u1a = u32_to_uniform(r.y);
+    u0b = u32_to_uniform(r.z); u1b = u32_to_uniform(r.w);
+}
+
+// ---------------------------------------------------------------------------------------------
+// MVUE24 (approximate): float32, one rounding per operation, left-to-right sums, IEEE division.
+// x[] is overwritten with x_i / p_i; returns the keep mask as bits 0..3.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mvue24_group(float (&x)[4], float u0, float u1) {
+    const float eps = 1.19209e-07f;
+    float a[4], t[4], kk[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = __fadd_rn(fabsf(x[i]), eps);
+    const float s = __fadd_rn(__fadd_rn(__fadd_rn(a[0], a[1]), a[2]), a[3]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        t[i] = __fdiv_rn(a[i], s);
+        kk[i] = __fdiv_rn(t[i], __fsub_rn(s, a[i]));
+    }
+    const float ks = __fadd_rn(__fadd_rn(__fadd_rn(kk[0], kk[1]), kk[2]), kk[3]);
+    const float t01 = __fadd_rn(t[0], t[1]);
+    const float t012 = __fadd_rn(t01, t[2]);
+    const bool m0 = u0 <= t[0];
+    const bool m1 = (u0 <= t01) && !m0;
+    const bool m2 = (u0 <= t012) && !m1 && !m0;
+    const bool m3 = !m2 && !m1 && !m0;
+    // (~m) * a : 0 * a when picked (NaN for an infinite a, like the reference), 1 * a otherwise
+    const float d0 = __fmul_rn(m0 ? 0.f : 1.f, a[0]);
+    const float d1 = __fmul_rn(m1 ? 0.f : 1.f, a[1]);
+    const float d2 = __fmul_rn(m2 ? 0.f : 1.f, a[2]);
+    const float d3 = __fmul_rn(m3 ? 0.f : 1.f, a[3]);
+    const float d01 = __fadd_rn(d0, d1);
+    const float d012 = __fadd_rn(d01, d2);
+    const float ds = __fadd_rn(d012, d3);
+    const float tt = __fmul_rn(u1, ds);
+    const bool e0 = tt <= d0;
+    const bool e1 = (tt <= d01) && !e0;
+    const bool e2 = (tt <= d012) && !e1 && !e0;
+    const bool e3 = !e2 && !e1 && !e0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float p = __fadd_rn(t[i], __fmul_rn(a[i], __fsub_rn(ks, kk[i])));
+        x[i] = __fdiv_rn(x[i], p);
+    }
+    return (uint32_t)(m0 || e0) | ((uint32_t)(m1 || e1) << 1) | ((uint32_t)(m2 || e2) << 2) |
+           ((uint32_t)(m3 || e3) << 3);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host-side helpers
+// ---------------------------------------------------------------------------------------------
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int dtype_size(int dt) {
+    switch (dt) {
+        case SP24_F32: return 4;
+        case SP24_F16: case SP24_BF16: return 2;
+        case SP24_E4M3: case SP24_E5M2: case SP24_I8: return 1;
+        default: return 0;
+    }
+}
+int check_device();            // SP24_OK when the current device is compute capability 10.x
+int launch_status();           // maps cudaGetLastError() to SP24_OK / SP24_ERR_CUDA
+
+}  // namespace sp24

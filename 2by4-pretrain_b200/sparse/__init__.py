@@ -1,0 +1,24 @@
+"""Drop-in ``sparse`` package: the 2:4 sparse-training hot path on B200 (sm_100a) CUDA kernels.
+
+Public names follow sparse/__init__.py of the reference for everything on that path, plus the
+classes the reference only lists in its README (``SparseLinearTranspose``,
+``sparse_linear_transpose``, ``mask_select``).
+"""
+from .triton_ops import MVUE24_approx_triton, sparse24_triton, soft_threshold24_triton
+from .decay import masked_add_
+from .transposable_semi_structured import TransposableSparse, select_and_compress
+from .semi_structured import to_sparse_semi_structured, SparseSemiStructuredTensor
+
+mask_select = TransposableSparse()
+
+__all__ = [
+    'MVUE24_approx_triton',
+    'sparse24_triton',
+    'soft_threshold24_triton',
+    'masked_add_',
+    'TransposableSparse',
+    'mask_select',
+    'select_and_compress',
+    'to_sparse_semi_structured',
+    'SparseSemiStructuredTensor',
+]

@@ -1,0 +1,87 @@
+"""Transposable 4x4 mask select (sparse/transposable_semi_structured.py:50-200 of the reference)."""
+import itertools
+
+import torch
+from torch import Tensor, nn
+
+from . import _ext
+
+
+def _pattern_table() -> torch.Tensor:
+    """The 90 4x4 patterns with two ones per row and column, descending lexicographic order."""
+    pairs = ((0, 1), (0, 2), (0, 3), (1, 2), (1, 3), (2, 3))
+    rows = []
+    for combo in itertools.product(range(6), repeat=4):
+        cnt = [0] * 4
+        for i in combo:
+            cnt[pairs[i][0]] += 1
+            cnt[pairs[i][1]] += 1
+        if cnt == [2, 2, 2, 2]:
+            bits = []
+            for i in combo:
+                r = [0, 0, 0, 0]
+                r[pairs[i][0]] = r[pairs[i][1]] = 1
+                bits += r
+            rows.append(bits)
+    return torch.tensor(rows, dtype=torch.float32)
+
+
+def _to_transposable_sparse_semi_structured(dense, mask_pattern=None, abs=True, need_sparse=True):
+    if dense.dim() != 2:
+        raise RuntimeError(f"Expected 2-dimensional dense tensor, got {dense.dim()}-dimensional tensor")
+    m, k = dense.shape
+    if dense.dtype not in [torch.float16, torch.bfloat16, torch.float32]:
+        raise RuntimeError(f"Invalid datatype {dense.dtype} of dense matrix")
+    if m % 32 != 0:
+        raise RuntimeError(f"Number rows columns of dense matrix {m} must be divisible by 32")
+    if k % 64 != 0:
+        raise RuntimeError(f"Number of columns of dense matrix {k} must be divisible by {64}")
+    _ext.require_cuda(dense)
+    x = _ext.as_layout(dense.detach(), 0)
+    sparse = torch.empty((m, k), dtype=dense.dtype, device=dense.device) if need_sparse else None
+    mask = torch.empty((m, k), dtype=torch.bool, device=dense.device)
+    rc = _ext.lib().sp24_transposable_select(x.data_ptr(), _ext.dt(x.dtype), m, k, _ext.layout_of(x)[1], 1 if abs else 0,
+                                             _ext.ptr(sparse), k, mask.data_ptr(), k, _ext.stream())
+    _ext.check(rc, "sp24_transposable_select")
+    return sparse, mask
+
+
+class TransposableSparse(nn.Module):
+    r"""
+    :return sparse, mask
+    """
+
+    def __init__(self, abs=True):
+        super().__init__()
+        self.abs = abs
+        self.mask_pattern = _pattern_table()  # kept for API compatibility; the kernel enumerates it itself
+
+    def forward(self, x: Tensor):
+        return _to_transposable_sparse_semi_structured(x, self.mask_pattern, self.abs)
+
+
+def select_and_compress(weight: Tensor, mask: Tensor = None, dtype: torch.dtype = torch.float16):
+    """One pass over ``weight`` (m, k): transposable mask (recomputed when ``mask`` is None, else read)
+    plus the 2:4 compression of W and of W^T.  Returns (mask, (packed_w, meta_w), (packed_t, meta_t))
+    where packed_t is the column-major (k, m/2) view the reference gets from
+    ``to_sparse_semi_structured(W.T, mask=mask.T)``."""
+    _ext.require_cuda(weight, mask)
+    m, k = weight.shape
+    w = _ext.as_layout(weight.detach(), 0)
+    select = mask is None
+    if select:
+        mask = torch.empty((m, k), dtype=torch.bool, device=w.device)
+    else:
+        mask = _ext.as_layout(mask if mask.dtype in (torch.bool, torch.uint8) else mask != 0, 0)
+    buf_w = torch.empty(m * k * 9 // 16, dtype=dtype, device=w.device)
+    buf_t = torch.empty(m * k * 9 // 16, dtype=dtype, device=w.device)
+    packed_w = buf_w[: m * k // 2].view(m, k // 2)
+    meta_w = buf_w[m * k // 2:].view(torch.int16).view(m, k // 16)
+    packed_t = buf_t[: m * k // 2].view(m // 2, k).t()
+    meta_t = buf_t[m * k // 2:].view(torch.int16).view(k, m // 16)
+    rc = _ext.lib().sp24_select_dual_compress(
+        w.data_ptr(), _ext.dt(w.dtype), m, k, _ext.layout_of(w)[1], 1 if select else 0, mask.data_ptr(),
+        _ext.layout_of(mask)[1], packed_w.data_ptr(), _ext.dt(dtype), k // 2, meta_w.data_ptr(), packed_t.data_ptr(), k,
+        meta_t.data_ptr(), _ext.stream())
+    _ext.check(rc, "sp24_select_dual_compress")
+    return mask, (packed_w, meta_w), (packed_t, meta_t)

@@ -1,0 +1,413 @@
+#!/usr/bin/env python
+"""Benchmark of the 2:4 sparse-training hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+Prints ONE JSON line (rank 0).  Default workload ``select_dual_compress``: one mask refresh of a
+training layer — transposable 4x4 mask select plus 2:4 compression of W and W^T — on 4096 x 4096
+fp16 weights ~N(0, 0.02), seed 2 (+ matrix index).  One step processes a batch of 8 such matrices
+(distinct buffers, 672 MiB of traffic per step, larger than the 126 MB L2, so no flush is needed).
+
+  value      algorithmic GB/s with inputs resident in HBM (CUDA events on the launching stream)
+  e2e        the same metric through the public Python API from pinned HOST buffers: H2D copy of W,
+             kernel, D2H copy of mask + both compressed copies, all inside the timed region
+  roofline   HBM: algorithmic bytes per launch / average launch time, against the measured copy
+             bandwidth in MEASURED_PEAKS.json (fallback 6650 GB/s)
+  cpu_baseline  the CPU restatement of the reference's path (oracle/), timed on the host cores
+
+With N > 1 (torchrun) every rank processes its own batch of matrices (independent objects, no
+collective in the data path); time is the max over ranks.  ``--impl reference`` times the CPU arm
+alone, on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "2by4-pretrain_b200"))
+
+import torch  # noqa: E402
+
+M = K = 4096
+BATCH = 8
+BYTES_PER_ELEM = 2 + 1 + 2 * (2 / 2 + 1 / 8)  # read fp16 W, write bool mask, write 2 x (fp16 values/2 + 4 bits/4 elems)
+ALG_BYTES_PER_MATRIX = M * K * BYTES_PER_ELEM
+METRIC = "prune/compress HBM GB/s (transposable select + dual 2:4 compress)"
+# dram__bytes_read.sum + dram__bytes_write.sum of one ts_dual_kernel launch on this workload, from the
+# ncu capture summarised in profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append(line.strip())
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            parts = [p.strip() for p in r.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_weights(n, device, seed0=2):
+    ws = []
+    for i in range(n):
+        g = torch.Generator().manual_seed(seed0 + i)
+        ws.append((torch.randn(M, K, generator=g) * 0.02).half())
+    return ws
+
+
+def cpu_arm(seconds_budget=12.0, max_reps=6):
+    """Times the CPU restatement of the path (mask select in the reference's matmul form + both
+    compressions) on full 4096 x 4096 matrices; returns (GB/s, cores, description)."""
+    from oracle import sp24_oracle as O
+    w = make_weights(1, "cpu")[0]
+    O.cpu_select_and_dual_compress(w[:512], matmul_scores=True)  # warm-up (thread pools, page faults)
+    times = []
+    t_end = time.perf_counter() + seconds_budget
+    while len(times) < max_reps and (not times or time.perf_counter() < t_end):
+        t0 = time.perf_counter()
+        O.cpu_select_and_dual_compress(w, matmul_scores=True)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return ALG_BYTES_PER_MATRIX / med / 1e9, torch.get_num_threads(), \
+        f"{len(times)} x one full {M}x{K} fp16 matrix (median), torch CPU threads={torch.get_num_threads()}", med
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    per_step = []
+    from oracle import sp24_oracle as O
+    w = make_weights(1, "cpu")[0]
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        O.cpu_select_and_dual_compress(w, matmul_scores=True)
+        dt = time.perf_counter() - t0
+        if i >= args.warmup:
+            per_step.append(dt)
+    total = sum(per_step)
+    val = ALG_BYTES_PER_MATRIX * len(per_step) / total / 1e9
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / len(per_step) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"transposable select + dual 2:4 compress, {M}x{K} fp16 N(0,0.02)",
+                   "step": "one matrix per step (bounded sample of the GPU arm's 8-matrix batch)"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{len(per_step)} steps x one {M}x{K} matrix; CPU restatement of the reference "
+                                   "path (matmul-form mask select + pure-torch compress)"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the per-kernel side measurements")
+    ap.add_argument("--case", default=None,
+                    help="profiling aid: run ONE named kernel case (1 warm-up + 3 launches, inputs > L2) and exit; "
+                         "prints no benchmark line")
+    args = ap.parse_args()
+    if args.case:
+        run_case(args.case)
+        return
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the GPU arm has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import sparse
+    from sparse import _ext
+
+    lib = _ext.lib()
+    ws_cpu = make_weights(BATCH, "cpu", seed0=2 + rank * BATCH)
+    ws = [w.to(dev) for w in ws_cpu]
+    outs = []
+    for _ in range(BATCH):
+        mask = torch.empty(M, K, dtype=torch.bool, device=dev)
+        bw = torch.empty(M * K * 9 // 16, dtype=torch.float16, device=dev)
+        bt = torch.empty(M * K * 9 // 16, dtype=torch.float16, device=dev)
+        outs.append((mask, bw, bt))
+    stream = torch.cuda.current_stream()
+
+    def step_device():
+        sp = stream.cuda_stream
+        for w, (mask, bw, bt) in zip(ws, outs):
+            rc = lib.sp24_select_dual_compress(
+                w.data_ptr(), _ext.F16, M, K, K, 1, mask.data_ptr(), K, bw.data_ptr(), _ext.F16, K // 2,
+                bw.data_ptr() + M * K, bt.data_ptr(), K, bt.data_ptr() + M * K, sp)
+            if rc:
+                _ext.check(rc, "sp24_select_dual_compress")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_device()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step_device()
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    launches = args.steps * BATCH
+    total_bytes = ALG_BYTES_PER_MATRIX * BATCH * args.steps * world
+    value = total_bytes / (ms * 1e-3) / 1e9
+    per_launch_s = ms * 1e-3 / launches
+    achieved = ALG_BYTES_PER_MATRIX / per_launch_s / 1e9
+
+    # end-to-end through the public API with host buffers
+    pinned = [w.pin_memory() for w in ws_cpu]
+    host_out = [(torch.empty(M, K, dtype=torch.bool).pin_memory(),
+                 torch.empty(M, K // 2, dtype=torch.float16).pin_memory(), torch.empty(M, K // 16, dtype=torch.int16).pin_memory(),
+                 torch.empty(M // 2, K, dtype=torch.float16).pin_memory(), torch.empty(K, M // 16, dtype=torch.int16).pin_memory())
+                for _ in range(BATCH)]
+
+    def step_e2e():
+        for wh, ho in zip(pinned, host_out):
+            wd = wh.to(dev, non_blocking=True)
+            mask, (pw, mw), (pt, mt) = sparse.select_and_compress(wd)
+            ho[0].copy_(mask, non_blocking=True)
+            ho[1].copy_(pw, non_blocking=True)
+            ho[2].copy_(mw, non_blocking=True)
+            ho[3].copy_(pt.t(), non_blocking=True)
+            ho[4].copy_(mt, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    step_e2e()
+    barrier()
+    ev0.record(stream)
+    for _ in range(e2e_steps):
+        step_e2e()
+    ev1.record(stream)
+    barrier()
+    t = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e_val = ALG_BYTES_PER_MATRIX * BATCH * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
+    h2d = BATCH * M * K * 2
+    d2h = BATCH * (M * K + 2 * (M * K + M * K // 8))
+
+    extra = None
+    if rank == 0 and world == 1 and not args.no_extra:
+        extra = side_measurements(dev)
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"cfg2: transposable select + dual 2:4 compress, {M}x{K} fp16 N(0,0.02) seed 2+i",
+                       "batch_per_step_per_gpu": BATCH, "alg_bytes_per_elem": BYTES_PER_ELEM,
+                       "l2": "inputs+outputs per step = 672 MiB > 126 MB L2, no flush",
+                       "parallelism": f"independent matrices x{world}"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind, "kernel": "ts_dual_kernel",
+                         "alg_bytes_per_launch": ALG_BYTES_PER_MATRIX},
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        if not args.no_cpu and world == 1:
+            v, cores, sample, _ = cpu_arm()
+            line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+        elif not args.no_cpu:
+            v, cores, sample, _ = cpu_arm(seconds_budget=4.0, max_reps=2)
+            line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+        if extra:
+            line["kernels"] = extra
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_case(name):
+    """One kernel on a case a little larger than L2 (a few hundred MB on the device), for ncu captures."""
+    import sparse
+    from sparse._semi_structured_conversions import prune_compress
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if name == "dual":
+        w = (torch.randn(8192, 8192, device=dev) * 0.02).half()
+        fn = lambda: sparse.select_and_compress(w)
+    elif name == "select":
+        w = (torch.randn(8192, 8192, device=dev) * 0.02).half()
+        fn = lambda: sparse.mask_select(w)
+    elif name in ("mvue_row", "mse_row", "mvue_col", "mse_col"):
+        m, k = 16384, 4096
+        g = (torch.randn(m, k, device=dev) * 1e-3).bfloat16()
+        mode = 2 if name.startswith("mvue") else 0
+        if name.endswith("col"):
+            g = g.t()
+            packed = torch.empty(m // 2, k, dtype=torch.bfloat16, device=dev).t()
+            meta = torch.empty(k, m // 16, dtype=torch.int16, device=dev)
+        else:
+            packed = torch.empty(m, k // 2, dtype=torch.bfloat16, device=dev)
+            meta = torch.empty(m, k // 16, dtype=torch.int16, device=dev)
+        fn = lambda: prune_compress(g, packed, meta, mode=mode, seed=1)
+    elif name == "soft":
+        g = (torch.randn(16384, 4096, device=dev) * 1e-3).bfloat16()
+        fn = lambda: sparse.soft_threshold24_triton(g)
+    elif name == "masked_add":
+        p = torch.randn(8192, 4096, device=dev)
+        gr = torch.randn(8192, 4096, device=dev)
+        mk = torch.rand(8192, 4096, device=dev) < 0.5
+        fn = lambda: sparse.masked_add_(gr, p, mk, alpha=2e-4)
+    else:
+        raise SystemExit(f"unknown case {name}")
+    for _ in range(4):
+        fn()
+    torch.cuda.synchronize()
+    print(f"case {name}: done")
+
+
+def side_measurements(dev):
+    """Per-kernel GB/s of the other conversion kernels (outside the headline timing): each timed over
+    a rotating set of buffers larger than L2, CUDA events, 3 warm-up + 10 timed passes."""
+    import sparse
+    from sparse import _ext
+    from sparse._semi_structured_conversions import prune_compress
+    peak, _ = measured_peak()
+    res = {}
+
+    def timeit(fn, nbuf, reps=10):
+        for i in range(3):
+            fn(i % nbuf)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            fn(i % nbuf)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / reps
+
+    m, k = 8192, 4096
+    n = m * k
+    nb = 4
+    G = [(torch.randn(m, k, device=dev) * 1e-3).bfloat16() for _ in range(nb)]
+    packed = [torch.empty(m, k // 2, dtype=torch.bfloat16, device=dev) for _ in range(nb)]
+    meta = [torch.empty(m, k // 16, dtype=torch.int16, device=dev) for _ in range(nb)]
+
+    def rec(name, secs, nbytes):
+        res[name] = {"ms": secs * 1e3, "GB/s": nbytes / secs / 1e9, "frac_of_hbm_peak": nbytes / secs / 1e9 / peak}
+
+    rec("cfg3 mvue compress row bf16 8192x4096",
+        timeit(lambda i: prune_compress(G[i], packed[i], meta[i], mode=2, seed=1, offset=i), nb), n * (2 + 1 + 0.125))
+    rec("cfg3 magnitude compress row bf16 8192x4096",
+        timeit(lambda i: prune_compress(G[i], packed[i], meta[i], mode=0), nb), n * (2 + 1 + 0.125))
+    Gt = [g.t() for g in G]  # column-major view of a (4096, 8192) logical matrix
+    packed_t = [torch.empty(m // 2, k, dtype=torch.bfloat16, device=dev).t() for _ in range(nb)]
+    meta_t = [torch.empty(k, m // 16, dtype=torch.int16, device=dev) for _ in range(nb)]
+    rec("mvue compress col-major bf16 (dY^T form) 4096x8192",
+        timeit(lambda i: prune_compress(Gt[i], packed_t[i], meta_t[i], mode=2, seed=1, offset=i), nb), n * (2 + 1 + 0.125))
+    rec("cfg3 soft_threshold24 bf16 8192x4096", timeit(lambda i: sparse.soft_threshold24_triton(G[i]), nb), n * 6)
+    rec("sparse24 bf16 8192x4096", timeit(lambda i: sparse.sparse24_triton(G[i]), nb), n * 6)
+    rec("mvue24 dense bf16 8192x4096", timeit(lambda i: sparse.MVUE24_approx_triton(G[i], seed=3, offset=i), nb), n * 4)
+    del packed, meta, packed_t, meta_t
+    Wf = [torch.randn(4096, 4096, device=dev) * 0.02 for _ in range(nb)]
+    rec("transposable select fp32 4096x4096 (sparse+mask)", timeit(lambda i: sparse.mask_select(Wf[i]), nb), 4096 * 4096 * 9)
+    rec("select+dual compress fp32->fp16 4096x4096", timeit(lambda i: sparse.select_and_compress(Wf[i]), nb),
+        4096 * 4096 * (4 + 1 + 2.25))
+    p = [torch.randn(m, k, device=dev) * 0.02 for _ in range(2)]
+    gr = [torch.randn(m, k, device=dev) * 1e-3 for _ in range(2)]
+    mk = [torch.rand(m, k, device=dev) < 0.5 for _ in range(2)]
+    rec("cfg3 masked_add_ fp32 8192x4096", timeit(lambda i: sparse.masked_add_(gr[i], p[i], mk[i], alpha=2e-4), 2), n * 13)
+    return res
+
+
+if __name__ == "__main__":
+    main()

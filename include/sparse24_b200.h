@@ -1,0 +1,163 @@
+/*
+ * sparse24_b200 — C ABI of the B200 (sm_100a) kernels for the 2:4 sparse-training hot path.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream), validates
+ * its arguments BEFORE launching anything, and returns SP24_OK (0) or a negative
+ * error code.  Nothing here allocates, synchronises, throws or traps: outputs and
+ * workspaces are caller-allocated, launches are asynchronous on `stream`.
+ * Matrices are described as "logical (rows, cols) + storage order + leading
+ * dimension in elements": col_major = 0 means element (r, c) is at r*ld + c,
+ * col_major = 1 means it is at c*ld + r.
+ *
+ * The reference project has one native entry point (a pybind11 function) and
+ * launches all its other kernels from Python through Triton; each declaration
+ * below names the reference interface it replaces (paths are relative to the
+ * reference project root).
+ */
+#ifndef SPARSE24_B200_H
+#define SPARSE24_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+enum {
+    SP24_F32 = 0,
+    SP24_F16 = 1,
+    SP24_BF16 = 2,
+    SP24_E4M3 = 3, /* float8_e4m3fn */
+    SP24_E5M2 = 4, /* float8_e5m2 */
+    SP24_I8 = 5
+};
+
+/* pruning rule of the dense -> 2:4 conversion */
+enum {
+    SP24_PRUNE_MSE = 0,  /* keep the two largest magnitudes of every four (ties keep the higher index) */
+    SP24_PRUNE_MASK = 1, /* keep what a supplied 0/1 byte mask says */
+    SP24_PRUNE_MVUE = 2  /* minimum-variance unbiased 2-of-4 sampling, rescaled */
+};
+
+/* error codes */
+enum {
+    SP24_OK = 0,
+    SP24_ERR_SHAPE = -1,       /* a dimension is not a positive multiple of what the op needs */
+    SP24_ERR_STRIDE = -2,      /* leading dimension too small or not a multiple of the vector width */
+    SP24_ERR_DTYPE = -3,       /* element-type combination not supported */
+    SP24_ERR_ALIGN = -4,       /* pointer not 16-byte aligned */
+    SP24_ERR_ARG = -5,         /* null pointer / contradictory flags / value out of range */
+    SP24_ERR_CUDA = -6,        /* the CUDA runtime reported an error at launch */
+    SP24_ERR_DEVICE = -7,      /* current device is not compute capability 10.x */
+    SP24_ERR_TOO_LARGE = -8    /* size beyond a stated fixed capacity */
+};
+
+/* Human-readable text for an error code (static storage). */
+const char *sp24_strerror(int code);
+
+/* ABI version of the loaded library (bumped when a signature changes). */
+int sp24_abi_version(void);
+
+/*
+ * Dense -> 2:4 compressed (values + reordered metadata), fused prune + compress + metadata.
+ * Replaces sparse_semi_structured_from_dense_triton and the Triton kernels
+ * _sparse_semi_structured_from_dense_triton_16 / _8
+ * (sparse/_semi_structured_conversions.py:431-661, :664-1069, launcher :1072-1132).
+ *
+ *   dense      logical (m, k), dense_dtype in {F32, F16, BF16}; with packed_dtype I8 also I8
+ *   col_major  storage order of dense; packed, mask and uniforms use the same order
+ *   packed     logical (m, k/2), packed_dtype in {F16, BF16, E4M3, E5M2, I8}; values are cast on store
+ *   meta       m*k/16 int16 (16-bit packed types) or m*k/32 int32 (8-bit), in the reference's
+ *              reordered layout (row interleave by 8 within groups of 32 / 16 rows, 2x2 swizzle,
+ *              column-major interleaved by 2)
+ *   mode       SP24_PRUNE_*; mask (bytes, non-zero = keep, logical (m, k)) only for SP24_PRUNE_MASK
+ *   uniforms   optional, MVUE only: float32 logical (m, k); group g of row r uses [r,4g] and [r,4g+1].
+ *              When NULL the kernel draws from Philox4x32-10 keyed by (seed, offset):
+ *              group index gi = r*(k/4)+g, counter = (gi>>1, offset), key = seed, even groups take
+ *              words 0,1 and odd groups words 2,3, u = (word >> 8) * 2^-24.
+ * Shape rules (sparse/semi_structured.py:24-30,188-200): m % 32 == 0; k % 64 == 0 (16-bit) or
+ * k % 128 == 0 (8-bit).  Leading dimensions must keep every row/column start 16-byte aligned.
+ */
+int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense, int col_major,
+                        void *packed, int packed_dtype, int64_t ld_packed, void *meta, int mode,
+                        const void *mask, int64_t ld_mask, const float *uniforms, int64_t ld_uniforms,
+                        uint64_t seed, uint64_t offset, void *stream);
+
+/*
+ * 2:4 compressed -> dense (zeros at pruned positions).  Replaces
+ * _sparse_semi_structured_to_dense_triton / _sparse_semi_structured_to_dense
+ * (sparse/_semi_structured_conversions.py:1163-1274, :217-328).
+ * packed is row-major (m, k/2) with leading dimension ld_packed; dense is row-major (m, k).
+ * dtype: F16, BF16 (int16 metadata) or E4M3, E5M2, I8 (int32 metadata).
+ */
+int sp24_to_dense(const void *packed, int dtype, int64_t m, int64_t k, int64_t ld_packed, const void *meta,
+                  void *dense, int64_t ld_dense, void *stream);
+
+/*
+ * Dense-shaped MVUE24: out = x_i / p_i at the two sampled positions of every group of four, +0 elsewhere.
+ * Replaces MVUE24_approx_triton (sparse/triton_ops.py:10-81; arithmetic sparse/utils.py:5-59).
+ * dtype in {F32, F16, BF16}; uniforms / seed / offset as in sp24_prune_compress.
+ */
+int sp24_mvue24_dense(const void *x, int dtype, int64_t m, int64_t k, int64_t ld_x, int col_major, void *out,
+                      int64_t ld_out, const float *uniforms, int64_t ld_uniforms, uint64_t seed, uint64_t offset,
+                      void *stream);
+
+/*
+ * Magnitude 2:4 pruning, dense-shaped: sparse = x where kept else +0, mask = 1 / 0 in x's dtype.
+ * Replaces sparse24_triton (sparse/triton_ops.py:84-154).  Every output element is written.
+ */
+int sp24_sparse24(const void *x, int dtype, int64_t m, int64_t k, int64_t ld_x, int col_major, void *sparse,
+                  int64_t ld_sparse, void *mask, int64_t ld_mask, void *stream);
+
+/*
+ * S-STE soft threshold: kept values move toward zero by the group's second-smallest magnitude
+ * (one rounding in x's dtype); mask = 1 / 0 in x's dtype.  Replaces soft_threshold24_triton
+ * (sparse/triton_ops.py:157-227; arithmetic sparse/utils.py:72-90).  With use_scale != 0 the kept
+ * values are further multiplied by `scale` (one more rounding in x's dtype), which folds the
+ * `weight_sparse * scale` pass of the reference's S-STE recipe (README.md:233-260) into the store.
+ */
+int sp24_soft_threshold24(const void *x, int dtype, int64_t m, int64_t k, int64_t ld_x, int col_major, void *sparse,
+                          int64_t ld_sparse, void *mask, int64_t ld_mask, int use_scale, float scale, void *stream);
+
+/*
+ * Transposable 4x4 mask select: for every 4x4 block the first (in descending lexicographic order of
+ * the row-major bit string) of the 90 patterns with two ones per row and per column that maximises
+ * the float32 score (s0 + s1) + (s2 + s3), s_i = v[i][a_i] + v[i][b_i], v = |x| when use_abs.
+ * Replaces _to_transposable_sparse_semi_structured_kernel / TransposableSparse.forward
+ * (sparse/transposable_semi_structured.py:8-94, :198-200).
+ * x row-major (m, k), m % 32 == 0, k % 64 == 0, dtype in {F32, F16, BF16}.
+ * sparse_out (same dtype, may be NULL) = x where mask else +0; mask_out = bytes 0/1 (torch.bool).
+ */
+int sp24_transposable_select(const void *x, int dtype, int64_t m, int64_t k, int64_t ld_x, int use_abs,
+                             void *sparse_out, int64_t ld_sparse, void *mask_out, int64_t ld_mask, void *stream);
+
+/*
+ * One mask refresh of the training layer in a single pass over W: transposable select (as above,
+ * |w| scores) + 2:4 compression of W (row-major packed (m, k/2) + meta_w of m*k/16 int16) and of
+ * W^T under the transposed mask (packed_t is the column-major packed the reference produces for
+ * the W.T view: storage (m/2, k) row-major with leading dimension ld_packed_t; meta_t of k*m/16
+ * int16 for the logical (k, m) matrix).  Replaces the three-launch sequence of the reference's
+ * SparseLinearTranspose.forward (README.md:148-155): TransposableSparse, then
+ * to_sparse_semi_structured(W, mask) and to_sparse_semi_structured(W.T, mask.T).
+ * If select == 0 the mask is read from mask (bytes) instead of being recomputed.
+ * m % 64 == 0 and k % 64 == 0; packed_dtype in {F16, BF16}.
+ */
+int sp24_select_dual_compress(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select, void *mask,
+                              int64_t ld_mask, void *packed_w, int packed_dtype, int64_t ld_packed_w, void *meta_w,
+                              void *packed_t, int64_t ld_packed_t, void *meta_t, void *stream);
+
+/*
+ * Masked decay, in place: grad[i] += p[i] * alpha where mask[i] == 0 (two roundings, no fused
+ * multiply-add).  Replaces masked_add_ / masked_add_kernel (sparse/decay.py:7-37).
+ * grad, p: float32, n elements, contiguous; mask_itemsize 1 (bool / uint8), 2 (f16 / bf16) or 4 (f32),
+ * "zero" meaning numerically zero.
+ */
+int sp24_masked_add(void *grad, const void *p, const void *mask, int mask_itemsize, int64_t n, float alpha,
+                    void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSE24_B200_H */

@@ -480,10 +480,24 @@ def spmm_reference(packed: torch.Tensor, meta: torch.Tensor, dense_b: torch.Tens
 # ---------------------------------------------------------------------------
 # The reference's timed CPU path (used as the benchmark's CPU arm)
 # ---------------------------------------------------------------------------
-def cpu_select_and_dual_compress(w: torch.Tensor, out_dtype: torch.dtype = torch.float16):
+def transposable_mask_matmul(x: torch.Tensor) -> torch.Tensor:
+    """The reference's CPU formulation of the mask select (sparse/legacy.py:271-354): one fp32
+    matrix product of the flattened |4x4 blocks| with the 90 x 16 pattern table, then argmax.
+    Multi-threaded through torch; used as the timed CPU arm.  Its summation order is the BLAS
+    library's, so it equals ``transposable_mask`` only when the sums are exact."""
+    m, k = x.shape
+    blk = x.float().abs().reshape(m // 4, 4, k // 4, 4).permute(0, 2, 1, 3).reshape(-1, 16)
+    P = torch.from_numpy(transposable_patterns().astype(np.float32))
+    arg = (blk @ P.t()).argmax(dim=1)
+    mk = P.bool()[arg].reshape(m // 4, k // 4, 4, 4)
+    return mk.permute(0, 2, 1, 3).reshape(m, k).contiguous()
+
+
+def cpu_select_and_dual_compress(w: torch.Tensor, out_dtype: torch.dtype = torch.float16, matmul_scores: bool = False):
     """Transposable mask select followed by compression of W and of W^T with that mask:
-    the CPU form of one mask refresh of the training layer (README.md:148-155 of the reference)."""
-    mk = transposable_mask(w)
+    the CPU form of one mask refresh of the training layer (README.md:148-155 of the reference).
+    ``matmul_scores`` picks the reference's matmul formulation of the select (faster, timed arm)."""
+    mk = transposable_mask_matmul(w) if matmul_scores else transposable_mask(w)
     pw, mw = compress_with_mask(w, mk, out_dtype)
     pt, mt = compress_with_mask(w.t().contiguous(), mk.t().contiguous(), out_dtype)
     return mk, pw, mw, pt, mt

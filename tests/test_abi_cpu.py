@@ -1,0 +1,86 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the header declares,
+and rejects bad arguments before touching a GPU (argument checks come first in every entry point)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "sparse24_b200.h")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from sparse import _ext
+    if not os.path.exists(_ext.LIB_PATH):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("sp24_build", os.path.join(ROOT, "2by4-pretrain_b200", "build.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build()
+    return _ext.lib()
+
+
+def declared_symbols():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(sp24_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_symbols_exported(lib):
+    names = declared_symbols()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/sparse24_b200.h but not exported"
+
+
+def test_python_signatures_cover_header(lib):
+    from sparse import _ext
+    bound = set(_ext._SIGNATURES) | {"sp24_strerror", "sp24_abi_version"}
+    assert set(declared_symbols()) <= bound
+
+
+def test_error_strings(lib):
+    assert lib.sp24_strerror(0) == b"ok"
+    for code in range(-8, 0):
+        assert len(lib.sp24_strerror(code)) > 5
+    assert lib.sp24_abi_version() >= 1
+
+
+def test_bad_arguments_are_rejected_without_a_gpu(lib):
+    buf = ctypes.create_string_buffer(1 << 16)
+    base = (ctypes.addressof(buf) + 15) & ~15
+    p = ctypes.c_void_p(base)
+    q = ctypes.c_void_p(base + 4096)
+    r = ctypes.c_void_p(base + 8192)
+    F32, F16 = 0, 1
+    # rows not a multiple of 32
+    assert lib.sp24_prune_compress(p, F16, 33, 64, 64, 0, q, F16, 32, r, 0, None, 0, None, 0, 0, 0, None) == -1
+    # k not a multiple of 64
+    assert lib.sp24_prune_compress(p, F16, 32, 48, 48, 0, q, F16, 24, r, 0, None, 0, None, 0, 0, 0, None) == -1
+    # leading dimension smaller than the row
+    assert lib.sp24_prune_compress(p, F16, 32, 64, 32, 0, q, F16, 32, r, 0, None, 0, None, 0, 0, 0, None) == -2
+    # fp32 packed output does not exist
+    assert lib.sp24_prune_compress(p, F16, 32, 64, 64, 0, q, F32, 32, r, 0, None, 0, None, 0, 0, 0, None) == -3
+    # misaligned pointer
+    assert lib.sp24_prune_compress(ctypes.c_void_p(base + 2), F16, 32, 64, 64, 0, q, F16, 32, r, 0, None, 0, None, 0, 0,
+                                   0, None) == -4
+    # mask mode without a mask, mask with another mode, null output
+    assert lib.sp24_prune_compress(p, F16, 32, 64, 64, 0, q, F16, 32, r, 1, None, 0, None, 0, 0, 0, None) == -5
+    assert lib.sp24_prune_compress(p, F16, 32, 64, 64, 0, q, F16, 32, r, 0, r, 64, None, 0, 0, 0, None) == -5
+    assert lib.sp24_prune_compress(p, F16, 32, 64, 64, 0, None, F16, 32, r, 0, None, 0, None, 0, 0, 0, None) == -5
+    assert lib.sp24_transposable_select(p, F16, 32, 96, 96, 1, None, 0, q, 96, None) == -1
+    assert lib.sp24_select_dual_compress(p, F16, 32, 64, 64, 1, q, 64, q, F16, 32, r, q, 64, r, None) == -1
+    assert lib.sp24_masked_add(p, q, r, 3, 16, 0.5, None) == -3
+    assert lib.sp24_masked_add(p, q, r, 1, 0, 0.5, None) == 0  # empty input is a no-op
+    assert lib.sp24_sparse24(p, F16, 32, 12, 12, 0, q, 12, r, 12, None) == -1
+    assert lib.sp24_to_dense(p, F32, 32, 64, 32, q, r, 64, None) == -3
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from sparse import _ext
+    monkeypatch.setattr(_ext, "_lib", None)
+    monkeypatch.setattr(_ext, "LIB_PATH", "/nonexistent/libsparse24_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU or Triton fallback"):
+        _ext.lib()

@@ -1,0 +1,407 @@
+"""GPU parity tests: every CUDA kernel, called through the C ABI (ctypes), against the committed
+golden fixtures (outputs of the reference's own code) and against the CPU oracle on seeded inputs.
+Bit-exact throughout: masks, packed values, metadata, and the float results of MVUE / soft threshold /
+masked decay."""
+import numpy as np
+import pytest
+import torch
+
+from _golden import load, t, same_bits
+from oracle import sp24_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def S():
+    import sparse
+    return sparse
+
+
+def randn(shape, seed, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def with_ties(x, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = x.clone()
+    m, k = x.shape
+    x4 = x.view(m, k // 4, 4)
+    sel = torch.rand(m, k // 4, generator=g)
+    x4[sel < 0.10, 1] = x4[sel < 0.10, 0]
+    x4[(sel >= 0.10) & (sel < 0.15), 3] = -x4[(sel >= 0.10) & (sel < 0.15), 2]
+    x4[(sel >= 0.15) & (sel < 0.20)] = 0
+    return x
+
+
+def gpu_compress(dense_cpu, out_dtype, *, col=False, mode=0, mask=None, U=None, seed=0, offset=0):
+    """Runs sp24_prune_compress on the logical matrix in the requested storage order; returns CPU
+    (packed (m, k/2) contiguous, meta)."""
+    from sparse._semi_structured_conversions import prune_compress
+    m, k = dense_cpu.shape
+    d = dense_cpu.to(DEV)
+    if col:
+        d = d.t().contiguous().t()
+        packed = torch.empty(k // 2, m, dtype=out_dtype, device=DEV).t()
+    else:
+        packed = torch.empty(m, k // 2, dtype=out_dtype, device=DEV)
+    per = 16 if out_dtype in (torch.float16, torch.bfloat16) else 32
+    meta = torch.zeros(m, k // per, dtype=torch.int16 if per == 16 else torch.int32, device=DEV)
+    prune_compress(d, packed, meta, mode=mode, mask=None if mask is None else mask.to(DEV),
+                   uniforms=None if U is None else U.to(DEV), seed=seed, offset=offset)
+    torch.cuda.synchronize()
+    return packed.contiguous().cpu(), meta.cpu()
+
+
+# ------------------------------------------------------------------------------------------------
+# golden fixtures (reference outputs)
+# ------------------------------------------------------------------------------------------------
+def test_docstring_known_answer(S):
+    a = torch.tensor([0, 0, 1, 1.]).tile((128, 32)).half().to(DEV)
+    sp = S.to_sparse_semi_structured(a)
+    assert sp.shape == (128, 128) and sp.dtype == torch.float16
+    assert bool((sp.values() == 1).all()) and bool((sp.indices() == -4370).all())
+    assert sp.indices().dtype == torch.int16 and sp.indices().shape == (128, 8)
+    assert torch.equal(sp.to_dense(), a)
+
+
+@pytest.mark.parametrize("tag,bf", [("f16", False), ("bf16", True), ("i8", False)])
+def test_golden_pure_torch_converter(tag, bf):
+    g = load(f"from_dense_torch_{tag}")
+    dense = t(g["dense"], bf)
+    p, me = gpu_compress(dense, dense.dtype)
+    assert same_bits(p, t(g["packed"], bf)) and same_bits(me, t(g["meta"]))
+    from sparse._semi_structured_conversions import sparse_semi_structured_to_dense
+    back = sparse_semi_structured_to_dense(t(g["packed"], bf).to(DEV), t(g["meta"]).to(DEV)).cpu()
+    assert same_bits(back, t(g["back"], bf))
+
+
+@pytest.mark.parametrize("lay", ["row", "col"])
+@pytest.mark.parametrize("tag", ["f16_f16", "f32_f16"])
+def test_golden_triton_convert(tag, lay):
+    g = load(f"k1_mse_{tag}_{lay}")
+    p, me = gpu_compress(t(g["dense"]), torch.float16, col=lay == "col")
+    assert same_bits(p, t(g["packed"])) and same_bits(me, t(g["meta"]))
+    g = load(f"k1_mask_{tag}_{lay}")
+    p, me = gpu_compress(t(g["dense"]), torch.float16, col=lay == "col", mode=1, mask=t(g["mask"]))
+    assert same_bits(p, t(g["packed"])) and same_bits(me, t(g["meta"]))
+
+
+@pytest.mark.parametrize("lay", ["row", "col"])
+def test_golden_triton_convert_int8(lay):
+    g = load(f"k2_mse_i8_{lay}")
+    p, me = gpu_compress(t(g["dense"]), torch.int8, col=lay == "col")
+    assert same_bits(p, t(g["packed"])) and same_bits(me, t(g["meta"]))
+
+
+@pytest.mark.parametrize("tag", ["f16", "f32"])
+def test_golden_mvue_device_function(S, tag):
+    g = load(f"mvue_groups_{tag}")
+    x, u = t(g["x"]), t(g["u"])
+    out = S.MVUE24_approx_triton(x.to(DEV), uniforms=u.to(DEV)).cpu()
+    vals = torch.from_numpy(g["vals"])
+    want = torch.where(torch.from_numpy(g["mask"].astype(bool)), vals.to(x.dtype), torch.zeros((), dtype=x.dtype))
+    assert same_bits(out, want)
+
+
+@pytest.mark.parametrize("lay", ["row", "col"])
+@pytest.mark.parametrize("tag", ["f16", "f32"])
+def test_golden_dense_prune_ops(S, tag, lay):
+    for name, fn in (("sparse24", S.sparse24_triton), ("soft_threshold24", S.soft_threshold24_triton)):
+        g = load(f"{name}_{tag}_{lay}")
+        x = t(g["x"]).to(DEV)
+        if lay == "col":
+            x = x.t().contiguous().t()
+        s, mk = fn(x)
+        assert s.stride() == x.stride()
+        assert same_bits(s.cpu().contiguous(), t(g["sparse"])) and same_bits(mk.cpu().contiguous(), t(g["mask"]))
+
+
+def test_golden_dense_prune_ops_bf16(S):
+    g = load("soft_threshold24_bf16_legacy")
+    x = t(g["x"], True).to(DEV)
+    s, mk = S.soft_threshold24_triton(x)
+    assert torch.equal(mk.cpu().bool(), t(g["mask"]).bool())
+    assert torch.equal(s.cpu().float(), t(g["sparse"], True).float())
+
+
+@pytest.mark.parametrize("tag", ["f16", "f32"])
+def test_golden_transposable_kernel(S, tag):
+    g = load(f"transposable_k7_{tag}")
+    s, mk = S.mask_select(t(g["x"]).to(DEV))
+    assert mk.dtype == torch.bool
+    assert torch.equal(mk.cpu(), t(g["mask"])) and same_bits(s.cpu(), t(g["sparse"]))
+
+
+def test_golden_transposable_legacy(S):
+    g = load("transposable_legacy_f16")
+    _, mk = S.TransposableSparse(abs=True)(t(g["x"]).to(DEV))
+    assert torch.equal(mk.cpu(), t(g["mask"]))
+
+
+@pytest.mark.parametrize("name", ["masked_add_f32", "masked_add_example"])
+def test_golden_masked_add(S, name):
+    g = load(name)
+    grad = t(g["grad"]).to(DEV)
+    S.masked_add_(grad, t(g["p"]).to(DEV), t(g["mask"]).to(DEV), alpha=float(g["alpha"]))
+    assert same_bits(grad.cpu(), t(g["out"]))
+
+
+# ------------------------------------------------------------------------------------------------
+# oracle parity on seeded inputs: every dtype pair, both storage orders, all three pruning modes
+# ------------------------------------------------------------------------------------------------
+IN_DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+OUT_DTYPES = [torch.float16, torch.bfloat16, torch.float8_e4m3fn, torch.float8_e5m2]
+
+
+@pytest.mark.parametrize("col", [False, True])
+@pytest.mark.parametrize("od", OUT_DTYPES)
+@pytest.mark.parametrize("idt", IN_DTYPES)
+def test_compress_matches_oracle(idt, od, col):
+    m, k = 96, 640  # 640 = one full 512-wide tile + a ragged one; 96 = three row groups
+    x = with_ties(randn((m, k), 200), 1200).to(idt)
+    g = torch.Generator().manual_seed(201)
+    pats = torch.tensor([[1, 1, 0, 0], [1, 0, 1, 0], [1, 0, 0, 1], [0, 1, 1, 0], [0, 1, 0, 1], [0, 0, 1, 1]], dtype=torch.bool)
+    mask = pats[torch.randint(0, 6, (m, k // 4), generator=g)].reshape(m, k)
+    bad = torch.rand(m, k // 4, generator=g) < 0.05
+    mask = torch.where(bad.repeat_interleave(4, 1), torch.rand(m, k, generator=g) < 0.5, mask)
+    U = torch.rand(m, k, generator=g)
+    p, me = gpu_compress(x, od, col=col)
+    wp, wm = O.prune_compress(x, od)
+    assert same_bits(p, wp) and same_bits(me, wm)
+    p, me = gpu_compress(x, od, col=col, mode=1, mask=mask)
+    wp, wm = O.prune_compress(x, od, mask=mask)
+    assert same_bits(p, wp) and same_bits(me, wm)
+    xs = (x.float() * 1e-2).to(idt)
+    p, me = gpu_compress(xs, od, col=col, mode=2, U=U)
+    wp, wm = O.prune_compress(xs, od, mvue=True, U=U)
+    assert same_bits(p, wp) and same_bits(me, wm)
+    p, me = gpu_compress(xs, od, col=col, mode=2, seed=0x1234_5678_9ABC, offset=77)
+    wp, wm = O.prune_compress(xs, od, mvue=True, seed=0x1234_5678_9ABC, offset=77)
+    assert same_bits(p, wp) and same_bits(me, wm)
+
+
+@pytest.mark.parametrize("shape", [(32, 64), (32, 128), (64, 64), (32, 1088), (2048, 64)])
+def test_compress_edge_shapes(shape):
+    x = randn(shape, 210).half()
+    for col in (False, True):
+        p, me = gpu_compress(x, torch.float16, col=col)
+        wp, wm = O.prune_compress(x, torch.float16)
+        assert same_bits(p, wp) and same_bits(me, wm)
+
+
+def test_compress_padded_leading_dimension():
+    from sparse._semi_structured_conversions import prune_compress
+    m, k = 64, 128
+    big = randn((m, k + 64), 211).half().to(DEV)
+    x = big[:, :k]  # row stride k + 64
+    packed = torch.empty(m, k // 2 + 8, dtype=torch.float16, device=DEV)[:, : k // 2]
+    meta = torch.empty(m, k // 16, dtype=torch.int16, device=DEV)
+    prune_compress(x, packed, meta, mode=0)
+    wp, wm = O.prune_compress(x.cpu().contiguous(), torch.float16)
+    assert same_bits(packed.cpu().contiguous(), wp) and same_bits(meta.cpu(), wm)
+
+
+def test_to_sparse_semi_structured_api(S):
+    w = randn((128, 256), 220, 0.02).to(DEV)  # fp32 master weight, fp16 compressed copy
+    _, mask = S.mask_select(w)
+    a = S.to_sparse_semi_structured(w, mask=mask, dtype=torch.float16)
+    b = S.to_sparse_semi_structured(w.T, mask=mask.T, dtype=torch.float16)
+    assert a.shape == (128, 256) and b.shape == (256, 128)
+    assert a.sparse_tensor_cutlass.stride() == (128, 1)
+    assert b.sparse_tensor_cutlass.stride() == (1, 256)  # column-major packed, mirrors the W.T view
+    wp, wm = O.prune_compress(w.cpu(), torch.float16, mask=mask.cpu())
+    assert same_bits(a.values().cpu(), wp) and same_bits(a.indices().cpu(), wm)
+    wp, wm = O.prune_compress(w.cpu().t().contiguous(), torch.float16, mask=mask.cpu().t().contiguous())
+    assert same_bits(b.values().cpu().contiguous(), wp) and same_bits(b.indices().cpu(), wm)
+    want = torch.where(mask.cpu(), w.cpu(), torch.zeros(())).half()
+    assert same_bits(a.to_dense().cpu(), want) and same_bits(b.to_dense().cpu(), want.t().contiguous())
+    at = a.t()
+    assert at.shape == (256, 128) and at.transposed and at.sparse_tensor_cutlass is a.sparse_tensor_cutlass
+    with pytest.raises(RuntimeError, match="MVUE24 with mask"):
+        S.to_sparse_semi_structured(w, mask=mask, MVUE24=True)
+    with pytest.raises(RuntimeError, match="is not supported"):
+        S.to_sparse_semi_structured(w[:, :48])
+    with pytest.raises(RuntimeError, match="Only CUDA"):
+        S.to_sparse_semi_structured(w.cpu())
+    with pytest.raises(RuntimeError, match="Only 2d"):
+        S.to_sparse_semi_structured(w.view(2, 64, 256))
+
+
+@pytest.mark.parametrize("col", [False, True])
+@pytest.mark.parametrize("dt", IN_DTYPES)
+def test_dense_ops_match_oracle(S, dt, col):
+    m, k = 160, 264
+    x = with_ties(randn((m, k), 230), 1230).to(dt)
+    xg = x.to(DEV)
+    if col:
+        xg = xg.t().contiguous().t()
+    s, mk = S.sparse24_triton(xg)
+    ws, wm = O.sparse24(x)
+    assert same_bits(s.cpu().contiguous(), ws) and same_bits(mk.cpu().contiguous(), wm)
+    s, mk = S.soft_threshold24_triton(xg)
+    ws, wm = O.soft_threshold24(x)
+    assert same_bits(s.cpu().contiguous(), ws) and same_bits(mk.cpu().contiguous(), wm)
+    s, mk = S.soft_threshold24_triton(xg, scale=1.37)
+    ws, wm = O.soft_threshold24(x, scale=1.37)
+    assert same_bits(s.cpu().contiguous(), ws)
+    g = torch.Generator().manual_seed(231)
+    U = torch.rand(m, k, generator=g)
+    out = S.MVUE24_approx_triton(xg, uniforms=U.to(DEV))
+    assert same_bits(out.cpu().contiguous(), O.mvue24_dense(x, U=U))
+    out = S.MVUE24_approx_triton(xg, seed=99, offset=5)
+    assert same_bits(out.cpu().contiguous(), O.mvue24_dense(x, seed=99, offset=5))
+
+
+@pytest.mark.parametrize("dt", IN_DTYPES)
+def test_transposable_matches_oracle(S, dt):
+    x = randn((96, 192), 240, 0.02).to(dt)
+    x.view(-1)[::97] = 0
+    x[4:8, 8:12] = x[4, 8]  # a block of equal magnitudes: first pattern must win
+    for use_abs in (True, False):
+        s, mk = S.TransposableSparse(abs=use_abs)(x.to(DEV))
+        ws, wm = O.transposable_sparse(x, abs=use_abs)
+        assert torch.equal(mk.cpu(), wm) and same_bits(s.cpu(), ws)
+
+
+@pytest.mark.parametrize("dt", IN_DTYPES)
+@pytest.mark.parametrize("od", [torch.float16, torch.bfloat16])
+def test_fused_select_dual_compress(S, dt, od):
+    m, k = 128, 320
+    w = randn((m, k), 250, 0.02).to(dt)
+    mask, (pw, mw), (pt, mt) = S.select_and_compress(w.to(DEV), dtype=od)
+    wm = O.transposable_mask(w)
+    assert torch.equal(mask.cpu(), wm)
+    a, b = O.compress_with_mask(w, wm, od)
+    assert same_bits(pw.cpu(), a) and same_bits(mw.cpu(), b)
+    a, b = O.compress_with_mask(w.t().contiguous(), wm.t().contiguous(), od)
+    assert pt.shape == (k, m // 2) and pt.stride() == (1, k)
+    assert same_bits(pt.cpu().contiguous(), a) and same_bits(mt.cpu(), b)
+    # reuse of a given mask (no re-selection)
+    g = torch.Generator().manual_seed(251)
+    w2 = randn((m, k), 252, 0.02).to(dt)
+    mask2, (pw2, mw2), (pt2, mt2) = S.select_and_compress(w2.to(DEV), mask=mask, dtype=od)
+    a, b = O.compress_with_mask(w2, wm, od)
+    assert same_bits(pw2.cpu(), a) and same_bits(mw2.cpu(), b)
+    a, b = O.compress_with_mask(w2.t().contiguous(), wm.t().contiguous(), od)
+    assert same_bits(pt2.cpu().contiguous(), a) and same_bits(mt2.cpu(), b)
+
+
+@pytest.mark.parametrize("n", [1, 3, 4, 1023, 4096 + 5])
+@pytest.mark.parametrize("mdt", [torch.bool, torch.float16, torch.float32])
+def test_masked_add_matches_oracle(S, n, mdt):
+    g = torch.Generator().manual_seed(260 + n)
+    grad, p = torch.randn(n, generator=g) * 1e-3, torch.randn(n, generator=g) * 0.02
+    mask = (torch.rand(n, generator=g) < 0.5).to(mdt)
+    if mdt != torch.bool and n > 2:
+        mask[1] = -0.0  # negative zero counts as zero
+    gg = grad.to(DEV)
+    S.masked_add_(gg, p.to(DEV), mask.to(DEV), alpha=2e-4)
+    assert same_bits(gg.cpu(), O.masked_add(grad, p, mask != 0, 2e-4))
+
+
+def test_masked_add_rejects_mismatch(S):
+    a = torch.zeros(8, 8, device=DEV)
+    with pytest.raises(AssertionError):
+        S.masked_add_(a, a.t(), a.bool(), alpha=0.1)
+    with pytest.raises(RuntimeError, match="float32"):
+        S.masked_add_(a.half(), a.half(), a.bool(), alpha=0.1)
+
+
+# ------------------------------------------------------------------------------------------------
+# full-size configurations: size-independent properties + spot parity on a slab
+# ------------------------------------------------------------------------------------------------
+def _two_per_group(mask_bool):
+    m, k = mask_bool.shape
+    return bool((mask_bool.view(m, k // 4, 4).sum(-1) == 2).all())
+
+
+def test_config1_roundtrip(S):
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(1024, 1024, generator=g).half()
+    sp = S.to_sparse_semi_structured(w.to(DEV))
+    assert sp.values().shape == (1024, 512) and sp.indices().shape == (1024, 64)
+    wp, wm = O.prune_compress(w, torch.float16)
+    assert same_bits(sp.values().cpu(), wp) and same_bits(sp.indices().cpu(), wm)
+    dense = sp.to_dense().cpu()
+    want = torch.where(O.magnitude_mask24(w), w, torch.zeros((), dtype=w.dtype))
+    assert same_bits(dense, want)
+
+
+def test_config2_full_size_properties(S):
+    g = torch.Generator().manual_seed(2)
+    w = (torch.randn(4096, 4096, generator=g) * 0.02).half().to(DEV)
+    mask, (pw, mw), (pt, mt) = S.select_and_compress(w)
+    mk4 = mask.view(1024, 4, 1024, 4)
+    assert bool((mk4.sum(1) == 2).all()) and bool((mk4.sum(3) == 2).all())
+    # the fused kernel equals the three-launch sequence it replaces
+    _, mask2 = S.mask_select(w)
+    assert torch.equal(mask, mask2)
+    a = S.to_sparse_semi_structured(w, mask=mask)
+    b = S.to_sparse_semi_structured(w.T, mask=mask.T)
+    assert torch.equal(pw, a.values()) and torch.equal(mw, a.indices())
+    assert torch.equal(pt, b.values()) and torch.equal(mt, b.indices())
+    # round trip
+    from sparse._semi_structured_conversions import sparse_semi_structured_to_dense
+    want = torch.where(mask, w, torch.zeros((), dtype=w.dtype, device=DEV))
+    assert torch.equal(sparse_semi_structured_to_dense(pw, mw), want)
+    assert torch.equal(sparse_semi_structured_to_dense(pt.contiguous(), mt), want.t())
+    # oracle parity on a 256-row slab (independent 4x4 blocks and row groups make slabs self-contained)
+    sl = w[1024:1280].cpu()
+    assert torch.equal(mask[1024:1280].cpu(), O.transposable_mask(sl))
+    # a transposable mask cannot keep more magnitude than unconstrained row-wise 2:4 pruning, and on
+    # Gaussian weights it keeps most of it
+    kept = float((sl.float().abs() * mask[1024:1280].cpu()).sum())
+    bound = float((sl.float().abs() * O.magnitude_mask24(sl)).sum())
+    assert 0.9 * bound < kept <= bound
+
+
+def test_config3_full_size_properties(S):
+    g = torch.Generator().manual_seed(3)
+    G = torch.randn(8192, 4096, generator=g) * 1e-3
+    pos = torch.randperm(G.numel(), generator=torch.Generator().manual_seed(4))[: G.numel() // 100]
+    G.view(-1)[pos] *= 100
+    G = G.bfloat16()
+    U = torch.rand(8192, 4096, generator=torch.Generator().manual_seed(5))
+    Gg, Ug = G.to(DEV), U.to(DEV)
+    # MVUE compress, driven by U; parity on a slab, structure on everything
+    from sparse._semi_structured_conversions import prune_compress, sparse_semi_structured_to_dense
+    packed = torch.empty(8192, 2048, dtype=torch.bfloat16, device=DEV)
+    meta = torch.empty(8192, 256, dtype=torch.int16, device=DEV)
+    prune_compress(Gg, packed, meta, mode=2, uniforms=Ug)
+    dense = sparse_semi_structured_to_dense(packed, meta)
+    d_ref = S.MVUE24_approx_triton(Gg, uniforms=Ug)
+    assert torch.equal(dense, d_ref)  # compress then expand == dense-shaped MVUE with the same U
+    sl = slice(4096, 4096 + 128)
+    assert same_bits(d_ref[sl].cpu(), O.mvue24_dense(G[sl], U=U[sl]))
+    # unbiasedness over independent seeds (statistical, tolerance 6 sigma of the mean's estimator)
+    x = Gg[:256].float()
+    acc = torch.zeros_like(x)
+    sq = torch.zeros_like(x)
+    n = 200
+    for i in range(n):
+        d = S.MVUE24_approx_triton(Gg[:256], seed=1234, offset=i).float()
+        acc += d
+        sq += d * d
+    mean = acc / n
+    var = (sq / n - mean * mean).clamp_min(0) / n
+    z = (mean - x).abs() / (var.sqrt() + 1e-9 + x.abs() * 2 ** -8)  # bf16 output rounding allowance
+    assert float(z.mean()) < 1.5 and float((z > 6).float().mean()) < 1e-3
+    # soft threshold: parity on a slab, mask structure everywhere
+    s, mk = S.soft_threshold24_triton(Gg)
+    assert _two_per_group(mk.bool())
+    ws, wm = O.soft_threshold24(G[sl])
+    assert same_bits(s[sl].cpu(), ws) and same_bits(mk[sl].cpu(), wm)
+    # masked decay with the transposable mask of p itself
+    p = (torch.randn(8192, 4096, generator=torch.Generator().manual_seed(6)) * 0.02).to(DEV)
+    _, pm = S.mask_select(p)
+    grad = Gg.float()
+    before = grad.clone()
+    S.masked_add_(grad, p, pm, alpha=2e-4)
+    assert torch.equal(grad[pm], before[pm])
+    assert same_bits(grad[sl].cpu(), O.masked_add(before[sl].cpu(), p[sl].cpu(), pm[sl].cpu(), 2e-4))
+    ident = before + (p * 2e-4) * (~pm)
+    assert torch.equal(grad, ident)
