@@ -278,6 +278,18 @@ def mvue24_groups(x4: np.ndarray, u0: np.ndarray, u1: np.ndarray):
     return vals.astype(f), mask
 
 
+def mvue24_probabilities(x4: np.ndarray) -> np.ndarray:
+    """Inclusion probabilities p_i of sparse/utils.py:31-34 (float32 (..., 4)): the estimator stores
+    x_i / p_i with probability p_i, which is what makes it unbiased."""
+    f = np.float32
+    a = [np.abs(x4[..., i].astype(f)) + MVUE_EPS for i in range(4)]
+    s = ((a[0] + a[1]) + a[2]) + a[3]
+    t = [ai / s for ai in a]
+    kk = [ti / (s - ai) for ti, ai in zip(t, a)]
+    ks = ((kk[0] + kk[1]) + kk[2]) + kk[3]
+    return np.stack([t[i] + a[i] * (ks - kk[i]) for i in range(4)], axis=-1).astype(f)
+
+
 def _uniform_pairs_from_tensor(U: torch.Tensor):
     """Test-mode convention: group g of row r uses U[r, 4g] and U[r, 4g+1]."""
     m, k = U.shape

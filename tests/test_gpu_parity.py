@@ -377,19 +377,27 @@ def test_config3_full_size_properties(S):
     assert torch.equal(dense, d_ref)  # compress then expand == dense-shaped MVUE with the same U
     sl = slice(4096, 4096 + 128)
     assert same_bits(d_ref[sl].cpu(), O.mvue24_dense(G[sl], U=U[sl]))
-    # unbiasedness over independent seeds (statistical, tolerance 6 sigma of the mean's estimator)
-    x = Gg[:256].float()
-    acc = torch.zeros_like(x)
-    sq = torch.zeros_like(x)
-    n = 200
+    # unbiasedness over independent seeds, fp32 in/out so that output rounding adds no bias.  With the
+    # analytic inclusion probabilities p (oracle), E[out] = x and Var[out] = x^2 (1/p - 1): the signed
+    # sum of the errors over a slab and the kept-frequency sum must sit within 6 sigma (within-group
+    # correlation bounded by a factor 4 on the variance).
+    xs = Gg[:256].float()
+    n = 300
+    acc = torch.zeros_like(xs)
+    freq = torch.zeros_like(xs)
     for i in range(n):
-        d = S.MVUE24_approx_triton(Gg[:256], seed=1234, offset=i).float()
+        d = S.MVUE24_approx_triton(xs, seed=1234, offset=i)
         acc += d
-        sq += d * d
-    mean = acc / n
-    var = (sq / n - mean * mean).clamp_min(0) / n
-    z = (mean - x).abs() / (var.sqrt() + 1e-9 + x.abs() * 2 ** -8)  # bf16 output rounding allowance
-    assert float(z.mean()) < 1.5 and float((z > 6).float().mean()) < 1e-3
+        freq += (d != 0).float()
+    x_cpu = xs.cpu()
+    p = torch.from_numpy(O.mvue24_probabilities(x_cpu.reshape(256, -1, 4).numpy())).reshape(x_cpu.shape).double()
+    var = (x_cpu.double() ** 2) * (1 / p - 1).clamp_min(0)
+    err = float(((acc.cpu().double() / n) - x_cpu.double()).sum())
+    assert abs(err) <= 6 * float((4 * var.sum() / n).sqrt()), (err, float((4 * var.sum() / n).sqrt()))
+    nz = x_cpu != 0
+    ferr = float(((freq.cpu().double() / n) - p)[nz].sum())
+    assert abs(ferr) <= 6 * float((4 * (p * (1 - p))[nz].sum() / n).sqrt())
+    assert abs(float(p.reshape(-1, 4).sum(-1).mean()) - 2.0) < 1e-3  # two kept per group on average
     # soft threshold: parity on a slab, mask structure everywhere
     s, mk = S.soft_threshold24_triton(Gg)
     assert _two_per_group(mk.bool())
