@@ -71,7 +71,7 @@ def build(force=False, verbose=False):
     stamp = os.path.join(OBJDIR, "link.stamp")
     want = _digest(objs)
     if force or not os.path.exists(LIB) or not os.path.exists(stamp) or open(stamp).read() != want:
-        r = subprocess.run([nvcc, "-shared", "-o", LIB] + objs + ["-lcuda"], capture_output=True, text=True)
+        r = subprocess.run([nvcc, "-shared", "-o", LIB] + objs, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
         with open(stamp, "w") as f:

@@ -1,0 +1,520 @@
+// 2:4 sparse GEMM for sm_100a:  D (Ms x N) = A_sparse (Ms x K) * B (K x N)  [+ bias per row] [activation]
+//
+// The sparse operand is always the tensor-core "A" operand of tcgen05.mma.sp: compressed values are
+// staged in shared memory by TMA (128-byte swizzle), its metadata goes shared memory -> tensor memory
+// with tcgen05.cp, the dense operand B is staged by TMA, accumulators live in tensor memory and are read
+// back with tcgen05.ld by four epilogue warps.
+//
+// Warp roles in a CTA of 192 threads: warp 0 = TMA producer (one elected lane), warp 1 = tensor-memory
+// allocation + MMA issue (one elected lane), warps 2..5 = epilogue (one TMEM lane quadrant each).
+// One CTA computes one 128 x BN output tile; the K loop runs over stages of 128 bytes of compressed A
+// per row (logical K 128 for 16-bit types, 256 for 8-bit types) through a STAGES-deep mbarrier ring.
+//
+// Every wait on an mbarrier is bounded: when a wait gives up, the CTA records a code in *status,
+// raises a shared abort flag that cuts all other waits short, drains its own copies in flight (again
+// bounded), frees its tensor memory and returns.  Nothing traps.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstdlib>
+
+#include "sp24_common.cuh"
+
+namespace sp24 {
+namespace {
+
+constexpr int BM = 128;            // rows of the sparse operand per CTA tile (= TMEM lanes)
+constexpr int A_STAGE_BYTES = BM * 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;  // polls of mbarrier.try_wait before a wait gives up
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up (limit reached or another role raised the abort flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 0xFFu) == 0xFFu && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (status) atomicCAS(status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_128x128b(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+template <bool F8>
+__device__ __forceinline__ void mma_sp(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t e_tmem, uint32_t idesc,
+                                       uint32_t accumulate) {
+    if constexpr (F8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+            "tcgen05.mma.sp.cta_group::1.kind::f8f6f4 [%0], %1, %2, [%3], %4, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+            "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets (all >> 4),
+// descriptor version 1, swizzle mode in bits 61..63 (0 none, 2 = 128-byte).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swizzle) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)swizzle << 61;
+    return d;
+}
+
+struct SpmmParams {
+    const void *e_tc;       // metadata in tensor-core atom order
+    void *out;
+    const void *bias;       // per sparse row (output feature), in the output type, or null
+    int64_t ms, n, k;       // sparse rows, dense columns, logical K
+    int64_t ld_out;
+    int64_t k_atoms;        // number of 128-column metadata atoms per 128-row block (K padded up)
+    int *status;
+    uint32_t idesc;         // instruction descriptor without the metadata selector bits
+    int activation;         // 0 none, 1 relu, 2 silu
+    // experiment knobs of the descriptor builder (bytes)
+    uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep, b_atom_bytes, e_sbo, e_lbo, e_mode;
+};
+
+template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
+template <> __device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <typename OutT> __device__ __forceinline__ float from_out(OutT v);
+template <> __device__ __forceinline__ float from_out<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float from_out<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float from_out<float>(float v) { return v; }
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == 1) return v > 0.f ? v : 0.f;
+    if (act == 2) return v / (1.f + __expf(-v));
+    return v;
+}
+
+// BN: dense columns per tile.  A_MN / B_MN: operand stored with the non-K axis contiguous.
+// TRANS_OUT: write out[n][m] (row-major (N, Ms)) instead of out[m][n].
+template <int BN, int STAGES, bool F8, bool A_MN, bool B_MN, bool TRANS_OUT, typename OutT>
+__global__ void __launch_bounds__(192, 1)
+spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, SpmmParams P) {
+    constexpr int B_STAGE_BYTES = BN * 256;           // two 128-byte K atoms per row of B
+    constexpr int E_STAGE_BYTES = F8 ? 4096 : 2048;   // metadata atoms covering the stage's logical K
+    constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + E_STAGE_BYTES;
+    constexpr int KSTEPS = 4;                         // MMA instructions per stage (32 bytes of compressed A each)
+    constexpr uint32_t TMEM_COLS = BN <= 96 ? 128 : (BN <= 224 ? 256 : 512);
+    constexpr int E_COL0 = BN;                        // metadata columns start right after the accumulator
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_blk = blockIdx.y, n_blk = blockIdx.x;
+    const int64_t m0 = (int64_t)m_blk * BM, n0 = (int64_t)n_blk * BN;
+    const int logical_k_per_stage = F8 ? 256 : 128;
+    const int k_iters = (int)((P.k + logical_k_per_stage - 1) / logical_k_per_stage);
+
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_smem), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int it = 0; it < k_iters; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (it >= STAGES && !mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, P.status, 1)) break;
+                const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint32_t sb = sa + A_STAGE_BYTES;
+                const uint32_t se = sb + B_STAGE_BYTES;
+                const uint32_t full = full0 + 8 * s;
+                mbar_expect_tx(full, STAGE_BYTES);
+                // compressed A: 128 rows x 128 bytes
+                if constexpr (!A_MN) {
+                    tma_load_2d(sa, &map_a, it * (F8 ? 128 : 64), (int)m0, full);
+                } else {
+                    tma_load_2d(sa, &map_a, (int)m0, it * 64, full);
+                    tma_load_2d(sa + 8192, &map_a, (int)m0 + 64, it * 64, full);
+                }
+                // dense B: BN rows x 2 atoms of 128 bytes (K-major) or BN/64 atoms of 128 K-rows (MN-major)
+                if constexpr (!B_MN) {
+                    const int kx = it * (F8 ? 256 : 128);
+                    tma_load_2d(sb, &map_b, kx, (int)n0, full);
+                    tma_load_2d(sb + BN * 128, &map_b, kx + (F8 ? 128 : 64), (int)n0, full);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 16384, &map_b, (int)n0 + j * 64, it * 128, full);
+                }
+                // metadata atoms of this 128-row block
+                const uint8_t *e_src = static_cast<const uint8_t *>(P.e_tc) +
+                                       ((size_t)m_blk * P.k_atoms + (size_t)it * (E_STAGE_BYTES / 2048)) * 2048;
+                bulk_load(se, e_src, E_STAGE_BYTES, full);
+                ++issued;
+            }
+            if (abort_flag) {
+                // drain: wait (bounded) for the copies already issued so that none lands after exit
+                for (int it = (issued > STAGES ? issued - STAGES : 0); it < issued; ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    for (uint32_t w = 0; w < WAIT_LIMIT; ++w)
+                        if (mbar_try_wait(full0 + 8 * s, ph)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < k_iters && ok; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, P.status, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint32_t sb = sa + A_STAGE_BYTES;
+                const uint32_t se = sb + B_STAGE_BYTES;
+                const uint32_t e_cols = E_COL0 + (it & 1) * (F8 ? 8 : 4);
+                // metadata: shared memory -> tensor memory, 128 lanes x 16 bytes per atom
+                tc_cp_128x128b(tmem_base + e_cols, make_desc(se, P.e_lbo, P.e_sbo, 0));
+                if constexpr (F8) tc_cp_128x128b(tmem_base + e_cols + 4, make_desc(se + 2048, P.e_lbo, P.e_sbo, 0));
+#pragma unroll
+                for (int j = 0; j < KSTEPS; ++j) {
+                    const uint64_t adesc = make_desc(sa + j * P.a_kstep, P.a_lbo, P.a_sbo, 2);
+                    const uint32_t b_off = B_MN ? j * P.b_kstep : (uint32_t)(j >> 1) * P.b_atom_bytes + (j & 1) * P.b_kstep;
+                    const uint64_t bdesc = make_desc(sb + b_off, P.b_lbo, P.b_sbo, 2);
+                    const uint32_t ecol = e_cols + (F8 ? 2 * j : j);
+                    // 16-bit types: the instruction takes the even column of a pair plus a 1-bit selector
+                    const bool pair_sel = !F8 && P.e_mode == 0;
+                    const uint32_t e_addr = tmem_base + (pair_sel ? (ecol & ~1u) : ecol);
+                    const uint32_t idesc = P.idesc | (pair_sel ? (ecol & 1u) : 0u);
+                    mma_sp<F8>(tmem_base, adesc, bdesc, e_addr, idesc, (it > 0 || j > 0) ? 1u : 0u);
+                }
+                tc_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
+            }
+            tc_commit(accum_bar);           // accumulator complete (arrives even after an abort)
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+        const bool ok = mbar_wait(accum_bar, 0, &abort_flag, P.status, 3);
+        tc_fence_after();
+        if (ok && !abort_flag) {
+            const int64_t m = m0 + quad * 32 + lane;
+            OutT *out = static_cast<OutT *>(P.out);
+            float bias = 0.f;
+            if (P.bias) bias = from_out<OutT>(static_cast<const OutT *>(P.bias)[m]);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + c * 32, v);
+                tmem_ld_wait();
+                const int64_t nb = n0 + c * 32;
+                if constexpr (TRANS_OUT) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (nb + i < P.n)
+                            out[(nb + i) * P.ld_out + m] = to_out<OutT>(apply_act(__uint_as_float(v[i]) + bias, P.activation));
+                    }
+                } else {
+                    OutT *row = out + m * P.ld_out + nb;
+                    if (nb + 32 <= P.n) {
+                        constexpr int PER = 16 / sizeof(OutT);
+#pragma unroll
+                        for (int q = 0; q < 32 / PER; ++q) {
+                            Vec<OutT, PER> o;
+#pragma unroll
+                            for (int i = 0; i < PER; ++i)
+                                o.v[i] = to_out<OutT>(apply_act(__uint_as_float(v[q * PER + i]) + bias, P.activation));
+                            store_vec<OutT, PER>(row + q * PER, o);
+                        }
+                    } else {
+                        for (int i = 0; i < 32; ++i)
+                            if (nb + i < P.n) row[i] = to_out<OutT>(apply_act(__uint_as_float(v[i]) + bias, P.activation));
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// metadata: reference (reordered) layout -> tensor-core atom order
+// ------------------------------------------------------------------------------------------------
+// 16-bit types: atom = 128 rows x 128 logical columns = 2048 bytes, byte 16*L + 4*q + 2*h with
+// L = 16*(r/16) + 8*(c%2) + r%8, q = (c/2)%4, h = (r/8)%2 for row r (inside the 128-row block) and
+// 16-column metadata word c.  8-bit types: atom = 128 rows x 16 bytes, row-major.
+template <int MB>
+__global__ void meta_to_tc_kernel(const void *meta_api, uint8_t *e_tc, int64_t m, int64_t ncols, int64_t k_atoms) {
+    const int64_t words_per_atom = 2048 / MB;
+    const int64_t total = (m / 128) * k_atoms * words_per_atom;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t atom = idx / words_per_atom;
+    const int w = (int)(idx % words_per_atom);
+    const int64_t mb = atom / k_atoms, kb = atom % k_atoms;
+    int r, cw;  // row inside the block, metadata word inside the atom's 128 columns
+    if constexpr (MB == 2) {
+        const int L = w >> 3, q = (w >> 1) & 3, h = w & 1;
+        r = 16 * (L >> 4) + 8 * h + (L & 7);
+        cw = 2 * q + ((L >> 3) & 1);
+    } else {
+        r = w >> 2;
+        cw = w & 3;
+    }
+    const int64_t c = kb * (MB == 2 ? 8 : 4) + cw;
+    using MetaT = typename VecBytes<MB>::type;
+    MetaT val = 0;
+    if (c < ncols) val = static_cast<const MetaT *>(meta_api)[meta_offset<MB>(mb * 128 + r, c, m)];
+    reinterpret_cast<MetaT *>(e_tc)[idx] = val;
+}
+
+CUtensorMapDataType tmap_dtype(int dt) {
+    switch (dt) {
+        case SP24_F16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        case SP24_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        default: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    }
+}
+
+// cuTensorMapEncodeTiled is looked up through the runtime so that the library has no link-time
+// dependency on the driver library (it must load on machines without a GPU driver).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D tensor map over a row-major (rows, cols) array with leading dimension ld (elements), 128-byte swizzle.
+int make_map(CUtensorMap *map, const void *base, int dt, int64_t rows, int64_t cols, int64_t ld, uint32_t box_cols,
+             uint32_t box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * dtype_size(dt)};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return SP24_ERR_CUDA;
+    const CUresult r = encode(map, tmap_dtype(dt), 2, const_cast<void *>(base), dims, strides, box, estr,
+                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? SP24_OK : SP24_ERR_CUDA;
+}
+
+template <int BN, int STAGES, bool F8, bool A_MN, bool B_MN, bool TRANS, typename OutT>
+int launch_spmm(const CUtensorMap &ma, const CUtensorMap &mb, const SpmmParams &P, cudaStream_t st) {
+    constexpr int STAGE_BYTES = A_STAGE_BYTES + BN * 256 + (F8 ? 4096 : 2048);
+    constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
+    auto kern = spmm_kernel<BN, STAGES, F8, A_MN, B_MN, TRANS, OutT>;
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return SP24_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    dim3 grid((unsigned)((P.n + BN - 1) / BN), (unsigned)(P.ms / BM));
+    kern<<<grid, 192, SMEM, st>>>(ma, mb, P);
+    return launch_status();
+}
+
+}  // namespace
+}  // namespace sp24
+
+using namespace sp24;
+
+extern "C" int sp24_meta_to_tc(const void *meta, int meta_itemsize, int64_t m, int64_t k, void *e_tc, void *stream) {
+    if (!meta || !e_tc) return SP24_ERR_ARG;
+    if (meta_itemsize != 2 && meta_itemsize != 4) return SP24_ERR_DTYPE;
+    if (m <= 0 || k <= 0 || m % 128 || k % (meta_itemsize == 2 ? 64 : 128)) return SP24_ERR_SHAPE;
+    if (!aligned16(meta) || !aligned16(e_tc)) return SP24_ERR_ALIGN;
+    if (int rc = check_device()) return rc;
+    const int64_t k_atoms = (k + 127) / 128;
+    const int64_t total = (m / 128) * k_atoms * (2048 / meta_itemsize);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (meta_itemsize == 2)
+        meta_to_tc_kernel<2><<<blocks, 256, 0, st>>>(meta, static_cast<uint8_t *>(e_tc), m, k / 16, k_atoms);
+    else
+        meta_to_tc_kernel<4><<<blocks, 256, 0, st>>>(meta, static_cast<uint8_t *>(e_tc), m, k / 32, k_atoms);
+    return launch_status();
+}
+
+extern "C" int64_t sp24_meta_tc_bytes(int64_t m, int64_t k) {
+    if (m <= 0 || k <= 0) return 0;
+    return ((m + 127) / 128) * ((k + 127) / 128) * 2048;
+}
+
+extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms,
+                         int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype,
+                         int trans_out, int64_t ld_out, const void *bias, int activation, int *status, void *stream) {
+    if (!a_packed || !e_tc || !b || !out) return SP24_ERR_ARG;
+    const bool f8 = dtype == SP24_E4M3 || dtype == SP24_E5M2;
+    if (!f8 && dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
+    if (f8 ? out_dtype != SP24_F32 : out_dtype != dtype) return SP24_ERR_DTYPE;
+    if (f8 && (a_mn_major || b_mn_major)) return SP24_ERR_DTYPE;  // 8-bit operands are K-major only
+    if (activation < 0 || activation > 2) return SP24_ERR_ARG;
+    const int esz = f8 ? 1 : 2;
+    if (ms <= 0 || n <= 0 || k <= 0 || ms % 128 || k % (f8 ? 128 : 64) || n % 8) return SP24_ERR_SHAPE;
+    const int64_t a_inner = a_mn_major ? ms : k / 2, b_inner = b_mn_major ? n : k, o_inner = trans_out ? ms : n;
+    if (ld_a < a_inner || (ld_a * esz) % 16 || ld_b < b_inner || (ld_b * esz) % 16 || ld_out < o_inner) return SP24_ERR_STRIDE;
+    if ((ld_out * dtype_size(out_dtype)) % 16 && !trans_out) return SP24_ERR_STRIDE;
+    if (!aligned16(a_packed) || !aligned16(e_tc) || !aligned16(b) || !aligned16(out)) return SP24_ERR_ALIGN;
+    if (int rc = check_device()) return rc;
+
+    CUtensorMap map_a, map_b;
+    int rc;
+    if (!a_mn_major) rc = make_map(&map_a, a_packed, dtype, ms, k / 2, ld_a, f8 ? 128 : 64, 128);
+    else rc = make_map(&map_a, a_packed, dtype, k / 2, ms, ld_a, 64, 64);
+    if (rc) return rc;
+    constexpr int BN = 128;
+    if (!b_mn_major) rc = make_map(&map_b, b, dtype, n, k, ld_b, f8 ? 128 : 64, BN);
+    else rc = make_map(&map_b, b, dtype, k, n, ld_b, 64, 128);
+    if (rc) return rc;
+
+    SpmmParams P{};
+    P.e_tc = e_tc; P.out = out; P.bias = bias; P.ms = ms; P.n = n; P.k = k; P.ld_out = ld_out;
+    P.k_atoms = (k + 127) / 128; P.status = status; P.activation = activation;
+    const uint32_t fmt = (dtype == SP24_BF16 || dtype == SP24_E5M2) ? 1u : 0u;
+    P.idesc = (1u << 2) | (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) |
+              ((uint32_t)(b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart, 32 (A) / 64 (B) bytes per MMA inside the atom.
+    // MN-major: 64-element column blocks a whole TMA box apart, 8 K-rows per 1024 bytes.
+    P.a_lbo = a_mn_major ? 8192 : 16; P.a_sbo = 1024; P.a_kstep = a_mn_major ? 2048 : 32;
+    P.b_lbo = b_mn_major ? 16384 : 16; P.b_sbo = 1024; P.b_kstep = b_mn_major ? 4096 : 64; P.b_atom_bytes = BN * 128;
+    P.e_sbo = 128; P.e_lbo = 16;
+    if (const char *env = getenv("SP24_SPMM_KNOBS")) {
+        // debugging aid: "a_lbo,a_sbo,a_kstep,b_lbo,b_sbo,b_kstep,e_lbo,e_sbo,e_mode" (bytes); negative keeps the default
+        long v[9];
+        if (sscanf(env, "%ld,%ld,%ld,%ld,%ld,%ld,%ld,%ld,%ld", &v[0], &v[1], &v[2], &v[3], &v[4], &v[5], &v[6], &v[7],
+                   &v[8]) == 9) {
+            uint32_t *dst[9] = {&P.a_lbo, &P.a_sbo, &P.a_kstep, &P.b_lbo, &P.b_sbo, &P.b_kstep, &P.e_lbo, &P.e_sbo, &P.e_mode};
+            for (int i = 0; i < 9; ++i) if (v[i] >= 0) *dst[i] = (uint32_t)v[i];
+        }
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define SP24_LAUNCH(F8_, AMN_, BMN_, TR_, OT_) return launch_spmm<BN, 4, F8_, AMN_, BMN_, TR_, OT_>(map_a, map_b, P, st)
+    if (f8) {
+        if (trans_out) SP24_LAUNCH(true, false, false, true, float);
+        SP24_LAUNCH(true, false, false, false, float);
+    }
+    if (dtype == SP24_F16) {
+        if (!a_mn_major && !b_mn_major) { if (trans_out) SP24_LAUNCH(false, false, false, true, __half); SP24_LAUNCH(false, false, false, false, __half); }
+        if (a_mn_major && !b_mn_major) { if (trans_out) SP24_LAUNCH(false, true, false, true, __half); SP24_LAUNCH(false, true, false, false, __half); }
+        if (!a_mn_major && b_mn_major) { if (trans_out) SP24_LAUNCH(false, false, true, true, __half); SP24_LAUNCH(false, false, true, false, __half); }
+        if (trans_out) SP24_LAUNCH(false, true, true, true, __half);
+        SP24_LAUNCH(false, true, true, false, __half);
+    }
+    if (!a_mn_major && !b_mn_major) { if (trans_out) SP24_LAUNCH(false, false, false, true, __nv_bfloat16); SP24_LAUNCH(false, false, false, false, __nv_bfloat16); }
+    if (a_mn_major && !b_mn_major) { if (trans_out) SP24_LAUNCH(false, true, false, true, __nv_bfloat16); SP24_LAUNCH(false, true, false, false, __nv_bfloat16); }
+    if (!a_mn_major && b_mn_major) { if (trans_out) SP24_LAUNCH(false, false, true, true, __nv_bfloat16); SP24_LAUNCH(false, false, true, false, __nv_bfloat16); }
+    if (trans_out) SP24_LAUNCH(false, true, true, true, __nv_bfloat16);
+    SP24_LAUNCH(false, true, true, false, __nv_bfloat16);
+#undef SP24_LAUNCH
+}

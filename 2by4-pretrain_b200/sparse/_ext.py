@@ -51,6 +51,8 @@ def lib():
         h.sp24_strerror.restype = ctypes.c_char_p
         h.sp24_strerror.argtypes = [_i32]
         h.sp24_abi_version.restype = _i32
+        h.sp24_meta_tc_bytes.restype = _i64
+        h.sp24_meta_tc_bytes.argtypes = [_i64, _i64]
         for name, args in _SIGNATURES.items():
             fn = getattr(h, name, None)
             if fn is not None:

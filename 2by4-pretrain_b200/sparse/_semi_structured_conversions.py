@@ -54,6 +54,8 @@ def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, ma
         meta.data_ptr(), mode, _ext.ptr(mask), ld_m, _ext.ptr(uniforms), ld_u, seed & (2 ** 64 - 1),
         offset & (2 ** 64 - 1), _ext.stream())
     _ext.check(rc, "sp24_prune_compress")
+    from .spmm import invalidate_meta
+    invalidate_meta(meta)  # a refilled metadata buffer must not reuse a cached tensor-core copy
     return sparse, meta
 
 

@@ -1,5 +1,115 @@
-"""2:4 sparse GEMM host wrapper (placeholder until the kernel entry point is bound)."""
+"""Host side of the 2:4 sparse GEMM (tcgen05.mma.sp kernel behind ``sp24_spmm``).
+
+``sparse_linear`` has the contract of the reference's only native function,
+``my_sparse_semi_structured_linear(input, weight, meta, bias, activation)``
+(sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:498-817 of the reference): ``weight`` is the packed
+(ms, k/2) matrix (row- or column-major), ``meta`` its reordered metadata, ``input`` the dense (..., k)
+operand; the result is (..., ms) = input @ dense(weight).T (+ bias) (activation).
+"""
+import ctypes
+import weakref
+
+import torch
+
+from . import _ext
+
+_i64, _i32, _vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+_ext.register_signature("sp24_meta_to_tc", [_vp, _i32, _i64, _i64, _vp, _vp])
+_ext.register_signature("sp24_spmm", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i64, _vp, _i32, _i32,
+                                      _i64, _vp, _i32, _vp, _vp])
+
+_ACT = {None: 0, "none": 0, "relu": 1, "silu": 2}
+_tc_meta_cache = weakref.WeakKeyDictionary()
+_status = {}
+
+
+def _status_word(device):
+    t = _status.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[device] = t
+    return t
+
+
+def check_status(device=None):
+    """Synchronises and raises if a bounded on-device wait of the sparse GEMM ever gave up."""
+    for dev, t in _status.items():
+        if device is None or dev == device:
+            code = int(t.item())
+            if code:
+                t.zero_()
+                raise RuntimeError(f"sp24_spmm: an on-device wait gave up (role code {code}) on {dev}")
+
+
+def invalidate_meta(meta):
+    _tc_meta_cache.pop(meta, None)
+
+
+def tc_metadata(meta: torch.Tensor, ms: int, k: int) -> torch.Tensor:
+    """Metadata in the order the tensor cores consume (cached per metadata tensor object)."""
+    e = _tc_meta_cache.get(meta)
+    if e is None:
+        lib = _ext.lib()
+        lib.sp24_meta_tc_bytes.restype = _i64
+        lib.sp24_meta_tc_bytes.argtypes = [_i64, _i64]
+        nbytes = lib.sp24_meta_tc_bytes(ms, k)
+        e = torch.empty(nbytes, dtype=torch.uint8, device=meta.device)
+        src = meta if meta.is_contiguous() else meta.contiguous()
+        _ext.check(lib.sp24_meta_to_tc(src.data_ptr(), src.element_size(), ms, k, e.data_ptr(), _ext.stream()),
+                   "sp24_meta_to_tc")
+        _tc_meta_cache[meta] = e
+    return e
 
 
 def sparse_linear(input, weight, meta, bias=None, activation=None):
-    raise NotImplementedError("the sm_100a 2:4 sparse GEMM is not available in this build")
+    _ext.require_cuda(input, weight, meta, bias)
+    if activation not in _ACT:
+        raise RuntimeError(f"_sparse_semi_structured_linear: Invalid activation {activation}")
+    if weight.dim() != 2:
+        raise RuntimeError(f"_sparse_semi_structured_linear: Expected weight argument to be 2D tensor, got {weight.dim()} dims")
+    if input.dtype != weight.dtype:
+        raise RuntimeError(f"_sparse_semi_structured_linear: Expected input datatype {weight.dtype}, but got {input.dtype}")
+    ms, kh = weight.shape
+    k = 2 * kh
+    sizes = list(input.shape)
+    if sizes[-1] != k:
+        raise RuntimeError(f"_sparse_semi_structured_linear: Expected weight argument to have {sizes[-1] // 2} columns, but got {kh}")
+    x2 = input.reshape(-1, k)
+    n = x2.shape[0]
+    lay_a = _ext.layout_of(weight)
+    if lay_a is None:
+        raise RuntimeError(f"_sparse_semi_structured_linear: Invalid strides for weight argument: row stride = "
+                           f"{weight.stride(0)}, column stride = {weight.stride(1)}")
+    a_mn, ld_a = lay_a
+    lay_b = _ext.layout_of(x2)
+    if lay_b is None or x2.data_ptr() % 16 or (lay_b[1] * x2.element_size()) % 16:
+        x2 = x2.contiguous()
+        lay_b = (0, k)
+    # layout_of: 0 = rows contiguous along k (K-major for the GEMM), 1 = k strided (the caller passed B.t())
+    b_mn, ld_b = lay_b
+    f8 = weight.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
+    out_dtype = torch.float32 if f8 else weight.dtype
+    if bias is not None:
+        if bias.dim() != 1 or bias.shape[0] != ms:
+            raise RuntimeError(f"_sparse_semi_structured_linear: Expected bias argument to have {ms} elements, but got {bias.numel()}")
+        if bias.dtype != out_dtype:
+            raise RuntimeError(f"two_four_sgemm_cutlass: Expected spars GTEMM bias datatype {out_dtype}, but got {bias.dtype}")
+        bias = bias.contiguous()
+    if ms % 128:
+        raise RuntimeError("sparse GEMM on sm_100a: number of rows of the sparse matrix must be divisible by 128")
+    e_tc = tc_metadata(meta, ms, k)
+    status = _status_word(weight.device)
+    if b_mn:
+        # D (ms, n) row-major; the caller transposes it back (mm with the sparse matrix first)
+        out = torch.empty((ms, n), dtype=out_dtype, device=weight.device)
+        trans_out, ld_out = 0, n
+    else:
+        out = torch.empty((n, ms), dtype=out_dtype, device=weight.device)
+        trans_out, ld_out = 1, ms
+    rc = _ext.lib().sp24_spmm(weight.data_ptr(), _ext.dt(weight.dtype), a_mn, ld_a, e_tc.data_ptr(), ms, k, x2.data_ptr(),
+                              b_mn, ld_b, n, out.data_ptr(), _ext.dt(out_dtype), trans_out, ld_out, _ext.ptr(bias),
+                              _ACT[activation], status.data_ptr(), _ext.stream())
+    _ext.check(rc, "sp24_spmm")
+    res = out.t() if b_mn else out
+    sizes[-1] = ms
+    return res.reshape(sizes) if len(sizes) != 2 else res

@@ -157,6 +157,41 @@ int sp24_select_dual_compress(const void *w, int dtype, int64_t m, int64_t k, in
 int sp24_masked_add(void *grad, const void *p, const void *mask, int mask_itemsize, int64_t n, float alpha,
                     void *stream);
 
+/*
+ * Metadata re-layout for the tensor cores: the reference's reordered metadata (m*k/16 int16 or m*k/32
+ * int32) -> the order tcgen05.mma.sp consumes from tensor memory.  The result is a sequence of 2048-byte
+ * atoms, one per (128-row block, 128-column block), row blocks outermost; 16-bit types: atom byte
+ * 16*L + 4*q + 2*h with L = 16*(r/16) + 8*(c%2) + r%8, q = (c/2)%4, h = (r/8)%2 (r = row in the block,
+ * c = 16-column metadata word in the atom); 8-bit types: 128 rows x 16 bytes, row-major.  K is padded
+ * up to a multiple of 128 with zero words.  sp24_meta_tc_bytes gives the buffer size.  m % 128 == 0.
+ * No counterpart in the reference, whose CUTLASS kernel reads the reordered layout directly
+ * (sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:826-851 documents that layout).
+ */
+int64_t sp24_meta_tc_bytes(int64_t m, int64_t k);
+int sp24_meta_to_tc(const void *meta, int meta_itemsize, int64_t m, int64_t k, void *e_tc, void *stream);
+
+/*
+ * 2:4 sparse GEMM  D (ms x n) = A_sparse (ms x k) * B (k x n) [+ bias[row]] [activation], fp32 accumulate.
+ * Replaces my_sparse_semi_structured_linear and its CUTLASS SparseGemm instantiations
+ * (sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:498-817, :34-233; caller
+ * sparse/sparse_semi_structured_linear.py:4-5).
+ *
+ *   a_packed   compressed values, logical (ms, k/2); a_mn_major = 0: row-major with leading dimension ld_a,
+ *              1: column-major (storage (k/2, ms)), the form the reference produces for W.T and dY.T views
+ *   e_tc       metadata from sp24_meta_to_tc
+ *   b          dense operand, logical (k, n); b_mn_major = 0: stored as (n, k) row-major ("K-major", e.g. the
+ *              activations X (tokens, k)), 1: stored as (k, n) row-major
+ *   out        trans_out = 0: (ms, n) row-major; 1: (n, ms) row-major, i.e. already transposed back to
+ *              (tokens, features); leading dimension ld_out
+ *   dtype      F16 / BF16 (out_dtype = dtype) or E4M3 / E5M2 (out_dtype = F32, K-major operands only)
+ *   bias       ms values in the output type or NULL; activation 0 none, 1 relu, 2 silu
+ *   status     optional device int: set to a non-zero code if a bounded on-device wait gave up
+ * Shape rules: ms % 128 == 0, n % 8 == 0, k % 64 == 0 (16-bit) or k % 128 == 0 (8-bit).
+ */
+int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms, int64_t k,
+              const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype, int trans_out,
+              int64_t ld_out, const void *bias, int activation, int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
