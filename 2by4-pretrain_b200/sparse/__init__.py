@@ -8,10 +8,15 @@ from .triton_ops import MVUE24_approx_triton, sparse24_triton, soft_threshold24_
 from .decay import masked_add_
 from .transposable_semi_structured import TransposableSparse, select_and_compress
 from .semi_structured import to_sparse_semi_structured, SparseSemiStructuredTensor
+from .sparse_ops import MyLinear, SparseLinear, SparseLinearTranspose, sparse_linear_transpose
 
 mask_select = TransposableSparse()
 
 __all__ = [
+    'MyLinear',
+    'SparseLinear',
+    'SparseLinearTranspose',
+    'sparse_linear_transpose',
     'MVUE24_approx_triton',
     'sparse24_triton',
     'soft_threshold24_triton',

@@ -1,0 +1,178 @@
+"""Autograd linear layers of the 2:4 training recipes.
+
+``SparseLinearTranspose`` / ``sparse_linear_transpose`` are the FST layer the reference only lists in
+its README (README.md:125-200 of the reference): forward Y = X W_s^T with the weight compressed under
+a transposable 2:4 mask, backward dX = dY W_s through the separately compressed W^T, and
+dW = MVUE24(dY^T) X with the gradient compressed on the fly.  ``MyLinear`` / ``SparseLinear`` are the
+older dense-GEMM variants of sparse/sparse_ops.py:8-87 of the reference.
+"""
+import torch
+import torch.nn.functional as F
+from torch import autograd, nn
+from torch.amp import custom_fwd, custom_bwd
+
+from .semi_structured import SparseSemiStructuredTensor, to_sparse_semi_structured
+from .transposable_semi_structured import TransposableSparse, select_and_compress
+from .triton_ops import MVUE24_approx_triton
+
+
+class my_linear(autograd.Function):
+    @staticmethod
+    @custom_fwd(device_type='cuda')
+    def forward(ctx, input, weight, bias):
+        ctx.save_for_backward(input, weight, bias)
+        ctx.shape = input.shape
+        input = input.view(-1, input.shape[-1])
+        output = torch.mm(input, weight.t())
+        if bias is None:
+            return output.view(*ctx.shape[:-1], -1)
+        return output.view(*ctx.shape[:-1], -1) + bias
+
+    @staticmethod
+    @custom_bwd(device_type='cuda')
+    def backward(ctx, grad_output):
+        input, weight, bias = ctx.saved_tensors
+        grad_input = grad_weight = grad_bias = None
+        if ctx.needs_input_grad[0]:
+            grad_output = grad_output.reshape(-1, grad_output.shape[-1])
+            grad_input = torch.mm(grad_output, weight).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            input = input.view(-1, input.shape[-1])
+            grad_output = grad_output.reshape(-1, grad_output.shape[-1])
+            grad_weight = torch.mm(grad_output.t(), input)
+        if ctx.needs_input_grad[2]:
+            grad_bias = grad_output.reshape(-1, grad_output.shape[-1]).sum(0)
+        return grad_input, grad_weight, grad_bias
+
+
+class MyLinear(nn.Linear):
+    def forward(self, x):
+        return my_linear.apply(x, self.weight, self.bias)
+
+
+class sparse_linear(autograd.Function):
+    """Dense GEMMs; the backward pass multiplies dY with an MVUE 2:4 estimate of the weight
+    (sparse/sparse_ops.py:58-87 of the reference)."""
+
+    @staticmethod
+    @custom_fwd(device_type='cuda')
+    def forward(ctx, input, weight, bias):
+        ctx.save_for_backward(input, weight, bias)
+        ctx.shape = input.shape
+        input = input.view(-1, input.shape[-1])
+        output = torch.mm(input, weight.t())
+        if bias is None:
+            return output.view(*ctx.shape[:-1], -1)
+        return output.view(*ctx.shape[:-1], -1) + bias
+
+    @staticmethod
+    @custom_bwd(device_type='cuda')
+    def backward(ctx, grad_output):
+        input, weight, bias = ctx.saved_tensors
+        grad_input = grad_weight = grad_bias = None
+        if ctx.needs_input_grad[0]:
+            grad_output = grad_output.reshape(-1, grad_output.shape[-1])
+            grad_input = torch.mm(grad_output, MVUE24_approx_triton(weight.t()).t()).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            input = input.view(-1, input.shape[-1])
+            grad_output = grad_output.reshape(-1, grad_output.shape[-1])
+            grad_weight = torch.mm(grad_output.t(), input)
+        if ctx.needs_input_grad[2]:
+            grad_bias = grad_output.reshape(-1, grad_output.shape[-1]).sum(0)
+        return grad_input, grad_weight, grad_bias
+
+
+class SparseLinear(nn.Linear):
+    def forward(self, x):
+        return sparse_linear.apply(x, self.weight, self.bias)
+
+
+class sparse_linear_transpose(autograd.Function):
+    """README.md:169-200 of the reference.  Three sparse GEMMs per layer and micro-step."""
+
+    @staticmethod
+    @custom_fwd(device_type='cuda', cast_inputs=torch.float16)
+    def forward(ctx, input, weight, weight_sparse, weight_sparse_T, bias):
+        ctx.save_for_backward(input, weight_sparse_T, bias)
+        ctx.shape = input.shape
+        input = input.view(-1, input.shape[-1])
+        output = torch.mm(input, weight_sparse.t())
+        if bias is None:
+            return output.view(*ctx.shape[:-1], -1)
+        return output.view(*ctx.shape[:-1], -1) + bias
+
+    @staticmethod
+    @custom_bwd(device_type='cuda')
+    def backward(ctx, grad_output):
+        input, weight_T, bias = ctx.saved_tensors
+        grad_input = grad_weight = grad_bias = None
+        if grad_output.dim() == 3 and grad_output.stride() == (0, 0, 0):
+            grad_output = torch.ones_like(grad_output, device=grad_output.device, dtype=grad_output.dtype)
+        grad_output = grad_output.reshape(-1, grad_output.shape[-1])
+        if ctx.needs_input_grad[0]:
+            grad_input = torch.mm(grad_output, weight_T.t()).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            input = input.view(-1, input.shape[-1])
+            grad_weight = torch.mm(to_sparse_semi_structured(grad_output.t(), MVUE24=True, dtype=grad_output.dtype), input)
+        if ctx.needs_input_grad[4]:
+            grad_bias = grad_output.sum(0)
+        return grad_input, grad_weight, None, None, grad_bias
+
+
+class SparseLinearTranspose(nn.Linear):
+    """Drop-in for ``nn.Linear`` that trains with 2:4 sparse GEMMs (FST).
+
+    State lives on ``self.weight`` as in the reference listing: ``freq`` (mask refresh period in
+    optimizer steps), ``cnt`` (micro-steps since the last optimizer step; the training loop resets it
+    to 0 after each optimizer step), ``counter`` (optimizer steps), ``step`` (forward calls),
+    ``mask`` (bool, transposable 2:4), ``weight_sparse`` / ``weight_sparse_T`` and ``mode``
+    ('sparse' or 'dense').  When both the mask and the compressed copies are due, one fused kernel
+    produces all three from a single read of the weight.
+    """
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, func=lambda step: 'dense', **kwargs):
+        super().__init__(in_features, out_features, bias=bias, **kwargs)
+        self.weight.freq = 40  # update freq
+
+        self.weight.cnt = 0  # how many steps after an optim step
+        self.weight.counter = 0  # how many optim steps
+        self.weight.step = 0  # total training step
+
+        self.weight.mask = torch.ones_like(self.weight, dtype=torch.bool)
+        self.weight.weight_sparse = None
+        self.weight.weight_sparse_T = None
+        self.weight.mode = 'sparse'
+        self.func = func
+
+        self.transposable_sparse = TransposableSparse(abs=True)
+        SparseSemiStructuredTensor._FORCE_CUTLASS = True  # kept for parity with the reference; has no effect
+
+    def _refresh(self, reselect: bool):
+        w = self.weight
+        mask, (pw, mw), (pt, mt) = select_and_compress(w, mask=None if reselect else w.mask, dtype=torch.float16)
+        w.mask = mask
+        out_f, in_f = w.shape
+        w.weight_sparse = SparseSemiStructuredTensor(
+            None, original_shape=torch.Size([out_f, in_f]), sparse_tensor_cutlass=pw, meta_tensor_cutlass=mw,
+            dtype=torch.float16)
+        w.weight_sparse_T = SparseSemiStructuredTensor(
+            None, original_shape=torch.Size([in_f, out_f]), sparse_tensor_cutlass=pt, meta_tensor_cutlass=mt,
+            dtype=torch.float16)
+
+    def forward(self, x):
+        w = self.weight
+        if w.mode == 'dense':
+            x = F.linear(x, w, self.bias)
+        else:
+            w.mask = w.mask.to(device=w.device)
+            if w.cnt == 0:
+                self._refresh(reselect=(w.counter % w.freq == 0))
+            with torch.autocast(device_type='cuda', dtype=torch.float16):
+                x = sparse_linear_transpose.apply(x, w, w.weight_sparse, w.weight_sparse_T, self.bias)
+
+        if self.training:
+            if w.cnt == 0:
+                w.counter += 1
+            w.step += 1
+            w.cnt += 1
+        return x

@@ -19,7 +19,7 @@ _ext.register_signature("sp24_spmm", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _v
                                       _i64, _vp, _i32, _vp, _vp])
 
 _ACT = {None: 0, "none": 0, "relu": 1, "silu": 2}
-_tc_meta_cache = weakref.WeakKeyDictionary()
+_tc_meta_cache = {}  # id(meta tensor) -> (weak reference to it, tensor-core copy); tensors do not hash by value
 _status = {}
 
 
@@ -42,12 +42,13 @@ def check_status(device=None):
 
 
 def invalidate_meta(meta):
-    _tc_meta_cache.pop(meta, None)
+    _tc_meta_cache.pop(id(meta), None)
 
 
 def tc_metadata(meta: torch.Tensor, ms: int, k: int) -> torch.Tensor:
     """Metadata in the order the tensor cores consume (cached per metadata tensor object)."""
-    e = _tc_meta_cache.get(meta)
+    hit = _tc_meta_cache.get(id(meta))
+    e = hit[1] if hit is not None and hit[0]() is meta else None
     if e is None:
         lib = _ext.lib()
         lib.sp24_meta_tc_bytes.restype = _i64
@@ -57,7 +58,8 @@ def tc_metadata(meta: torch.Tensor, ms: int, k: int) -> torch.Tensor:
         src = meta if meta.is_contiguous() else meta.contiguous()
         _ext.check(lib.sp24_meta_to_tc(src.data_ptr(), src.element_size(), ms, k, e.data_ptr(), _ext.stream()),
                    "sp24_meta_to_tc")
-        _tc_meta_cache[meta] = e
+        key = id(meta)
+        _tc_meta_cache[key] = (weakref.ref(meta, lambda _r, key=key: _tc_meta_cache.pop(key, None)), e)
     return e
 
 

@@ -281,8 +281,10 @@ def main():
     d2h = BATCH * (M * K + 2 * (M * K + M * K // 8))
 
     extra = None
+    spmm_extra = None
     if rank == 0 and world == 1 and not args.no_extra:
         extra = side_measurements(dev)
+        spmm_extra = spmm_measurements(dev)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -309,6 +311,8 @@ def main():
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
         if extra:
             line["kernels"] = extra
+        if spmm_extra:
+            line["spmm_cfg4"] = spmm_extra
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -406,6 +410,84 @@ def side_measurements(dev):
     gr = [torch.randn(m, k, device=dev) * 1e-3 for _ in range(2)]
     mk = [torch.rand(m, k, device=dev) < 0.5 for _ in range(2)]
     rec("cfg3 masked_add_ fp32 8192x4096", timeit(lambda i: sparse.masked_add_(gr[i], p[i], mk[i], alpha=2e-4), 2), n * 13)
+    return res
+
+
+def spmm_measurements(dev):
+    """cfg4: one GPT-2 MLP projection, X 16384x768, W 3072x768 under a transposable 2:4 mask.
+    Times the three sparse GEMMs of a training step (forward, dX, dW with the MVUE compression of dY^T
+    included) against torch.mm (cuBLAS) dense GEMMs of the same shapes.  TFLOP/s are dense-equivalent
+    (2*T*N*K per GEMM).  L2 is flushed by rotating over several operand sets."""
+    import sparse
+    T, K, N = 16384, 768, 3072
+    flops = 2.0 * T * N * K
+    res = {}
+    for dtype, tag in ((torch.float16, "fp16"), (torch.bfloat16, "bf16")):
+        nb = 3
+        xs = [torch.randn(T, K, device=dev).to(dtype) for _ in range(nb)]
+        dys = [(torch.randn(T, N, device=dev) * 1e-2).to(dtype) for _ in range(nb)]
+        w = torch.randn(N, K, device=dev) * 0.02
+        mask, (pw, mw), (pt, mt) = sparse.select_and_compress(w, dtype=dtype)
+        ws = sparse.SparseSemiStructuredTensor(None, original_shape=w.shape, sparse_tensor_cutlass=pw,
+                                               meta_tensor_cutlass=mw, dtype=dtype)
+        wt = sparse.SparseSemiStructuredTensor(None, original_shape=w.t().shape, sparse_tensor_cutlass=pt,
+                                               meta_tensor_cutlass=mt, dtype=dtype)
+        wd = torch.where(mask, w, torch.zeros((), device=dev)).to(dtype)
+
+        def timeit(fn, reps=12):
+            for i in range(3):
+                fn(i % nb)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(reps):
+                fn(i % nb)
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e-3 / reps
+
+        t_fwd = timeit(lambda i: torch.mm(xs[i], ws.t()))
+        t_dx = timeit(lambda i: torch.mm(dys[i], wt.t()))
+        t_dw = timeit(lambda i: torch.mm(sparse.to_sparse_semi_structured(dys[i].t(), MVUE24=True, dtype=dtype), xs[i]))
+        t_dw_gemm_only = None
+        pre = [sparse.to_sparse_semi_structured(dys[i].t(), MVUE24=True, dtype=dtype) for i in range(nb)]
+        for i in range(nb):
+            torch.mm(pre[i], xs[i])
+        t_dw_gemm_only = timeit(lambda i: torch.mm(pre[i], xs[i]))
+        d_fwd = timeit(lambda i: torch.mm(xs[i], wd.t()))
+        d_dx = timeit(lambda i: torch.mm(dys[i], wd))
+        d_dw = timeit(lambda i: torch.mm(dys[i].t(), xs[i]))
+        sp_total, de_total = t_fwd + t_dx + t_dw, d_fwd + d_dx + d_dw
+        res[tag] = {
+            "sparse_ms": {"fwd": t_fwd * 1e3, "dx": t_dx * 1e3, "dw_incl_mvue_compress": t_dw * 1e3,
+                          "dw_gemm_only": t_dw_gemm_only * 1e3},
+            "dense_cublas_ms": {"fwd": d_fwd * 1e3, "dx": d_dx * 1e3, "dw": d_dw * 1e3},
+            "sparse_fwd_bwd_TFLOPs_dense_equiv": 3 * flops / sp_total / 1e12,
+            "dense_fwd_bwd_TFLOPs": 3 * flops / de_total / 1e12,
+            "speedup_vs_dense": de_total / sp_total,
+            "per_gemm_TFLOPs": {"fwd": flops / t_fwd / 1e12, "dx": flops / t_dx / 1e12,
+                                "dw_gemm_only": flops / t_dw_gemm_only / 1e12},
+        }
+        del xs, dys, pre
+    # fp8 e4m3 forward (per-tensor scales applied outside the GEMM), fp32 output
+    x = torch.randn(T, K, device=dev)
+    w = torch.randn(N, K, device=dev) * 0.02
+    _, mask = sparse.mask_select(w)
+    xq = (x / (x.abs().max() / 448)).to(torch.float8_e4m3fn)
+    ws8 = sparse.to_sparse_semi_structured(w / (w.abs().max() / 448), mask=mask, dtype=torch.float8_e4m3fn)
+    for _ in range(3):
+        torch.mm(xq, ws8.t())
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        torch.mm(xq, ws8.t())
+    e1.record()
+    torch.cuda.synchronize()
+    t8 = e0.elapsed_time(e1) * 1e-3 / 10
+    res["fp8_e4m3"] = {"fwd_ms": t8 * 1e3, "fwd_TFLOPs_dense_equiv": flops / t8 / 1e12, "note": "fp32 output (201 MB)"}
+    from sparse.spmm import check_status
+    check_status()
     return res
 
 

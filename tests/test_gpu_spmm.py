@@ -1,0 +1,222 @@
+"""GPU tests of the 2:4 sparse GEMM (tcgen05.mma.sp) and of the training layer built on it.
+
+Reference for every GEMM: an fp32 dense matmul of the masked (and, for fp8, dequantised) operands.
+Stated tolerances: max|y - y_ref| / max|y_ref| <= 1e-3 for fp16 output, 8e-3 for bf16 output,
+1e-5 for fp8 inputs with fp32 output; plus an element-wise bound |y - y_ref| <= tol * (|x| @ |w|^T)
+so that cancellation-heavy entries are not hidden by the max-norm."""
+import random
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+TOL = {torch.float16: 1e-3, torch.bfloat16: 8e-3, torch.float8_e4m3fn: 1e-5, torch.float8_e5m2: 1e-5}
+
+
+@pytest.fixture(scope="module")
+def S():
+    import sparse
+    return sparse
+
+
+def random_mask(m, k, g):
+    pats = torch.tensor([[1, 1, 0, 0], [1, 0, 1, 0], [1, 0, 0, 1], [0, 1, 1, 0], [0, 1, 0, 1], [0, 0, 1, 1]], dtype=torch.bool)
+    return pats[torch.randint(0, 6, (m, k // 4), generator=g)].reshape(m, k)
+
+
+def check(y, ref, xa, wa, dtype):
+    tol = TOL[dtype]
+    y = y.float()
+    scale = ref.abs().max()
+    assert float((y - ref).abs().max() / scale) <= tol, float((y - ref).abs().max() / scale)
+    bound = xa @ wa.t()
+    assert bool(((y - ref).abs() <= tol * bound + 1e-30).all())
+
+
+@pytest.mark.parametrize("a_col,b_col", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("ms,k,n", [(128, 64, 8), (256, 832, 200), (384, 1024, 1000)])
+def test_spmm_against_fp32_masked_matmul(S, dtype, a_col, b_col, ms, k, n):
+    from sparse.spmm import sparse_linear, check_status
+    g = torch.Generator().manual_seed(ms + k + n)
+    w = torch.randn(ms, k, generator=g).to(dtype).to(DEV)
+    mask = random_mask(ms, k, g).to(DEV)
+    x = torch.randn(n, k, generator=g).to(dtype).to(DEV)
+    src, mk = (w.t().contiguous().t(), mask.t().contiguous().t()) if a_col else (w, mask)
+    sp = S.to_sparse_semi_structured(src, mask=mk, dtype=dtype)
+    assert sp.sparse_tensor_cutlass.stride(0 if a_col else 1) == 1
+    xin = x.t().contiguous().t() if b_col else x
+    y = sparse_linear(xin, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass)
+    check_status()
+    assert y.shape == (n, ms) and y.dtype == dtype
+    wm = torch.where(mask, w, torch.zeros((), dtype=dtype, device=DEV)).float()
+    check(y, x.float() @ wm.t(), x.float().abs(), wm.abs(), dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("ms,k,n", [(128, 128, 16), (256, 896, 208)])
+def test_spmm_fp8(S, dtype, ms, k, n):
+    from sparse.spmm import sparse_linear, check_status
+    g = torch.Generator().manual_seed(7)
+    w = torch.randn(ms, k, generator=g).to(DEV)
+    mask = random_mask(ms, k, g).to(DEV)
+    x = torch.randn(n, k, generator=g).to(DEV).to(dtype)
+    sp = S.to_sparse_semi_structured(w, mask=mask, dtype=dtype)
+    y = sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass)
+    check_status()
+    assert y.dtype == torch.float32 and y.shape == (n, ms)
+    wq = torch.where(mask, w.to(dtype).float(), torch.zeros((), device=DEV))
+    check(y, x.float() @ wq.t(), x.float().abs(), wq.abs(), dtype)
+    assert torch.equal(sp.to_dense().float(), wq)
+
+
+@pytest.mark.parametrize("act", [None, "relu", "silu"])
+def test_spmm_bias_and_activation(S, act):
+    from sparse.spmm import sparse_linear
+    g = torch.Generator().manual_seed(3)
+    w = (torch.randn(256, 256, generator=g) * 0.1).half().to(DEV)
+    x = torch.randn(72, 256, generator=g).half().to(DEV)
+    b = torch.randn(256, generator=g).half().to(DEV)
+    sp = S.to_sparse_semi_structured(w)
+    y = sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, b, act)
+    ref = x.float() @ sp.to_dense().float().t() + b.float()
+    ref = {None: ref, "relu": torch.relu(ref), "silu": F.silu(ref)}[act]
+    assert float((y.float() - ref).abs().max() / ref.abs().max()) <= 2e-3
+    with pytest.raises(RuntimeError, match="activation"):
+        sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, b, "gelu")
+    with pytest.raises(RuntimeError, match="datatype"):
+        sparse_linear(x.bfloat16(), sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass)
+
+
+def test_dispatch_table(S):
+    g = torch.Generator().manual_seed(4)
+    w = (torch.randn(256, 128, generator=g) * 0.1).half().to(DEV)
+    sp = S.to_sparse_semi_structured(w)
+    wd = sp.to_dense().float()
+    x = torch.randn(13, 128, generator=g).half().to(DEV)      # 13 rows: exercises the padding to 16
+    b = torch.randn(256, generator=g).half().to(DEV)
+    y = torch.mm(x, sp.t())
+    assert y.shape == (13, 256) and float((y.float() - x.float() @ wd.t()).abs().max()) < 2e-2
+    ya = torch.addmm(b, x, sp.t())
+    assert float((ya.float() - (x.float() @ wd.t() + b.float())).abs().max()) < 2e-2
+    with torch.inference_mode():
+        x3 = torch.randn(2, 8, 128, generator=g).half().to(DEV)
+        yl = F.linear(x3, sp, b)
+        assert yl.shape == (2, 8, 256)
+        assert float((yl.float() - (x3.float() @ wd.t() + b.float())).abs().max()) < 2e-2
+    rhs = torch.randn(128, 40, generator=g).half().to(DEV)
+    z = torch.mm(sp, rhs)
+    assert z.shape == (256, 40) and z.is_contiguous()
+    assert float((z.float() - wd @ rhs.float()).abs().max()) < 2e-2
+    d = sp.detach()
+    assert isinstance(d, S.SparseSemiStructuredTensor) and d.sparse_tensor_cutlass is sp.sparse_tensor_cutlass
+    with pytest.raises(NotImplementedError):
+        torch.add(sp, sp)
+
+
+def test_sparse_linear_transpose_layer(S):
+    torch.manual_seed(0)
+    layer = S.SparseLinearTranspose(256, 384, bias=True).to(DEV)
+    ref = torch.nn.Linear(256, 384).to(DEV)
+    ref.load_state_dict(layer.state_dict())
+    x = torch.randn(4, 64, 256, device=DEV, requires_grad=True)
+    random.seed(123)
+    y = layer(x)
+    assert y.shape == (4, 64, 384) and y.dtype == torch.float16
+    mask = layer.weight.mask
+    m4 = mask.view(96, 4, 64, 4)
+    assert bool((m4.sum(1) == 2).all()) and bool((m4.sum(3) == 2).all())
+    wm = (layer.weight * mask).detach()
+    y_ref = F.linear(x.half().float(), wm.half().float(), layer.bias.half().float())
+    assert float((y.float() - y_ref).abs().max() / y_ref.abs().max()) < 2e-3
+    dy = torch.randn_like(y) * 1e-2
+    seed_state = random.getstate()
+    y.backward(dy)
+    # dX = dY @ W_masked
+    gx_ref = dy.float().view(-1, 384) @ wm.half().float()
+    assert float((x.grad.view(-1, 256) - gx_ref).abs().max() / gx_ref.abs().max()) < 2e-3
+    # dW = MVUE24(dY^T) @ X with the seed the layer drew from Python's random
+    random.setstate(seed_state)
+    seed = random.randint(0, 2 ** 31 - 1)
+    dyt = dy.view(-1, 384).t()
+    mv = S.MVUE24_approx_triton(dyt, seed=seed)
+    gw_ref = mv.float() @ x.detach().half().float().view(-1, 256)
+    gw = layer.weight.grad
+    assert gw.shape == (384, 256)
+    assert float((gw.float() - gw_ref).abs().max() / gw_ref.abs().max()) < 2e-3
+    assert float((layer.bias.grad.float() - dy.float().view(-1, 384).sum(0)).abs().max()) < 1e-2
+    # counters follow the listing: one micro-step done, mask refresh only every `freq` optimizer steps
+    w = layer.weight
+    assert (w.cnt, w.counter, w.step) == (1, 1, 1)
+    old = w.weight_sparse
+    layer(x.detach())
+    assert w.weight_sparse is old and (w.cnt, w.counter, w.step) == (2, 1, 2)
+    w.cnt = 0
+    layer(x.detach())
+    assert w.weight_sparse is not old and torch.equal(w.mask, mask)
+    w.mode = 'dense'
+    yd = layer(x.detach())
+    assert yd.dtype == torch.float32
+
+
+def test_dw_is_unbiased(S):
+    # averaged over seeds, MVUE24(dY^T) @ X approaches dY^T @ X
+    g = torch.Generator().manual_seed(9)
+    dy = (torch.randn(512, 128, generator=g) * 1e-2).half().to(DEV)
+    x = torch.randn(512, 64, generator=g).half().to(DEV)
+    exact = dy.float().t() @ x.float()
+    acc = torch.zeros_like(exact)
+    n = 64
+    for i in range(n):
+        random.seed(1000 + i)
+        sp = S.to_sparse_semi_structured(dy.t(), MVUE24=True)
+        acc += torch.mm(sp, x).float()
+    rel = float((acc / n - exact).norm() / exact.norm())
+    single = float((torch.mm(sp, x).float() - exact).norm() / exact.norm())
+    assert rel < single / 4  # error shrinks like 1/sqrt(n): the estimator has no bias floor
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_config4_forward_backward_full_size(S, dtype):
+    from sparse.spmm import check_status
+    T, K, N = 16384, 768, 3072
+    x = torch.randn(T, K, generator=torch.Generator().manual_seed(7)).to(dtype).to(DEV)
+    w = (torch.randn(N, K, generator=torch.Generator().manual_seed(8)) * 0.02).to(DEV)
+    dy = (torch.randn(T, N, generator=torch.Generator().manual_seed(9)) * 1e-2).to(dtype).to(DEV)
+    mask, (pw, mw), (pt, mt) = S.select_and_compress(w, dtype=dtype)
+    ws = S.SparseSemiStructuredTensor(None, original_shape=w.shape, sparse_tensor_cutlass=pw, meta_tensor_cutlass=mw, dtype=dtype)
+    wt = S.SparseSemiStructuredTensor(None, original_shape=w.t().shape, sparse_tensor_cutlass=pt, meta_tensor_cutlass=mt, dtype=dtype)
+    wm = torch.where(mask, w, torch.zeros((), device=DEV)).to(dtype).float()
+    y = torch.mm(x, ws.t())
+    check(y, x.float() @ wm.t(), x.float().abs(), wm.abs(), dtype)
+    dx = torch.mm(dy, wt.t())
+    check(dx, dy.float() @ wm, dy.float().abs(), wm.t().abs(), dtype)
+    random.seed(5)
+    st = random.getstate()
+    dys = S.to_sparse_semi_structured(dy.t(), MVUE24=True, dtype=dtype)
+    dw = torch.mm(dys, x)
+    random.setstate(st)
+    mv = S.MVUE24_approx_triton(dy.t(), seed=random.randint(0, 2 ** 31 - 1)).float()
+    assert torch.equal(dys.to_dense().float(), mv.contiguous())
+    check(dw.t(), x.float().t() @ mv.t(), x.float().t().abs(), mv.abs(), dtype)
+    check_status()
+
+
+def test_config4_fp8_forward(S):
+    T, K, N = 16384, 768, 3072
+    x = torch.randn(T, K, generator=torch.Generator().manual_seed(7)).to(DEV)
+    w = (torch.randn(N, K, generator=torch.Generator().manual_seed(8)) * 0.02).to(DEV)
+    _, mask = S.mask_select(w)
+    sx, sw = x.abs().max() / 448, w.abs().max() / 448
+    xq = (x / sx).to(torch.float8_e4m3fn)
+    ws = S.to_sparse_semi_structured(w / sw, mask=mask, dtype=torch.float8_e4m3fn)
+    y = torch.mm(xq, ws.t()) * (sx * sw)
+    wq = torch.where(mask, (w / sw).to(torch.float8_e4m3fn).float(), torch.zeros((), device=DEV))
+    ref = (xq.float() @ wq.t()) * (sx * sw)
+    assert float((y - ref).abs().max() / ref.abs().max()) <= 1e-5
+    # and the quantised result tracks the unquantised masked product to fp8 accuracy
+    full = x @ torch.where(mask, w, torch.zeros((), device=DEV)).t()
+    assert float((y - full).norm() / full.norm()) < 0.08
