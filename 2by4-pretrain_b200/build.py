@@ -57,6 +57,10 @@ def build(force=False, verbose=False):
         obj = os.path.join(OBJDIR, os.path.basename(src)[:-3] + "." + tag + ".o")
         log = obj[:-2] + ".log"
         if force or not os.path.exists(obj):
+            stem = os.path.basename(src)[:-3] + "."
+            for old in os.listdir(OBJDIR):  # drop objects and logs of earlier versions of this source
+                if old.startswith(stem) and not old.startswith(stem + tag):
+                    os.remove(os.path.join(OBJDIR, old))
             r = subprocess.run([nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj], capture_output=True, text=True)
             with open(log, "w") as f:
                 f.write(r.stdout + r.stderr)

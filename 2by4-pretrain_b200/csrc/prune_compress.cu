@@ -77,7 +77,9 @@ __global__ void __launch_bounds__(256) pc_row_kernel(PcParams P) {
     constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;    // bytes per metadata word
     constexpr int GROUP = MB == 2 ? 32 : 16;
     using MetaT = typename VecBytes<MB>::type;
-    constexpr int RPI = (CH * sizeof(TIn) >= 128) ? 1 : (CH * sizeof(TIn) >= 64 ? 2 : 4);  // rows in flight
+    // rows in flight per thread; MVUE is arithmetic-bound, so it trades memory-level parallelism for
+    // fewer registers (more resident warps)
+    constexpr int RPI = (MODE == SP24_PRUNE_MVUE || CH * sizeof(TIn) >= 128) ? 1 : (CH * sizeof(TIn) >= 64 ? 2 : 4);
 
     __shared__ __align__(16) MetaT smeta[16][64];
 
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(256) pc_row_kernel(PcParams P) {
     TOut *packed = static_cast<TOut *>(P.packed);
 
     if (c < ncols) {
-#pragma unroll
+#pragma unroll(MODE == SP24_PRUNE_MVUE ? 1 : 4)
         for (int it = 0; it < 4 / RPI; ++it) {
             TIn in[RPI][CH];
             uint8_t mk[RPI][CH];
@@ -157,12 +159,16 @@ __global__ void __launch_bounds__(256) pc_row_kernel(PcParams P) {
 // Everything is element-wise across r, so loads and stores are naturally coalesced along r.
 // Thread = V consecutive rows x one metadata column; warp = 32*V rows; 8 warps = 8 metadata columns.
 // ---------------------------------------------------------------------------------------------
-template <typename TIn, typename TOut, int MODE, bool HAS_U>
+template <typename TIn> struct ColVec {
+    static constexpr int wide = sizeof(TIn) == 1 ? 8 : 16 / sizeof(TIn);   // streaming modes: 16-byte (8 for int8) loads
+    static constexpr int narrow = sizeof(TIn) >= 4 ? 1 : 4 / sizeof(TIn);  // MVUE: 4-byte loads, few registers
+};
+
+template <typename TIn, typename TOut, int MODE, bool HAS_U, int V>
 __global__ void __launch_bounds__(256) pc_col_kernel(PcParams P) {
     constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;
     constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;
     constexpr int GROUP = MB == 2 ? 32 : 16;
-    constexpr int V = 16 / sizeof(TIn);
     constexpr int RT = 32 * V;  // rows per block
     using MetaT = typename VecBytes<MB>::type;
 
@@ -261,9 +267,10 @@ int launch(const PcParams &P, int col_major, cudaStream_t st) {
         dim3 grid((unsigned)((P.k / CH + 31) / 32), (unsigned)(P.m / 32));
         pc_row_kernel<TIn, TOut, MODE, HAS_U><<<grid, 256, 0, st>>>(P);
     } else {
-        constexpr int RT = 32 * (16 / (int)sizeof(TIn));
+        constexpr int V = MODE == SP24_PRUNE_MVUE ? ColVec<TIn>::narrow : ColVec<TIn>::wide;
+        constexpr int RT = 32 * V;
         dim3 grid((unsigned)((P.m + RT - 1) / RT), (unsigned)((P.k / CH + 7) / 8));
-        pc_col_kernel<TIn, TOut, MODE, HAS_U><<<grid, 256, 0, st>>>(P);
+        pc_col_kernel<TIn, TOut, MODE, HAS_U, V><<<grid, 256, 0, st>>>(P);
     }
     return launch_status();
 }

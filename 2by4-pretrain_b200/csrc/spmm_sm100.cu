@@ -121,6 +121,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets (all >> 4),
@@ -145,8 +153,6 @@ struct SpmmParams {
     int *status;
     uint32_t idesc;         // instruction descriptor without the metadata selector bits
     int activation;         // 0 none, 1 relu, 2 silu
-    // experiment knobs of the descriptor builder (bytes)
-    uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep, b_atom_bytes, e_sbo, e_lbo, e_mode;
 };
 
 template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
@@ -164,17 +170,36 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     return v;
 }
 
-// BN: dense columns per tile.  A_MN / B_MN: operand stored with the non-K axis contiguous.
-// TRANS_OUT: write out[n][m] (row-major (N, Ms)) instead of out[m][n].
-template <int BN, int STAGES, bool F8, bool A_MN, bool B_MN, bool TRANS_OUT, typename OutT>
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Geometry shared by the kernel and its launcher.
+template <int BN, bool F8> struct SpmmCfg {
+    static constexpr int E_BYTES = F8 ? 4096 : 2048;          // metadata of one 128-row block and one stage
+    static constexpr int B_BYTES = BN * 256;                  // two 128-byte K atoms per row of B
+    static constexpr int STAGE_BYTES = 2 * A_STAGE_BYTES + B_BYTES + 2 * E_BYTES;
+    static constexpr int STAGES = (227 * 1024 - 2048) / STAGE_BYTES >= 4 ? 4 : (227 * 1024 - 2048) / STAGE_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
+    static_assert(STAGES >= 2, "tile too large for a two-stage ring");
+    static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+};
+
+// One CTA computes a (256 x BN) output tile as two 128-row blocks that share every stage of B
+// (each byte of B staged once per 256 sparse rows).  A_MN / B_MN: operand stored with the non-K axis
+// contiguous.  TRANS_OUT: write out[n][m] (row-major (N, Ms)) instead of out[m][n].
+template <int BN, bool F8, bool A_MN, bool B_MN, bool TRANS_OUT, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, SpmmParams P) {
-    constexpr int B_STAGE_BYTES = BN * 256;           // two 128-byte K atoms per row of B
-    constexpr int E_STAGE_BYTES = F8 ? 4096 : 2048;   // metadata atoms covering the stage's logical K
-    constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES + E_STAGE_BYTES;
-    constexpr int KSTEPS = 4;                         // MMA instructions per stage (32 bytes of compressed A each)
-    constexpr uint32_t TMEM_COLS = BN <= 96 ? 128 : (BN <= 224 ? 256 : 512);
-    constexpr int E_COL0 = BN;                        // metadata columns start right after the accumulator
+    using Cfg = SpmmCfg<BN, F8>;
+    constexpr int STAGES = Cfg::STAGES;
+    constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr int E_BYTES = Cfg::E_BYTES;
+    constexpr int OFF_B = 2 * A_STAGE_BYTES, OFF_E = OFF_B + Cfg::B_BYTES;
+    constexpr int KSTEPS = 4;                 // MMA instructions per stage and row block (32 bytes of compressed A each)
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr int E_COL0 = 2 * BN;            // metadata columns behind the two accumulators
+    constexpr int E_SLOT = F8 ? 8 : 4;        // metadata columns of one row block and one stage
+    static_assert(E_COL0 + 4 * E_SLOT <= 512, "tensor memory columns exhausted");
+    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "invalid MMA N");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -183,10 +208,13 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_blk = blockIdx.y, n_blk = blockIdx.x;
-    const int64_t m0 = (int64_t)m_blk * BM, n0 = (int64_t)n_blk * BN;
+    const int n_blk = blockIdx.x;
+    const int mblk0 = blockIdx.y * 2;                                    // first 128-row block of this CTA
+    const int n_mblk = (P.ms / BM - mblk0) >= 2 ? 2 : 1;                   // 1 on a ragged last CTA
+    const int64_t m0 = (int64_t)mblk0 * BM, n0 = (int64_t)n_blk * BN;
     const int logical_k_per_stage = F8 ? 256 : 128;
     const int k_iters = (int)((P.k + logical_k_per_stage - 1) / logical_k_per_stage);
+    const uint32_t stage_tx = (uint32_t)(n_mblk * (A_STAGE_BYTES + E_BYTES) + Cfg::B_BYTES);
 
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
 
@@ -217,18 +245,26 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const uint32_t ph = (it / STAGES) & 1;
                 if (it >= STAGES && !mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, P.status, 1)) break;
                 const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
-                const uint32_t sb = sa + A_STAGE_BYTES;
-                const uint32_t se = sb + B_STAGE_BYTES;
+                const uint32_t sb = sa + OFF_B;
+                const uint32_t se = sa + OFF_E;
                 const uint32_t full = full0 + 8 * s;
-                mbar_expect_tx(full, STAGE_BYTES);
-                // compressed A: 128 rows x 128 bytes
-                if constexpr (!A_MN) {
-                    tma_load_2d(sa, &map_a, it * (F8 ? 128 : 64), (int)m0, full);
-                } else {
-                    tma_load_2d(sa, &map_a, (int)m0, it * 64, full);
-                    tma_load_2d(sa + 8192, &map_a, (int)m0 + 64, it * 64, full);
+                mbar_expect_tx(full, stage_tx);
+                for (int mb = 0; mb < n_mblk; ++mb) {
+                    const int mrow = (int)m0 + mb * BM;
+                    const uint32_t sam = sa + mb * A_STAGE_BYTES;
+                    // compressed A: 128 rows x 128 bytes
+                    if constexpr (!A_MN) {
+                        tma_load_2d(sam, &map_a, it * (F8 ? 128 : 64), mrow, full);
+                    } else {
+                        tma_load_2d(sam, &map_a, mrow, it * 64, full);
+                        tma_load_2d(sam + 8192, &map_a, mrow + 64, it * 64, full);
+                    }
+                    // metadata atoms of this 128-row block
+                    const uint8_t *e_src = static_cast<const uint8_t *>(P.e_tc) +
+                                           ((size_t)(mblk0 + mb) * P.k_atoms + (size_t)it * (E_BYTES / 2048)) * 2048;
+                    bulk_load(se + mb * E_BYTES, e_src, E_BYTES, full);
                 }
-                // dense B: BN rows x 2 atoms of 128 bytes (K-major) or BN/64 atoms of 128 K-rows (MN-major)
+                // dense B: BN rows x 2 atoms of 128 bytes (K-major) or column blocks of 64 x 128 K-rows (MN-major)
                 if constexpr (!B_MN) {
                     const int kx = it * (F8 ? 256 : 128);
                     tma_load_2d(sb, &map_b, kx, (int)n0, full);
@@ -237,10 +273,6 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
                     for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 16384, &map_b, (int)n0 + j * 64, it * 128, full);
                 }
-                // metadata atoms of this 128-row block
-                const uint8_t *e_src = static_cast<const uint8_t *>(P.e_tc) +
-                                       ((size_t)m_blk * P.k_atoms + (size_t)it * (E_STAGE_BYTES / 2048)) * 2048;
-                bulk_load(se, e_src, E_STAGE_BYTES, full);
                 ++issued;
             }
             if (abort_flag) {
@@ -256,6 +288,10 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
+            // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart, 32 (A) / 64 (B) bytes per MMA inside
+            // the atom.  MN-major: 64-element column blocks one TMA box apart, 8 K-rows per 1024 bytes.
+            constexpr uint32_t A_LBO = A_MN ? 8192 : 16, A_KSTEP = A_MN ? 2048 : 32;
+            constexpr uint32_t B_LBO = B_MN ? 16384 : 16, B_KSTEP = B_MN ? 4096 : 64;
             bool ok = true;
             for (int it = 0; it < k_iters && ok; ++it) {
                 const int s = it % STAGES;
@@ -264,56 +300,82 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
-                const uint32_t sb = sa + A_STAGE_BYTES;
-                const uint32_t se = sb + B_STAGE_BYTES;
-                const uint32_t e_cols = E_COL0 + (it & 1) * (F8 ? 8 : 4);
-                // metadata: shared memory -> tensor memory, 128 lanes x 16 bytes per atom
-                tc_cp_128x128b(tmem_base + e_cols, make_desc(se, P.e_lbo, P.e_sbo, 0));
-                if constexpr (F8) tc_cp_128x128b(tmem_base + e_cols + 4, make_desc(se + 2048, P.e_lbo, P.e_sbo, 0));
+                const uint32_t sb = sa + OFF_B;
+                const uint32_t se = sa + OFF_E;
+                for (int mb = 0; mb < n_mblk; ++mb) {
+                    const uint32_t e_cols = E_COL0 + ((it & 1) * 2 + mb) * E_SLOT;
+                    // metadata: shared memory -> tensor memory, 128 lanes x 16 bytes per atom
+                    tc_cp_128x128b(tmem_base + e_cols, make_desc(se + mb * E_BYTES, 16, 128, 0));
+                    if constexpr (F8) tc_cp_128x128b(tmem_base + e_cols + 4, make_desc(se + mb * E_BYTES + 2048, 16, 128, 0));
 #pragma unroll
-                for (int j = 0; j < KSTEPS; ++j) {
-                    const uint64_t adesc = make_desc(sa + j * P.a_kstep, P.a_lbo, P.a_sbo, 2);
-                    const uint32_t b_off = B_MN ? j * P.b_kstep : (uint32_t)(j >> 1) * P.b_atom_bytes + (j & 1) * P.b_kstep;
-                    const uint64_t bdesc = make_desc(sb + b_off, P.b_lbo, P.b_sbo, 2);
-                    const uint32_t ecol = e_cols + (F8 ? 2 * j : j);
-                    // 16-bit types: the instruction takes the even column of a pair plus a 1-bit selector
-                    const bool pair_sel = !F8 && P.e_mode == 0;
-                    const uint32_t e_addr = tmem_base + (pair_sel ? (ecol & ~1u) : ecol);
-                    const uint32_t idesc = P.idesc | (pair_sel ? (ecol & 1u) : 0u);
-                    mma_sp<F8>(tmem_base, adesc, bdesc, e_addr, idesc, (it > 0 || j > 0) ? 1u : 0u);
+                    for (int j = 0; j < KSTEPS; ++j) {
+                        const uint64_t adesc = make_desc(sa + mb * A_STAGE_BYTES + j * A_KSTEP, A_LBO, 1024, 2);
+                        const uint32_t b_off = B_MN ? j * B_KSTEP : (uint32_t)(j >> 1) * (BN * 128) + (j & 1) * B_KSTEP;
+                        const uint64_t bdesc = make_desc(sb + b_off, B_LBO, 1024, 2);
+                        const uint32_t ecol = e_cols + (F8 ? 2 * j : j);
+                        // 16-bit types: the instruction takes the even column of a pair plus a 1-bit selector
+                        const uint32_t e_addr = tmem_base + (F8 ? ecol : (ecol & ~1u));
+                        const uint32_t idesc = P.idesc | (F8 ? 0u : (ecol & 1u));
+                        mma_sp<F8>(tmem_base + mb * BN, adesc, bdesc, e_addr, idesc, (it > 0 || j > 0) ? 1u : 0u);
+                    }
                 }
                 tc_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
             }
-            tc_commit(accum_bar);           // accumulator complete (arrives even after an abort)
+            tc_commit(accum_bar);           // accumulators complete (arrives even after an abort)
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
         const int quad = warp & 3;  // TMEM lane quadrant this warp may read
         const bool ok = mbar_wait(accum_bar, 0, &abort_flag, P.status, 3);
         tc_fence_after();
-        if (ok && !abort_flag) {
-            const int64_t m = m0 + quad * 32 + lane;
-            OutT *out = static_cast<OutT *>(P.out);
+        const bool run = ok && !abort_flag;
+        OutT *out = static_cast<OutT *>(P.out);
+        for (int mb = 0; mb < n_mblk; ++mb) {
+            const int64_t mrow0 = m0 + mb * BM;
+            const int64_t m = mrow0 + quad * 32 + lane;
             float bias = 0.f;
-            if (P.bias) bias = from_out<OutT>(static_cast<const OutT *>(P.bias)[m]);
+            if (run && P.bias) bias = from_out<OutT>(static_cast<const OutT *>(P.bias)[m]);
+            if constexpr (TRANS_OUT) {
+                // stage the 128 x BN block transposed in shared memory (the operand ring is idle now), then
+                // write rows of 128 consecutive outputs with 16-byte stores
+                OutT *stg = reinterpret_cast<OutT *>(smem);
+                if (mb > 0) epilogue_bar_sync();
+                if (run) {
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + c * 32, v);
-                tmem_ld_wait();
-                const int64_t nb = n0 + c * 32;
-                if constexpr (TRANS_OUT) {
+                    for (int c = 0; c < BN / 16; ++c) {
+                        uint32_t v[16];
+                        tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + mb * BN + c * 16, v);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (nb + i < P.n)
-                            out[(nb + i) * P.ld_out + m] = to_out<OutT>(apply_act(__uint_as_float(v[i]) + bias, P.activation));
+                        for (int i = 0; i < 16; ++i)
+                            stg[(c * 16 + i) * BM + quad * 32 + lane] =
+                                to_out<OutT>(apply_act(__uint_as_float(v[i]) + bias, P.activation));
                     }
-                } else {
+                }
+                epilogue_bar_sync();
+                if (run) {
+                    constexpr int PER = 16 / sizeof(OutT);          // elements per 16-byte piece
+                    constexpr int PIECES = BM / PER;                // pieces per output row
+                    const int tid = (warp - 2) * 32 + lane;
+                    for (int i = tid; i < BN * PIECES; i += 128) {
+                        const int nrow = i / PIECES, piece = i % PIECES;
+                        if (n0 + nrow < P.n)
+                            *reinterpret_cast<uint4 *>(out + (n0 + nrow) * P.ld_out + mrow0 + piece * PER) =
+                                *reinterpret_cast<const uint4 *>(stg + nrow * BM + piece * PER);
+                    }
+                }
+            } else if (run) {
+#pragma unroll 1
+                for (int c = 0; c < BN / 16; ++c) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + mb * BN + c * 16, v);
+                    tmem_ld_wait();
+                    const int64_t nb = n0 + c * 16;
                     OutT *row = out + m * P.ld_out + nb;
-                    if (nb + 32 <= P.n) {
+                    if (nb + 16 <= P.n) {
                         constexpr int PER = 16 / sizeof(OutT);
 #pragma unroll
-                        for (int q = 0; q < 32 / PER; ++q) {
+                        for (int q = 0; q < 16 / PER; ++q) {
                             Vec<OutT, PER> o;
 #pragma unroll
                             for (int i = 0; i < PER; ++i)
@@ -321,7 +383,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             store_vec<OutT, PER>(row + q * PER, o);
                         }
                     } else {
-                        for (int i = 0; i < 32; ++i)
+                        for (int i = 0; i < 16; ++i)
                             if (nb + i < P.n) row[i] = to_out<OutT>(apply_act(__uint_as_float(v[i]) + bias, P.activation));
                     }
                 }
@@ -407,21 +469,70 @@ int make_map(CUtensorMap *map, const void *base, int dt, int64_t rows, int64_t c
     return r == CUDA_SUCCESS ? SP24_OK : SP24_ERR_CUDA;
 }
 
-template <int BN, int STAGES, bool F8, bool A_MN, bool B_MN, bool TRANS, typename OutT>
-int launch_spmm(const CUtensorMap &ma, const CUtensorMap &mb, const SpmmParams &P, cudaStream_t st) {
-    constexpr int STAGE_BYTES = A_STAGE_BYTES + BN * 256 + (F8 ? 4096 : 2048);
-    constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
-    auto kern = spmm_kernel<BN, STAGES, F8, A_MN, B_MN, TRANS, OutT>;
+template <int BN, bool F8, bool A_MN, bool B_MN, bool TRANS, typename OutT>
+int launch_spmm(const CUtensorMap &ma, const CUtensorMap &mb, SpmmParams P, cudaStream_t st) {
+    using Cfg = SpmmCfg<BN, F8>;
+    auto kern = spmm_kernel<BN, F8, A_MN, B_MN, TRANS, OutT>;
     static bool attr_set[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return SP24_ERR_CUDA;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
+            return SP24_ERR_CUDA;
         attr_set[dev] = true;
     }
-    dim3 grid((unsigned)((P.n + BN - 1) / BN), (unsigned)(P.ms / BM));
-    kern<<<grid, 192, SMEM, st>>>(ma, mb, P);
+    P.idesc |= (uint32_t)(BN >> 3) << 17;
+    dim3 grid((unsigned)((P.n + BN - 1) / BN), (unsigned)((P.ms / BM + 1) / 2));
+    kern<<<grid, 192, Cfg::SMEM, st>>>(ma, mb, P);
     return launch_status();
+}
+
+// Tile width: the candidates trade operand traffic per output (wide is better) against how evenly the
+// CTAs fill the SMs.  Cost model: waves x K iterations x bytes staged per iteration.
+int pick_bn(int64_t ms, int64_t n, int sm_count, bool b_mn) {
+    const int cand[3] = {240, 176, 128};
+    int best = 128;
+    double best_cost = 1e300;
+    for (int i = 0; i < 3; ++i) {
+        const int bn = cand[i];
+        if (b_mn && bn % 64) continue;  // MN-major B is staged in 64-column blocks
+        const int64_t ctas = ((n + bn - 1) / bn) * ((ms / BM + 1) / 2);
+        const double waves = (double)((ctas + sm_count - 1) / sm_count);
+        const double cost = waves * (2 * A_STAGE_BYTES + bn * 256 + 4096);
+        if (cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
+int sm_count_cached() {
+    static int cached[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+template <bool F8, bool A_MN, bool B_MN, bool TRANS, typename OutT>
+int dispatch_bn(int bn, const void *b, int dtype, int64_t n, int64_t k, int64_t ld_b, const CUtensorMap &ma,
+                const SpmmParams &P, cudaStream_t st) {
+    CUtensorMap mb;
+    int rc;
+    if (!B_MN) rc = make_map(&mb, b, dtype, n, k, ld_b, F8 ? 128 : 64, (uint32_t)bn);
+    else rc = make_map(&mb, b, dtype, k, n, ld_b, 64, 128);
+    if (rc) return rc;
+    if constexpr (B_MN) {
+        if (bn == 128) return launch_spmm<128, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
+        return launch_spmm<192, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
+    } else {
+        if (bn == 240) return launch_spmm<240, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
+        if (bn == 176) return launch_spmm<176, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
+        return launch_spmm<128, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
+    }
 }
 
 }  // namespace
@@ -464,57 +575,51 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     if (ms <= 0 || n <= 0 || k <= 0 || ms % 128 || k % (f8 ? 128 : 64) || n % 8) return SP24_ERR_SHAPE;
     const int64_t a_inner = a_mn_major ? ms : k / 2, b_inner = b_mn_major ? n : k, o_inner = trans_out ? ms : n;
     if (ld_a < a_inner || (ld_a * esz) % 16 || ld_b < b_inner || (ld_b * esz) % 16 || ld_out < o_inner) return SP24_ERR_STRIDE;
-    if ((ld_out * dtype_size(out_dtype)) % 16 && !trans_out) return SP24_ERR_STRIDE;
+    if ((ld_out * dtype_size(out_dtype)) % 16) return SP24_ERR_STRIDE;
     if (!aligned16(a_packed) || !aligned16(e_tc) || !aligned16(b) || !aligned16(out)) return SP24_ERR_ALIGN;
     if (int rc = check_device()) return rc;
 
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a;
     int rc;
     if (!a_mn_major) rc = make_map(&map_a, a_packed, dtype, ms, k / 2, ld_a, f8 ? 128 : 64, 128);
     else rc = make_map(&map_a, a_packed, dtype, k / 2, ms, ld_a, 64, 64);
-    if (rc) return rc;
-    constexpr int BN = 128;
-    if (!b_mn_major) rc = make_map(&map_b, b, dtype, n, k, ld_b, f8 ? 128 : 64, BN);
-    else rc = make_map(&map_b, b, dtype, k, n, ld_b, 64, 128);
     if (rc) return rc;
 
     SpmmParams P{};
     P.e_tc = e_tc; P.out = out; P.bias = bias; P.ms = ms; P.n = n; P.k = k; P.ld_out = ld_out;
     P.k_atoms = (k + 127) / 128; P.status = status; P.activation = activation;
     const uint32_t fmt = (dtype == SP24_BF16 || dtype == SP24_E5M2) ? 1u : 0u;
+    // sparse flag, fp32 accumulate, operand formats, operand majors, M = 128 (N is added by the launcher)
     P.idesc = (1u << 2) | (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) |
-              ((uint32_t)(b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-    // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart, 32 (A) / 64 (B) bytes per MMA inside the atom.
-    // MN-major: 64-element column blocks a whole TMA box apart, 8 K-rows per 1024 bytes.
-    P.a_lbo = a_mn_major ? 8192 : 16; P.a_sbo = 1024; P.a_kstep = a_mn_major ? 2048 : 32;
-    P.b_lbo = b_mn_major ? 16384 : 16; P.b_sbo = 1024; P.b_kstep = b_mn_major ? 4096 : 64; P.b_atom_bytes = BN * 128;
-    P.e_sbo = 128; P.e_lbo = 16;
-    if (const char *env = getenv("SP24_SPMM_KNOBS")) {
-        // debugging aid: "a_lbo,a_sbo,a_kstep,b_lbo,b_sbo,b_kstep,e_lbo,e_sbo,e_mode" (bytes); negative keeps the default
-        long v[9];
-        if (sscanf(env, "%ld,%ld,%ld,%ld,%ld,%ld,%ld,%ld,%ld", &v[0], &v[1], &v[2], &v[3], &v[4], &v[5], &v[6], &v[7],
-                   &v[8]) == 9) {
-            uint32_t *dst[9] = {&P.a_lbo, &P.a_sbo, &P.a_kstep, &P.b_lbo, &P.b_sbo, &P.b_kstep, &P.e_lbo, &P.e_sbo, &P.e_mode};
-            for (int i = 0; i < 9; ++i) if (v[i] >= 0) *dst[i] = (uint32_t)v[i];
-        }
-    }
+              ((uint32_t)(b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BM >> 4) << 24);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define SP24_LAUNCH(F8_, AMN_, BMN_, TR_, OT_) return launch_spmm<BN, 4, F8_, AMN_, BMN_, TR_, OT_>(map_a, map_b, P, st)
+    int bn;
+    if (b_mn_major) {
+        // candidates 192 and 128 (multiples of the 64-column staging block)
+        const int sms = sm_count_cached();
+        const int64_t mp = (ms / BM + 1) / 2;
+        const double c192 = (double)((((n + 191) / 192) * mp + sms - 1) / sms) * (2 * A_STAGE_BYTES + 192 * 256 + 4096);
+        const double c128 = (double)((((n + 127) / 128) * mp + sms - 1) / sms) * (2 * A_STAGE_BYTES + 128 * 256 + 4096);
+        bn = c192 <= c128 ? 192 : 128;
+    } else {
+        bn = pick_bn(ms, n, sm_count_cached(), false);
+    }
+#define SP24_GO(F8_, AMN_, BMN_, TR_, OT_) return dispatch_bn<F8_, AMN_, BMN_, TR_, OT_>(bn, b, dtype, n, k, ld_b, map_a, P, st)
     if (f8) {
-        if (trans_out) SP24_LAUNCH(true, false, false, true, float);
-        SP24_LAUNCH(true, false, false, false, float);
+        if (trans_out) SP24_GO(true, false, false, true, float);
+        SP24_GO(true, false, false, false, float);
     }
     if (dtype == SP24_F16) {
-        if (!a_mn_major && !b_mn_major) { if (trans_out) SP24_LAUNCH(false, false, false, true, __half); SP24_LAUNCH(false, false, false, false, __half); }
-        if (a_mn_major && !b_mn_major) { if (trans_out) SP24_LAUNCH(false, true, false, true, __half); SP24_LAUNCH(false, true, false, false, __half); }
-        if (!a_mn_major && b_mn_major) { if (trans_out) SP24_LAUNCH(false, false, true, true, __half); SP24_LAUNCH(false, false, true, false, __half); }
-        if (trans_out) SP24_LAUNCH(false, true, true, true, __half);
-        SP24_LAUNCH(false, true, true, false, __half);
+        if (!a_mn_major && !b_mn_major) { if (trans_out) SP24_GO(false, false, false, true, __half); SP24_GO(false, false, false, false, __half); }
+        if (a_mn_major && !b_mn_major) { if (trans_out) SP24_GO(false, true, false, true, __half); SP24_GO(false, true, false, false, __half); }
+        if (!a_mn_major && b_mn_major) { if (trans_out) SP24_GO(false, false, true, true, __half); SP24_GO(false, false, true, false, __half); }
+        if (trans_out) SP24_GO(false, true, true, true, __half);
+        SP24_GO(false, true, true, false, __half);
     }
-    if (!a_mn_major && !b_mn_major) { if (trans_out) SP24_LAUNCH(false, false, false, true, __nv_bfloat16); SP24_LAUNCH(false, false, false, false, __nv_bfloat16); }
-    if (a_mn_major && !b_mn_major) { if (trans_out) SP24_LAUNCH(false, true, false, true, __nv_bfloat16); SP24_LAUNCH(false, true, false, false, __nv_bfloat16); }
-    if (!a_mn_major && b_mn_major) { if (trans_out) SP24_LAUNCH(false, false, true, true, __nv_bfloat16); SP24_LAUNCH(false, false, true, false, __nv_bfloat16); }
-    if (trans_out) SP24_LAUNCH(false, true, true, true, __nv_bfloat16);
-    SP24_LAUNCH(false, true, true, false, __nv_bfloat16);
-#undef SP24_LAUNCH
+    if (!a_mn_major && !b_mn_major) { if (trans_out) SP24_GO(false, false, false, true, __nv_bfloat16); SP24_GO(false, false, false, false, __nv_bfloat16); }
+    if (a_mn_major && !b_mn_major) { if (trans_out) SP24_GO(false, true, false, true, __nv_bfloat16); SP24_GO(false, true, false, false, __nv_bfloat16); }
+    if (!a_mn_major && b_mn_major) { if (trans_out) SP24_GO(false, false, true, true, __nv_bfloat16); SP24_GO(false, false, true, false, __nv_bfloat16); }
+    if (trans_out) SP24_GO(false, true, true, true, __nv_bfloat16);
+    SP24_GO(false, true, true, false, __nv_bfloat16);
+#undef SP24_GO
 }
