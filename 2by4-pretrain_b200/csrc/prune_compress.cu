@@ -72,7 +72,7 @@ __device__ __forceinline__ uint32_t do_group(const TIn (&in)[4], uint32_t given_
 // Tile = 32 rows x 32 metadata columns; 8 warps, lane = metadata column, warp w owns rows 4w..4w+3.
 // ---------------------------------------------------------------------------------------------
 template <typename TIn, typename TOut, int MODE, bool HAS_U>
-__global__ void __launch_bounds__(256) pc_row_kernel(PcParams P) {
+__global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_kernel(PcParams P) {
     constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;  // dense elements per metadata word
     constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;    // bytes per metadata word
     constexpr int GROUP = MB == 2 ? 32 : 16;
@@ -165,7 +165,7 @@ template <typename TIn> struct ColVec {
 };
 
 template <typename TIn, typename TOut, int MODE, bool HAS_U, int V>
-__global__ void __launch_bounds__(256) pc_col_kernel(PcParams P) {
+__global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_kernel(PcParams P) {
     constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;
     constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;
     constexpr int GROUP = MB == 2 ? 32 : 16;

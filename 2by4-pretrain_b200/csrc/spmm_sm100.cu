@@ -153,6 +153,8 @@ struct SpmmParams {
     int *status;
     uint32_t idesc;         // instruction descriptor without the metadata selector bits
     int activation;         // 0 none, 1 relu, 2 silu
+    unsigned long long *trace;  // optional timing trace of CTA 0 (debugging aid), else null
+    int mblk_per_tile;      // 128-row blocks per tile: 2 (B staged once per 256 rows) or 1 (more, smaller tiles)
 };
 
 template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
@@ -170,26 +172,42 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     return v;
 }
 
+__device__ __forceinline__ unsigned long long globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// trace layout: 3 roles x 256 slots of nanosecond timestamps, CTA 0 only
+#define SP24_TRACE(role, slot) do { if (P.trace && blockIdx.x == 0 && (slot) < 256) P.trace[(role) * 256 + (slot)] = globaltimer(); } while (0)
+
 __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // Geometry shared by the kernel and its launcher.
-template <int BN, bool F8> struct SpmmCfg {
+template <int BN, bool F8, bool TRANS_OUT, typename OutT> struct SpmmCfg {
     static constexpr int E_BYTES = F8 ? 4096 : 2048;          // metadata of one 128-row block and one stage
     static constexpr int B_BYTES = BN * 256;                  // two 128-byte K atoms per row of B
     static constexpr int STAGE_BYTES = 2 * A_STAGE_BYTES + B_BYTES + 2 * E_BYTES;
-    static constexpr int STAGES = (227 * 1024 - 2048) / STAGE_BYTES >= 4 ? 4 : (227 * 1024 - 2048) / STAGE_BYTES;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
+    // transposed output: each accumulator is first copied row by row (16-byte stores) into a staging
+    // buffer of 128 rows x STG_COLS columns (+16 bytes of padding per row against bank conflicts), then
+    // written out column by column
+    static constexpr int STG_COLS = sizeof(OutT) == 4 ? 64 : BN;
+    static constexpr int STG_ROW_BYTES = STG_COLS * (int)sizeof(OutT) + 16;
+    static constexpr int STG_BYTES = TRANS_OUT ? BM * STG_ROW_BYTES : 0;
+    static constexpr int AVAIL = 227 * 1024 - 2048 - STG_BYTES;
+    static constexpr int STAGES = AVAIL / STAGE_BYTES >= 4 ? 4 : AVAIL / STAGE_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 1024;
     static_assert(STAGES >= 2, "tile too large for a two-stage ring");
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
 };
 
-// One CTA computes a (256 x BN) output tile as two 128-row blocks that share every stage of B
-// (each byte of B staged once per 256 sparse rows).  A_MN / B_MN: operand stored with the non-K axis
-// contiguous.  TRANS_OUT: write out[n][m] (row-major (N, Ms)) instead of out[m][n].
+// Persistent kernel: CTA c processes tiles c, c + gridDim.x, ... ; a tile is (256 sparse rows) x (BN dense
+// columns), computed as two 128-row blocks that share every stage of B.  The operand ring keeps filling
+// across tile boundaries; the epilogue drains tensor memory into a staging buffer and releases each
+// accumulator as soon as it has been read, so the next tile's MMAs overlap the global stores.
 template <int BN, bool F8, bool A_MN, bool B_MN, bool TRANS_OUT, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, SpmmParams P) {
-    using Cfg = SpmmCfg<BN, F8>;
+    using Cfg = SpmmCfg<BN, F8, TRANS_OUT, OutT>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
     constexpr int E_BYTES = Cfg::E_BYTES;
@@ -199,24 +217,24 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     constexpr int E_COL0 = 2 * BN;            // metadata columns behind the two accumulators
     constexpr int E_SLOT = F8 ? 8 : 4;        // metadata columns of one row block and one stage
     static_assert(E_COL0 + 4 * E_SLOT <= 512, "tensor memory columns exhausted");
-    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "invalid MMA N");
+    static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "invalid tile width");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 3];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_blk = blockIdx.x;
-    const int mblk0 = blockIdx.y * 2;                                    // first 128-row block of this CTA
-    const int n_mblk = (P.ms / BM - mblk0) >= 2 ? 2 : 1;                   // 1 on a ragged last CTA
-    const int64_t m0 = (int64_t)mblk0 * BM, n0 = (int64_t)n_blk * BN;
+    const int n_tiles_n = (int)((P.n + BN - 1) / BN);
+    const int n_mblocks = (int)(P.ms / BM);
+    const int mpt = P.mblk_per_tile;
+    const int n_tiles = n_tiles_n * ((n_mblocks + mpt - 1) / mpt);
     const int logical_k_per_stage = F8 ? 256 : 128;
     const int k_iters = (int)((P.k + logical_k_per_stage - 1) / logical_k_per_stage);
-    const uint32_t stage_tx = (uint32_t)(n_mblk * (A_STAGE_BYTES + E_BYTES) + Cfg::B_BYTES);
 
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum_bar = smem_u32(&bars[2 * STAGES]);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t tmem_full = smem_u32(&bars[2 * STAGES]), tmem_empty0 = smem_u32(&bars[2 * STAGES + 1]);
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -224,7 +242,9 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(accum_bar, 1);
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty0, 4);      // one arrival per epilogue warp
+        mbar_init(tmem_empty0 + 8, 4);
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -239,47 +259,55 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            int issued = 0;
-            for (int it = 0; it < k_iters; ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                if (it >= STAGES && !mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, P.status, 1)) break;
-                const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
-                const uint32_t sb = sa + OFF_B;
-                const uint32_t se = sa + OFF_E;
-                const uint32_t full = full0 + 8 * s;
-                mbar_expect_tx(full, stage_tx);
-                for (int mb = 0; mb < n_mblk; ++mb) {
-                    const int mrow = (int)m0 + mb * BM;
-                    const uint32_t sam = sa + mb * A_STAGE_BYTES;
-                    // compressed A: 128 rows x 128 bytes
-                    if constexpr (!A_MN) {
-                        tma_load_2d(sam, &map_a, it * (F8 ? 128 : 64), mrow, full);
-                    } else {
-                        tma_load_2d(sam, &map_a, mrow, it * 64, full);
-                        tma_load_2d(sam + 8192, &map_a, mrow + 64, it * 64, full);
+            int g = 0;  // stages issued so far (ring position across tiles)
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int mblk0 = (tile / n_tiles_n) * mpt;
+                const int n_mblk = (n_mblocks - mblk0) >= mpt ? mpt : 1;
+                const int64_t m0 = (int64_t)mblk0 * BM, n0 = (int64_t)(tile % n_tiles_n) * BN;
+                const uint32_t stage_tx = (uint32_t)(n_mblk * (A_STAGE_BYTES + E_BYTES) + Cfg::B_BYTES);
+                for (int it = 0; it < k_iters; ++it, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (g / STAGES) & 1;
+                    if (g >= STAGES && !mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, P.status, 1)) { ok = false; break; }
+                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint32_t sb = sa + OFF_B;
+                    const uint32_t se = sa + OFF_E;
+                    const uint32_t full = full0 + 8 * s;
+                    mbar_expect_tx(full, stage_tx);
+                    for (int mb = 0; mb < n_mblk; ++mb) {
+                        const int mrow = (int)m0 + mb * BM;
+                        const uint32_t sam = sa + mb * A_STAGE_BYTES;
+                        // compressed A: 128 rows x 128 bytes
+                        if constexpr (!A_MN) {
+                            tma_load_2d(sam, &map_a, it * (F8 ? 128 : 64), mrow, full);
+                        } else {
+                            tma_load_2d(sam, &map_a, mrow, it * 64, full);
+                            tma_load_2d(sam + 8192, &map_a, mrow + 64, it * 64, full);
+                        }
+                        // metadata atoms of this 128-row block
+                        const uint8_t *e_src = static_cast<const uint8_t *>(P.e_tc) +
+                                               ((size_t)(mblk0 + mb) * P.k_atoms + (size_t)it * (E_BYTES / 2048)) * 2048;
+                        bulk_load(se + mb * E_BYTES, e_src, E_BYTES, full);
                     }
-                    // metadata atoms of this 128-row block
-                    const uint8_t *e_src = static_cast<const uint8_t *>(P.e_tc) +
-                                           ((size_t)(mblk0 + mb) * P.k_atoms + (size_t)it * (E_BYTES / 2048)) * 2048;
-                    bulk_load(se + mb * E_BYTES, e_src, E_BYTES, full);
-                }
-                // dense B: BN rows x 2 atoms of 128 bytes (K-major) or column blocks of 64 x 128 K-rows (MN-major)
-                if constexpr (!B_MN) {
-                    const int kx = it * (F8 ? 256 : 128);
-                    tma_load_2d(sb, &map_b, kx, (int)n0, full);
-                    tma_load_2d(sb + BN * 128, &map_b, kx + (F8 ? 128 : 64), (int)n0, full);
-                } else {
+                    // dense B: BN rows x 2 atoms of 128 bytes (K-major) or column blocks of 64 x 128 K-rows (MN-major)
+                    if constexpr (!B_MN) {
+                        const int kx = it * (F8 ? 256 : 128);
+                        tma_load_2d(sb, &map_b, kx, (int)n0, full);
+                        tma_load_2d(sb + BN * 128, &map_b, kx + (F8 ? 128 : 64), (int)n0, full);
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 16384, &map_b, (int)n0 + j * 64, it * 128, full);
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(sb + j * 16384, &map_b, (int)n0 + j * 64, it * 128, full);
+                    }
+                    SP24_TRACE(0, g);
                 }
-                ++issued;
             }
             if (abort_flag) {
                 // drain: wait (bounded) for the copies already issued so that none lands after exit
-                for (int it = (issued > STAGES ? issued - STAGES : 0); it < issued; ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
+                for (int q = (g > STAGES ? g - STAGES : 0); q < g; ++q) {
+                    const int s = q % STAGES;
+                    const uint32_t ph = (q / STAGES) & 1;
                     for (uint32_t w = 0; w < WAIT_LIMIT; ++w)
                         if (mbar_try_wait(full0 + 8 * s, ph)) break;
                 }
@@ -292,101 +320,178 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             // the atom.  MN-major: 64-element column blocks one TMA box apart, 8 K-rows per 1024 bytes.
             constexpr uint32_t A_LBO = A_MN ? 8192 : 16, A_KSTEP = A_MN ? 2048 : 32;
             constexpr uint32_t B_LBO = B_MN ? 16384 : 16, B_KSTEP = B_MN ? 4096 : 64;
+            int g = 0, tl = 0;
             bool ok = true;
-            for (int it = 0; it < k_iters && ok; ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, P.status, 2);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
-                const uint32_t sb = sa + OFF_B;
-                const uint32_t se = sa + OFF_E;
-                for (int mb = 0; mb < n_mblk; ++mb) {
-                    const uint32_t e_cols = E_COL0 + ((it & 1) * 2 + mb) * E_SLOT;
-                    // metadata: shared memory -> tensor memory, 128 lanes x 16 bytes per atom
-                    tc_cp_128x128b(tmem_base + e_cols, make_desc(se + mb * E_BYTES, 16, 128, 0));
-                    if constexpr (F8) tc_cp_128x128b(tmem_base + e_cols + 4, make_desc(se + mb * E_BYTES + 2048, 16, 128, 0));
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tl) {
+                const int mblk0 = (tile / n_tiles_n) * mpt;
+                const int n_mblk = (n_mblocks - mblk0) >= mpt ? mpt : 1;
+                for (int it = 0; it < k_iters && ok; ++it, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (g / STAGES) & 1;
+                    ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, P.status, 2);
+                    if (!ok) break;
+                    SP24_TRACE(1, 2 * g);
+                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint32_t sb = sa + OFF_B;
+                    const uint32_t se = sa + OFF_E;
+                    for (int mb = 0; mb < n_mblk && ok; ++mb) {
+                        if (it == 0) {
+                            // the epilogue of this CTA's previous tile must have drained this accumulator
+                            ok = mbar_wait(tmem_empty0 + 8 * mb, (tl & 1) ^ 1, &abort_flag, P.status, 4);
+                            if (!ok) break;
+                        }
+                        tc_fence_after();
+                        const uint32_t e_cols = E_COL0 + ((g & 1) * 2 + mb) * E_SLOT;
+                        // metadata: shared memory -> tensor memory, 128 lanes x 16 bytes per atom
+                        tc_cp_128x128b(tmem_base + e_cols, make_desc(se + mb * E_BYTES, 16, 128, 0));
+                        if constexpr (F8)
+                            tc_cp_128x128b(tmem_base + e_cols + 4, make_desc(se + mb * E_BYTES + 2048, 16, 128, 0));
 #pragma unroll
-                    for (int j = 0; j < KSTEPS; ++j) {
-                        const uint64_t adesc = make_desc(sa + mb * A_STAGE_BYTES + j * A_KSTEP, A_LBO, 1024, 2);
-                        const uint32_t b_off = B_MN ? j * B_KSTEP : (uint32_t)(j >> 1) * (BN * 128) + (j & 1) * B_KSTEP;
-                        const uint64_t bdesc = make_desc(sb + b_off, B_LBO, 1024, 2);
-                        const uint32_t ecol = e_cols + (F8 ? 2 * j : j);
-                        // 16-bit types: the instruction takes the even column of a pair plus a 1-bit selector
-                        const uint32_t e_addr = tmem_base + (F8 ? ecol : (ecol & ~1u));
-                        const uint32_t idesc = P.idesc | (F8 ? 0u : (ecol & 1u));
-                        mma_sp<F8>(tmem_base + mb * BN, adesc, bdesc, e_addr, idesc, (it > 0 || j > 0) ? 1u : 0u);
+                        for (int j = 0; j < KSTEPS; ++j) {
+                            const uint64_t adesc = make_desc(sa + mb * A_STAGE_BYTES + j * A_KSTEP, A_LBO, 1024, 2);
+                            const uint32_t b_off = B_MN ? j * B_KSTEP : (uint32_t)(j >> 1) * (BN * 128) + (j & 1) * B_KSTEP;
+                            const uint64_t bdesc = make_desc(sb + b_off, B_LBO, 1024, 2);
+                            const uint32_t ecol = e_cols + (F8 ? 2 * j : j);
+                            // 16-bit types: the instruction takes the even column of a pair plus a 1-bit selector
+                            const uint32_t e_addr = tmem_base + (F8 ? ecol : (ecol & ~1u));
+                            const uint32_t idesc = P.idesc | (F8 ? 0u : (ecol & 1u));
+                            mma_sp<F8>(tmem_base + mb * BN, adesc, bdesc, e_addr, idesc, (it > 0 || j > 0) ? 1u : 0u);
+                        }
                     }
+                    tc_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
+                    SP24_TRACE(1, 2 * g + 1);
                 }
-                tc_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
+                tc_commit(tmem_full);           // accumulators of this tile complete (also arrives after an abort)
             }
-            tc_commit(accum_bar);           // accumulators complete (arrives even after an abort)
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
+        // No early exit here: the four warps meet at named barrier 1, so after an abort they keep walking
+        // the tile list (waits return at once) and simply skip the work.
         const int quad = warp & 3;  // TMEM lane quadrant this warp may read
-        const bool ok = mbar_wait(accum_bar, 0, &abort_flag, P.status, 3);
-        tc_fence_after();
-        const bool run = ok && !abort_flag;
         OutT *out = static_cast<OutT *>(P.out);
-        for (int mb = 0; mb < n_mblk; ++mb) {
-            const int64_t mrow0 = m0 + mb * BM;
-            const int64_t m = mrow0 + quad * 32 + lane;
-            float bias = 0.f;
-            if (run && P.bias) bias = from_out<OutT>(static_cast<const OutT *>(P.bias)[m]);
-            if constexpr (TRANS_OUT) {
-                // stage the 128 x BN block transposed in shared memory (the operand ring is idle now), then
-                // write rows of 128 consecutive outputs with 16-byte stores
-                OutT *stg = reinterpret_cast<OutT *>(smem);
-                if (mb > 0) epilogue_bar_sync();
-                if (run) {
+        OutT *stg = reinterpret_cast<OutT *>(smem + (size_t)STAGES * STAGE_BYTES);
+        int tl = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tl) {
+            const int mblk0 = (tile / n_tiles_n) * mpt;
+            const int n_mblk = (n_mblocks - mblk0) >= mpt ? mpt : 1;
+            const int64_t m0 = (int64_t)mblk0 * BM, n0 = (int64_t)(tile % n_tiles_n) * BN;
+            const bool ok = mbar_wait(tmem_full, tl & 1, &abort_flag, P.status, 3);
+            tc_fence_after();
+            if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl);
+            const bool run = ok && !abort_flag;
+            for (int mb = 0; mb < n_mblk; ++mb) {
+                const int64_t mrow0 = m0 + mb * BM;
+                const int64_t m = mrow0 + quad * 32 + lane;
+                float bias = 0.f;
+                if (run && P.bias) bias = from_out<OutT>(static_cast<const OutT *>(P.bias)[m]);
+                const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + mb * BN;
+                if constexpr (TRANS_OUT) {
+                    constexpr int CHUNKS = BN / Cfg::STG_COLS;
+                    constexpr int PER = 16 / sizeof(OutT);              // elements per 16-byte piece
+                    uint8_t *stg_row = reinterpret_cast<uint8_t *>(stg) + (size_t)(quad * 32 + lane) * Cfg::STG_ROW_BYTES;
 #pragma unroll 1
-                    for (int c = 0; c < BN / 16; ++c) {
-                        uint32_t v[16];
-                        tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + mb * BN + c * 16, v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            stg[(c * 16 + i) * BM + quad * 32 + lane] =
-                                to_out<OutT>(apply_act(__uint_as_float(v[i]) + bias, P.activation));
-                    }
-                }
-                epilogue_bar_sync();
-                if (run) {
-                    constexpr int PER = 16 / sizeof(OutT);          // elements per 16-byte piece
-                    constexpr int PIECES = BM / PER;                // pieces per output row
-                    const int tid = (warp - 2) * 32 + lane;
-                    for (int i = tid; i < BN * PIECES; i += 128) {
-                        const int nrow = i / PIECES, piece = i % PIECES;
-                        if (n0 + nrow < P.n)
-                            *reinterpret_cast<uint4 *>(out + (n0 + nrow) * P.ld_out + mrow0 + piece * PER) =
-                                *reinterpret_cast<const uint4 *>(stg + nrow * BM + piece * PER);
-                    }
-                }
-            } else if (run) {
+                    for (int ch = 0; ch < CHUNKS; ++ch) {
+                        if (run) {
 #pragma unroll 1
-                for (int c = 0; c < BN / 16; ++c) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + mb * BN + c * 16, v);
-                    tmem_ld_wait();
-                    const int64_t nb = n0 + c * 16;
-                    OutT *row = out + m * P.ld_out + nb;
-                    if (nb + 16 <= P.n) {
-                        constexpr int PER = 16 / sizeof(OutT);
+                            for (int c = 0; c < Cfg::STG_COLS / 32; ++c) {
+                                uint32_t v[32];
+                                tmem_ld32(acc + ch * Cfg::STG_COLS + c * 32, v);
+                                tmem_ld_wait();
 #pragma unroll
-                        for (int q = 0; q < 16 / PER; ++q) {
-                            Vec<OutT, PER> o;
+                                for (int q = 0; q < 32 / PER; ++q) {
+                                    Vec<OutT, PER> o;
 #pragma unroll
-                            for (int i = 0; i < PER; ++i)
-                                o.v[i] = to_out<OutT>(apply_act(__uint_as_float(v[q * PER + i]) + bias, P.activation));
-                            store_vec<OutT, PER>(row + q * PER, o);
+                                    for (int i = 0; i < PER; ++i)
+                                        o.v[i] = to_out<OutT>(apply_act(__uint_as_float(v[q * PER + i]) + bias, P.activation));
+                                    *reinterpret_cast<uint4 *>(stg_row + (c * 32 + q * PER) * sizeof(OutT)) =
+                                        *reinterpret_cast<const uint4 *>(&o);
+                                }
+                            }
                         }
-                    } else {
-                        for (int i = 0; i < 16; ++i)
-                            if (nb + i < P.n) row[i] = to_out<OutT>(apply_act(__uint_as_float(v[i]) + bias, P.activation));
+                        if (ch == CHUNKS - 1) {
+                            // this accumulator has been read completely: hand it back to the MMA warp
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(tmem_empty0 + 8 * mb);
+                            if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 1 + mb);
+                        }
+                        epilogue_bar_sync();
+                        if (run) {
+                            // thread = two adjacent output rows (dense columns n, n+1) x 8 consecutive features
+                            const int tid = (warp - 2) * 32 + lane;
+                            const int64_t nbase = n0 + ch * Cfg::STG_COLS;
+                            const uint8_t *stg_b = reinterpret_cast<const uint8_t *>(stg);
+                            if constexpr (sizeof(OutT) == 2) {
+                                // a warp instruction covers 8 row pairs x 4 feature groups: 64-byte runs per row
+                                for (int i = tid; i < (Cfg::STG_COLS / 2) * (BM / 8); i += 128) {
+                                    const int mg = (i & 3) + 4 * ((i >> 5) & 3), np = ((i >> 2) & 7) + 8 * (i >> 7);
+                                    uint32_t w[8];
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j)
+                                        w[j] = *reinterpret_cast<const uint32_t *>(stg_b + (size_t)(mg * 8 + j) * Cfg::STG_ROW_BYTES + np * 4);
+                                    uint4 lo, hi;
+                                    lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
+                                    lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
+                                    lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
+                                    lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
+                                    const int64_t nrow = nbase + 2 * np;
+                                    OutT *dst = out + nrow * P.ld_out + mrow0 + mg * 8;
+                                    if (nrow < P.n) *reinterpret_cast<uint4 *>(dst) = lo;
+                                    if (nrow + 1 < P.n) *reinterpret_cast<uint4 *>(dst + P.ld_out) = hi;
+                                }
+                            } else {
+                                // 4-byte outputs: thread = one output row x 4 consecutive features
+                                for (int i = tid; i < Cfg::STG_COLS * (BM / 4); i += 128) {
+                                    const int nn = i % Cfg::STG_COLS, mg = i / Cfg::STG_COLS;
+                                    uint4 o;
+                                    o.x = *reinterpret_cast<const uint32_t *>(stg_b + (size_t)(mg * 4 + 0) * Cfg::STG_ROW_BYTES + nn * 4);
+                                    o.y = *reinterpret_cast<const uint32_t *>(stg_b + (size_t)(mg * 4 + 1) * Cfg::STG_ROW_BYTES + nn * 4);
+                                    o.z = *reinterpret_cast<const uint32_t *>(stg_b + (size_t)(mg * 4 + 2) * Cfg::STG_ROW_BYTES + nn * 4);
+                                    o.w = *reinterpret_cast<const uint32_t *>(stg_b + (size_t)(mg * 4 + 3) * Cfg::STG_ROW_BYTES + nn * 4);
+                                    if (nbase + nn < P.n)
+                                        *reinterpret_cast<uint4 *>(out + (nbase + nn) * P.ld_out + mrow0 + mg * 4) = o;
+                                }
+                            }
+                        }
+                        epilogue_bar_sync();
                     }
+                } else {
+                    if (run) {
+#pragma unroll 1
+                        for (int c = 0; c < BN / 32; ++c) {
+                            uint32_t v[32];
+                            tmem_ld32(acc + c * 32, v);
+                            tmem_ld_wait();
+                            const int64_t nb = n0 + c * 32;
+                            OutT *row = out + m * P.ld_out + nb;
+                            if (nb + 32 <= P.n) {
+                                constexpr int PER = 16 / sizeof(OutT);
+#pragma unroll
+                                for (int q = 0; q < 32 / PER; ++q) {
+                                    Vec<OutT, PER> o;
+#pragma unroll
+                                    for (int i = 0; i < PER; ++i)
+                                        o.v[i] = to_out<OutT>(apply_act(__uint_as_float(v[q * PER + i]) + bias, P.activation));
+                                    store_vec<OutT, PER>(row + q * PER, o);
+                                }
+                            } else {
+                                for (int i = 0; i < 32; ++i)
+                                    if (nb + i < P.n)
+                                        row[i] = to_out<OutT>(apply_act(__uint_as_float(v[i]) + bias, P.activation));
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tmem_empty0 + 8 * mb);
                 }
+            }
+            if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 3);
+            if (n_mblk == 1) {
+                // keep the second accumulator's barrier in step with the tile count
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty0 + 8);
             }
         }
         tc_fence_before();
@@ -469,41 +574,6 @@ int make_map(CUtensorMap *map, const void *base, int dt, int64_t rows, int64_t c
     return r == CUDA_SUCCESS ? SP24_OK : SP24_ERR_CUDA;
 }
 
-template <int BN, bool F8, bool A_MN, bool B_MN, bool TRANS, typename OutT>
-int launch_spmm(const CUtensorMap &ma, const CUtensorMap &mb, SpmmParams P, cudaStream_t st) {
-    using Cfg = SpmmCfg<BN, F8>;
-    auto kern = spmm_kernel<BN, F8, A_MN, B_MN, TRANS, OutT>;
-    static bool attr_set[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
-            return SP24_ERR_CUDA;
-        attr_set[dev] = true;
-    }
-    P.idesc |= (uint32_t)(BN >> 3) << 17;
-    dim3 grid((unsigned)((P.n + BN - 1) / BN), (unsigned)((P.ms / BM + 1) / 2));
-    kern<<<grid, 192, Cfg::SMEM, st>>>(ma, mb, P);
-    return launch_status();
-}
-
-// Tile width: the candidates trade operand traffic per output (wide is better) against how evenly the
-// CTAs fill the SMs.  Cost model: waves x K iterations x bytes staged per iteration.
-int pick_bn(int64_t ms, int64_t n, int sm_count, bool b_mn) {
-    const int cand[3] = {240, 176, 128};
-    int best = 128;
-    double best_cost = 1e300;
-    for (int i = 0; i < 3; ++i) {
-        const int bn = cand[i];
-        if (b_mn && bn % 64) continue;  // MN-major B is staged in 64-column blocks
-        const int64_t ctas = ((n + bn - 1) / bn) * ((ms / BM + 1) / 2);
-        const double waves = (double)((ctas + sm_count - 1) / sm_count);
-        const double cost = waves * (2 * A_STAGE_BYTES + bn * 256 + 4096);
-        if (cost < best_cost) { best_cost = cost; best = bn; }
-    }
-    return best;
-}
-
 int sm_count_cached() {
     static int cached[64];
     int dev = 0;
@@ -517,6 +587,41 @@ int sm_count_cached() {
     return cached[dev];
 }
 
+template <int BN, bool F8, bool A_MN, bool B_MN, bool TRANS, typename OutT>
+int launch_spmm(const CUtensorMap &ma, const CUtensorMap &mb, SpmmParams P, cudaStream_t st) {
+    using Cfg = SpmmCfg<BN, F8, TRANS, OutT>;
+    auto kern = spmm_kernel<BN, F8, A_MN, B_MN, TRANS, OutT>;
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
+            return SP24_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    P.idesc |= (uint32_t)(BN >> 3) << 17;
+    const int64_t tiles = ((P.n + BN - 1) / BN) * ((P.ms / BM + P.mblk_per_tile - 1) / P.mblk_per_tile);
+    const int sms = sm_count_cached();
+    kern<<<(unsigned)(tiles < sms ? tiles : sms), 192, Cfg::SMEM, st>>>(ma, mb, P);
+    return launch_status();
+}
+
+// Tile shape: wide / tall tiles stage fewer operand bytes per output, small ones fill the SMs more evenly.
+// Cost model per candidate (BN, row blocks per tile): rounds of tiles per CTA x bytes staged per K iteration.
+void pick_tile(int64_t ms, int64_t n, int sm_count, int &bn_out, int &mpt_out) {
+    const int cand_bn[2] = {192, 128};
+    double best_cost = 1e300;
+    for (int mpt = 2; mpt >= 1; --mpt) {
+        for (int i = 0; i < 2; ++i) {
+            const int bn = cand_bn[i];
+            const int64_t tiles = ((n + bn - 1) / bn) * ((ms / BM + mpt - 1) / mpt);
+            const double rounds = (double)((tiles + sm_count - 1) / sm_count);
+            const double cost = rounds * (mpt * (A_STAGE_BYTES + 2048) + bn * 256);
+            if (cost < best_cost) { best_cost = cost; bn_out = bn; mpt_out = mpt; }
+        }
+    }
+}
+
 template <bool F8, bool A_MN, bool B_MN, bool TRANS, typename OutT>
 int dispatch_bn(int bn, const void *b, int dtype, int64_t n, int64_t k, int64_t ld_b, const CUtensorMap &ma,
                 const SpmmParams &P, cudaStream_t st) {
@@ -525,14 +630,8 @@ int dispatch_bn(int bn, const void *b, int dtype, int64_t n, int64_t k, int64_t 
     if (!B_MN) rc = make_map(&mb, b, dtype, n, k, ld_b, F8 ? 128 : 64, (uint32_t)bn);
     else rc = make_map(&mb, b, dtype, k, n, ld_b, 64, 128);
     if (rc) return rc;
-    if constexpr (B_MN) {
-        if (bn == 128) return launch_spmm<128, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
-        return launch_spmm<192, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
-    } else {
-        if (bn == 240) return launch_spmm<240, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
-        if (bn == 176) return launch_spmm<176, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
-        return launch_spmm<128, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
-    }
+    if (bn == 192) return launch_spmm<192, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
+    return launch_spmm<128, F8, A_MN, B_MN, TRANS, OutT>(ma, mb, P, st);
 }
 
 }  // namespace
@@ -588,22 +687,16 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     SpmmParams P{};
     P.e_tc = e_tc; P.out = out; P.bias = bias; P.ms = ms; P.n = n; P.k = k; P.ld_out = ld_out;
     P.k_atoms = (k + 127) / 128; P.status = status; P.activation = activation;
+    P.trace = nullptr;
+    if (const char *env = getenv("SP24_SPMM_TRACE_PTR")) P.trace = reinterpret_cast<unsigned long long *>(strtoull(env, nullptr, 0));
     const uint32_t fmt = (dtype == SP24_BF16 || dtype == SP24_E5M2) ? 1u : 0u;
     // sparse flag, fp32 accumulate, operand formats, operand majors, M = 128 (N is added by the launcher)
     P.idesc = (1u << 2) | (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) |
               ((uint32_t)(b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BM >> 4) << 24);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int bn;
-    if (b_mn_major) {
-        // candidates 192 and 128 (multiples of the 64-column staging block)
-        const int sms = sm_count_cached();
-        const int64_t mp = (ms / BM + 1) / 2;
-        const double c192 = (double)((((n + 191) / 192) * mp + sms - 1) / sms) * (2 * A_STAGE_BYTES + 192 * 256 + 4096);
-        const double c128 = (double)((((n + 127) / 128) * mp + sms - 1) / sms) * (2 * A_STAGE_BYTES + 128 * 256 + 4096);
-        bn = c192 <= c128 ? 192 : 128;
-    } else {
-        bn = pick_bn(ms, n, sm_count_cached(), false);
-    }
+    int bn = 128, mpt = 2;
+    pick_tile(ms, n, sm_count_cached(), bn, mpt);
+    P.mblk_per_tile = mpt;
 #define SP24_GO(F8_, AMN_, BMN_, TR_, OT_) return dispatch_bn<F8_, AMN_, BMN_, TR_, OT_>(bn, b, dtype, n, k, ld_b, map_a, P, st)
     if (f8) {
         if (trans_out) SP24_GO(true, false, false, true, float);

@@ -19,6 +19,12 @@ _ext.register_signature("sp24_spmm", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _v
                                       _i64, _vp, _i32, _vp, _vp])
 
 _ACT = {None: 0, "none": 0, "relu": 1, "silu": 2}
+
+# Layout of the (tokens, features) result when the dense operand is token-major.  False (default): a
+# contiguous (tokens, features) tensor, written by a transposing epilogue.  True: what the reference
+# returns (sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:813-815 of the reference), a transposed view
+# of the (features, tokens) product; downstream element-wise ops and the next sparse GEMM accept it as is.
+RETURN_TRANSPOSED_VIEW = False
 _tc_meta_cache = {}  # id(meta tensor) -> (weak reference to it, tensor-core copy); tensors do not hash by value
 _status = {}
 
@@ -101,8 +107,10 @@ def sparse_linear(input, weight, meta, bias=None, activation=None):
         raise RuntimeError("sparse GEMM on sm_100a: number of rows of the sparse matrix must be divisible by 128")
     e_tc = tc_metadata(meta, ms, k)
     status = _status_word(weight.device)
-    if b_mn:
-        # D (ms, n) row-major; the caller transposes it back (mm with the sparse matrix first)
+    as_view = b_mn or RETURN_TRANSPOSED_VIEW
+    if as_view:
+        # D (ms, n) row-major, returned as its transposed view (the caller of mm-with-sparse-first
+        # transposes it back, so that result ends up contiguous)
         out = torch.empty((ms, n), dtype=out_dtype, device=weight.device)
         trans_out, ld_out = 0, n
     else:
@@ -112,6 +120,6 @@ def sparse_linear(input, weight, meta, bias=None, activation=None):
                               b_mn, ld_b, n, out.data_ptr(), _ext.dt(out_dtype), trans_out, ld_out, _ext.ptr(bias),
                               _ACT[activation], status.data_ptr(), _ext.stream())
     _ext.check(rc, "sp24_spmm")
-    res = out.t() if b_mn else out
+    res = out.t() if as_view else out
     sizes[-1] = ms
     return res.reshape(sizes) if len(sizes) != 2 else res

@@ -342,6 +342,22 @@ def run_case(name):
             packed = torch.empty(m, k // 2, dtype=torch.bfloat16, device=dev)
             meta = torch.empty(m, k // 16, dtype=torch.int16, device=dev)
         fn = lambda: prune_compress(g, packed, meta, mode=mode, seed=1)
+    elif name in ("spmm_fwd", "spmm_dx", "spmm_dw"):
+        T, K, N = 16384, 768, 3072
+        dt = torch.float16
+        x = torch.randn(T, K, device=dev).to(dt)
+        dy = (torch.randn(T, N, device=dev) * 1e-2).to(dt)
+        w = torch.randn(N, K, device=dev) * 0.02
+        mask, (pw, mw), (pt, mt) = sparse.select_and_compress(w, dtype=dt)
+        ws = sparse.SparseSemiStructuredTensor(None, original_shape=w.shape, sparse_tensor_cutlass=pw, meta_tensor_cutlass=mw, dtype=dt)
+        wt = sparse.SparseSemiStructuredTensor(None, original_shape=w.t().shape, sparse_tensor_cutlass=pt, meta_tensor_cutlass=mt, dtype=dt)
+        dys = sparse.to_sparse_semi_structured(dy.t(), MVUE24=True, dtype=dt)
+        if name == "spmm_fwd":
+            fn = lambda: torch.mm(x, ws.t())
+        elif name == "spmm_dx":
+            fn = lambda: torch.mm(dy, wt.t())
+        else:
+            fn = lambda: torch.mm(dys, x)
     elif name == "soft":
         g = (torch.randn(16384, 4096, device=dev) * 1e-3).bfloat16()
         fn = lambda: sparse.soft_threshold24_triton(g)
@@ -447,6 +463,11 @@ def spmm_measurements(dev):
             return e0.elapsed_time(e1) * 1e-3 / reps
 
         t_fwd = timeit(lambda i: torch.mm(xs[i], ws.t()))
+        from sparse import spmm as _spmm
+        _spmm.RETURN_TRANSPOSED_VIEW = True
+        t_fwd_view = timeit(lambda i: torch.mm(xs[i], ws.t()))
+        t_dx_view = timeit(lambda i: torch.mm(dys[i], wt.t()))
+        _spmm.RETURN_TRANSPOSED_VIEW = False
         t_dx = timeit(lambda i: torch.mm(dys[i], wt.t()))
         t_dw = timeit(lambda i: torch.mm(sparse.to_sparse_semi_structured(dys[i].t(), MVUE24=True, dtype=dtype), xs[i]))
         t_dw_gemm_only = None
@@ -460,7 +481,9 @@ def spmm_measurements(dev):
         sp_total, de_total = t_fwd + t_dx + t_dw, d_fwd + d_dx + d_dw
         res[tag] = {
             "sparse_ms": {"fwd": t_fwd * 1e3, "dx": t_dx * 1e3, "dw_incl_mvue_compress": t_dw * 1e3,
-                          "dw_gemm_only": t_dw_gemm_only * 1e3},
+                          "dw_gemm_only": t_dw_gemm_only * 1e3,
+                          "fwd_transposed_view_like_reference": t_fwd_view * 1e3,
+                          "dx_transposed_view_like_reference": t_dx_view * 1e3},
             "dense_cublas_ms": {"fwd": d_fwd * 1e3, "dx": d_dx * 1e3, "dw": d_dw * 1e3},
             "sparse_fwd_bwd_TFLOPs_dense_equiv": 3 * flops / sp_total / 1e12,
             "dense_fwd_bwd_TFLOPs": 3 * flops / de_total / 1e12,
