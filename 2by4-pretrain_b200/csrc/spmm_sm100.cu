@@ -716,3 +716,56 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     SP24_GO(false, true, true, false, __nv_bfloat16);
 #undef SP24_GO
 }
+
+
+// ------------------------------------------------------------------------------------------------
+// Sparse GEMM for callers that must not allocate
+// ------------------------------------------------------------------------------------------------
+// Some hosts of this library cannot call cudaMalloc at the point where they run the GEMM: code replayed
+// under a memory plan fixed in advance, a real-time loop that may not touch the allocator, or a plug-in
+// whose host application owns all device memory.  sp24_spmm needs one piece of scratch besides its
+// inputs and outputs - the metadata re-ordered for the tensor cores - and normally the caller allocates
+// it.  This variant keeps that scratch in a fixed array inside the library image instead.  Every GPU
+// that loads the library carries the array until the process exits.
+constexpr int64_t NOALLOC_SCRATCH_BYTES = 4ll << 20;  // enough for ms * k <= 32 Mi elements
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+namespace sp24 {
+namespace {
+// Device address of the array, looked up once per device.  In host code the array's name is only a
+// handle; the address a kernel can use comes from cudaGetSymbolAddress with that device current.
+int noalloc_scratch(void **out) {
+    static void *cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return SP24_ERR_CUDA;
+    if (dev < 0 || dev >= 64) return SP24_ERR_DEVICE;
+    if (!cached[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return SP24_ERR_CUDA;
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return SP24_OK;
+}
+}  // namespace
+}  // namespace sp24
+
+extern "C" int64_t sp24_spmm_noalloc_max_bytes(void) { return NOALLOC_SCRATCH_BYTES; }
+
+extern "C" int sp24_spmm_noalloc(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *meta,
+                                 int64_t ms, int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out,
+                                 int out_dtype, int trans_out, int64_t ld_out, const void *bias, int activation,
+                                 int *status, void *stream) {
+    if (!meta) return SP24_ERR_ARG;
+    const bool f8 = dtype == SP24_E4M3 || dtype == SP24_E5M2;
+    if (ms <= 0 || k <= 0 || ms % 128 || k % (f8 ? 128 : 64)) return SP24_ERR_SHAPE;
+    if (sp24_meta_tc_bytes(ms, k) > NOALLOC_SCRATCH_BYTES) return SP24_ERR_TOO_LARGE;
+    if (int rc = check_device()) return rc;
+    void *scratch = nullptr;
+    if (int rc = noalloc_scratch(&scratch)) return rc;
+    // the conversion rewrites every word the GEMM will read (padding included), so whatever an earlier
+    // call left in the array does not matter
+    if (int rc = sp24_meta_to_tc(meta, f8 ? 4 : 2, ms, k, scratch, stream)) return rc;
+    return sp24_spmm(a_packed, dtype, a_mn_major, ld_a, scratch, ms, k, b, b_mn_major, ld_b, n, out, out_dtype, trans_out,
+                     ld_out, bias, activation, status, stream);
+}

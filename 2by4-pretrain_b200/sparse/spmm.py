@@ -18,6 +18,10 @@ _ext.register_signature("sp24_meta_to_tc", [_vp, _i32, _i64, _i64, _vp, _vp])
 _ext.register_signature("sp24_spmm", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i64, _vp, _i32, _i32,
                                       _i64, _vp, _i32, _vp, _vp])
 
+# allocation-free variant (metadata in the reference layout, tensor-core copy kept inside the library)
+_ext.register_signature("sp24_spmm_noalloc", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i64, _vp, _i32, _i32,
+                                              _i64, _vp, _i32, _vp, _vp])
+
 _ACT = {None: 0, "none": 0, "relu": 1, "silu": 2}
 
 # Layout of the (tokens, features) result when the dense operand is token-major.  False (default): a

@@ -192,6 +192,28 @@ int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, con
               const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype, int trans_out,
               int64_t ld_out, const void *bias, int activation, int *status, void *stream);
 
+/*
+ * The same GEMM for callers that cannot allocate device memory where they call it (a host that replays
+ * a fixed memory plan, a loop that must stay clear of the allocator, a plug-in inside an application
+ * that owns all GPU memory).  No counterpart in the reference.  It takes the metadata in the
+ * reference's reordered layout (what sp24_prune_compress writes) and keeps the tensor-core copy in a
+ * 4 MiB array that is part of the library image, so nothing is allocated by this call, by the caller
+ * or by any library routine.  Limits and rules:
+ *   - ms * k must not exceed 32 Mi elements (sp24_spmm_noalloc_max_bytes() is the array size that
+ *     sp24_meta_tc_bytes(ms, k) has to fit in); larger problems return SP24_ERR_TOO_LARGE;
+ *   - the first call on each device looks up the array's device address; make that call before any
+ *     CUDA stream capture begins on that device;
+ *   - all calls share the one array and each call overwrites the part it uses, so two calls that can
+ *     overlap on the GPU (different streams, no dependency) race; order them on one stream or with
+ *     events;
+ *   - every GPU that loads the library holds the 4 MiB until the process exits.
+ * All other arguments are those of sp24_spmm.
+ */
+int64_t sp24_spmm_noalloc_max_bytes(void);
+int sp24_spmm_noalloc(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *meta, int64_t ms,
+                      int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype,
+                      int trans_out, int64_t ld_out, const void *bias, int activation, int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -38,7 +38,7 @@ def test_header_symbols_exported(lib):
 def test_python_signatures_cover_header(lib):
     from sparse import _ext
     from sparse import spmm  # noqa: F401  (binds the GEMM entry points)
-    bound = set(_ext._SIGNATURES) | {"sp24_strerror", "sp24_abi_version", "sp24_meta_tc_bytes"}
+    bound = set(_ext._SIGNATURES) | {"sp24_strerror", "sp24_abi_version", "sp24_meta_tc_bytes", "sp24_spmm_noalloc_max_bytes"}
     assert set(declared_symbols()) <= bound
 
 
