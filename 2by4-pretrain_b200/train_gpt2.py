@@ -1,0 +1,185 @@
+"""Data-parallel 2:4 sparse pre-training of a GPT-2-124M-shaped model on synthetic tokens.
+
+    python 2by4-pretrain_b200/train_gpt2.py --steps 20                      # one GPU
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        2by4-pretrain_b200/train_gpt2.py --steps 20                         # 8 GPUs, NCCL
+
+The model is written from the hyper-parameters alone (12 layers, d_model 768, 12 heads, MLP 3072,
+sequence 1024, vocabulary 50304, normal(0, 0.02) init); every ``nn.Linear`` inside the blocks is a
+``SparseLinearTranspose``.  The step follows the reference's recipe (README.md:125-226 of the reference):
+forward / backward with three sparse GEMMs per layer, then masked decay
+``masked_add_(p.grad, p.data, p.mask, alpha)`` on every sparse weight and ``p.cnt = 0``, then AdamW.
+Gradients are averaged by ``DistributedDataParallel`` (bucketed NCCL all-reduce overlapped with backward).
+Masks need no communication: the weights are identical on all ranks after the reduce, so every rank
+recomputes the same transposable mask.  MVUE seeds come from Python's ``random``, seeded per rank.
+"""
+import argparse
+import math
+import os
+import random
+import sys
+import time
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+class Block(nn.Module):
+    def __init__(self, d, heads, linear):
+        super().__init__()
+        self.heads = heads
+        self.ln1 = nn.LayerNorm(d)
+        self.attn_qkv = linear(d, 3 * d)
+        self.attn_proj = linear(d, d)
+        self.ln2 = nn.LayerNorm(d)
+        self.fc = linear(d, 4 * d)
+        self.proj = linear(4 * d, d)
+
+    def forward(self, x):
+        b, t, d = x.shape
+        q, k, v = self.attn_qkv(self.ln1(x)).split(d, dim=2)
+        q, k, v = (z.view(b, t, self.heads, d // self.heads).transpose(1, 2) for z in (q, k, v))
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.attn_proj(y.transpose(1, 2).reshape(b, t, d))
+        x = x + self.proj(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+        return x
+
+
+class GPT2(nn.Module):
+    def __init__(self, linear, layers=12, d=768, heads=12, seq=1024, vocab=50304):
+        super().__init__()
+        self.seq = seq
+        self.wte = nn.Embedding(vocab, d)
+        self.wpe = nn.Embedding(seq, d)
+        self.blocks = nn.ModuleList(Block(d, heads, linear) for _ in range(layers))
+        self.ln_f = nn.LayerNorm(d)
+        self.apply(self._init)
+
+    @staticmethod
+    def _init(m):
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(m.weight, mean=0.0, std=0.02)
+            if getattr(m, "bias", None) is not None:
+                nn.init.zeros_(m.bias)
+
+    def forward(self, idx, targets):
+        b, t = idx.shape
+        x = self.wte(idx) + self.wpe(torch.arange(t, device=idx.device))
+        for blk in self.blocks:
+            x = blk(x)
+        logits = F.linear(self.ln_f(x), self.wte.weight)  # tied output head
+        return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.reshape(-1))
+
+
+def masked_decay_(model, alpha):
+    """README.md:205-214 of the reference: decay pruned weights through the gradient, reset ``cnt``."""
+    import sparse
+    with torch.no_grad():
+        for p in model.parameters():
+            if hasattr(p, "mask") and p.mode == "sparse" and p.grad is not None:
+                p.grad = p.grad.float()
+                sparse.masked_add_(p.grad.data, p.data, p.mask, alpha=alpha)
+                p.cnt = 0
+
+
+def build(mode, device, layers=12, d=768, heads=12, seq=1024, vocab=50304, seed=11):
+    import sparse
+    torch.manual_seed(seed)  # same initial weights on every rank
+
+    def linear(i, o):
+        return sparse.SparseLinearTranspose(i, o, bias=True)
+
+    model = GPT2(linear, layers, d, heads, seq, vocab).to(device)
+    for p in model.parameters():
+        if hasattr(p, "mask"):
+            p.mode = mode
+            p.mask = p.mask.to(device)
+    return model
+
+
+def run(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12, d=768, heads=12, alpha=2e-4,
+        lr=6e-4, verbose=False):
+    """Returns a dict with tokens/s (whole job) and ms per step, timed on the device, max over ranks."""
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    own_group = False
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+        own_group = True
+    random.seed(1234 + rank)  # MVUE streams differ per rank
+    model = build(mode, dev, layers, d, heads, seq, vocab)
+    net = model
+    if world > 1:
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True)
+    decay, no_decay = [], []
+    for n_, p in model.named_parameters():
+        (no_decay if p.dim() < 2 or hasattr(p, "mask") else decay).append(p)
+    opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": no_decay, "weight_decay": 0.0}],
+                            lr=lr, betas=(0.9, 0.95), fused=True)
+    gen = torch.Generator(device="cpu").manual_seed(10 + rank)
+    losses = []
+
+    def one_step():
+        tok = torch.randint(0, vocab, (batch, seq + 1), generator=gen)
+        tok = tok.pin_memory().to(dev, non_blocking=True)
+        x, y = tok[:, :-1], tok[:, 1:]
+        with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+            loss = net(x, y)
+        loss.backward()
+        if mode == "sparse":
+            masked_decay_(model, alpha)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    for _ in range(warmup):
+        one_step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        losses.append(one_step().detach())
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    last = float(torch.stack(losses).float()[-1].item())
+    res = {"tokens_per_s": batch * seq * world * steps / (ms * 1e-3), "ms_per_step": ms / steps, "world": world,
+           "tokens_per_step": batch * seq * world, "last_loss": last, "mode": mode, "loss_finite": math.isfinite(last)}
+    if mode == "sparse":
+        from sparse.spmm import check_status
+        check_status()
+    del opt, net, model
+    torch.cuda.empty_cache()
+    if own_group:
+        dist.destroy_process_group()
+    if verbose and rank == 0:
+        print(res)
+    return res
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--mode", default="sparse", choices=["sparse", "dense"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=12)
+    a = ap.parse_args()
+    t0 = time.time()
+    r = run(a.steps, a.warmup, a.mode, batch=a.batch, layers=a.layers, verbose=True)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(f"wall {time.time() - t0:.1f}s")

@@ -286,6 +286,10 @@ def main():
         extra = side_measurements(dev)
         spmm_extra = spmm_measurements(dev)
 
+    gpt2 = None
+    if not args.no_extra:
+        gpt2 = gpt2_measurements(world)
+
     if rank == 0:
         peak, peak_kind = measured_peak()
         line = {
@@ -313,6 +317,8 @@ def main():
             line["kernels"] = extra
         if spmm_extra:
             line["spmm_cfg4"] = spmm_extra
+        if gpt2:
+            line["gpt2_124m"] = gpt2
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -427,6 +433,26 @@ def side_measurements(dev):
     mk = [torch.rand(m, k, device=dev) < 0.5 for _ in range(2)]
     rec("cfg3 masked_add_ fp32 8192x4096", timeit(lambda i: sparse.masked_add_(gr[i], p[i], mk[i], alpha=2e-4), 2), n * 13)
     return res
+
+
+def gpt2_measurements(world):
+    """cfg5: GPT-2-124M-shaped model, 8 x 1024 synthetic tokens per GPU and step, data-parallel over the
+    ranks of this job (NCCL all-reduce through DistributedDataParallel).  Tokens/s of the sparse recipe
+    (SparseLinearTranspose in every block, masked decay, AdamW) and of the same model with dense linears."""
+    sys.path.insert(0, os.path.join(ROOT, "2by4-pretrain_b200"))
+    import train_gpt2
+    out = {}
+    try:
+        sp = train_gpt2.run(steps=8, warmup=3, mode="sparse")
+        de = train_gpt2.run(steps=8, warmup=3, mode="dense")
+        out = {"sparse_tokens_per_s": sp["tokens_per_s"], "sparse_ms_per_step": sp["ms_per_step"],
+               "dense_tokens_per_s": de["tokens_per_s"], "dense_ms_per_step": de["ms_per_step"],
+               "sparse_over_dense": sp["tokens_per_s"] / de["tokens_per_s"], "tokens_per_step": sp["tokens_per_step"],
+               "loss_finite": sp["loss_finite"], "n_gpus": world,
+               "note": "timed steps lie between mask refreshes (every 40 optimizer steps)"}
+    except Exception as exc:  # the headline line must still be printed
+        out = {"error": repr(exc)[:300]}
+    return out
 
 
 def spmm_measurements(dev):

@@ -220,3 +220,16 @@ def test_config4_fp8_forward(S):
     # and the quantised result tracks the unquantised masked product to fp8 accuracy
     full = x @ torch.where(mask, w, torch.zeros((), device=DEV)).t()
     assert float((y - full).norm() / full.norm()) < 0.08
+
+
+def test_gpt2_training_steps_tiny(S):
+    """Three optimizer steps of a small GPT-2-shaped model with SparseLinearTranspose in every block:
+    losses stay finite, every weight keeps a transposable 2:4 mask, pruned weights decay."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "2by4-pretrain_b200"))
+    import train_gpt2
+    res = train_gpt2.run(steps=3, warmup=1, mode="sparse", batch=2, seq=128, vocab=512, layers=2, d=256, heads=4)
+    assert res["loss_finite"] and res["tokens_per_step"] == 256 and res["last_loss"] < 8.0
+    dense = train_gpt2.run(steps=3, warmup=1, mode="dense", batch=2, seq=128, vocab=512, layers=2, d=256, heads=4)
+    assert dense["loss_finite"]
