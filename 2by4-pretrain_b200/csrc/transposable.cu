@@ -1,79 +1,152 @@
 // Transposable 4x4 mask select, alone and fused with the 2:4 compression of W and of W^T.
 //
-// One thread owns one 4x4 block.  The 90 admissible patterns (two ones per row and per column) are
-// enumerated at compile time in descending lexicographic order of the row-major bit string, which is
-// the nested order "row 0 pair, row 1 pair, row 2 pair, row 3 pair" over the pair list
-// (0,1) (0,2) (0,3) (1,2) (1,3) (2,3).  Scores are float32 with a fixed association,
-// (s0 + s1) + (s2 + s3), s_i = v[i][a] + v[i][b], and the first maximum wins.
+// One thread owns one 4x4 block.  The 90 admissible patterns (two ones per row and per column), in
+// descending lexicographic order of the row-major bit string, are the nested order "row 0 pair, row 1
+// pair, row 2 pair, row 3 pair" over the pair list (0,1) (0,2) (0,3) (1,2) (1,3) (2,3).  Scores are
+// float32 with a fixed association, (s0 + s1) + (s2 + s3), s_i = v[i][a] + v[i][b], and the first
+// maximum wins.  The search is hierarchical (best bottom per top pair, then first top, then first
+// bottom) and returns exactly what the flat scan over the 90 patterns would.
 #include "sp24_common.cuh"
 
 namespace sp24 {
 namespace {
 
+// ---------------------------------------------------------------------------------------------
+// compile-time description of the 90 patterns
+// ---------------------------------------------------------------------------------------------
+// Column pairs in table order: 0:(0,1) 1:(0,2) 2:(0,3) 3:(1,2) 4:(1,3) 5:(2,3); pair 5-p is the complement of p.
 __host__ __device__ constexpr int pair_a(int i) { return i < 3 ? 0 : (i < 5 ? 1 : 2); }
 __host__ __device__ constexpr int pair_b(int i) { return i < 3 ? i + 1 : (i < 5 ? i - 1 : 3); }
 __host__ __device__ constexpr int row_bits(int i) { return (1 << pair_a(i)) | (1 << pair_b(i)); }
-__host__ __device__ constexpr bool cols_ok(int i0, int i1, int i2, int i3) {
-    for (int c = 0; c < 4; ++c) {
-        int n = 0;
-        n += (pair_a(i0) == c) + (pair_b(i0) == c);
-        n += (pair_a(i1) == c) + (pair_b(i1) == c);
-        n += (pair_a(i2) == c) + (pair_b(i2) == c);
-        n += (pair_a(i3) == c) + (pair_b(i3) == c);
-        if (n != 2) return false;
-    }
-    return true;
+__host__ __device__ constexpr int pair_of(int c0, int c1) {
+    const int lo = c0 < c1 ? c0 : c1, hi = c0 < c1 ? c1 : c0;
+    return lo == 0 ? hi - 1 : (lo == 1 ? hi + 1 : 5);
 }
+// A pattern is (a, b, c, d) = the pairs of rows 0..3.  Given the pairs (a, b) of the two top rows, the
+// admissible bottoms are: a == b -> only (5-a, 5-a); b == 5-a -> (c, 5-c) for every c; otherwise the two
+// top rows share one column s and leave one column r unused, and the bottoms are {r,p},{r,q} in either
+// order (p, q = the unshared columns of a and b).
+__host__ __device__ constexpr int top_type(int a, int b) { return a == b ? 0 : (b == 5 - a ? 2 : 1); }
+__host__ __device__ constexpr int shared_bottom(int a, int b, int which) {
+    const int a0 = pair_a(a), a1 = pair_b(a), b0 = pair_a(b), b1 = pair_b(b);
+    const int s = (a0 == b0 || a0 == b1) ? a0 : a1;
+    const int p = a0 == s ? a1 : a0, q = b0 == s ? b1 : b0;
+    const int r = 6 - s - p - q;
+    const int x0 = pair_of(r, p), y0 = pair_of(r, q);
+    const int x = x0 < y0 ? x0 : y0, y = x0 < y0 ? y0 : x0;
+    return which == 0 ? x : y;
+}
+constexpr uint32_t PATTERN0 = 0x33CCu & 0xFFFFu;  // rows (0,1),(0,1),(2,3),(2,3): bits 0011 0011 1100 1100 read high to low
 
-template <int I0, int I1, int I2, int I3> struct PatternStep {
-    __device__ static __forceinline__ void run(const float (&s)[4][6], float &best, uint32_t &bits) {
-        if constexpr (cols_ok(I0, I1, I2, I3)) {
-            const float sc = __fadd_rn(__fadd_rn(s[0][I0], s[1][I1]), __fadd_rn(s[2][I2], s[3][I3]));
-            constexpr uint32_t B = row_bits(I0) | (row_bits(I1) << 4) | (row_bits(I2) << 8) | (row_bits(I3) << 12);
-            if (sc > best) { best = sc; bits = B; }
+// Lookup words.  [0,36): per top (a*6+b): bits 0..7 rows 0-1, 8..15 first bottom, 16..23 second bottom,
+// 24..25 type.  [36,42): bottoms (c, 5-c).  [48,64): per 4-bit keep mask: bits 0..3 metadata code
+// idx0 | idx1 << 2, bits 8..23 byte-permute selector that gathers the 16-bit elements idx0, idx1 of
+// a (lo, hi) register pair.
+struct SelectLut { uint32_t v[64]; };
+__host__ __device__ constexpr uint32_t encode_nibble_c(uint32_t mask) {
+    const uint32_t m0 = mask & 1u, m1 = (mask >> 1) & 1u, m2 = (mask >> 2) & 1u;
+    const uint32_t bit0 = (m0 ^ 1u) & m1, bit1 = (m0 ^ 1u) & (m1 ^ 1u);
+    const uint32_t bit2 = bit1 | (m2 ^ 1u), bit3 = bit0 | (m1 ^ 1u) | m2;
+    return bit0 | (bit1 << 1) | (bit2 << 2) | (bit3 << 3);
+}
+constexpr SelectLut make_select_lut() {
+    SelectLut L{};
+    for (int a = 0; a < 6; ++a)
+        for (int b = 0; b < 6; ++b) {
+            const int ty = top_type(a, b);
+            uint32_t bot0 = 0, bot1 = 0;
+            if (ty == 0) bot0 = row_bits(5 - a) | (row_bits(5 - a) << 4);
+            if (ty == 1) {
+                const int x = shared_bottom(a, b, 0), y = shared_bottom(a, b, 1);
+                bot0 = row_bits(x) | (row_bits(y) << 4);
+                bot1 = row_bits(y) | (row_bits(x) << 4);
+            }
+            L.v[a * 6 + b] = (uint32_t)(row_bits(a) | (row_bits(b) << 4)) | (bot0 << 8) | (bot1 << 16) | ((uint32_t)ty << 24);
         }
+    for (int c = 0; c < 6; ++c) L.v[36 + c] = row_bits(c) | (row_bits(5 - c) << 4);
+    for (uint32_t k = 0; k < 16; ++k) {
+        const uint32_t nib = encode_nibble_c(k), i0 = nib & 3u, i1 = nib >> 2;
+        const uint32_t sel = (2 * i0) | ((2 * i0 + 1) << 4) | ((2 * i1) << 8) | ((2 * i1 + 1) << 12);
+        L.v[48 + k] = nib | (sel << 8);
     }
-};
+    return L;
+}
+__constant__ SelectLut kSelectLut = make_select_lut();
 
-// Two nested compile-time loops (36 x 36 candidates, 90 survive the column check), kept shallow so
-// that the template recursion depth stays small.
-template <int I0, int I1, int N> struct InnerLoop {
-    __device__ static __forceinline__ void run(const float (&s)[4][6], float &best, uint32_t &bits) {
-        InnerLoop<I0, I1, N - 1>::run(s, best, bits);
-        PatternStep<I0, I1, (N - 1) / 6, (N - 1) % 6>::run(s, best, bits);
-    }
-};
-template <int I0, int I1> struct InnerLoop<I0, I1, 0> {
-    __device__ static __forceinline__ void run(const float (&)[4][6], float &, uint32_t &) {}
-};
-template <int N> struct OuterLoop {
-    __device__ static __forceinline__ void run(const float (&s)[4][6], float &best, uint32_t &bits) {
-        OuterLoop<N - 1>::run(s, best, bits);
-        InnerLoop<(N - 1) / 6, (N - 1) % 6, 36>::run(s, best, bits);
-    }
-};
-template <> struct OuterLoop<0> {
-    __device__ static __forceinline__ void run(const float (&)[4][6], float &, uint32_t &) {}
-};
-
-// v: the 4x4 block (already |.| when requested).  Returns the 16-bit pattern, bit 4*i+j = keep (i, j).
-__device__ __forceinline__ uint32_t select_pattern(const float (&v)[4][4]) {
+// v: the 4x4 block (already |.| when requested); lut: shared-memory copy of kSelectLut.
+// Returns the 16-bit pattern (bit 4*i+j = keep (i, j)) that a scan over all 90 patterns in table order with
+// "first maximum wins" would return, but needs far fewer compare/select instructions: the best bottom for
+// every top pair is a max over at most six sums (rounding is monotone, so max-then-add equals add-then-max),
+// the winning top is the first whose best total equals the global maximum, and the winning bottom is the
+// first admissible one that reaches the maximum with that top.
+__device__ __forceinline__ uint32_t select_pattern(const float (&v)[4][4], const uint32_t *lut) {
     float s[4][6];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int p = 0; p < 6; ++p) s[i][p] = __fadd_rn(v[i][pair_a(p)], v[i][pair_b(p)]);
-    float best = -INFINITY;
-    // pattern 0 stays when no score compares greater than -inf (all NaN / -inf)
-    uint32_t bits = row_bits(0) | (row_bits(0) << 4) | (row_bits(5) << 8) | (row_bits(5) << 12);
-    OuterLoop<36>::run(s, best, bits);
+    // Everything below is recomputed from the 24 row sums instead of being kept in registers: the float
+    // adder has headroom, registers (occupancy) do not.
+    auto top = [&](int a, int b) { return __fadd_rn(s[0][a], s[1][b]); };
+    auto bot = [&](int c, int d) { return __fadd_rn(s[2][c], s[3][d]); };
+    float max_c = bot(0, 5);
+#pragma unroll
+    for (int c = 1; c < 6; ++c) max_c = fmaxf(max_c, bot(c, 5 - c));
+    auto best_total = [&](int a, int b) {
+        float bb;
+        if (top_type(a, b) == 0) bb = bot(5 - a, 5 - a);
+        else if (top_type(a, b) == 2) bb = max_c;
+        else bb = fmaxf(bot(shared_bottom(a, b, 0), shared_bottom(a, b, 1)), bot(shared_bottom(a, b, 1), shared_bottom(a, b, 0)));
+        return __fadd_rn(top(a, b), bb);
+    };
+    float m = best_total(0, 0);
+#pragma unroll
+    for (int t = 1; t < 36; ++t) m = fmaxf(m, best_total(t / 6, t % 6));
+    // keep the compiler from carrying the 36 totals of the first pass over to the second
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int p = 0; p < 6; ++p) asm volatile("" : "+f"(s[i][p]));
+    // first top (table order) whose best total is the maximum: walk backwards, later writes win
+    int tstar = 0;
+    float t_val = top(0, 0), cand0 = 0.f;
+#pragma unroll
+    for (int t = 35; t >= 0; --t) {
+        if (best_total(t / 6, t % 6) == m) {
+            tstar = t;
+            t_val = top(t / 6, t % 6);
+            if (top_type(t / 6, t % 6) == 1) cand0 = bot(shared_bottom(t / 6, t % 6, 0), shared_bottom(t / 6, t % 6, 1));
+        }
+    }
+    const bool first = __fadd_rn(t_val, cand0) == m;
+    int cstar = 0;
+#pragma unroll
+    for (int c = 5; c >= 0; --c)
+        if (__fadd_rn(t_val, bot(c, 5 - c)) == m) cstar = c;
+    const uint32_t e = lut[tstar];
+    const uint32_t ty = e >> 24;
+    const uint32_t bot_bits = ty == 2 ? lut[36 + cstar] : ((ty == 1 && !first) ? ((e >> 16) & 0xFFu) : ((e >> 8) & 0xFFu));
+    uint32_t bits = (e & 0xFFu) | (bot_bits << 8);
+    if (!(m > -INFINITY)) bits = row_bits(0) | (row_bits(0) << 4) | (row_bits(5) << 8) | (row_bits(5) << 12);
     return bits;
+}
+
+__device__ __forceinline__ void load_select_lut(uint32_t *lut) {
+    if (threadIdx.x < 64) lut[threadIdx.x] = kSelectLut.v[threadIdx.x];
+    __syncthreads();
 }
 
 template <typename T> __device__ __forceinline__ void load_row4(const T *p, T (&out)[4]) {
     Vec<T, 4> v = load_vec<T, 4>(p);
 #pragma unroll
     for (int j = 0; j < 4; ++j) out[j] = v.v[j];
+}
+
+// keep bits of one row -> four mask bytes (0 / 1)
+__device__ __forceinline__ uint32_t spread_mask_bytes(uint32_t rb) { return (rb * 0x00204081u) & 0x01010101u; }
+// four mask bytes (non-zero = keep) -> keep bits
+__device__ __forceinline__ uint32_t gather_mask_bytes(uint32_t mw) {
+    return ((__vcmpne4(mw, 0u) & 0x01010101u) * 0x01020408u) >> 24;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -83,6 +156,8 @@ template <typename T> __device__ __forceinline__ void load_row4(const T *p, T (&
 template <typename T>
 __global__ void __launch_bounds__(256) ts_select_kernel(const T *x, T *sparse, uint8_t *mask, int64_t k, int64_t ld_x,
                                                         int64_t ld_s, int64_t ld_m, int use_abs) {
+    __shared__ uint32_t lut[64];
+    load_select_lut(lut);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t r = (int64_t)blockIdx.y * 32 + warp * 4;
     const int64_t c = (int64_t)blockIdx.x * 128 + lane * 4;
@@ -98,13 +173,12 @@ __global__ void __launch_bounds__(256) ts_select_kernel(const T *x, T *sparse, u
             const float f = Elem<T>::to_f32(w[i][j]);
             v[i][j] = use_abs ? fabsf(f) : f;
         }
-    const uint32_t bits = select_pattern(v);
+    const uint32_t bits = select_pattern(v, lut);
     const T zero = Elem<T>::from_f32(0.f);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t rb = (bits >> (4 * i)) & 0xFu;
-        const uint32_t mword = (rb & 1u) | ((rb & 2u) << 7) | ((rb & 4u) << 14) | ((rb & 8u) << 21);
-        *reinterpret_cast<uint32_t *>(mask + (r + i) * ld_m + c) = mword;
+        *reinterpret_cast<uint32_t *>(mask + (r + i) * ld_m + c) = spread_mask_bytes(rb);
         if (sparse) {
             Vec<T, 4> o;
 #pragma unroll
@@ -125,123 +199,163 @@ struct DualParams {
     int64_t m, k, ld_w, ld_mask, ld_pw, ld_pt;
 };
 
+// four elements of a row as two registers of packed 16-bit output values (low half = lower column)
+template <typename T, typename TOut> __device__ __forceinline__ void pack_row(const T (&w)[4], uint32_t &lo, uint32_t &hi) {
+    if constexpr (std::is_same<T, TOut>::value) {
+        lo = *reinterpret_cast<const uint32_t *>(&w[0]);
+        hi = *reinterpret_cast<const uint32_t *>(&w[2]);
+    } else {
+        TOut o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = convert<TOut>(w[j]);
+        lo = (uint32_t) * reinterpret_cast<const uint16_t *>(&o[0]) | ((uint32_t) * reinterpret_cast<const uint16_t *>(&o[1]) << 16);
+        hi = (uint32_t) * reinterpret_cast<const uint16_t *>(&o[2]) | ((uint32_t) * reinterpret_cast<const uint16_t *>(&o[3]) << 16);
+    }
+}
+
 template <typename T, typename TOut, bool SELECT>
-__global__ void __launch_bounds__(256) ts_dual_kernel(DualParams P) {
+__global__ void __launch_bounds__(256, 2) ts_dual_kernel(DualParams P) {
     __shared__ __align__(16) uint16_t smeta_w[4][64];   // 4 column pairs x (32 rows x 2)
     __shared__ __align__(16) uint16_t smeta_t[256];     // 1 column pair x (128 rows x 2)
-    __shared__ __align__(4) uint8_t nib_t[128][8];      // [W column][block row]
+    __shared__ __align__(4) uint8_t nib_t[8][128];      // [block row][W column]
+    __shared__ uint32_t lut[64];
+    load_select_lut(lut);
 
+    // A block covers 64 rows x 128 columns as two 32-row halves.  Both halves are loaded up front so that
+    // the second half's global loads are in flight while the first half is being searched.
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t r0 = (int64_t)blockIdx.y * 32, c0 = (int64_t)blockIdx.x * 128;
-    const int64_t r = r0 + warp * 4, c = c0 + lane * 4;
+    const int64_t c0 = (int64_t)blockIdx.x * 128, c = c0 + lane * 4;
     const bool active = c < P.k;
     const T *w_ptr = static_cast<const T *>(P.w);
-    TOut *pw = static_cast<TOut *>(P.packed_w);
-    TOut *pt = static_cast<TOut *>(P.packed_t);
+    uint16_t *pw = static_cast<uint16_t *>(P.packed_w);
+    uint16_t *pt = static_cast<uint16_t *>(P.packed_t);
 
-    uint32_t bits = 0;
-    T w[4][4];
+    T w[4][4], w_next[4][4];
+    uint32_t mw[4] = {0, 0, 0, 0}, mw_next[4] = {0, 0, 0, 0};
     if (active) {
+        const int64_t ra = (int64_t)blockIdx.y * 64 + warp * 4;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) load_row4<T>(w_ptr + (r + i) * P.ld_w + c, w[i]);
-        if constexpr (SELECT) {
-            float v[4][4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) v[i][j] = fabsf(Elem<T>::to_f32(w[i][j]));
-            bits = select_pattern(v);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t rb = (bits >> (4 * i)) & 0xFu;
-                *reinterpret_cast<uint32_t *>(P.mask + (r + i) * P.ld_mask + c) =
-                    (rb & 1u) | ((rb & 2u) << 7) | ((rb & 4u) << 14) | ((rb & 8u) << 21);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t mw = *reinterpret_cast<const uint32_t *>(P.mask + (r + i) * P.ld_mask + c);
-                const uint32_t rb = ((mw & 0xFFu) != 0) | (((mw >> 8) & 0xFFu) != 0) << 1 | (((mw >> 16) & 0xFFu) != 0) << 2 |
-                                    ((mw >> 24) != 0) << 3;
-                bits |= rb << (4 * i);
+        for (int i = 0; i < 4; ++i) {
+            load_row4<T>(w_ptr + (ra + i) * P.ld_w + c, w[i]);
+            load_row4<T>(w_ptr + (ra + 32 + i) * P.ld_w + c, w_next[i]);
+            if constexpr (!SELECT) {
+                mw[i] = *reinterpret_cast<const uint32_t *>(P.mask + (ra + i) * P.ld_mask + c);
+                mw_next[i] = *reinterpret_cast<const uint32_t *>(P.mask + (ra + 32 + i) * P.ld_mask + c);
             }
         }
     }
-    // rows of W: one nibble per row, four horizontally adjacent lanes make one 16-bit word
-    uint32_t nib_row[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t rb = (bits >> (4 * i)) & 0xFu;
-        const uint32_t nib = encode_nibble(rb);
-        nib_row[i] = nib;
+
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+        const int64_t r0 = (int64_t)blockIdx.y * 64 + half * 32;
+        const int64_t r = r0 + warp * 4;
+        uint32_t bits = 0;
+        uint32_t h[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // the block as packed 16-bit output values
         if (active) {
-            Vec<TOut, 2> o;
-            o.v[0] = convert<TOut>(pick4(nib & 3u, w[i][0], w[i][1], w[i][2], w[i][3]));
-            o.v[1] = convert<TOut>(pick4(nib >> 2, w[i][0], w[i][1], w[i][2], w[i][3]));
-            store_vec<TOut, 2>(pw + (r + i) * P.ld_pw + (c >> 1), o);
-        }
-    }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint32_t word = nib_row[i] << (4 * (lane & 3));
-        word |= __shfl_xor_sync(0xFFFFFFFFu, word, 1);
-        word |= __shfl_xor_sync(0xFFFFFFFFu, word, 2);
+            for (int i = 0; i < 4; ++i) pack_row<T, TOut>(w[i], h[i][0], h[i][1]);
+            if constexpr (SELECT) {
+                float v[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[i][j] = fabsf(Elem<T>::to_f32(w[i][j]));
+                bits = select_pattern(v, lut);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    *reinterpret_cast<uint32_t *>(P.mask + (r + i) * P.ld_mask + c) = spread_mask_bytes((bits >> (4 * i)) & 0xFu);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) bits |= gather_mask_bytes(mw[i]) << (4 * i);
+            }
+        }
+        // rows of W: table lookup gives the metadata code and the byte-permute selector of the two kept values
+        uint32_t nib01 = 0, nib23 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t e = lut[48 + ((bits >> (4 * i)) & 0xFu)];
+            if (active) *reinterpret_cast<uint32_t *>(pw + (r + i) * P.ld_pw + (c >> 1)) = __byte_perm(h[i][0], h[i][1], e >> 8);
+            if (i < 2) nib01 |= (e & 0xFu) << (16 * i);
+            else nib23 |= (e & 0xFu) << (16 * (i - 2));
+        }
+        // four horizontally adjacent lanes make one 16-bit metadata word per row (two rows per register)
+        nib01 <<= 4 * (lane & 3);
+        nib23 <<= 4 * (lane & 3);
+        nib01 |= __shfl_xor_sync(0xFFFFFFFFu, nib01, 1);
+        nib23 |= __shfl_xor_sync(0xFFFFFFFFu, nib23, 1);
+        nib01 |= __shfl_xor_sync(0xFFFFFFFFu, nib01, 2);
+        nib23 |= __shfl_xor_sync(0xFFFFFFFFu, nib23, 2);
         if ((lane & 3) == 0) {
             const int mc = lane >> 2;  // metadata column inside the tile (0..7)
-            smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + i, mc & 1)] = (uint16_t)word;
+            smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 0, mc & 1)] = (uint16_t)nib01;
+            smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 1, mc & 1)] = (uint16_t)(nib01 >> 16);
+            smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 2, mc & 1)] = (uint16_t)nib23;
+            smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 3, mc & 1)] = (uint16_t)(nib23 >> 16);
         }
-    }
-    // columns of W (= rows of W^T): one nibble per column
-    {
-        Vec<TOut, 4> o0, o1;
+        // columns of W (= rows of W^T): transpose the 4x4 block of 16-bit values, then the same table lookup
+        {
+            uint32_t pj[4], nibs = 0;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t cb = ((bits >> j) & 1u) | (((bits >> (4 + j)) & 1u) << 1) | (((bits >> (8 + j)) & 1u) << 2) |
-                                (((bits >> (12 + j)) & 1u) << 3);
-            const uint32_t nib = encode_nibble(cb);
-            nib_t[lane * 4 + j][warp] = (uint8_t)nib;
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t sel_t = (j & 1) ? 0x7632u : 0x5410u;
+                const uint32_t c_lo = __byte_perm(h[0][j >> 1], h[1][j >> 1], sel_t);  // (w[0][j], w[1][j])
+                const uint32_t c_hi = __byte_perm(h[2][j >> 1], h[3][j >> 1], sel_t);  // (w[2][j], w[3][j])
+                const uint32_t cb = ((((bits >> j) & 0x1111u) * 0x1248u) >> 12) & 0xFu;  // keep bits of column j
+                const uint32_t e = lut[48 + cb];
+                pj[j] = __byte_perm(c_lo, c_hi, e >> 8);
+                nibs |= (e & 0xFu) << (8 * j);
+            }
+            // one 32-bit store per thread: [block row][column] keeps the four columns of a thread together
+            *reinterpret_cast<uint32_t *>(&nib_t[0][0] + (warp * 128 + lane * 4)) = nibs;
             if (active) {
-                o0.v[j] = convert<TOut>(pick4(nib & 3u, w[0][j], w[1][j], w[2][j], w[3][j]));
-                o1.v[j] = convert<TOut>(pick4(nib >> 2, w[0][j], w[1][j], w[2][j], w[3][j]));
+                uint2 o0, o1;
+                o0.x = __byte_perm(pj[0], pj[1], 0x5410u); o0.y = __byte_perm(pj[2], pj[3], 0x5410u);
+                o1.x = __byte_perm(pj[0], pj[1], 0x7632u); o1.y = __byte_perm(pj[2], pj[3], 0x7632u);
+                *reinterpret_cast<uint2 *>(pt + (r >> 1) * P.ld_pt + c) = o0;
+                *reinterpret_cast<uint2 *>(pt + ((r >> 1) + 1) * P.ld_pt + c) = o1;
             }
         }
-        if (active) {
-            store_vec<TOut, 4>(pt + (r >> 1) * P.ld_pt + c, o0);
-            store_vec<TOut, 4>(pt + ((r >> 1) + 1) * P.ld_pt + c, o1);
+        __syncthreads();
+        {
+            // thread t: W column t>>1, metadata column parity t&1 of the transposed matrix; the bytes of
+            // block rows 4*par .. 4*par+3 for that column sit 128 bytes apart
+            const int col = threadIdx.x >> 1, par = threadIdx.x & 1;
+            const uint8_t *nb = &nib_t[0][0] + (par * 4) * 128 + col;
+            const uint32_t word = (uint32_t)nb[0] | ((uint32_t)nb[128] << 4) | ((uint32_t)nb[256] << 8) | ((uint32_t)nb[384] << 12);
+            smeta_t[(col / 32) * 64 + meta_run_pos<2>(col % 32, par)] = (uint16_t)word;
         }
-    }
-    __syncthreads();
-    {
-        // thread t: W column t>>1, metadata column parity t&1 of the transposed matrix
-        const int col = threadIdx.x >> 1, par = threadIdx.x & 1;
-        const uint32_t b4 = *reinterpret_cast<const uint32_t *>(&nib_t[col][par * 4]);
-        const uint32_t word = (b4 & 0xFu) | ((b4 >> 4) & 0xF0u) | ((b4 >> 8) & 0xF00u) | ((b4 >> 12) & 0xF000u);
-        smeta_t[(col / 32) * 64 + meta_run_pos<2>(col % 32, par)] = (uint16_t)word;
-    }
-    __syncthreads();
-    // write-out: W metadata 4 pairs x 128 B, W^T metadata up to 512 B
-    if (threadIdx.x < 32) {
-        const int pair = threadIdx.x >> 3, piece = threadIdx.x & 7;
-        const int64_t cp = c0 / 32 + pair;
-        if (cp * 2 < P.k / 16) {
-            char *dst = reinterpret_cast<char *>(P.meta_w) + (cp * 2 * P.m + 2 * r0) * 2 + piece * 16;
-            *reinterpret_cast<uint4 *>(dst) =
-                *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(&smeta_w[pair][0]) + piece * 16);
+        __syncthreads();
+        // write-out: W metadata 4 pairs x 128 B, W^T metadata up to 512 B
+        if (threadIdx.x < 32) {
+            const int pair = threadIdx.x >> 3, piece = threadIdx.x & 7;
+            const int64_t cp = c0 / 32 + pair;
+            if (cp * 2 < P.k / 16) {
+                char *dst = reinterpret_cast<char *>(P.meta_w) + (cp * 2 * P.m + 2 * r0) * 2 + piece * 16;
+                *reinterpret_cast<uint4 *>(dst) =
+                    *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(&smeta_w[pair][0]) + piece * 16);
+            }
+        } else if (threadIdx.x < 64) {
+            const int piece = threadIdx.x - 32;
+            const int64_t cols_here = (P.k - c0 < 128) ? (P.k - c0) : 128;
+            if (piece * 8 < cols_here * 2) {
+                const int64_t cp = r0 / 32;  // column pair of the (k, m) metadata matrix
+                char *dst = reinterpret_cast<char *>(P.meta_t) + (cp * 2 * P.k + 2 * c0) * 2 + piece * 16;
+                *reinterpret_cast<uint4 *>(dst) =
+                    *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(smeta_t) + piece * 16);
+            }
         }
-    } else if (threadIdx.x < 64) {
-        const int piece = threadIdx.x - 32;
-        const int64_t cols_here = (P.k - c0 < 128) ? (P.k - c0) : 128;
-        if (piece * 8 < cols_here * 2) {
-            const int64_t cp = r0 / 32;  // column pair of the (k, m) metadata matrix
-            char *dst = reinterpret_cast<char *>(P.meta_t) + (cp * 2 * P.k + 2 * c0) * 2 + piece * 16;
-            *reinterpret_cast<uint4 *>(dst) =
-                *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(smeta_t) + piece * 16);
+        __syncthreads();  // the staging arrays are rewritten by the next half
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[i][j] = w_next[i][j];
+            mw[i] = mw_next[i];
         }
     }
 }
 
 template <typename T, typename TOut> int launch_dual(const DualParams &P, int select, cudaStream_t st) {
-    dim3 grid((unsigned)((P.k + 127) / 128), (unsigned)(P.m / 32));
+    dim3 grid((unsigned)((P.k + 127) / 128), (unsigned)(P.m / 64));
     if (select) ts_dual_kernel<T, TOut, true><<<grid, 256, 0, st>>>(P);
     else ts_dual_kernel<T, TOut, false><<<grid, 256, 0, st>>>(P);
     return launch_status();

@@ -14,6 +14,7 @@ from torch.amp import custom_fwd, custom_bwd
 from .semi_structured import SparseSemiStructuredTensor, to_sparse_semi_structured
 from .transposable_semi_structured import TransposableSparse, select_and_compress
 from .triton_ops import MVUE24_approx_triton
+from .spmm import sparse_linear as _spmm
 
 
 class my_linear(autograd.Function):
@@ -95,8 +96,10 @@ class sparse_linear_transpose(autograd.Function):
     def forward(ctx, input, weight, weight_sparse, weight_sparse_T, bias):
         ctx.save_for_backward(input, weight_sparse_T, bias)
         ctx.shape = input.shape
-        input = input.view(-1, input.shape[-1])
-        output = torch.mm(input, weight_sparse.t())
+        input = input.reshape(-1, input.shape[-1])
+        # same product as torch.mm(input, weight_sparse.t()); calling the GEMM wrapper directly skips the
+        # Python-level tensor-subclass dispatch
+        output = _spmm(input, weight_sparse.sparse_tensor_cutlass, weight_sparse.meta_tensor_cutlass)
         if bias is None:
             return output.view(*ctx.shape[:-1], -1)
         return output.view(*ctx.shape[:-1], -1) + bias
@@ -110,10 +113,13 @@ class sparse_linear_transpose(autograd.Function):
             grad_output = torch.ones_like(grad_output, device=grad_output.device, dtype=grad_output.dtype)
         grad_output = grad_output.reshape(-1, grad_output.shape[-1])
         if ctx.needs_input_grad[0]:
-            grad_input = torch.mm(grad_output, weight_T.t()).view(ctx.shape)
+            # torch.mm(grad_output, weight_T.t())
+            grad_input = _spmm(grad_output, weight_T.sparse_tensor_cutlass, weight_T.meta_tensor_cutlass).view(ctx.shape)
         if ctx.needs_input_grad[1]:
-            input = input.view(-1, input.shape[-1])
-            grad_weight = torch.mm(to_sparse_semi_structured(grad_output.t(), MVUE24=True, dtype=grad_output.dtype), input)
+            input = input.reshape(-1, input.shape[-1])
+            # torch.mm(to_sparse_semi_structured(grad_output.t(), MVUE24=True), input)
+            gs = to_sparse_semi_structured(grad_output.t(), MVUE24=True, dtype=grad_output.dtype)
+            grad_weight = _spmm(input.t(), gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass).t()
         if ctx.needs_input_grad[4]:
             grad_bias = grad_output.sum(0)
         return grad_input, grad_weight, None, None, grad_bias

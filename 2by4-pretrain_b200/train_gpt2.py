@@ -146,8 +146,10 @@ def run(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12,
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t_cpu = time.perf_counter()
     for _ in range(steps):
         losses.append(one_step().detach())
+    t_cpu = time.perf_counter() - t_cpu  # host time to enqueue the steps (no synchronisation inside)
     e1.record()
     if world > 1:
         dist.barrier()
@@ -158,7 +160,8 @@ def run(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12,
     ms = float(ms.item())
     last = float(torch.stack(losses).float()[-1].item())
     res = {"tokens_per_s": batch * seq * world * steps / (ms * 1e-3), "ms_per_step": ms / steps, "world": world,
-           "tokens_per_step": batch * seq * world, "last_loss": last, "mode": mode, "loss_finite": math.isfinite(last)}
+           "tokens_per_step": batch * seq * world, "last_loss": last, "mode": mode, "loss_finite": math.isfinite(last),
+           "host_enqueue_ms_per_step": t_cpu * 1e3 / steps}
     if mode == "sparse":
         from sparse.spmm import check_status
         check_status()
