@@ -84,7 +84,11 @@ def dt(dtype: torch.dtype) -> int:
 
 
 def stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of the current CUDA stream of the current device."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
+    except AttributeError:  # older / newer torch without the private fast path
+        return torch.cuda.current_stream().cuda_stream
 
 
 def ptr(t):

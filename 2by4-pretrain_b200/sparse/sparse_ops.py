@@ -125,6 +125,42 @@ class sparse_linear_transpose(autograd.Function):
         return grad_input, grad_weight, None, None, grad_bias
 
 
+class _fst_linear(autograd.Function):
+    """What ``sparse_linear_transpose`` computes, on the raw compressed buffers: no tensor-subclass objects,
+    no cast of the (unused) fp32 weight.  ``weight`` only routes the gradient."""
+
+    @staticmethod
+    def forward(ctx, input, weight, pw, mw, pt, mt, bias):
+        x = input.reshape(-1, input.shape[-1])
+        if x.dtype != pw.dtype:
+            x = x.to(pw.dtype)
+        b = None if bias is None else (bias if bias.dtype == pw.dtype else bias.to(pw.dtype))
+        ctx.save_for_backward(x, pt, mt)
+        ctx.shape = input.shape
+        ctx.has_bias = bias is not None
+        output = _spmm(x, pw, mw)
+        output = output.view(*input.shape[:-1], -1)
+        return output if b is None else output + b
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, pt, mt = ctx.saved_tensors
+        grad_input = grad_weight = grad_bias = None
+        if grad_output.dim() == 3 and grad_output.stride() == (0, 0, 0):
+            grad_output = torch.ones_like(grad_output)
+        g = grad_output.reshape(-1, grad_output.shape[-1])
+        if g.dtype != pt.dtype:
+            g = g.to(pt.dtype)
+        if ctx.needs_input_grad[0]:
+            grad_input = _spmm(g, pt, mt).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            gs = to_sparse_semi_structured(g.t(), MVUE24=True, dtype=g.dtype)
+            grad_weight = _spmm(x.t(), gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass).t()
+        if ctx.has_bias and ctx.needs_input_grad[6]:
+            grad_bias = g.sum(0)
+        return grad_input, grad_weight, None, None, None, None, grad_bias
+
+
 class SparseLinearTranspose(nn.Linear):
     """Drop-in for ``nn.Linear`` that trains with 2:4 sparse GEMMs (FST).
 
@@ -134,7 +170,14 @@ class SparseLinearTranspose(nn.Linear):
     ``mask`` (bool, transposable 2:4), ``weight_sparse`` / ``weight_sparse_T`` and ``mode``
     ('sparse' or 'dense').  When both the mask and the compressed copies are due, one fused kernel
     produces all three from a single read of the weight.
+
+    ``materialize_sparse_tensors`` (class attribute, default False): when True the compressed copies are
+    also wrapped as ``SparseSemiStructuredTensor`` objects in ``weight.weight_sparse`` /
+    ``weight.weight_sparse_T`` after every refresh, as in the listing; the layer itself works on the raw
+    buffers (``weight.compressed`` = (packed_w, meta_w, packed_t, meta_t)) to keep the host cost low.
     """
+
+    materialize_sparse_tensors = False
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, func=lambda step: 'dense', **kwargs):
         super().__init__(in_features, out_features, bias=bias, **kwargs)
@@ -147,6 +190,7 @@ class SparseLinearTranspose(nn.Linear):
         self.weight.mask = torch.ones_like(self.weight, dtype=torch.bool)
         self.weight.weight_sparse = None
         self.weight.weight_sparse_T = None
+        self.weight.compressed = None
         self.weight.mode = 'sparse'
         self.func = func
 
@@ -157,6 +201,10 @@ class SparseLinearTranspose(nn.Linear):
         w = self.weight
         mask, (pw, mw), (pt, mt) = select_and_compress(w, mask=None if reselect else w.mask, dtype=torch.float16)
         w.mask = mask
+        w.compressed = (pw, mw, pt, mt)
+        if not self.materialize_sparse_tensors:
+            w.weight_sparse = w.weight_sparse_T = None
+            return
         out_f, in_f = w.shape
         w.weight_sparse = SparseSemiStructuredTensor(
             None, original_shape=torch.Size([out_f, in_f]), sparse_tensor_cutlass=pw, meta_tensor_cutlass=mw,
@@ -170,11 +218,12 @@ class SparseLinearTranspose(nn.Linear):
         if w.mode == 'dense':
             x = F.linear(x, w, self.bias)
         else:
-            w.mask = w.mask.to(device=w.device)
+            if w.mask.device != w.device:
+                w.mask = w.mask.to(device=w.device)
             if w.cnt == 0:
                 self._refresh(reselect=(w.counter % w.freq == 0))
-            with torch.autocast(device_type='cuda', dtype=torch.float16):
-                x = sparse_linear_transpose.apply(x, w, w.weight_sparse, w.weight_sparse_T, self.bias)
+            pw, mw, pt, mt = w.compressed
+            x = _fst_linear.apply(x, w, pw, mw, pt, mt, self.bias)
 
         if self.training:
             if w.cnt == 0:

@@ -151,12 +151,18 @@ def test_sparse_linear_transpose_layer(S):
     # counters follow the listing: one micro-step done, mask refresh only every `freq` optimizer steps
     w = layer.weight
     assert (w.cnt, w.counter, w.step) == (1, 1, 1)
-    old = w.weight_sparse
+    old = w.compressed
     layer(x.detach())
-    assert w.weight_sparse is old and (w.cnt, w.counter, w.step) == (2, 1, 2)
+    assert w.compressed is old and (w.cnt, w.counter, w.step) == (2, 1, 2)
     w.cnt = 0
+    layer.materialize_sparse_tensors = True
     layer(x.detach())
-    assert w.weight_sparse is not old and torch.equal(w.mask, mask)
+    assert w.compressed is not old and torch.equal(w.mask, mask)
+    assert isinstance(w.weight_sparse, S.SparseSemiStructuredTensor) and w.weight_sparse_T.shape == (256, 384)
+    # the listing's own Function gives the same result on the materialised tensors
+    with torch.autocast(device_type="cuda", dtype=torch.float16):
+        y2 = S.sparse_linear_transpose.apply(x.detach(), w, w.weight_sparse, w.weight_sparse_T, layer.bias)
+    assert torch.equal(y2, layer(x.detach()))
     w.mode = 'dense'
     yd = layer(x.detach())
     assert yd.dtype == torch.float32
