@@ -68,6 +68,59 @@ __device__ __forceinline__ uint32_t do_group(const TIn (&in)[4], uint32_t given_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Table-driven group processing for 16-bit -> same 16-bit type (magnitude and mask modes).
+// Words 0..63: indexed by the six magnitude comparisons x1 | x2<<1 | x3<<2 | x4<<3 | x5<<4 | x6<<5
+// (x1 = |a0|>|a1|, x2 = |a0|>|a2|, x3 = |a0|>|a3|, x4 = |a1|>|a2|, x5 = |a1|>|a3|, x6 = |a2|>|a3|);
+// words 64..79: indexed by a 4-bit keep mask.  Each word: bits 0..3 the metadata code idx0 | idx1<<2,
+// bits 8..23 the byte-permute selector that gathers elements idx0, idx1 from a (lo, hi) register pair.
+// ---------------------------------------------------------------------------------------------
+struct GroupLut { uint32_t v[80]; };
+__host__ __device__ constexpr uint32_t lut_word_for_keep(uint32_t keep) {
+    const uint32_t m0 = keep & 1u, m1 = (keep >> 1) & 1u, m2 = (keep >> 2) & 1u;
+    const uint32_t bit0 = (m0 ^ 1u) & m1, bit1 = (m0 ^ 1u) & (m1 ^ 1u);
+    const uint32_t bit2 = bit1 | (m2 ^ 1u), bit3 = bit0 | (m1 ^ 1u) | m2;
+    const uint32_t i0 = bit0 | (bit1 << 1), i1 = bit2 | (bit3 << 1);
+    const uint32_t sel = (2 * i0) | ((2 * i0 + 1) << 4) | ((2 * i1) << 8) | ((2 * i1 + 1) << 12);
+    return (i0 | (i1 << 2)) | (sel << 8);
+}
+constexpr GroupLut make_group_lut() {
+    GroupLut L{};
+    for (uint32_t i = 0; i < 64; ++i) {
+        const bool x1 = i & 1, x2 = i & 2, x3 = i & 4, x4 = i & 8, x5 = i & 16, x6 = i & 32;
+        const bool m0 = (x2 && x3) || (x1 && x2) || (x1 && x3);
+        const bool m1 = (!x1 && x5) || (x4 && x5) || (!x1 && x4);
+        const bool m2 = (!x2 && !x4) || (!x2 && x6) || (!x4 && x6);
+        const bool m3 = (!x3 && !x5) || (!x3 && !x6) || (!x5 && !x6);
+        L.v[i] = lut_word_for_keep((uint32_t)m0 | ((uint32_t)m1 << 1) | ((uint32_t)m2 << 2) | ((uint32_t)m3 << 3));
+    }
+    for (uint32_t k = 0; k < 16; ++k) L.v[64 + k] = lut_word_for_keep(k);
+    return L;
+}
+__constant__ GroupLut kGroupLut = make_group_lut();
+
+template <typename T> struct Packed16;
+template <> struct Packed16<__half> {
+    __device__ static uint32_t gt_mask(uint32_t a, uint32_t b) {
+        return __hgt2_mask(*reinterpret_cast<const __half2 *>(&a), *reinterpret_cast<const __half2 *>(&b));
+    }
+};
+template <> struct Packed16<__nv_bfloat16> {
+    __device__ static uint32_t gt_mask(uint32_t a, uint32_t b) {
+        return __hgt2_mask(*reinterpret_cast<const __nv_bfloat162 *>(&a), *reinterpret_cast<const __nv_bfloat162 *>(&b));
+    }
+};
+
+// lo = (x0, x1), hi = (x2, x3) as packed 16-bit values.  Returns the table word of the magnitude rule.
+template <typename T> __device__ __forceinline__ uint32_t mse_lookup(uint32_t lo, uint32_t hi, const uint32_t *lut) {
+    const uint32_t a = lo & 0x7FFF7FFFu, b = hi & 0x7FFF7FFFu;          // |x0|,|x1| and |x2|,|x3|
+    const uint32_t c1 = Packed16<T>::gt_mask(a, b);                       // x2 (low half), x5 (high half)
+    const uint32_t c2 = Packed16<T>::gt_mask(a, __byte_perm(b, b, 0x1032));  // x3, x4
+    const uint32_t c3 = Packed16<T>::gt_mask(__byte_perm(a, b, 0x5410), __byte_perm(a, b, 0x7632));  // x1, x6
+    const uint32_t t = (c3 & 0x00200001u) | (c1 & 0x00100002u) | (c2 & 0x00080004u);
+    return lut[(t | (t >> 16)) & 0x3Fu];
+}
+
+// ---------------------------------------------------------------------------------------------
 // row-major storage: groups of four run along the contiguous axis.
 // Tile = 32 rows x 32 metadata columns; 8 warps, lane = metadata column, warp w owns rows 4w..4w+3.
 // ---------------------------------------------------------------------------------------------
@@ -82,6 +135,12 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
     constexpr int RPI = (MODE == SP24_PRUNE_MVUE || CH * sizeof(TIn) >= 128) ? 1 : (CH * sizeof(TIn) >= 64 ? 2 : 4);
 
     __shared__ __align__(16) MetaT smeta[16][64];
+    constexpr bool PACKED = MODE != SP24_PRUNE_MVUE && std::is_same<TIn, TOut>::value && sizeof(TIn) == 2;
+    __shared__ uint32_t glut[PACKED ? 80 : 1];
+    if constexpr (PACKED) {
+        if (threadIdx.x < 80) glut[threadIdx.x] = kGroupLut.v[threadIdx.x];
+        __syncthreads();
+    }
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t ncols = P.k / CH;
@@ -107,6 +166,23 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
                 const int64_t r = r0 + rr;
                 TOut out[CH / 2];
                 uint32_t word = 0;
+                if constexpr (PACKED) {
+                    // one table lookup and one byte permute per group of four
+                    const uint32_t *raw = reinterpret_cast<const uint32_t *>(&in[j][0]);
+                    uint32_t *o32 = reinterpret_cast<uint32_t *>(&out[0]);
+#pragma unroll
+                    for (int g = 0; g < CH / 4; ++g) {
+                        uint32_t e;
+                        if constexpr (MODE == SP24_PRUNE_MASK) {
+                            const uint32_t mw = *reinterpret_cast<const uint32_t *>(&mk[j][4 * g]);
+                            e = glut[64 + (((__vcmpne4(mw, 0u) & 0x01010101u) * 0x01020408u) >> 24)];
+                        } else {
+                            e = mse_lookup<TIn>(raw[2 * g], raw[2 * g + 1], glut);
+                        }
+                        o32[g] = __byte_perm(raw[2 * g], raw[2 * g + 1], e >> 8);
+                        word |= (e & 0xFu) << (4 * g);
+                    }
+                } else
 #pragma unroll
                 for (int g2 = 0; g2 < CH / 8; ++g2) {
                     float u[4] = {0.f, 0.f, 0.f, 0.f};
