@@ -53,8 +53,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when it gave up (limit reached or another role raised the abort flag).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                          uint32_t limit = WAIT_LIMIT) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 0xFFu) == 0xFFu && *abort_flag) return false;
     }
@@ -717,6 +718,34 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
 #undef SP24_GO
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one CTA waits on a barrier that nothing ever signals, with a small
+// poll limit.  The wait must give up, record code 9 in *status and let the kernel return normally.
+// ------------------------------------------------------------------------------------------------
+namespace sp24 {
+namespace {
+__global__ void wait_selftest_kernel(int *status, uint32_t limit) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 9, limit);
+    __syncthreads();
+}
+}  // namespace
+}  // namespace sp24
+
+extern "C" int sp24_selftest_bounded_wait(int *status, int polls, void *stream) {
+    if (!status || polls <= 0 || polls > (1 << 20)) return SP24_ERR_ARG;
+    if (int rc = check_device()) return rc;
+    wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, (uint32_t)polls);
+    return launch_status();
+}
 
 // ------------------------------------------------------------------------------------------------
 // Sparse GEMM for callers that must not allocate

@@ -22,6 +22,8 @@ _ext.register_signature("sp24_spmm", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _v
 _ext.register_signature("sp24_spmm_noalloc", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i64, _vp, _i32, _i32,
                                               _i64, _vp, _i32, _vp, _vp])
 
+_ext.register_signature("sp24_selftest_bounded_wait", [_vp, _i32, _vp])
+
 _ACT = {None: 0, "none": 0, "relu": 1, "silu": 2}
 
 # Layout of the (tokens, features) result when the dense operand is token-major.  False (default): a

@@ -193,6 +193,14 @@ int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, con
               int64_t ld_out, const void *bias, int activation, int *status, void *stream);
 
 /*
+ * Self-test of the failure path of the GEMM kernels: launches one CTA that waits, with a limit of `polls`
+ * polls (1 .. 2^20), on a barrier nothing signals.  The wait gives up, *status (a device int the caller
+ * zeroed) becomes 9 and the kernel returns normally; the context stays usable.  No counterpart in the
+ * reference (its kernels have no bounded waits).
+ */
+int sp24_selftest_bounded_wait(int *status, int polls, void *stream);
+
+/*
  * The same GEMM for callers that cannot allocate device memory where they call it (a host that replays
  * a fixed memory plan, a loop that must stay clear of the allocator, a plug-in inside an application
  * that owns all GPU memory).  No counterpart in the reference.  It takes the metadata in the

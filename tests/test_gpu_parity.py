@@ -413,3 +413,57 @@ def test_config3_full_size_properties(S):
     assert same_bits(grad[sl].cpu(), O.masked_add(before[sl].cpu(), p[sl].cpu(), pm[sl].cpu(), 2e-4))
     ident = before + (p * 2e-4) * (~pm)
     assert torch.equal(grad, ident)
+
+
+# ------------------------------------------------------------------------------------------------
+# degenerate and special-value inputs
+# ------------------------------------------------------------------------------------------------
+def test_all_zero_and_all_equal_inputs(S):
+    z = torch.zeros(64, 128, dtype=torch.float16)
+    p, me = gpu_compress(z, torch.float16)
+    wp, wm = O.prune_compress(z, torch.float16)
+    assert same_bits(p, wp) and same_bits(me, wm) and bool((me == -4370).all())  # ties keep elements 2, 3
+    s, mk = S.mask_select(z.to(DEV))
+    assert torch.equal(mk.cpu(), O.transposable_mask(z))  # every score ties: the first pattern wins
+    blk = mk.cpu().view(16, 4, 32, 4).permute(0, 2, 1, 3)[0, 0]
+    assert blk.int().tolist() == [[1, 1, 0, 0], [1, 1, 0, 0], [0, 0, 1, 1], [0, 0, 1, 1]]
+    one = torch.full((64, 128), -3.0)
+    for fn, ofn in ((S.sparse24_triton, O.sparse24), (S.soft_threshold24_triton, O.soft_threshold24)):
+        a, b = fn(one.to(DEV))
+        wa, wb = ofn(one)
+        assert same_bits(a.cpu(), wa) and same_bits(b.cpu(), wb)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16])
+def test_transposable_special_values_match_flat_scan(S, dt):
+    """NaN, infinities, negative zeros, huge dynamic range (rounding ties) and small integers (exact ties):
+    the hierarchical search must return what the scan over all 90 patterns returns."""
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(128, 256, generator=g)
+    x[0:32] = torch.randint(0, 3, (32, 256), generator=g).float()              # many exact ties
+    x[32:64] = x[32:64].abs() * torch.tensor([1e-6, 1.0, 1e4])[torch.randint(0, 3, (32, 256), generator=g)]
+    x[64, 0] = float("nan"); x[68, 5] = float("inf"); x[72, 9] = float("-inf"); x[76:80, 16:20] = float("nan")
+    x[80:84, 20:24] = float("inf"); x[84, 24:28] = -0.0
+    x = x.to(dt)
+    for use_abs in (True, False):
+        s, mk = S.TransposableSparse(abs=use_abs)(x.to(DEV))
+        assert torch.equal(mk.cpu(), O.transposable_mask(x, abs=use_abs))
+
+
+def test_large_matrix_round_trip(S):
+    """8192 x 8192 bf16 (128 MiB) in both storage orders: structure and round trip."""
+    from sparse._semi_structured_conversions import sparse_semi_structured_to_dense
+    g = torch.Generator(device=DEV).manual_seed(5)
+    x = torch.randn(8192, 8192, device=DEV, generator=g).bfloat16()
+    a = S.to_sparse_semi_structured(x, dtype=torch.bfloat16)
+    b = S.to_sparse_semi_structured(x.t(), dtype=torch.bfloat16)      # column-major view, groups along rows of x
+    da = a.to_dense()
+    assert _two_per_group(da != 0) or bool(((da != 0).view(8192, 2048, 4).sum(-1) <= 2).all())
+    keep = (da != 0)
+    assert torch.equal(torch.where(keep, x, torch.zeros((), dtype=x.dtype, device=DEV)), da)
+    frac = float(da.float().abs().sum()) / float(x.float().abs().sum())
+    assert 0.73 < frac < 0.76   # keeping the two largest of four Gaussians keeps ~74.5 % of the L1 mass
+    db = sparse_semi_structured_to_dense(b.values().contiguous(), b.indices())
+    sl = x[:, :256].t().contiguous().cpu()                                       # first 256 rows of x^T
+    wp, wm = O.prune_compress(sl, torch.bfloat16)
+    assert same_bits(db[:256].cpu(), O.to_dense(wp, wm))

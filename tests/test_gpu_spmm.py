@@ -239,3 +239,24 @@ def test_gpt2_training_steps_tiny(S):
     assert res["loss_finite"] and res["tokens_per_step"] == 256 and res["last_loss"] < 8.0
     dense = train_gpt2.run(steps=3, warmup=1, mode="dense", batch=2, seq=128, vocab=512, layers=2, d=256, heads=4)
     assert dense["loss_finite"]
+
+
+def test_bounded_wait_reports_through_status_word(S):
+    """Failure detection without a GPU fault: a wait that nothing satisfies runs into its poll limit,
+    the kernel records a code in the status word and returns; the context keeps working."""
+    from sparse import _ext, spmm
+    status = spmm._status_word(torch.device(DEV))
+    status.zero_()
+    rc = _ext.lib().sp24_selftest_bounded_wait(status.data_ptr(), 4096, _ext.stream())
+    assert rc == 0
+    with pytest.raises(RuntimeError, match="gave up"):
+        spmm.check_status()
+    assert int(status.item()) == 0  # check_status clears the word
+    # the device is still usable and a real GEMM leaves the word clean
+    w = torch.randn(128, 128, device=DEV).half()
+    x = torch.randn(64, 128, device=DEV).half()
+    sp = S.to_sparse_semi_structured(w)
+    y = torch.mm(x, sp.t())
+    spmm.check_status()
+    assert float((y.float() - x.float() @ sp.to_dense().float().t()).abs().max()) < 0.1
+    assert _ext.lib().sp24_selftest_bounded_wait(None, 16, None) == -5
