@@ -3,10 +3,11 @@
 // The sparse operand is always the tensor-core "A" operand of tcgen05.mma.sp: compressed values are
 // staged in shared memory by TMA (128-byte swizzle), its metadata goes shared memory -> tensor memory
 // with tcgen05.cp, the dense operand B is staged by TMA, accumulators live in tensor memory and are read
-// back with tcgen05.ld by four epilogue warps.
+// back with tcgen05.ld by eight epilogue warps.
 //
-// Warp roles in a CTA of 192 threads: warp 0 = TMA producer (one elected lane), warp 1 = tensor-memory
-// allocation + MMA issue (one elected lane), warps 2..5 = epilogue (one TMEM lane quadrant each).
+// Warp roles in a CTA of 320 threads: warp 0 = TMA producer (one elected lane), warp 1 = tensor-memory
+// allocation + MMA issue (one elected lane), warps 2..9 = epilogue (two per TMEM lane quadrant, half of the
+// columns each).
 // One CTA computes one 128 x BN output tile; the K loop runs over stages of 128 bytes of compressed A
 // per row (logical K 128 for 16-bit types, 256 for 8-bit types) through a STAGES-deep mbarrier ring.
 //
@@ -130,6 +131,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr)
         : "memory");
 }
+// fp32 vector reduction into global memory (sm_90+), address 16-byte aligned
+__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets (all >> 4),
@@ -153,8 +158,9 @@ struct SpmmParams {
     int64_t k_atoms;        // number of 128-column metadata atoms per 128-row block (K padded up)
     int *status;
     uint32_t idesc;         // instruction descriptor without the metadata selector bits
-    int activation;         // 0 none, 1 relu, 2 silu
+    int activation;         // 0 none, 1 relu, 2 silu, 3 gelu (tanh form)
     unsigned long long *trace;  // optional timing trace of CTA 0 (debugging aid), else null
+    int k_splits;           // work units per tile along K (> 1 only for the accumulating fp32 output)
     int mblk_per_tile;      // 128-row blocks per tile: 2 (B staged once per 256 rows) or 1 (more, smaller tiles)
 };
 
@@ -170,6 +176,17 @@ template <> __device__ __forceinline__ float from_out<float>(float v) { return v
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == 1) return v > 0.f ? v : 0.f;
     if (act == 2) return v / (1.f + __expf(-v));
+    if (act == 3) {  // GELU, tanh form: v * sigmoid(2 * sqrt(2 / pi) * (v + 0.044715 v^3))
+        const float u = 1.5957691216f * (v + 0.044715f * v * v * v);
+        return v / (1.f + __expf(-u));
+    }
+    return v;
+}
+
+// The activation is compiled in only for launches that ask for one (template parameter ACT): the plain
+// epilogue carries no per-element tests.
+template <bool ACT> __device__ __forceinline__ float finish(float v, int act) {
+    if constexpr (ACT) return apply_act(v, act);
     return v;
 }
 
@@ -181,7 +198,7 @@ __device__ __forceinline__ unsigned long long globaltimer() {
 // trace layout: 3 roles x 256 slots of nanosecond timestamps, CTA 0 only
 #define SP24_TRACE(role, slot) do { if (P.trace && blockIdx.x == 0 && (slot) < 256) P.trace[(role) * 256 + (slot)] = globaltimer(); } while (0)
 
-__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Geometry shared by the kernel and its launcher.
 template <int BN, bool F8, bool TRANS_OUT, typename OutT> struct SpmmCfg {
@@ -193,7 +210,10 @@ template <int BN, bool F8, bool TRANS_OUT, typename OutT> struct SpmmCfg {
     // written out column by column
     static constexpr int STG_COLS = sizeof(OutT) == 4 ? 64 : BN;
     static constexpr int STG_ROW_BYTES = STG_COLS * (int)sizeof(OutT) + 16;
-    static constexpr int STG_BYTES = TRANS_OUT ? BM * STG_ROW_BYTES : 0;
+    // 16-bit outputs of wide tiles go through the staging buffer in both output orders (the second accumulator
+    // waits in registers, so the tensor memory is free again early); narrow tiles keep a third operand stage
+    static constexpr bool STAGED16 = sizeof(OutT) == 2 && (TRANS_OUT || BN > 128);
+    static constexpr int STG_BYTES = (TRANS_OUT || STAGED16) ? BM * STG_ROW_BYTES : 0;
     static constexpr int AVAIL = 227 * 1024 - 2048 - STG_BYTES;
     static constexpr int STAGES = AVAIL / STAGE_BYTES >= 4 ? 4 : AVAIL / STAGE_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 1024;
@@ -205,8 +225,8 @@ template <int BN, bool F8, bool TRANS_OUT, typename OutT> struct SpmmCfg {
 // columns), computed as two 128-row blocks that share every stage of B.  The operand ring keeps filling
 // across tile boundaries; the epilogue drains tensor memory into a staging buffer and releases each
 // accumulator as soon as it has been read, so the next tile's MMAs overlap the global stores.
-template <int BN, bool F8, bool A_MN, bool B_MN, bool TRANS_OUT, typename OutT>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, bool F8, bool A_MN, bool B_MN, bool TRANS_OUT, typename OutT, bool ACT>
+__global__ void __launch_bounds__(320, 1)
 spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, SpmmParams P) {
     using Cfg = SpmmCfg<BN, F8, TRANS_OUT, OutT>;
     constexpr int STAGES = Cfg::STAGES;
@@ -217,6 +237,8 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     constexpr uint32_t TMEM_COLS = 512;
     constexpr int E_COL0 = 2 * BN;            // metadata columns behind the two accumulators
     constexpr int E_SLOT = F8 ? 8 : 4;        // metadata columns of one row block and one stage
+    // 16-bit operands with a direct fp32 output: the accumulating form (D += A * B), the only one that splits K
+    constexpr bool ACCUM = !F8 && !TRANS_OUT && sizeof(OutT) == 4;
     static_assert(E_COL0 + 4 * E_SLOT <= 512, "tensor memory columns exhausted");
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "invalid tile width");
 
@@ -230,7 +252,12 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int n_tiles_n = (int)((P.n + BN - 1) / BN);
     const int n_mblocks = (int)(P.ms / BM);
     const int mpt = P.mblk_per_tile;
-    const int n_tiles = n_tiles_n * ((n_mblocks + mpt - 1) / mpt);
+    // tile index -> (row tile, column tile) with the row tile varying fastest: the CTAs running at one time
+    // cover whole rows of the transposed output (long contiguous runs in DRAM) and share their B tiles in L2
+    const int n_tiles_m = (n_mblocks + mpt - 1) / mpt;
+    const int n_tiles = n_tiles_n * n_tiles_m;
+    // work unit u = (tile u % n_tiles, K slice u / n_tiles); one slice unless the output accumulates
+    const int n_units = n_tiles * P.k_splits;
     const int logical_k_per_stage = F8 ? 256 : 128;
     const int k_iters = (int)((P.k + logical_k_per_stage - 1) / logical_k_per_stage);
 
@@ -244,8 +271,8 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             mbar_init(empty0 + 8 * s, 1);
         }
         mbar_init(tmem_full, 1);
-        mbar_init(tmem_empty0, 4);      // one arrival per epilogue warp
-        mbar_init(tmem_empty0 + 8, 4);
+        mbar_init(tmem_empty0, 8);      // one arrival per epilogue warp
+        mbar_init(tmem_empty0 + 8, 8);
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -262,12 +289,14 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (lane == 0) {
             int g = 0;  // stages issued so far (ring position across tiles)
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int mblk0 = (tile / n_tiles_n) * mpt;
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+                const int tile = unit % n_tiles, ks = unit / n_tiles;
+                const int it0 = (int)((int64_t)ks * k_iters / P.k_splits), it1 = (int)((int64_t)(ks + 1) * k_iters / P.k_splits);
+                const int mblk0 = (tile % n_tiles_m) * mpt;
                 const int n_mblk = (n_mblocks - mblk0) >= mpt ? mpt : 1;
-                const int64_t m0 = (int64_t)mblk0 * BM, n0 = (int64_t)(tile % n_tiles_n) * BN;
+                const int64_t m0 = (int64_t)mblk0 * BM, n0 = (int64_t)(tile / n_tiles_m) * BN;
                 const uint32_t stage_tx = (uint32_t)(n_mblk * (A_STAGE_BYTES + E_BYTES) + Cfg::B_BYTES);
-                for (int it = 0; it < k_iters; ++it, ++g) {
+                for (int it = it0; it < it1; ++it, ++g) {
                     const int s = g % STAGES;
                     const uint32_t ph = (g / STAGES) & 1;
                     if (g >= STAGES && !mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, P.status, 1)) { ok = false; break; }
@@ -323,10 +352,12 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             constexpr uint32_t B_LBO = B_MN ? 16384 : 16, B_KSTEP = B_MN ? 4096 : 64;
             int g = 0, tl = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tl) {
-                const int mblk0 = (tile / n_tiles_n) * mpt;
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ++tl) {
+                const int tile = unit % n_tiles, ks = unit / n_tiles;
+                const int it0 = (int)((int64_t)ks * k_iters / P.k_splits), it1 = (int)((int64_t)(ks + 1) * k_iters / P.k_splits);
+                const int mblk0 = (tile % n_tiles_m) * mpt;
                 const int n_mblk = (n_mblocks - mblk0) >= mpt ? mpt : 1;
-                for (int it = 0; it < k_iters && ok; ++it, ++g) {
+                for (int it = it0; it < it1 && ok; ++it, ++g) {
                     const int s = g % STAGES;
                     const uint32_t ph = (g / STAGES) & 1;
                     ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, P.status, 2);
@@ -336,7 +367,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     const uint32_t sb = sa + OFF_B;
                     const uint32_t se = sa + OFF_E;
                     for (int mb = 0; mb < n_mblk && ok; ++mb) {
-                        if (it == 0) {
+                        if (it == it0) {
                             // the epilogue of this CTA's previous tile must have drained this accumulator
                             ok = mbar_wait(tmem_empty0 + 8 * mb, (tl & 1) ^ 1, &abort_flag, P.status, 4);
                             if (!ok) break;
@@ -356,7 +387,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             // 16-bit types: the instruction takes the even column of a pair plus a 1-bit selector
                             const uint32_t e_addr = tmem_base + (F8 ? ecol : (ecol & ~1u));
                             const uint32_t idesc = P.idesc | (F8 ? 0u : (ecol & 1u));
-                            mma_sp<F8>(tmem_base + mb * BN, adesc, bdesc, e_addr, idesc, (it > 0 || j > 0) ? 1u : 0u);
+                            mma_sp<F8>(tmem_base + mb * BN, adesc, bdesc, e_addr, idesc, (it > it0 || j > 0) ? 1u : 0u);
                         }
                     }
                     tc_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
@@ -366,85 +397,188 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (warps 2..5)
-        // No early exit here: the four warps meet at named barrier 1, so after an abort they keep walking
-        // the tile list (waits return at once) and simply skip the work.
-        const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+        // ---------------------------------------------------------------- epilogue (warps 2..9)
+        // Two warps per tensor-memory lane quadrant, each taking half of the tile's columns.  No early exit
+        // here: the eight warps meet at named barrier 1, so after an abort they keep walking the tile list
+        // (waits return at once) and simply skip the work.
+        const int quad = warp & 3;          // TMEM lane quadrant this warp may read
+        const int half = (warp - 2) >> 2;   // which half of the columns
+        const int tid = (warp - 2) * 32 + lane;
         OutT *out = static_cast<OutT *>(P.out);
         OutT *stg = reinterpret_cast<OutT *>(smem + (size_t)STAGES * STAGE_BYTES);
         int tl = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tl) {
-            const int mblk0 = (tile / n_tiles_n) * mpt;
+        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++tl) {
+            const int tile = unit % n_tiles;
+            const int mblk0 = (tile % n_tiles_m) * mpt;
             const int n_mblk = (n_mblocks - mblk0) >= mpt ? mpt : 1;
-            const int64_t m0 = (int64_t)mblk0 * BM, n0 = (int64_t)(tile % n_tiles_n) * BN;
+            const int64_t m0 = (int64_t)mblk0 * BM, n0 = (int64_t)(tile / n_tiles_m) * BN;
             const bool ok = mbar_wait(tmem_full, tl & 1, &abort_flag, P.status, 3);
             tc_fence_after();
             if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl);
             const bool run = ok && !abort_flag;
-            for (int mb = 0; mb < n_mblk; ++mb) {
-                const int64_t mrow0 = m0 + mb * BM;
-                const int64_t m = mrow0 + quad * 32 + lane;
-                float bias = 0.f;
-                if (run && P.bias) bias = from_out<OutT>(static_cast<const OutT *>(P.bias)[m]);
-                const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + mb * BN;
-                if constexpr (TRANS_OUT) {
-                    constexpr int CHUNKS = BN / Cfg::STG_COLS;
-                    constexpr int PER = 16 / sizeof(OutT);              // elements per 16-byte piece
-                    uint8_t *stg_row = reinterpret_cast<uint8_t *>(stg) + (size_t)(quad * 32 + lane) * Cfg::STG_ROW_BYTES;
-#pragma unroll 1
-                    for (int ch = 0; ch < CHUNKS; ++ch) {
+            const int row_in_blk = quad * 32 + lane;
+            if constexpr (Cfg::STAGED16) {
+                // 16-bit output through the staging buffer.  Row r of the staging buffer holds one feature's BN values; its
+                // 16-byte pieces are permuted by (r / 8) % 4 so that the column-wise reads below (four groups
+                // of eight rows per warp instruction) fall on 32 different banks.
+                constexpr int HC = BN / 2;                  // columns per warp
+                constexpr int NREG = HC / 2;
+                uint8_t *stg_row = reinterpret_cast<uint8_t *>(stg) + (size_t)row_in_blk * Cfg::STG_ROW_BYTES;
+                const int swz = 2 * ((row_in_blk >> 3) & 3);
+                uint32_t held[NREG];                        // second accumulator, converted, two values per word
+                float bias0 = 0.f, bias1 = 0.f;
+                if (run && P.bias) {
+                    bias0 = from_out<OutT>(static_cast<const OutT *>(P.bias)[m0 + row_in_blk]);
+                    if (n_mblk == 2) bias1 = from_out<OutT>(static_cast<const OutT *>(P.bias)[m0 + BM + row_in_blk]);
+                }
+                const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + half * HC;
+                if (run) {
+#pragma unroll
+                    for (int c = 0; c < HC / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(acc + c * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            Vec<OutT, 8> o;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                o.v[i] = to_out<OutT>(finish<ACT>(__uint_as_float(v[q * 8 + i]) + bias0, P.activation));
+                            const int piece = (half * HC + c * 32) / 8 + q;
+                            *reinterpret_cast<uint4 *>(stg_row + ((piece ^ swz) << 4)) = *reinterpret_cast<const uint4 *>(&o);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty0);
+                if (n_mblk == 2) {
+                    if (run) {
+#pragma unroll
+                        for (int c = 0; c < HC / 32; ++c) {
+                            uint32_t v[32];
+                            tmem_ld32(acc + BN + c * 32, v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                Vec<OutT, 2> o;
+                                o.v[0] = to_out<OutT>(finish<ACT>(__uint_as_float(v[2 * i]) + bias1, P.activation));
+                                o.v[1] = to_out<OutT>(finish<ACT>(__uint_as_float(v[2 * i + 1]) + bias1, P.activation));
+                                held[c * 16 + i] = *reinterpret_cast<const uint32_t *>(&o);
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                }
+                // both accumulators are in shared memory / registers now: the next tile's MMAs may start
+                if (lane == 0) mbar_arrive(tmem_empty0 + 8);
+                if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 1);
+                for (int mb = 0; mb < n_mblk; ++mb) {
+                    if (mb == 1) {
                         if (run) {
-#pragma unroll 1
-                            for (int c = 0; c < Cfg::STG_COLS / 32; ++c) {
-                                uint32_t v[32];
-                                tmem_ld32(acc + ch * Cfg::STG_COLS + c * 32, v);
-                                tmem_ld_wait();
 #pragma unroll
-                                for (int q = 0; q < 32 / PER; ++q) {
-                                    Vec<OutT, PER> o;
+                            for (int q = 0; q < NREG / 4; ++q) {
+                                const int piece = (half * HC) / 8 + q;
+                                *reinterpret_cast<uint4 *>(stg_row + ((piece ^ swz) << 4)) =
+                                    make_uint4(held[4 * q], held[4 * q + 1], held[4 * q + 2], held[4 * q + 3]);
+                            }
+                        }
+                    }
+                    epilogue_bar_sync();
+                    if (run) {
+                        const int64_t mrow0 = m0 + mb * BM;
+                        const uint8_t *stg_b = reinterpret_cast<const uint8_t *>(stg);
+                        if constexpr (TRANS_OUT) {
+                            // thread = two adjacent output rows (dense columns n, n+1) x 8 consecutive features;
+                            // a warp instruction covers 8 row pairs x 4 feature groups: 64-byte runs per row
+                            for (int i = tid; i < (BN / 2) * (BM / 8); i += 256) {
+                                const int mg = (i & 3) + 4 * ((i >> 5) & 3), np = ((i >> 2) & 7) + 8 * (i >> 7);
+                                const int word = np ^ ((i & 3) << 3);   // rows mg*8..mg*8+7 share (r / 8) % 4 = mg % 4
+                                uint32_t w[8];
 #pragma unroll
-                                    for (int i = 0; i < PER; ++i)
-                                        o.v[i] = to_out<OutT>(apply_act(__uint_as_float(v[q * PER + i]) + bias, P.activation));
-                                    *reinterpret_cast<uint4 *>(stg_row + (c * 32 + q * PER) * sizeof(OutT)) =
-                                        *reinterpret_cast<const uint4 *>(&o);
+                                for (int j = 0; j < 8; ++j)
+                                    w[j] = *reinterpret_cast<const uint32_t *>(stg_b + (size_t)(mg * 8 + j) * Cfg::STG_ROW_BYTES + word * 4);
+                                uint4 lo, hi;
+                                lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
+                                lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
+                                lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
+                                lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
+                                const int64_t nrow = n0 + 2 * np;
+                                OutT *dst = out + nrow * P.ld_out + mrow0 + mg * 8;
+                                if (nrow < P.n) *reinterpret_cast<uint4 *>(dst) = lo;
+                                if (nrow + 1 < P.n) *reinterpret_cast<uint4 *>(dst + P.ld_out) = hi;
+                            }
+                        } else {
+                            // thread = 8 consecutive columns of one row; a warp writes 512 contiguous bytes
+                            constexpr int PIECES = BN / 8;
+                            for (int i = tid; i < PIECES * BM; i += 256) {
+                                const int row = i / PIECES, piece = i % PIECES;
+                                const uint4 v = *reinterpret_cast<const uint4 *>(
+                                    stg_b + (size_t)row * Cfg::STG_ROW_BYTES + ((piece ^ (2 * ((row >> 3) & 3))) << 4));
+                                const int64_t nb = n0 + piece * 8;
+                                OutT *dst = out + (mrow0 + row) * P.ld_out + nb;
+                                if (nb + 8 <= P.n) {
+                                    *reinterpret_cast<uint4 *>(dst) = v;
+                                } else {
+                                    const OutT *e = reinterpret_cast<const OutT *>(&v);
+                                    for (int j = 0; j < 8; ++j)
+                                        if (nb + j < P.n) dst[j] = e[j];
                                 }
                             }
                         }
-                        if (ch == CHUNKS - 1) {
-                            // this accumulator has been read completely: hand it back to the MMA warp
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(tmem_empty0 + 8 * mb);
-                            if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 1 + mb);
-                        }
-                        epilogue_bar_sync();
-                        if (run) {
-                            // thread = two adjacent output rows (dense columns n, n+1) x 8 consecutive features
-                            const int tid = (warp - 2) * 32 + lane;
-                            const int64_t nbase = n0 + ch * Cfg::STG_COLS;
-                            const uint8_t *stg_b = reinterpret_cast<const uint8_t *>(stg);
-                            if constexpr (sizeof(OutT) == 2) {
-                                // a warp instruction covers 8 row pairs x 4 feature groups: 64-byte runs per row
-                                for (int i = tid; i < (Cfg::STG_COLS / 2) * (BM / 8); i += 128) {
-                                    const int mg = (i & 3) + 4 * ((i >> 5) & 3), np = ((i >> 2) & 7) + 8 * (i >> 7);
-                                    uint32_t w[8];
+                    }
+                    epilogue_bar_sync();
+                }
+            } else {
+                for (int mb = 0; mb < n_mblk; ++mb) {
+                    const int64_t mrow0 = m0 + mb * BM;
+                    const int64_t m = mrow0 + row_in_blk;
+                    float bias = 0.f;
+                    if (run && P.bias) bias = from_out<OutT>(static_cast<const OutT *>(P.bias)[m]);
+                    const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + mb * BN;
+                    if constexpr (TRANS_OUT) {
+                        // 4-byte transposed output, STG_COLS columns at a time; each warp copies its half of a chunk
+                        constexpr int CHUNKS = BN / Cfg::STG_COLS;
+                        constexpr int HC = Cfg::STG_COLS / 2;
+                        static_assert(HC % 32 == 0, "a warp reads whole 32-column pieces");
+                        uint8_t *stg_row = reinterpret_cast<uint8_t *>(stg) + (size_t)row_in_blk * Cfg::STG_ROW_BYTES;
+#pragma unroll 1
+                        for (int ch = 0; ch < CHUNKS; ++ch) {
+                            if (run) {
+#pragma unroll 1
+                                for (int c = 0; c < HC / 32; ++c) {
+                                    uint32_t v[32];
+                                    const int col = half * HC + c * 32;
+                                    tmem_ld32(acc + ch * Cfg::STG_COLS + col, v);
+                                    tmem_ld_wait();
 #pragma unroll
-                                    for (int j = 0; j < 8; ++j)
-                                        w[j] = *reinterpret_cast<const uint32_t *>(stg_b + (size_t)(mg * 8 + j) * Cfg::STG_ROW_BYTES + np * 4);
-                                    uint4 lo, hi;
-                                    lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
-                                    lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
-                                    lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
-                                    lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
-                                    const int64_t nrow = nbase + 2 * np;
-                                    OutT *dst = out + nrow * P.ld_out + mrow0 + mg * 8;
-                                    if (nrow < P.n) *reinterpret_cast<uint4 *>(dst) = lo;
-                                    if (nrow + 1 < P.n) *reinterpret_cast<uint4 *>(dst + P.ld_out) = hi;
+                                    for (int q = 0; q < 8; ++q) {
+                                        float4 o;
+                                        o.x = finish<ACT>(__uint_as_float(v[q * 4 + 0]) + bias, P.activation);
+                                        o.y = finish<ACT>(__uint_as_float(v[q * 4 + 1]) + bias, P.activation);
+                                        o.z = finish<ACT>(__uint_as_float(v[q * 4 + 2]) + bias, P.activation);
+                                        o.w = finish<ACT>(__uint_as_float(v[q * 4 + 3]) + bias, P.activation);
+                                        *reinterpret_cast<float4 *>(stg_row + (col + q * 4) * 4) = o;
+                                    }
                                 }
-                            } else {
-                                // 4-byte outputs: thread = one output row x 4 consecutive features
-                                for (int i = tid; i < Cfg::STG_COLS * (BM / 4); i += 128) {
-                                    const int nn = i % Cfg::STG_COLS, mg = i / Cfg::STG_COLS;
+                            }
+                            if (ch == CHUNKS - 1) {
+                                // this accumulator has been read completely: hand it back to the MMA warp
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(tmem_empty0 + 8 * mb);
+                                if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 1 + mb);
+                            }
+                            epilogue_bar_sync();
+                            if (run) {
+                                // thread = one output row x 4 consecutive features; lane pairs cover 8 features of
+                                // the same row, so every warp instruction writes whole 32-byte sectors
+                                const int64_t nbase = n0 + ch * Cfg::STG_COLS;
+                                const uint8_t *stg_b = reinterpret_cast<const uint8_t *>(stg);
+                                for (int i = tid; i < Cfg::STG_COLS * (BM / 4); i += 256) {
+                                    const int pr = i >> 1;
+                                    const int nn = pr % Cfg::STG_COLS, mg = 2 * (pr / Cfg::STG_COLS) + (i & 1);
                                     uint4 o;
                                     o.x = *reinterpret_cast<const uint32_t *>(stg_b + (size_t)(mg * 4 + 0) * Cfg::STG_ROW_BYTES + nn * 4);
                                     o.y = *reinterpret_cast<const uint32_t *>(stg_b + (size_t)(mg * 4 + 1) * Cfg::STG_ROW_BYTES + nn * 4);
@@ -454,46 +588,59 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                         *reinterpret_cast<uint4 *>(out + (nbase + nn) * P.ld_out + mrow0 + mg * 4) = o;
                                 }
                             }
+                            epilogue_bar_sync();
                         }
-                        epilogue_bar_sync();
-                    }
-                } else {
-                    if (run) {
+                    } else {
+                        constexpr int HC = BN / 2;
+                        if (run) {
 #pragma unroll 1
-                        for (int c = 0; c < BN / 32; ++c) {
-                            uint32_t v[32];
-                            tmem_ld32(acc + c * 32, v);
-                            tmem_ld_wait();
-                            const int64_t nb = n0 + c * 32;
-                            OutT *row = out + m * P.ld_out + nb;
-                            if (nb + 32 <= P.n) {
-                                constexpr int PER = 16 / sizeof(OutT);
+                            for (int c = 0; c < HC / 32; ++c) {
+                                uint32_t v[32];
+                                const int col = half * HC + c * 32;
+                                tmem_ld32(acc + col, v);
+                                tmem_ld_wait();
+                                const int64_t nb = n0 + col;
+                                OutT *row = out + m * P.ld_out + nb;
+                                if constexpr (ACCUM) {
+                                    // D += partial product: fp32 reductions in L2, 16 bytes each, no return value
+                                    if (nb + 32 <= P.n) {
 #pragma unroll
-                                for (int q = 0; q < 32 / PER; ++q) {
-                                    Vec<OutT, PER> o;
+                                        for (int q = 0; q < 8; ++q)
+                                            red_add_v4(reinterpret_cast<float *>(row) + q * 4, __uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]),
+                                                       __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
+                                    } else {
+                                        for (int i = 0; i < 32; ++i)
+                                            if (nb + i < P.n) atomicAdd(reinterpret_cast<float *>(row) + i, __uint_as_float(v[i]));
+                                    }
+                                } else if (nb + 32 <= P.n) {
+                                    constexpr int PER = 16 / sizeof(OutT);
 #pragma unroll
-                                    for (int i = 0; i < PER; ++i)
-                                        o.v[i] = to_out<OutT>(apply_act(__uint_as_float(v[q * PER + i]) + bias, P.activation));
-                                    store_vec<OutT, PER>(row + q * PER, o);
+                                    for (int q = 0; q < 32 / PER; ++q) {
+                                        Vec<OutT, PER> o;
+#pragma unroll
+                                        for (int i = 0; i < PER; ++i)
+                                            o.v[i] = to_out<OutT>(finish<ACT>(__uint_as_float(v[q * PER + i]) + bias, P.activation));
+                                        store_vec<OutT, PER>(row + q * PER, o);
+                                    }
+                                } else {
+                                    for (int i = 0; i < 32; ++i)
+                                        if (nb + i < P.n)
+                                            row[i] = to_out<OutT>(finish<ACT>(__uint_as_float(v[i]) + bias, P.activation));
                                 }
-                            } else {
-                                for (int i = 0; i < 32; ++i)
-                                    if (nb + i < P.n)
-                                        row[i] = to_out<OutT>(apply_act(__uint_as_float(v[i]) + bias, P.activation));
                             }
                         }
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tmem_empty0 + 8 * mb);
                     }
-                    tc_fence_before();
+                }
+                if (n_mblk == 1) {
+                    // keep the second accumulator's barrier in step with the tile count
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(tmem_empty0 + 8 * mb);
+                    if (lane == 0) mbar_arrive(tmem_empty0 + 8);
                 }
             }
             if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 3);
-            if (n_mblk == 1) {
-                // keep the second accumulator's barrier in step with the tile count
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_empty0 + 8);
-            }
         }
         tc_fence_before();
     }
@@ -591,19 +738,21 @@ int sm_count_cached() {
 template <int BN, bool F8, bool A_MN, bool B_MN, bool TRANS, typename OutT>
 int launch_spmm(const CUtensorMap &ma, const CUtensorMap &mb, SpmmParams P, cudaStream_t st) {
     using Cfg = SpmmCfg<BN, F8, TRANS, OutT>;
-    auto kern = spmm_kernel<BN, F8, A_MN, B_MN, TRANS, OutT>;
-    static bool attr_set[64];
+    auto kern = P.activation ? spmm_kernel<BN, F8, A_MN, B_MN, TRANS, OutT, true>
+                             : spmm_kernel<BN, F8, A_MN, B_MN, TRANS, OutT, false>;
+    static bool attr_set[64][2];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    const int which = P.activation ? 1 : 0;
+    if (dev >= 0 && dev < 64 && !attr_set[dev][which]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
             return SP24_ERR_CUDA;
-        attr_set[dev] = true;
+        attr_set[dev][which] = true;
     }
     P.idesc |= (uint32_t)(BN >> 3) << 17;
-    const int64_t tiles = ((P.n + BN - 1) / BN) * ((P.ms / BM + P.mblk_per_tile - 1) / P.mblk_per_tile);
+    const int64_t tiles = ((P.n + BN - 1) / BN) * ((P.ms / BM + P.mblk_per_tile - 1) / P.mblk_per_tile) * P.k_splits;
     const int sms = sm_count_cached();
-    kern<<<(unsigned)(tiles < sms ? tiles : sms), 192, Cfg::SMEM, st>>>(ma, mb, P);
+    kern<<<(unsigned)(tiles < sms ? tiles : sms), 320, Cfg::SMEM, st>>>(ma, mb, P);
     return launch_status();
 }
 
@@ -670,9 +819,12 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     if (!f8 && dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
     if (f8 ? out_dtype != SP24_F32 : out_dtype != dtype) return SP24_ERR_DTYPE;
     if (f8 && (a_mn_major || b_mn_major)) return SP24_ERR_DTYPE;  // 8-bit operands are K-major only
-    if (activation < 0 || activation > 2) return SP24_ERR_ARG;
+    if (activation < 0 || activation > 3) return SP24_ERR_ARG;
     const int esz = f8 ? 1 : 2;
-    if (ms <= 0 || n <= 0 || k <= 0 || ms % 128 || k % (f8 ? 128 : 64) || n % 8) return SP24_ERR_SHAPE;
+    if (ms <= 0 || n <= 0 || k <= 0 || ms % 128 || k % (f8 ? 128 : 64)) return SP24_ERR_SHAPE;
+    // n is free when B is stored (n, k) and the output (n, ms): rows past n are zero-filled on load and skipped
+    // on store.  The other layouts have n as a contiguous extent, which must keep 16-byte row pitches.
+    if ((b_mn_major || !trans_out) && n % 8) return SP24_ERR_SHAPE;
     const int64_t a_inner = a_mn_major ? ms : k / 2, b_inner = b_mn_major ? n : k, o_inner = trans_out ? ms : n;
     if (ld_a < a_inner || (ld_a * esz) % 16 || ld_b < b_inner || (ld_b * esz) % 16 || ld_out < o_inner) return SP24_ERR_STRIDE;
     if ((ld_out * dtype_size(out_dtype)) % 16) return SP24_ERR_STRIDE;
@@ -689,6 +841,7 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     P.e_tc = e_tc; P.out = out; P.bias = bias; P.ms = ms; P.n = n; P.k = k; P.ld_out = ld_out;
     P.k_atoms = (k + 127) / 128; P.status = status; P.activation = activation;
     P.trace = nullptr;
+    P.k_splits = 1;
     if (const char *env = getenv("SP24_SPMM_TRACE_PTR")) P.trace = reinterpret_cast<unsigned long long *>(strtoull(env, nullptr, 0));
     const uint32_t fmt = (dtype == SP24_BF16 || dtype == SP24_E5M2) ? 1u : 0u;
     // sparse flag, fp32 accumulate, operand formats, operand majors, M = 128 (N is added by the launcher)
@@ -797,4 +950,54 @@ extern "C" int sp24_spmm_noalloc(const void *a_packed, int dtype, int a_mn_major
     if (int rc = sp24_meta_to_tc(meta, f8 ? 4 : 2, ms, k, scratch, stream)) return rc;
     return sp24_spmm(a_packed, dtype, a_mn_major, ld_a, scratch, ms, k, b, b_mn_major, ld_b, n, out, out_dtype, trans_out,
                      ld_out, bias, activation, status, stream);
+}
+
+
+// D (ms x n, fp32, row-major) += A_sparse (ms x k) * B (k x n, stored row-major): the weight-gradient form.
+// K is cut into slices so that tiles x slices fills the SMs; every slice adds its partial product with fp32
+// reductions, so the caller zeroes D for a plain product or passes a gradient buffer to accumulate into.
+extern "C" int sp24_spmm_accumulate_f32(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc,
+                                        int64_t ms, int64_t k, const void *b, int64_t ld_b, int64_t n, float *out,
+                                        int64_t ld_out, int k_splits, int *status, void *stream) {
+    if (!a_packed || !e_tc || !b || !out || !status) return SP24_ERR_ARG;
+    if (dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
+    if (ms <= 0 || n <= 0 || k <= 0 || ms % 128 || k % 64 || n % 8) return SP24_ERR_SHAPE;
+    if (k_splits < 0) return SP24_ERR_ARG;
+    const int64_t a_inner = a_mn_major ? ms : k / 2;
+    if (ld_a < a_inner || (ld_a * 2) % 16 || ld_b < n || (ld_b * 2) % 16 || ld_out < n || (ld_out * 4) % 16) return SP24_ERR_STRIDE;
+    if (!aligned16(a_packed) || !aligned16(e_tc) || !aligned16(b) || !aligned16(out)) return SP24_ERR_ALIGN;
+    if (int rc = check_device()) return rc;
+
+    CUtensorMap map_a, map_b;
+    int rc;
+    if (!a_mn_major) rc = make_map(&map_a, a_packed, dtype, ms, k / 2, ld_a, 64, 128);
+    else rc = make_map(&map_a, a_packed, dtype, k / 2, ms, ld_a, 64, 64);
+    if (rc) return rc;
+    rc = make_map(&map_b, b, dtype, k, n, ld_b, 64, 128);
+    if (rc) return rc;
+
+    SpmmParams P{};
+    P.e_tc = e_tc; P.out = out; P.bias = nullptr; P.ms = ms; P.n = n; P.k = k; P.ld_out = ld_out;
+    P.k_atoms = (k + 127) / 128; P.status = status; P.activation = 0; P.trace = nullptr;
+    const uint32_t fmt = dtype == SP24_BF16 ? 1u : 0u;
+    P.idesc = (1u << 2) | (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) | (1u << 16) |
+              ((uint32_t)(BM >> 4) << 24);
+    // widest tile (least operand traffic per output), then as many K slices as idle SMs allow
+    const int sms = sm_count_cached();
+    const bool wide = n >= 192;
+    const int bn = wide ? 192 : 128;
+    P.mblk_per_tile = ms >= 256 ? 2 : 1;
+    const int64_t tiles = ((n + bn - 1) / bn) * ((ms / BM + P.mblk_per_tile - 1) / P.mblk_per_tile);
+    const int64_t k_iters = (k + 127) / 128;
+    int64_t splits = k_splits ? k_splits : sms / tiles;
+    if (splits < 1) splits = 1;
+    if (splits > k_iters) splits = k_iters;
+    P.k_splits = (int)splits;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // fp16 and bf16 operands share these kernels: the element type only enters through the tensor maps and the
+    // instruction descriptor
+    if (a_mn_major) return wide ? launch_spmm<192, false, true, true, false, float>(map_a, map_b, P, st)
+                                : launch_spmm<128, false, true, true, false, float>(map_a, map_b, P, st);
+    return wide ? launch_spmm<192, false, false, true, false, float>(map_a, map_b, P, st)
+                : launch_spmm<128, false, false, true, false, float>(map_a, map_b, P, st);
 }

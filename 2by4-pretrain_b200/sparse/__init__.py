@@ -8,7 +8,9 @@ from .triton_ops import MVUE24_approx_triton, sparse24_triton, soft_threshold24_
 from .decay import masked_add_
 from .transposable_semi_structured import TransposableSparse, select_and_compress
 from .semi_structured import to_sparse_semi_structured, SparseSemiStructuredTensor
-from .sparse_ops import MyLinear, SparseLinear, SparseLinearTranspose, sparse_linear_transpose
+from .sparse_ops import (MyLinear, SparseLinear, SparseLinearTranspose, sparse_linear_transpose, sparse_state,
+                         load_sparse_state)
+from .sste import SoftThreshold, SoftThresholdLinear
 
 mask_select = TransposableSparse()
 
@@ -26,4 +28,8 @@ __all__ = [
     'select_and_compress',
     'to_sparse_semi_structured',
     'SparseSemiStructuredTensor',
+    'SoftThreshold',
+    'SoftThresholdLinear',
+    'sparse_state',
+    'load_sparse_state',
 ]

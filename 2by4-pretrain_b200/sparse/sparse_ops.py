@@ -14,7 +14,7 @@ from torch.amp import custom_fwd, custom_bwd
 from .semi_structured import SparseSemiStructuredTensor, to_sparse_semi_structured
 from .transposable_semi_structured import TransposableSparse, select_and_compress
 from .triton_ops import MVUE24_approx_triton
-from .spmm import sparse_linear as _spmm
+from .spmm import sparse_linear as _spmm, sparse_mm_accumulate_ as _spmm_acc
 
 
 class my_linear(autograd.Function):
@@ -138,6 +138,7 @@ class _fst_linear(autograd.Function):
         ctx.save_for_backward(x, pt, mt)
         ctx.shape = input.shape
         ctx.has_bias = bias is not None
+        ctx.fp32_grad = weight.dtype == torch.float32 and x.shape[1] % 8 == 0
         output = _spmm(x, pw, mw)
         output = output.view(*input.shape[:-1], -1)
         return output if b is None else output + b
@@ -155,7 +156,12 @@ class _fst_linear(autograd.Function):
             grad_input = _spmm(g, pt, mt).view(ctx.shape)
         if ctx.needs_input_grad[1]:
             gs = to_sparse_semi_structured(g.t(), MVUE24=True, dtype=g.dtype)
-            grad_weight = _spmm(x.t(), gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass).t()
+            if ctx.fp32_grad:
+                # split-K GEMM with fp32 accumulation: the gradient arrives in the dtype of the master weight
+                grad_weight = torch.zeros((g.shape[1], x.shape[1]), dtype=torch.float32, device=g.device)
+                _spmm_acc(grad_weight, gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass, x)
+            else:
+                grad_weight = _spmm(x.t(), gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass).t()
         if ctx.has_bias and ctx.needs_input_grad[6]:
             grad_bias = g.sum(0)
         return grad_input, grad_weight, None, None, None, None, grad_bias
@@ -222,6 +228,8 @@ class SparseLinearTranspose(nn.Linear):
                 w.mask = w.mask.to(device=w.device)
             if w.cnt == 0:
                 self._refresh(reselect=(w.counter % w.freq == 0))
+            elif w.compressed is None:   # state restored in the middle of an accumulation window
+                self._refresh(reselect=False)
             pw, mw, pt, mt = w.compressed
             x = _fst_linear.apply(x, w, pw, mw, pt, mt, self.bias)
 
@@ -231,3 +239,31 @@ class SparseLinearTranspose(nn.Linear):
             w.step += 1
             w.cnt += 1
         return x
+
+
+def sparse_state(model: nn.Module) -> dict:
+    """Training state the FST layers keep outside ``state_dict()``: per sparse weight its mask, counters,
+    refresh period and mode, keyed by parameter name.  Save it next to the checkpoint."""
+    out = {}
+    for name, p in model.named_parameters():
+        if hasattr(p, 'mask'):
+            out[name] = {'mask': p.mask.detach().cpu(), 'cnt': p.cnt, 'counter': p.counter, 'step': p.step,
+                         'freq': p.freq, 'mode': p.mode}
+    return out
+
+
+def load_sparse_state(model: nn.Module, state: dict) -> None:
+    """Inverse of ``sparse_state``; call after ``load_state_dict``.  The compressed copies are dropped,
+    so the next forward pass of a layer in the middle of an accumulation window (``cnt`` != 0)
+    rebuilds them from the restored weight under the restored mask."""
+    params = dict(model.named_parameters())
+    for name, st in state.items():
+        if name not in params or not hasattr(params[name], 'mask'):
+            raise RuntimeError(f"load_sparse_state: {name} is not a sparse weight of this model")
+        p = params[name]
+        if tuple(st['mask'].shape) != tuple(p.shape):
+            raise RuntimeError(f"load_sparse_state: mask of {name} has shape {tuple(st['mask'].shape)}, expected {tuple(p.shape)}")
+        p.mask = st['mask'].to(device=p.device, dtype=torch.bool)
+        p.cnt, p.counter, p.step, p.freq, p.mode = st['cnt'], st['counter'], st['step'], st['freq'], st['mode']
+        p.compressed = None
+        p.weight_sparse = p.weight_sparse_T = None

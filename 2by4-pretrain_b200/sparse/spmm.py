@@ -23,8 +23,10 @@ _ext.register_signature("sp24_spmm_noalloc", [_vp, _i32, _i32, _i64, _vp, _i64, 
                                               _i64, _vp, _i32, _vp, _vp])
 
 _ext.register_signature("sp24_selftest_bounded_wait", [_vp, _i32, _vp])
+_ext.register_signature("sp24_spmm_accumulate_f32", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64,
+                                                     _i32, _vp, _vp])
 
-_ACT = {None: 0, "none": 0, "relu": 1, "silu": 2}
+_ACT = {None: 0, "none": 0, "relu": 1, "silu": 2, "gelu": 3}  # gelu (tanh form) is an addition to the reference's set
 
 # Layout of the (tokens, features) result when the dense operand is token-major.  False (default): a
 # contiguous (tokens, features) tensor, written by a transposing epilogue.  True: what the reference
@@ -129,3 +131,35 @@ def sparse_linear(input, weight, meta, bias=None, activation=None):
     res = out.t() if as_view else out
     sizes[-1] = ms
     return res.reshape(sizes) if len(sizes) != 2 else res
+
+
+def sparse_mm_accumulate_(out: torch.Tensor, weight: torch.Tensor, meta: torch.Tensor, dense: torch.Tensor,
+                          k_splits: int = 0) -> torch.Tensor:
+    """out (ms, n) fp32 += sparse (ms, k) @ dense (k, n).  ``weight`` / ``meta`` are the compressed sparse
+    operand (row- or column-major packed values), ``dense`` is row-major.  K is split over idle SMs and the
+    partial products are added with fp32 reductions, so ``out`` may already hold a gradient to add to."""
+    _ext.require_cuda(out, weight, meta, dense)
+    if out.dtype != torch.float32 or out.dim() != 2 or out.stride(1) != 1:
+        raise RuntimeError("sparse_mm_accumulate_: out must be a row-major fp32 matrix")
+    if weight.dtype not in (torch.float16, torch.bfloat16) or dense.dtype != weight.dtype:
+        raise RuntimeError(f"sparse_mm_accumulate_: expected matching fp16 / bf16 operands, got {weight.dtype} and {dense.dtype}")
+    ms, kh = weight.shape
+    k = 2 * kh
+    if dense.dim() != 2 or dense.shape[0] != k:
+        raise RuntimeError(f"sparse_mm_accumulate_: dense operand must have {k} rows, got {tuple(dense.shape)}")
+    n = dense.shape[1]
+    if tuple(out.shape) != (ms, n):
+        raise RuntimeError(f"sparse_mm_accumulate_: out must be {(ms, n)}, got {tuple(out.shape)}")
+    lay_a = _ext.layout_of(weight)
+    if lay_a is None:
+        raise RuntimeError("sparse_mm_accumulate_: invalid strides for the packed values")
+    a_mn, ld_a = lay_a
+    if dense.stride(1) != 1 or dense.data_ptr() % 16 or (dense.stride(0) * dense.element_size()) % 16:
+        dense = dense.contiguous()
+    e_tc = tc_metadata(meta, ms, k)
+    status = _status_word(weight.device)
+    rc = _ext.lib().sp24_spmm_accumulate_f32(weight.data_ptr(), _ext.dt(weight.dtype), a_mn, ld_a, e_tc.data_ptr(), ms, k,
+                                             dense.data_ptr(), dense.stride(0), n, out.data_ptr(), out.stride(0),
+                                             k_splits, status.data_ptr(), _ext.stream())
+    _ext.check(rc, "sp24_spmm_accumulate_f32")
+    return out

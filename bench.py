@@ -308,6 +308,10 @@ def main():
         extra = side_measurements(dev)
         spmm_extra = spmm_measurements(dev)
 
+    sharded = None
+    if world > 1 and not args.no_extra:
+        sharded = sharded_spmm_measurements(dev, rank, world)
+
     gpt2 = None
     if not args.no_extra:
         gpt2 = gpt2_measurements(world)
@@ -332,8 +336,12 @@ def main():
         if not args.no_cpu and world == 1:
             v, cores, sample, _ = cpu_arm()
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+            if not args.no_extra:
+                line["cpu_side"] = cpu_side_measurements()
         if extra:
             line["kernels"] = extra
+        if sharded:
+            line["spmm_cfg4_column_parallel"] = sharded
         if spmm_extra:
             line["spmm_cfg4"] = spmm_extra
         if gpt2:
@@ -462,16 +470,96 @@ def gpt2_measurements(world):
     import train_gpt2
     out = {}
     try:
-        sp = train_gpt2.run(steps=8, warmup=3, mode="sparse")
-        de = train_gpt2.run(steps=8, warmup=3, mode="dense")
+        sp = train_gpt2.run(steps=50, warmup=3, mode="sparse")
+        de = train_gpt2.run(steps=20, warmup=3, mode="dense")
         out = {"sparse_tokens_per_s": sp["tokens_per_s"], "sparse_ms_per_step": sp["ms_per_step"],
                "dense_tokens_per_s": de["tokens_per_s"], "dense_ms_per_step": de["ms_per_step"],
                "sparse_over_dense": sp["tokens_per_s"] / de["tokens_per_s"], "tokens_per_step": sp["tokens_per_step"],
                "loss_finite": sp["loss_finite"], "n_gpus": world,
-               "note": "timed steps lie between mask refreshes (every 40 optimizer steps)"}
+               "host_enqueue_ms_per_step": sp["host_enqueue_ms_per_step"],
+               "note": "50 timed sparse steps, mean; they include the mask refresh at optimizer step 40 (every 40 steps)"}
     except Exception as exc:  # the headline line must still be printed
         out = {"error": repr(exc)[:300]}
     return out
+
+
+def sharded_spmm_measurements(dev, rank, world):
+    """cfg4 forward GEMM split by blocks of output features over the ranks (X replicated, every rank holds its
+    rows of W compressed as its own matrix): whole-job dense-equivalent TFLOP/s without and with the
+    all-gather of Y, device time, max over ranks."""
+    import torch.distributed as dist
+    from sparse.sharded import ColumnParallelSparseWeight, all_gather_columns
+    T, K, N = 16384, 768, 3072
+    g = torch.Generator(device="cpu").manual_seed(8)
+    w = (torch.randn(N, K, generator=g) * 0.02).to(dev)
+    xs = [torch.randn(T, K, device=dev).half() for _ in range(3)]
+    sh = ColumnParallelSparseWeight(w, rank=rank, world=world)
+
+    def timed(fn, reps=10):
+        for i in range(3):
+            fn(i)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_local = timed(lambda i: sh.forward_local(xs[i % 3]))
+    ms_gather = timed(lambda i: all_gather_columns(sh.forward_local(xs[i % 3]), N, world))
+    flops = 2.0 * T * K * N
+    return {"rows_of_W_per_rank": sh.r1 - sh.r0, "fwd_ms": ms_local, "fwd_TFLOPs_dense_equiv": flops / ms_local / 1e9,
+            "fwd_plus_allgather_ms": ms_gather, "fwd_plus_allgather_TFLOPs_dense_equiv": flops / ms_gather / 1e9,
+            "n_gpus": world, "scaling": "strong (one GEMM split over the ranks)"}
+
+
+def cpu_side_measurements():
+    """The other operations of the path on the host cores (CPU restatements of the reference's own CPU
+    formulations), one warm-up and the median of three runs each; sizes reduced where stated."""
+    from oracle import sp24_oracle as O
+    res = {"threads": torch.get_num_threads()}
+
+    def med(fn, reps=3):
+        fn()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return statistics.median(ts)
+
+    g = torch.Generator().manual_seed(3)
+    m, k = 2048, 4096                                   # a quarter of cfg3's rows
+    G = (torch.randn(m, k, generator=g) * 1e-3).bfloat16()
+    n = m * k
+    t = med(lambda: O.prune_compress(G, torch.bfloat16))
+    res["magnitude compress bf16 2048x4096"] = {"ms": t * 1e3, "GB/s": n * 3.125 / t / 1e9}
+    packed, meta = O.prune_compress(G, torch.bfloat16)[:2]
+    t = med(lambda: O.to_dense(packed, meta))
+    res["to_dense bf16 2048x4096"] = {"ms": t * 1e3, "GB/s": n * 3.125 / t / 1e9}
+    t = med(lambda: O.soft_threshold24(G))
+    res["soft_threshold24 bf16 2048x4096"] = {"ms": t * 1e3, "GB/s": n * 6 / t / 1e9}
+    t = med(lambda: O.mvue24_dense(G[:512], seed=1, offset=0), reps=1)
+    res["mvue24 dense bf16 512x4096"] = {"ms": t * 1e3, "GB/s": 512 * k * 4 / t / 1e9}
+    p = torch.randn(m, k, generator=g) * 0.02
+    gr = torch.randn(m, k, generator=g) * 1e-3
+    mk = torch.rand(m, k, generator=g) < 0.5
+    t = med(lambda: O.masked_add(gr.clone(), p, mk, 2e-4))
+    res["masked_add fp32 2048x4096 (includes one clone of grad)"] = {"ms": t * 1e3, "GB/s": n * 13 / t / 1e9}
+    # cfg4 forward GEMM as a dense fp32 matmul of the masked weight, one eighth of the tokens
+    T, K, N = 2048, 768, 3072
+    x = torch.randn(T, K, generator=g)
+    w = torch.randn(N, K, generator=g) * 0.02
+    wm = torch.where(O.magnitude_mask24(w), w, torch.zeros(()))
+    t = med(lambda: x @ wm.t())
+    res["dense fp32 masked matmul 2048x768x3072"] = {"ms": t * 1e3, "TFLOP/s": 2.0 * T * K * N / t / 1e12}
+    return res
 
 
 def spmm_measurements(dev):
@@ -520,13 +608,25 @@ def spmm_measurements(dev):
         for i in range(nb):
             torch.mm(pre[i], xs[i])
         t_dw_gemm_only = timeit(lambda i: torch.mm(pre[i], xs[i]))
+        # split-K form with fp32 accumulation into a zeroed gradient buffer (what the training layer uses)
+        gw = torch.zeros(N, K, dtype=torch.float32, device=dev)
+
+        def dw_splitk(i, compress=True):
+            sp = sparse.to_sparse_semi_structured(dys[i].t(), MVUE24=True, dtype=dtype) if compress else pre[i]
+            gw.zero_()
+            _spmm.sparse_mm_accumulate_(gw, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, xs[i])
+
+        t_dw_splitk = timeit(lambda i: dw_splitk(i))
+        t_dw_splitk_gemm = timeit(lambda i: dw_splitk(i, False))
         d_fwd = timeit(lambda i: torch.mm(xs[i], wd.t()))
         d_dx = timeit(lambda i: torch.mm(dys[i], wd))
         d_dw = timeit(lambda i: torch.mm(dys[i].t(), xs[i]))
-        sp_total, de_total = t_fwd + t_dx + t_dw, d_fwd + d_dx + d_dw
+        sp_total, de_total = t_fwd + t_dx + min(t_dw, t_dw_splitk), d_fwd + d_dx + d_dw
         res[tag] = {
             "sparse_ms": {"fwd": t_fwd * 1e3, "dx": t_dx * 1e3, "dw_incl_mvue_compress": t_dw * 1e3,
                           "dw_gemm_only": t_dw_gemm_only * 1e3,
+                          "dw_splitk_fp32_incl_mvue_compress": t_dw_splitk * 1e3,
+                          "dw_splitk_fp32_gemm_and_memset_only": t_dw_splitk_gemm * 1e3,
                           "fwd_transposed_view_like_reference": t_fwd_view * 1e3,
                           "dx_transposed_view_like_reference": t_dx_view * 1e3},
             "dense_cublas_ms": {"fwd": d_fwd * 1e3, "dx": d_dx * 1e3, "dw": d_dw * 1e3},
@@ -534,7 +634,8 @@ def spmm_measurements(dev):
             "dense_fwd_bwd_TFLOPs": 3 * flops / de_total / 1e12,
             "speedup_vs_dense": de_total / sp_total,
             "per_gemm_TFLOPs": {"fwd": flops / t_fwd / 1e12, "dx": flops / t_dx / 1e12,
-                                "dw_gemm_only": flops / t_dw_gemm_only / 1e12},
+                                "dw_gemm_only": flops / t_dw_gemm_only / 1e12,
+                                "dw_splitk_fp32_gemm_and_memset_only": flops / t_dw_splitk_gemm / 1e12},
         }
         del xs, dys, pre
     # fp8 e4m3 forward (per-tensor scales applied outside the GEMM), fp32 output

@@ -184,13 +184,28 @@ int sp24_meta_to_tc(const void *meta, int meta_itemsize, int64_t m, int64_t k, v
  *   out        trans_out = 0: (ms, n) row-major; 1: (n, ms) row-major, i.e. already transposed back to
  *              (tokens, features); leading dimension ld_out
  *   dtype      F16 / BF16 (out_dtype = dtype) or E4M3 / E5M2 (out_dtype = F32, K-major operands only)
- *   bias       ms values in the output type or NULL; activation 0 none, 1 relu, 2 silu
+ *   bias       ms values in the output type or NULL; activation 0 none, 1 relu, 2 silu, 3 gelu (tanh form; not in the reference)
  *   status     optional device int: set to a non-zero code if a bounded on-device wait gave up
- * Shape rules: ms % 128 == 0, n % 8 == 0, k % 64 == 0 (16-bit) or k % 128 == 0 (8-bit).
+ * Shape rules: ms % 128 == 0, k % 64 == 0 (16-bit) or k % 128 == 0 (8-bit); n % 8 == 0 unless B is stored (n, k)
+ * and the output (n, ms) (b_mn_major == 0 and trans_out == 1), where any n > 0 is accepted.
  */
 int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms, int64_t k,
               const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype, int trans_out,
               int64_t ld_out, const void *bias, int activation, int *status, void *stream);
+
+/*
+ * Weight-gradient form of the sparse GEMM with fp32 accumulation into the output:
+ *   D (ms x n, fp32, row-major, pitch ld_out) += A_sparse (ms x k) * B (k x n, stored row-major, pitch ld_b).
+ * Replaces torch.mm(to_sparse_semi_structured(grad_output.t(), MVUE24=True), input) of the reference's training
+ * layer (README.md:190-192 of the reference) followed by the cast of the gradient to fp32 (README.md:211).
+ * K is cut into k_splits slices (0 = as many as idle SMs allow); every slice adds its partial product with
+ * fp32 reductions in L2, so the caller zeroes D for a plain product, or passes a gradient buffer to accumulate
+ * into.  The order of the slice sums is not fixed: results can differ in the last fp32 bits between runs.
+ * dtype: SP24_F16 or SP24_BF16 (both operands).  Shape rules: ms % 128 == 0, k % 64 == 0, n % 8 == 0.
+ */
+int sp24_spmm_accumulate_f32(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc,
+                             int64_t ms, int64_t k, const void *b, int64_t ld_b, int64_t n, float *out,
+                             int64_t ld_out, int k_splits, int *status, void *stream);
 
 /*
  * Self-test of the failure path of the GEMM kernels: launches one CTA that waits, with a limit of `polls`

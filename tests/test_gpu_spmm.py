@@ -73,7 +73,7 @@ def test_spmm_fp8(S, dtype, ms, k, n):
     assert torch.equal(sp.to_dense().float(), wq)
 
 
-@pytest.mark.parametrize("act", [None, "relu", "silu"])
+@pytest.mark.parametrize("act", [None, "relu", "silu", "gelu"])
 def test_spmm_bias_and_activation(S, act):
     from sparse.spmm import sparse_linear
     g = torch.Generator().manual_seed(3)
@@ -83,10 +83,10 @@ def test_spmm_bias_and_activation(S, act):
     sp = S.to_sparse_semi_structured(w)
     y = sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, b, act)
     ref = x.float() @ sp.to_dense().float().t() + b.float()
-    ref = {None: ref, "relu": torch.relu(ref), "silu": F.silu(ref)}[act]
+    ref = {None: ref, "relu": torch.relu(ref), "silu": F.silu(ref), "gelu": F.gelu(ref, approximate="tanh")}[act]
     assert float((y.float() - ref).abs().max() / ref.abs().max()) <= 2e-3
     with pytest.raises(RuntimeError, match="activation"):
-        sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, b, "gelu")
+        sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, b, "tanh")
     with pytest.raises(RuntimeError, match="datatype"):
         sparse_linear(x.bfloat16(), sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass)
 
@@ -260,3 +260,128 @@ def test_bounded_wait_reports_through_status_word(S):
     spmm.check_status()
     assert float((y.float() - x.float() @ sp.to_dense().float().t()).abs().max()) < 0.1
     assert _ext.lib().sp24_selftest_bounded_wait(None, 16, None) == -5
+
+
+def test_column_parallel_shards_reproduce_the_unsharded_layer(S):
+    """Output-feature blocks of W, each compressed as its own matrix, give the columns of the unsharded
+    product bit for bit (same masks, same K order), and the dX terms add up to the unsharded dX."""
+    from sparse.sharded import ColumnParallelSparseWeight, row_block
+    from sparse.spmm import sparse_linear
+    g = torch.Generator().manual_seed(77)
+    w = (torch.randn(1280, 512, generator=g) * 0.02).cuda()
+    x = torch.randn(304, 512, generator=g).half().cuda()
+    dy = (torch.randn(304, 1280, generator=g) * 0.1).half().cuda()
+    bias = torch.randn(1280, generator=g).half().cuda()
+    mask, (pw, mw), (pt, mt) = S.select_and_compress(w, mask=None, dtype=torch.float16)
+    y_full = sparse_linear(x, pw, mw, bias=bias)
+    dx_full = sparse_linear(dy, pt, mt).float()
+    world = 3
+    ys, dx = [], torch.zeros_like(dx_full)
+    for r in range(world):
+        sh = ColumnParallelSparseWeight(w, rank=r, world=world)
+        r0, r1 = row_block(1280, r, world)
+        assert torch.equal(sh.mask, mask[r0:r1])
+        ys.append(sh.forward_local(x, bias))
+        dx += sh.grad_input_partial(dy[:, r0:r1]).float()
+    assert torch.equal(torch.cat(ys, dim=1), y_full)
+    assert float((dx - dx_full).abs().max() / dx_full.abs().max()) < 2e-3
+
+
+def test_soft_threshold_linear_matches_the_dense_formulation(S):
+    """S-STE layer: fused scale == separate multiply; the sparse-tensor-core forward equals the dense one
+    within the fp16 GEMM tolerance; gradients pass straight through to the weight."""
+    from sparse.sste import SoftThresholdLinear, SoftThreshold
+    torch.manual_seed(5)
+    lin = SoftThresholdLinear(512, 384, bias=True).to(DEV)
+    lin.init_scale()
+    w_s, _ = S.soft_threshold24_triton(lin.weight.detach())
+    scale = float(torch.dot(lin.weight.detach().flatten(), w_s.flatten()) / torch.dot(w_s.flatten(), w_s.flatten()))
+    assert abs(float(lin.scale) - scale) < 1e-6 and 1.0 < scale < 5.0
+    assert torch.equal(lin.get_sparse_weights(), w_s * lin.scale)
+    nz = (lin.get_sparse_weights().reshape(-1, 4) != 0).sum(1)
+    assert int(nz.max()) <= 2
+    x = torch.randn(6, 50, 512, device=DEV, requires_grad=True)
+    y = lin(x)
+    y_ref = F.linear(x, w_s * lin.scale, lin.bias)
+    assert torch.allclose(y, y_ref, atol=1e-5, rtol=1e-5)
+    y.sum().backward()
+    assert torch.allclose(lin.weight.grad, torch.ones(300, 384, device=DEV).t() @ x.detach().reshape(-1, 512), rtol=1e-4, atol=1e-4)
+    # same layer through the sparse GEMM
+    lin2 = SoftThresholdLinear(512, 384, bias=True, spmm=True).to(DEV)
+    lin2.load_state_dict(lin.state_dict())
+    x2 = x.detach().clone().requires_grad_(True)
+    y2 = lin2(x2)
+    assert y2.dtype == torch.float16 and y2.shape == y.shape
+    assert float((y2.float() - y_ref).abs().max() / y_ref.abs().max()) < 2e-3
+    (y2.float() * 0.01).sum().backward()
+    gx_ref = (torch.full((300, 384), 0.01, device=DEV) @ (w_s * lin.scale)).view(6, 50, 512)
+    assert float((x2.grad - gx_ref).abs().max() / gx_ref.abs().max()) < 2e-3
+    assert lin2.weight.grad.shape == lin2.weight.shape
+
+
+def test_sparse_state_round_trip(S):
+    """Masks and counters of the FST layers survive a save / load cycle next to the ordinary state_dict."""
+    from sparse.sparse_ops import sparse_state, load_sparse_state
+    torch.manual_seed(9)
+    a = torch.nn.Sequential(S.SparseLinearTranspose(256, 128), S.SparseLinearTranspose(128, 256)).to(DEV)
+    x = torch.randn(64, 256, device=DEV)
+    for _ in range(3):
+        a(x).sum().backward()
+        for p in a.parameters():
+            if hasattr(p, "mask"):
+                p.cnt = 0
+    st = sparse_state(a)
+    b = torch.nn.Sequential(S.SparseLinearTranspose(256, 128), S.SparseLinearTranspose(128, 256)).to(DEV)
+    b.load_state_dict(a.state_dict())
+    load_sparse_state(b, st)
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        if hasattr(pa, "mask"):
+            assert torch.equal(pa.mask, pb.mask) and (pa.counter, pa.step, pa.cnt, pa.mode, pa.freq) == \
+                (pb.counter, pb.step, pb.cnt, pb.mode, pb.freq)
+    # the restored model continues with the saved masks (no reselect before the period is over)
+    ya, yb = a(x), b(x)
+    assert torch.equal(ya, yb)
+
+
+@pytest.mark.parametrize("n", [1, 13, 301])
+def test_token_count_need_not_be_a_multiple_of_eight(S, n):
+    """Token-major input and output: rows past n are zero-filled on load and skipped on store."""
+    from sparse.spmm import sparse_linear, check_status
+    g = torch.Generator().manual_seed(n)
+    w = torch.randn(256, 192, generator=g).half().to(DEV)
+    x = torch.randn(n, 192, generator=g).half().to(DEV)
+    sp = S.to_sparse_semi_structured(w)
+    guard = torch.full((n + 2, 256), 7.0, dtype=torch.float16, device=DEV)
+    y = sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass)
+    check_status()
+    wm = sp.to_dense().float()
+    check(y, x.float() @ wm.t(), x.float().abs(), wm.abs(), torch.float16)
+    assert y.shape == (n, 256) and bool((guard == 7.0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("a_col", [False, True])
+@pytest.mark.parametrize("ms,k,n,splits", [(128, 64, 8, 0), (256, 1024, 200, 0), (384, 2048, 192, 1), (512, 4096, 328, 5)])
+def test_accumulating_split_k_gemm(S, dtype, a_col, ms, k, n, splits):
+    """D += A_sparse B with fp32 reductions: equals the fp32 matmul of the masked operands to fp32 rounding
+    (1e-5 of the largest entry), on a zeroed output and on top of an existing gradient."""
+    from sparse.spmm import sparse_mm_accumulate_, check_status
+    g = torch.Generator().manual_seed(ms + k + n)
+    w = torch.randn(ms, k, generator=g).to(dtype).to(DEV)
+    mask = random_mask(ms, k, g).to(DEV)
+    b = torch.randn(k, n, generator=g).to(dtype).to(DEV)
+    src, mk = (w.t().contiguous().t(), mask.t().contiguous().t()) if a_col else (w, mask)
+    sp = S.to_sparse_semi_structured(src, mask=mk, dtype=dtype)
+    wm = torch.where(mask, w, torch.zeros((), dtype=dtype, device=DEV)).double()
+    ref = (wm @ b.double()).float()
+    out = torch.zeros(ms, n, dtype=torch.float32, device=DEV)
+    sparse_mm_accumulate_(out, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, b, k_splits=splits)
+    check_status()
+    scale = float(ref.abs().max())
+    assert float((out - ref).abs().max()) <= 1e-5 * scale
+    prev = torch.randn(ms, n, generator=g).to(DEV)
+    out2 = prev.clone()
+    sparse_mm_accumulate_(out2, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, b, k_splits=splits)
+    assert float((out2 - (prev + ref)).abs().max()) <= 1e-5 * max(scale, 1.0)
+    with pytest.raises(RuntimeError):
+        sparse_mm_accumulate_(out.half(), sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, b)
