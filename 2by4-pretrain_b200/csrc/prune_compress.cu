@@ -18,6 +18,7 @@ struct PcParams {
     const float *uniforms;
     int64_t m, k, ld_dense, ld_packed, ld_mask, ld_u;
     uint64_t seed, offset;
+    const unsigned long long *offset_dev;   // optional device word added to offset at run time
 };
 
 template <typename T, int N> __device__ __forceinline__ void load_elems(const T *p, T (&out)[N]) {
@@ -126,6 +127,7 @@ template <typename T> __device__ __forceinline__ uint32_t mse_lookup(uint32_t lo
 // ---------------------------------------------------------------------------------------------
 template <typename TIn, typename TOut, int MODE, bool HAS_U>
 __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_kernel(PcParams P) {
+    const uint64_t rng_offset = P.offset + (P.offset_dev ? *P.offset_dev : 0ull);
     constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;  // dense elements per metadata word
     constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;    // bytes per metadata word
     constexpr int GROUP = MB == 2 ? 32 : 16;
@@ -194,7 +196,7 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
                             u[0] = ua.x; u[1] = ua.y; u[2] = ub.x; u[3] = ub.y;
                         } else {
                             const uint64_t gi = (uint64_t)r * (uint64_t)(P.k / 4) + (uint64_t)(c * (CH / 4) + g2 * 2);
-                            mvue_uniform_pairs(gi >> 1, P.seed, P.offset, u[0], u[1], u[2], u[3]);
+                            mvue_uniform_pairs(gi >> 1, P.seed, rng_offset, u[0], u[1], u[2], u[3]);
                         }
                     }
 #pragma unroll
@@ -242,6 +244,7 @@ template <typename TIn> struct ColVec {
 
 template <typename TIn, typename TOut, int MODE, bool HAS_U, int V>
 __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_kernel(PcParams P) {
+    const uint64_t rng_offset = P.offset + (P.offset_dev ? *P.offset_dev : 0ull);
     constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;
     constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;
     constexpr int GROUP = MB == 2 ? 32 : 16;
@@ -289,7 +292,7 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_k
 #pragma unroll
                         for (int v = 0; v < V; ++v) {
                             const uint64_t gi = (uint64_t)(r + v) * (uint64_t)(P.k / 4) + (uint64_t)gcol;
-                            mvue_uniform_pairs(gi >> 1, P.seed, P.offset, u[v][0], u[v][1], u[v][2], u[v][3]);
+                            mvue_uniform_pairs(gi >> 1, P.seed, rng_offset, u[v][0], u[v][1], u[v][2], u[v][3]);
                         }
                     }
                 }
@@ -379,10 +382,11 @@ template <typename TIn> int dispatch_out(const PcParams &P, int packed_dtype, in
 }  // namespace
 }  // namespace sp24
 
-extern "C" int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
-                                   int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
-                                   int mode, const void *mask, int64_t ld_mask, const float *uniforms,
-                                   int64_t ld_uniforms, uint64_t seed, uint64_t offset, void *stream) {
+static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
+                               int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
+                               int mode, const void *mask, int64_t ld_mask, const float *uniforms,
+                               int64_t ld_uniforms, uint64_t seed, uint64_t offset, const uint64_t *offset_dev,
+                               void *stream) {
     using namespace sp24;
     if (!dense || !packed || !meta) return SP24_ERR_ARG;
     const int so = dtype_size(packed_dtype), si = dtype_size(dense_dtype);
@@ -405,7 +409,7 @@ extern "C" int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m
         return SP24_ERR_ALIGN;
     if (int rc = check_device()) return rc;
     PcParams P{dense, packed, meta, static_cast<const uint8_t *>(mask), uniforms, m, k, ld_dense, ld_packed, ld_mask,
-               ld_uniforms, seed, offset};
+               ld_uniforms, seed, offset, reinterpret_cast<const unsigned long long *>(offset_dev)};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dense_dtype) {
         case SP24_F32: return dispatch_out<float>(P, packed_dtype, mode, col_major, st);
@@ -414,4 +418,25 @@ extern "C" int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m
         case SP24_I8: return dispatch_mode<int8_t, int8_t>(P, mode, col_major, st);
         default: return SP24_ERR_DTYPE;
     }
+}
+
+extern "C" int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
+                                   int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
+                                   int mode, const void *mask, int64_t ld_mask, const float *uniforms,
+                                   int64_t ld_uniforms, uint64_t seed, uint64_t offset, void *stream) {
+    return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode,
+                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, nullptr, stream);
+}
+
+// Same conversion; the Philox offset is `offset` plus the 64-bit word at `offset_dev` (device memory), read when
+// the kernel runs.  A launch recorded once (a CUDA graph) then draws fresh uniforms on every replay if the
+// caller bumps that word between replays.
+extern "C" int sp24_prune_compress_devoffset(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
+                                             int col_major, void *packed, int packed_dtype, int64_t ld_packed,
+                                             void *meta, int mode, const void *mask, int64_t ld_mask,
+                                             const float *uniforms, int64_t ld_uniforms, uint64_t seed, uint64_t offset,
+                                             const uint64_t *offset_dev, void *stream) {
+    if (!offset_dev || (reinterpret_cast<uintptr_t>(offset_dev) & 7u)) return SP24_ERR_ARG;
+    return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode,
+                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, offset_dev, stream);
 }

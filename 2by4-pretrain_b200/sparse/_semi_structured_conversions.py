@@ -19,6 +19,21 @@ if hasattr(torch, "float8_e4m3fn"):
     _META_DTYPE[torch.float8_e5m2] = torch.int32
 
 
+# Optional int64 device tensor (one element) whose value is added to the Philox offset of every seeded MVUE
+# conversion when the kernel runs.  A training step recorded as a CUDA graph bakes the host-side seeds into the
+# graph; bumping this word between replays gives every replay fresh uniforms.
+_DEVICE_RNG_OFFSET: Optional[Tensor] = None
+
+
+def set_device_rng_offset(counter: Optional[Tensor]) -> None:
+    """Install (or, with None, remove) the device word added to the MVUE Philox offset."""
+    global _DEVICE_RNG_OFFSET
+    if counter is not None:
+        if counter.dtype != torch.int64 or counter.numel() != 1 or not counter.is_cuda:
+            raise RuntimeError("set_device_rng_offset: expected a one-element int64 CUDA tensor")
+    _DEVICE_RNG_OFFSET = counter
+
+
 def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, mask: Optional[Tensor] = None,
                    uniforms: Optional[Tensor] = None, seed: int = 0, offset: int = 0):
     """Low-level entry: fills ``sparse`` (packed values) and ``meta`` (reordered metadata) in place.
@@ -49,10 +64,17 @@ def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, ma
         ld_u = _ext.layout_of(uniforms)[1]
     if not meta.is_contiguous():
         raise RuntimeError("metadata buffer must be contiguous")
-    rc = _ext.lib().sp24_prune_compress(
-        dense.data_ptr(), _ext.dt(dense.dtype), m, k, ld_d, col_major, sparse.data_ptr(), _ext.dt(sparse.dtype), ld_p,
-        meta.data_ptr(), mode, _ext.ptr(mask), ld_m, _ext.ptr(uniforms), ld_u, seed & (2 ** 64 - 1),
-        offset & (2 ** 64 - 1), _ext.stream())
+    dev_off = _DEVICE_RNG_OFFSET if mode == _ext.PRUNE_MVUE and uniforms is None else None
+    if dev_off is not None:
+        rc = _ext.lib().sp24_prune_compress_devoffset(
+            dense.data_ptr(), _ext.dt(dense.dtype), m, k, ld_d, col_major, sparse.data_ptr(), _ext.dt(sparse.dtype), ld_p,
+            meta.data_ptr(), mode, _ext.ptr(mask), ld_m, _ext.ptr(uniforms), ld_u, seed & (2 ** 64 - 1),
+            offset & (2 ** 64 - 1), dev_off.data_ptr(), _ext.stream())
+    else:
+        rc = _ext.lib().sp24_prune_compress(
+            dense.data_ptr(), _ext.dt(dense.dtype), m, k, ld_d, col_major, sparse.data_ptr(), _ext.dt(sparse.dtype), ld_p,
+            meta.data_ptr(), mode, _ext.ptr(mask), ld_m, _ext.ptr(uniforms), ld_u, seed & (2 ** 64 - 1),
+            offset & (2 ** 64 - 1), _ext.stream())
     _ext.check(rc, "sp24_prune_compress")
     from .spmm import invalidate_meta
     invalidate_meta(meta)  # a refilled metadata buffer must not reuse a cached tensor-core copy

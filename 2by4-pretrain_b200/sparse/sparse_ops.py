@@ -98,11 +98,11 @@ class sparse_linear_transpose(autograd.Function):
         ctx.shape = input.shape
         input = input.reshape(-1, input.shape[-1])
         # same product as torch.mm(input, weight_sparse.t()); calling the GEMM wrapper directly skips the
-        # Python-level tensor-subclass dispatch
-        output = _spmm(input, weight_sparse.sparse_tensor_cutlass, weight_sparse.meta_tensor_cutlass)
-        if bias is None:
-            return output.view(*ctx.shape[:-1], -1)
-        return output.view(*ctx.shape[:-1], -1) + bias
+        # Python-level tensor-subclass dispatch; the bias is added in the GEMM epilogue (one rounding instead of
+        # the listing's two)
+        b = None if bias is None else bias.to(input.dtype)
+        output = _spmm(input, weight_sparse.sparse_tensor_cutlass, weight_sparse.meta_tensor_cutlass, bias=b)
+        return output.view(*ctx.shape[:-1], -1)
 
     @staticmethod
     @custom_bwd(device_type='cuda')
@@ -139,9 +139,8 @@ class _fst_linear(autograd.Function):
         ctx.shape = input.shape
         ctx.has_bias = bias is not None
         ctx.fp32_grad = weight.dtype == torch.float32 and x.shape[1] % 8 == 0
-        output = _spmm(x, pw, mw)
-        output = output.view(*input.shape[:-1], -1)
-        return output if b is None else output + b
+        output = _spmm(x, pw, mw, bias=b)     # bias added in the GEMM epilogue
+        return output.view(*input.shape[:-1], -1)
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -205,7 +204,15 @@ class SparseLinearTranspose(nn.Linear):
 
     def _refresh(self, reselect: bool):
         w = self.weight
-        mask, (pw, mw), (pt, mt) = select_and_compress(w, mask=None if reselect else w.mask, dtype=torch.float16)
+        # a reselected mask overwrites the existing buffer, so w.mask keeps one address for the whole run
+        reuse = w.mask if (reselect and w.mask.is_cuda and w.mask.is_contiguous() and w.mask.dtype == torch.bool) else None
+        # compressed copies in the autocast dtype when it is bf16 (no cast passes over the activations);
+        # fp16 otherwise, like the reference layer (custom_fwd(cast_inputs=torch.float16))
+        dtype = torch.float16
+        if torch.is_autocast_enabled('cuda') and torch.get_autocast_dtype('cuda') == torch.bfloat16:
+            dtype = torch.bfloat16
+        mask, (pw, mw), (pt, mt) = select_and_compress(w, mask=None if reselect else w.mask, dtype=dtype,
+                                                       mask_out=reuse)
         w.mask = mask
         w.compressed = (pw, mw, pt, mt)
         if not self.materialize_sparse_tensors:
@@ -214,10 +221,10 @@ class SparseLinearTranspose(nn.Linear):
         out_f, in_f = w.shape
         w.weight_sparse = SparseSemiStructuredTensor(
             None, original_shape=torch.Size([out_f, in_f]), sparse_tensor_cutlass=pw, meta_tensor_cutlass=mw,
-            dtype=torch.float16)
+            dtype=dtype)
         w.weight_sparse_T = SparseSemiStructuredTensor(
             None, original_shape=torch.Size([in_f, out_f]), sparse_tensor_cutlass=pt, meta_tensor_cutlass=mt,
-            dtype=torch.float16)
+            dtype=dtype)
 
     def forward(self, x):
         w = self.weight

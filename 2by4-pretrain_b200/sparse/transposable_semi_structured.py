@@ -60,17 +60,24 @@ class TransposableSparse(nn.Module):
         return _to_transposable_sparse_semi_structured(x, self.mask_pattern, self.abs)
 
 
-def select_and_compress(weight: Tensor, mask: Tensor = None, dtype: torch.dtype = torch.float16):
+def select_and_compress(weight: Tensor, mask: Tensor = None, dtype: torch.dtype = torch.float16,
+                        mask_out: Tensor = None):
     """One pass over ``weight`` (m, k): transposable mask (recomputed when ``mask`` is None, else read)
     plus the 2:4 compression of W and of W^T.  Returns (mask, (packed_w, meta_w), (packed_t, meta_t))
     where packed_t is the column-major (k, m/2) view the reference gets from
-    ``to_sparse_semi_structured(W.T, mask=mask.T)``."""
-    _ext.require_cuda(weight, mask)
+    ``to_sparse_semi_structured(W.T, mask=mask.T)``.  ``mask_out`` (bool, contiguous, (m, k)): when the
+    mask is recomputed, write it there instead of into a new tensor (a buffer with a fixed address)."""
+    _ext.require_cuda(weight, mask, mask_out)
     m, k = weight.shape
     w = _ext.as_layout(weight.detach(), 0)
     select = mask is None
     if select:
-        mask = torch.empty((m, k), dtype=torch.bool, device=w.device)
+        if mask_out is not None:
+            if mask_out.dtype != torch.bool or tuple(mask_out.shape) != (m, k) or not mask_out.is_contiguous():
+                raise RuntimeError("select_and_compress: mask_out must be a contiguous bool tensor of the weight's shape")
+            mask = mask_out
+        else:
+            mask = torch.empty((m, k), dtype=torch.bool, device=w.device)
     else:
         mask = _ext.as_layout(mask if mask.dtype in (torch.bool, torch.uint8) else mask != 0, 0)
     buf_w = torch.empty(m * k * 9 // 16, dtype=dtype, device=w.device)

@@ -12,6 +12,12 @@ forward / backward with three sparse GEMMs per layer, then masked decay
 Gradients are averaged by ``DistributedDataParallel`` (bucketed NCCL all-reduce overlapped with backward).
 Masks need no communication: the weights are identical on all ranks after the reduce, so every rank
 recomputes the same transposable mask.  MVUE seeds come from Python's ``random``, seeded per rank.
+
+``--graphs`` replays the step from CUDA graphs instead of launching ~2000 kernels from Python: one graph for
+forward + backward on a mask-refresh step, one for the other steps, one for masked decay + AdamW.  Gradients
+live in one flat fp32 buffer that is all-reduced with a single NCCL call between the graphs (no collective
+is captured).  The MVUE seeds recorded in a graph stay fixed, so the kernels add a device counter, bumped
+inside the graph, to their Philox offset: every replay draws fresh uniforms.
 """
 import argparse
 import math
@@ -174,6 +180,151 @@ def run(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12,
     return res
 
 
+def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12, d=768, heads=12, alpha=2e-4,
+               lr=6e-4, freq=40, verbose=False, return_losses=False):
+    """The same step as ``run`` replayed from CUDA graphs.  Returns the same dict."""
+    import torch.distributed as dist
+    import sparse
+    from sparse._semi_structured_conversions import set_device_rng_offset
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    own_group = False
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+        own_group = True
+    random.seed(1234 + rank)
+    model = build(mode, dev, layers, d, heads, seq, vocab)
+    params = [p for p in model.parameters()]
+    sparse_params = [p for p in params if hasattr(p, "mask") and p.mode == "sparse"]
+    for p in sparse_params:
+        p.freq = freq
+    # one flat fp32 gradient buffer; every p.grad is a view of it for the whole run
+    flat = torch.zeros(sum(p.numel() for p in params), dtype=torch.float32, device=dev)
+    off = 0
+    for p in params:
+        p.grad = flat[off:off + p.numel()].view_as(p)
+        off += p.numel()
+    decay, no_decay = [], []
+    for n_, p in model.named_parameters():
+        (no_decay if p.dim() < 2 or hasattr(p, "mask") else decay).append(p)
+    opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": no_decay, "weight_decay": 0.0}],
+                            lr=lr, betas=(0.9, 0.95), fused=True, capturable=True)
+    rng_counter = torch.zeros(1, dtype=torch.int64, device=dev)
+    set_device_rng_offset(rng_counter if mode == "sparse" else None)
+    static_tok = torch.zeros((batch, seq + 1), dtype=torch.long, device=dev)
+    gen = torch.Generator(device="cpu").manual_seed(10 + rank)
+
+    def set_phase(reselect):
+        # what SparseLinearTranspose.forward looks at: cnt == 0 -> rebuild the compressed copies,
+        # counter % freq == 0 -> reselect the mask first
+        for p in sparse_params:
+            p.cnt = 0
+            p.counter = 0 if reselect else 1
+
+    def fwd_bwd():
+        flat.zero_()
+        rng_counter.add_(1)
+        x, y = static_tok[:, :-1], static_tok[:, 1:]
+        with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+            loss = model(x, y)
+        loss.backward()
+        return loss.detach()
+
+    def update():
+        if mode == "sparse":
+            with torch.no_grad():
+                for p in sparse_params:
+                    sparse.masked_add_(p.grad, p.data, p.mask, alpha=alpha)
+        opt.step()
+
+    def next_tokens():
+        tok = torch.randint(0, vocab, (batch, seq + 1), generator=gen).pin_memory()
+        static_tok.copy_(tok, non_blocking=True)
+
+    def reduce_grads():
+        if world > 1:
+            dist.all_reduce(flat, op=dist.ReduceOp.AVG)
+
+    # eager warm-up on a side stream (allocator, cuBLAS workspaces, optimizer state, kernel attributes)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(3):
+            next_tokens()
+            set_phase(i == 0)
+            fwd_bwd()
+            reduce_grads()
+            update()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+
+    pool = torch.cuda.graph_pool_handle()
+    graphs = {}
+    losses_static = {}
+    for key in ((True, False) if mode == "sparse" else (False,)):
+        set_phase(key)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=pool):
+            losses_static[key] = fwd_bwd()
+        graphs[key] = g
+    g_upd = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_upd, pool=pool):
+        update()
+
+    def one_step(i):
+        next_tokens()
+        key = (mode == "sparse") and (i % freq == 0)
+        graphs[key].replay()
+        reduce_grads()
+        g_upd.replay()
+        return losses_static[key]
+
+    it = 0
+    for _ in range(warmup):
+        one_step(it)
+        it += 1
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    losses = []
+    e0.record()
+    t_cpu = time.perf_counter()
+    for _ in range(steps):
+        losses.append(one_step(it).clone())
+        it += 1
+    t_cpu = time.perf_counter() - t_cpu
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    loss_list = [float(v) for v in torch.stack(losses).float().cpu()]
+    res = {"tokens_per_s": batch * seq * world * steps / (ms * 1e-3), "ms_per_step": ms / steps, "world": world,
+           "tokens_per_step": batch * seq * world, "last_loss": loss_list[-1], "mode": mode,
+           "loss_finite": all(math.isfinite(v) for v in loss_list), "host_enqueue_ms_per_step": t_cpu * 1e3 / steps,
+           "graphs": True}
+    if return_losses:
+        res["losses"] = loss_list
+    if mode == "sparse":
+        from sparse.spmm import check_status
+        check_status()
+    set_device_rng_offset(None)
+    del graphs, g_upd, opt, model, flat
+    torch.cuda.empty_cache()
+    if own_group:
+        dist.destroy_process_group()
+    if verbose and rank == 0:
+        print({k: v for k, v in res.items() if k != "losses"})
+    return res
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=20)
@@ -181,8 +332,10 @@ if __name__ == "__main__":
     ap.add_argument("--mode", default="sparse", choices=["sparse", "dense"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=12)
+    ap.add_argument("--graphs", action="store_true", help="replay the step from CUDA graphs")
     a = ap.parse_args()
     t0 = time.time()
-    r = run(a.steps, a.warmup, a.mode, batch=a.batch, layers=a.layers, verbose=True)
+    fn = run_graphs if a.graphs else run
+    r = fn(a.steps, a.warmup, a.mode, batch=a.batch, layers=a.layers, verbose=True)
     if int(os.environ.get("RANK", "0")) == 0:
         print(f"wall {time.time() - t0:.1f}s")

@@ -86,6 +86,18 @@ int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m, int64_t k
                         uint64_t seed, uint64_t offset, void *stream);
 
 /*
+ * sp24_prune_compress with a Philox offset that is read on the device: the stream is keyed by
+ * (seed, offset + *offset_dev), *offset_dev being a 64-bit word in device memory (8-byte aligned, not NULL) read
+ * when the kernel runs.  A launch that is recorded once and replayed (a CUDA graph of the training step) draws
+ * fresh uniforms on every replay if the caller bumps that word between replays.  The reference draws a new
+ * host seed per call (sparse/_semi_structured_conversions.py:1076) and has no replayable form.
+ */
+int sp24_prune_compress_devoffset(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
+                                  int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta, int mode,
+                                  const void *mask, int64_t ld_mask, const float *uniforms, int64_t ld_uniforms,
+                                  uint64_t seed, uint64_t offset, const uint64_t *offset_dev, void *stream);
+
+/*
  * 2:4 compressed -> dense (zeros at pruned positions).  Replaces
  * _sparse_semi_structured_to_dense_triton / _sparse_semi_structured_to_dense
  * (sparse/_semi_structured_conversions.py:1163-1274, :217-328).
