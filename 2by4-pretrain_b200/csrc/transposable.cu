@@ -75,49 +75,51 @@ __constant__ SelectLut kSelectLut = make_select_lut();
 
 // v: the 4x4 block (already |.| when requested); lut: shared-memory copy of kSelectLut.
 // Returns the 16-bit pattern (bit 4*i+j = keep (i, j)) that a scan over all 90 patterns in table order with
-// "first maximum wins" would return, but needs far fewer compare/select instructions: the best bottom for
-// every top pair is a max over at most six sums (rounding is monotone, so max-then-add equals add-then-max),
-// the winning top is the first whose best total equals the global maximum, and the winning bottom is the
-// first admissible one that reaches the maximum with that top.
+// "replace only when strictly greater" would return, with far fewer instructions: the best bottom for every
+// top pair is a max over at most six sums (rounding is monotone, so max-then-add equals add-then-max), the
+// 36 top pairs are scanned once in table order with a running strict maximum, and the winning bottom is the
+// first admissible one that reaches the maximum with the winning top.
 __device__ __forceinline__ uint32_t select_pattern(const float (&v)[4][4], const uint32_t *lut) {
     float s[4][6];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int p = 0; p < 6; ++p) s[i][p] = __fadd_rn(v[i][pair_a(p)], v[i][pair_b(p)]);
-    // Everything below is recomputed from the 24 row sums instead of being kept in registers: the float
-    // adder has headroom, registers (occupancy) do not.
     auto top = [&](int a, int b) { return __fadd_rn(s[0][a], s[1][b]); };
     auto bot = [&](int c, int d) { return __fadd_rn(s[2][c], s[3][d]); };
     float max_c = bot(0, 5);
 #pragma unroll
     for (int c = 1; c < 6; ++c) max_c = fmaxf(max_c, bot(c, 5 - c));
-    auto best_total = [&](int a, int b) {
-        float bb;
+    // One pass over the 36 top pairs in table order, as two independent chains of 18 (instruction-level
+    // parallelism): a candidate replaces the running best only when strictly greater, so the first maximum
+    // wins inside a chain, and the second chain replaces the first only when strictly greater.  NaN totals
+    // never win; if nothing ever exceeds -inf the answer stays at top 0 (pattern 0), like the flat scan.
+    float best[2] = {-INFINITY, -INFINITY}, tv[2] = {0.f, 0.f}, c0v[2] = {0.f, 0.f};
+    int ts[2] = {0, 18};
+#pragma unroll
+    for (int t = 0; t < 36; ++t) {
+        const int a = t / 6, b = t % 6, h = t / 18;
+        const float tp = top(a, b);
+        float bb, first_bot = 0.f;
         if (top_type(a, b) == 0) bb = bot(5 - a, 5 - a);
         else if (top_type(a, b) == 2) bb = max_c;
-        else bb = fmaxf(bot(shared_bottom(a, b, 0), shared_bottom(a, b, 1)), bot(shared_bottom(a, b, 1), shared_bottom(a, b, 0)));
-        return __fadd_rn(top(a, b), bb);
-    };
-    float m = best_total(0, 0);
-#pragma unroll
-    for (int t = 1; t < 36; ++t) m = fmaxf(m, best_total(t / 6, t % 6));
-    // keep the compiler from carrying the 36 totals of the first pass over to the second
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int p = 0; p < 6; ++p) asm volatile("" : "+f"(s[i][p]));
-    // first top (table order) whose best total is the maximum: walk backwards, later writes win
-    int tstar = 0;
-    float t_val = top(0, 0), cand0 = 0.f;
-#pragma unroll
-    for (int t = 35; t >= 0; --t) {
-        if (best_total(t / 6, t % 6) == m) {
-            tstar = t;
-            t_val = top(t / 6, t % 6);
-            if (top_type(t / 6, t % 6) == 1) cand0 = bot(shared_bottom(t / 6, t % 6, 0), shared_bottom(t / 6, t % 6, 1));
+        else {
+            first_bot = bot(shared_bottom(a, b, 0), shared_bottom(a, b, 1));
+            bb = fmaxf(first_bot, bot(shared_bottom(a, b, 1), shared_bottom(a, b, 0)));
+        }
+        const float tot = __fadd_rn(tp, bb);
+        if (tot > best[h]) {
+            best[h] = tot;
+            ts[h] = t;
+            tv[h] = tp;
+            if (top_type(a, b) == 1) c0v[h] = first_bot;
         }
     }
+    const bool second = best[1] > best[0];
+    const float m = second ? best[1] : best[0];
+    const int tstar = second ? ts[1] : ts[0];
+    const float t_val = second ? tv[1] : tv[0];
+    const float cand0 = second ? c0v[1] : c0v[0];
     const bool first = __fadd_rn(t_val, cand0) == m;
     int cstar = 0;
 #pragma unroll
@@ -214,7 +216,8 @@ template <typename T, typename TOut> __device__ __forceinline__ void pack_row(co
 }
 
 template <typename T, typename TOut, bool SELECT>
-__global__ void __launch_bounds__(256, 2) ts_dual_kernel(DualParams P) {
+// three CTAs per SM for 16-bit inputs (80 registers); fp32 inputs need more registers and keep two
+__global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(DualParams P) {
     __shared__ __align__(16) uint16_t smeta_w[4][64];   // 4 column pairs x (32 rows x 2)
     __shared__ __align__(16) uint16_t smeta_t[256];     // 1 column pair x (128 rows x 2)
     __shared__ __align__(4) uint8_t nib_t[8][128];      // [block row][W column]

@@ -40,9 +40,9 @@ BYTES_PER_ELEM = 2 + 1 + 2 * (2 / 2 + 1 / 8)  # read fp16 W, write bool mask, wr
 ALG_BYTES_PER_MATRIX = M * K * BYTES_PER_ELEM
 METRIC = "prune/compress HBM GB/s (transposable select + dual 2:4 compress)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one ts_dual_kernel launch on this workload, from the
-# ncu capture summarised in profiles/ts_dual_kernel_8192x8192_fp16.md: (134.2 + 164.7) MB for an 8192 x 8192
+# ncu capture summarised in profiles/ts_dual_kernel_8192x8192_fp16.md: (134.2 + 162.9) MB for an 8192 x 8192
 # matrix, scaled by the element count (1/4) to one 4096 x 4096 launch
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 74.7e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 74.3e6
 
 
 def measured_peak():
