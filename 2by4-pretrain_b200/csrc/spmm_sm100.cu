@@ -652,6 +652,283 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 }
 
 // ------------------------------------------------------------------------------------------------
+// Two-CTA form (cluster of 2, tcgen05 cta_group::2) for 16-bit types, B stored (n, k), output (n, ms).
+// ------------------------------------------------------------------------------------------------
+// A CTA pair computes tiles of 256 sparse rows x 192 dense columns: every MMA instruction has M = 256 (128
+// rows per CTA) and N = 192, and reads half of its B operand from each CTA's shared memory, so a CTA stages
+// only 96 rows of B per stage: 42 KB per stage and 128-row block, where the single-CTA kernel needs 66 KB
+// (or 84 KB for two blocks).  One accumulator per tile leaves room for two accumulator buffers in tensor
+// memory, so the epilogue of a tile runs entirely under the next tile's MMAs, and five operand stages fit.
+// Each CTA loads its own A block, metadata and B half with TMA (cta_group::2 form, completing on the leader's
+// barrier), drains its own accumulator and reports its release to the leader's barrier.  CTA 0 of the pair
+// (the leader) issues all MMAs and metadata copies; its commits arrive on the barriers of both CTAs.  No load
+// is multicast.
+namespace two {
+constexpr int BN2 = 192;                                   // columns of a pair tile
+constexpr int B_HALF_BYTES = (BN2 / 2) * 256;              // 96 rows x two 128-byte K atoms
+constexpr int STAGE2_BYTES = A_STAGE_BYTES + B_HALF_BYTES + 2048;   // 43008
+constexpr int STAGES2 = 5;
+constexpr int SMEM2 = STAGES2 * STAGE2_BYTES + 1024;
+static_assert(STAGE2_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+static_assert(SMEM2 <= 227 * 1024, "shared memory budget");
+}  // namespace two
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cta address -> shared::cluster address of the same location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_cp_128x128b_pair(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void mma_sp_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t e_tmem, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.sp.cta_group::2.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <bool A_MN, typename OutT>
+__global__ void __launch_bounds__(320, 1)
+spmm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_e, SpmmParams P) {
+    using namespace two;
+    constexpr int BN = BN2;
+    constexpr int STAGES = STAGES2;
+    constexpr int OFF_B = A_STAGE_BYTES, OFF_E = OFF_B + B_HALF_BYTES;
+    constexpr int KSTEPS = 4;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr int E_COL0 = 2 * BN, E_SLOT = 4;    // two accumulator buffers, then two metadata slots
+    static_assert(sizeof(OutT) == 2, "16-bit outputs only");
+    static_assert(E_COL0 + 2 * E_SLOT <= 512, "tensor memory columns exhausted");
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int n_tiles_n = (int)((P.n + BN - 1) / BN);
+    const int n_tiles_m = (int)(P.ms / (2 * BM));     // 256-row blocks: one 128-row block per CTA
+    const int n_tiles = n_tiles_n * n_tiles_m;        // row block varies fastest over the tile index
+    const int k_iters = (int)((P.k + 127) / 128);
+
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t tmem_full0 = smem_u32(&bars[2 * STAGES]), tmem_empty0 = smem_u32(&bars[2 * STAGES + 2]);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);      // used in the leader only: one expect_tx arrival, bytes of both CTAs
+            mbar_init(empty0 + 8 * s, 1);     // one commit arrival per CTA
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tmem_full0 + 8 * b, 1);
+            mbar_init(tmem_empty0 + 8 * b, 16);   // used in the leader only: eight epilogue warps of each CTA
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(&tmem_base_smem), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                       // the peer's barriers are initialised before anything targets them
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (one per CTA)
+        if (lane == 0) {
+            int g = 0;
+            bool ok = true;
+            constexpr uint32_t cta_tx = A_STAGE_BYTES + 2048 + B_HALF_BYTES;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                const int mblk = (tile % n_tiles_m) * 2 + (int)rank;
+                const int mrow = mblk * BM;
+                const int brow = (tile / n_tiles_m) * BN + (int)rank * (BN / 2);
+                for (int it = 0; it < k_iters; ++it, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (g / STAGES) & 1;
+                    if (g >= STAGES && !mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, P.status, 1)) { ok = false; break; }
+                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE2_BYTES);
+                    const uint32_t sb = sa + OFF_B;
+                    const uint32_t full_leader = map_to_cta(full0 + 8 * s, 0);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * cta_tx);
+                    if constexpr (!A_MN) {
+                        tma_load_2d_pair(sa, &map_a, it * 64, mrow, full_leader);
+                    } else {
+                        tma_load_2d_pair(sa, &map_a, mrow, it * 64, full_leader);
+                        tma_load_2d_pair(sa + 8192, &map_a, mrow + 64, it * 64, full_leader);
+                    }
+                    // metadata atom of this row block and K step: two rows of 1024 bytes in the atom table
+                    tma_load_2d_pair(sa + OFF_E, &map_e, 0, (int)(((int64_t)mblk * P.k_atoms + it) * 2), full_leader);
+                    // this CTA's half of B: 96 rows x two 128-byte K atoms
+                    tma_load_2d_pair(sb, &map_b, it * 128, brow, full_leader);
+                    tma_load_2d_pair(sb + (BN / 2) * 128, &map_b, it * 128 + 64, brow, full_leader);
+                    SP24_TRACE(0, g);
+                }
+            }
+            if (abort_flag && rank == 0) {
+                for (int q = (g > STAGES ? g - STAGES : 0); q < g; ++q) {
+                    const int s = q % STAGES;
+                    const uint32_t ph = (q / STAGES) & 1;
+                    for (uint32_t w = 0; w < WAIT_LIMIT; ++w)
+                        if (mbar_try_wait(full0 + 8 * s, ph)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t A_LBO = A_MN ? 8192 : 16, A_KSTEP = A_MN ? 2048 : 32;
+            const uint32_t idesc0 = P.idesc;   // M = 256, N = 192 set by the launcher
+            int g = 0, tl = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++tl) {
+                const int buf = tl & 1;
+                // the epilogues of both CTAs must have drained this accumulator buffer (two tiles ago)
+                ok = mbar_wait(tmem_empty0 + 8 * buf, ((tl >> 1) & 1) ^ 1, &abort_flag, P.status, 4);
+                for (int it = 0; it < k_iters && ok; ++it, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (g / STAGES) & 1;
+                    ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, P.status, 2);
+                    if (!ok) break;
+                    SP24_TRACE(1, 2 * g);
+                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE2_BYTES);
+                    const uint32_t sb = sa + OFF_B;
+                    tc_fence_after();
+                    const uint32_t e_cols = E_COL0 + (g & 1) * E_SLOT;
+                    tc_cp_128x128b_pair(tmem_base + e_cols, make_desc(sa + OFF_E, 16, 128, 0));
+#pragma unroll
+                    for (int j = 0; j < KSTEPS; ++j) {
+                        const uint64_t adesc = make_desc(sa + j * A_KSTEP, A_LBO, 1024, 2);
+                        const uint32_t b_off = (uint32_t)(j >> 1) * ((BN / 2) * 128) + (j & 1) * 64;
+                        const uint64_t bdesc = make_desc(sb + b_off, 16, 1024, 2);
+                        const uint32_t ecol = e_cols + j;
+                        mma_sp_pair(tmem_base + buf * BN, adesc, bdesc, tmem_base + (ecol & ~1u), idesc0 | (ecol & 1u),
+                                    (it > 0 || j > 0) ? 1u : 0u);
+                    }
+                    tc_commit_pair(empty0 + 8 * s);
+                    SP24_TRACE(1, 2 * g + 1);
+                }
+                tc_commit_pair(tmem_full0 + 8 * buf);   // also arrives after an abort
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..9 of both CTAs)
+        // No staging buffer: a warp packs its 96 columns of the accumulator into 48 registers, hands the buffer
+        // back, then stores 16-bit values directly; the 32 lanes of a store are 32 consecutive features of one
+        // token, 64 contiguous bytes.
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        constexpr int HC = BN / 2, NREG = HC / 2;
+        OutT *out = static_cast<OutT *>(P.out);
+        const uint32_t empty_leader0 = map_to_cta(tmem_empty0, 0);
+        int tl = 0;
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
+            const int buf = tl & 1;
+            const int mrow = ((tile % n_tiles_m) * 2 + (int)rank) * BM + quad * 32 + lane;
+            const int64_t tok0 = (int64_t)(tile / n_tiles_m) * BN + half * HC;
+            const bool ok = mbar_wait(tmem_full0 + 8 * buf, (tl >> 1) & 1, &abort_flag, P.status, 3);
+            tc_fence_after();
+            if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl);
+            const bool run = ok && !abort_flag;
+            uint32_t held[NREG];
+            if (run) {
+                float bias = 0.f;
+                if (P.bias) bias = from_out<OutT>(static_cast<const OutT *>(P.bias)[mrow]);
+                const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + half * HC;
+#pragma unroll
+                for (int c = 0; c < HC / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(acc + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        Vec<OutT, 2> o;
+                        o.v[0] = to_out<OutT>(__uint_as_float(v[2 * i]) + bias);
+                        o.v[1] = to_out<OutT>(__uint_as_float(v[2 * i + 1]) + bias);
+                        held[c * 16 + i] = *reinterpret_cast<const uint32_t *>(&o);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(empty_leader0 + 8 * buf);
+            if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 1);
+            if (run) {
+                uint16_t *dst = reinterpret_cast<uint16_t *>(out) + tok0 * P.ld_out + mrow;
+                if (tok0 + HC <= P.n) {
+#pragma unroll
+                    for (int c2 = 0; c2 < NREG; ++c2) {
+                        dst[0] = (uint16_t)(held[c2] & 0xFFFFu);
+                        dst[P.ld_out] = (uint16_t)(held[c2] >> 16);
+                        dst += 2 * P.ld_out;
+                        asm volatile("" : "+l"(dst));   // one running pointer, not 96 precomputed addresses
+                    }
+                } else {
+#pragma unroll
+                    for (int c2 = 0; c2 < NREG; ++c2) {
+                        if (tok0 + 2 * c2 < P.n) dst[0] = (uint16_t)(held[c2] & 0xFFFFu);
+                        if (tok0 + 2 * c2 + 1 < P.n) dst[P.ld_out] = (uint16_t)(held[c2] >> 16);
+                        dst += 2 * P.ld_out;
+                        asm volatile("" : "+l"(dst));
+                    }
+                }
+            }
+            if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 3);
+        }
+        tc_fence_before();
+    }
+    // nobody leaves while the peer may still read this CTA's shared memory or signal its barriers
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // metadata: reference (reordered) layout -> tensor-core atom order
 // ------------------------------------------------------------------------------------------------
 // 16-bit types: atom = 128 rows x 128 logical columns = 2048 bytes, byte 16*L + 4*q + 2*h with
@@ -756,6 +1033,52 @@ int launch_spmm(const CUtensorMap &ma, const CUtensorMap &mb, SpmmParams P, cuda
     return launch_status();
 }
 
+// Metadata atoms as a 2-D tensor for TMA: rows of 1024 bytes (256 int32), two rows per 2048-byte atom, no swizzle.
+int make_map_e(CUtensorMap *map, const void *e_tc, int64_t n_atoms) {
+    const cuuint64_t dims[2] = {256, (cuuint64_t)(2 * n_atoms)};
+    const cuuint64_t strides[1] = {1024};
+    const cuuint32_t box[2] = {256, 2};
+    const cuuint32_t estr[2] = {1, 1};
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return SP24_ERR_CUDA;
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void *>(e_tc), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? SP24_OK : SP24_ERR_CUDA;
+}
+
+template <bool A_MN, typename OutT>
+int launch_spmm_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &me, SpmmParams P, cudaStream_t st) {
+    auto kern = spmm_pair_kernel<A_MN, OutT>;
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, two::SMEM2) != cudaSuccess)
+            return SP24_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    // M = 256 over the CTA pair, N = 192
+    P.idesc = (P.idesc & ~(0x1Fu << 24)) | ((uint32_t)(256 >> 4) << 24) | ((uint32_t)(two::BN2 >> 3) << 17);
+    const int64_t tiles = ((P.n + two::BN2 - 1) / two::BN2) * (P.ms / 256);
+    const int64_t pairs_max = sm_count_cached() / 2;
+    const unsigned pairs = (unsigned)(tiles < pairs_max ? tiles : pairs_max);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(320, 1, 1);
+    cfg.dynamicSmemBytes = two::SMEM2;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, ma, mb, me, P) != cudaSuccess) return SP24_ERR_CUDA;
+    return launch_status();
+}
+
 // Tile shape: wide / tall tiles stage fewer operand bytes per output, small ones fill the SMs more evenly.
 // Cost model per candidate (BN, row blocks per tile): rounds of tiles per CTA x bytes staged per K iteration.
 void pick_tile(int64_t ms, int64_t n, int sm_count, int &bn_out, int &mpt_out) {
@@ -848,6 +1171,21 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     P.idesc = (1u << 2) | (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) |
               ((uint32_t)(b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BM >> 4) << 24);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // CTA-pair kernel: 16-bit types, token-major B and output, whole 256-row blocks, no activation
+    bool pair_form = !f8 && !b_mn_major && trans_out && ms % 256 == 0 && activation == 0 && n >= 1024;
+    if (const char *env = getenv("SP24_SPMM_PAIR")) pair_form = pair_form && atoi(env) != 0;
+    if (pair_form) {
+        CUtensorMap map_b, map_e;
+        rc = make_map(&map_b, b, dtype, n, k, ld_b, 64, two::BN2 / 2);
+        if (rc) return rc;
+        rc = make_map_e(&map_e, e_tc, (ms / 128) * P.k_atoms);
+        if (rc) return rc;
+        if (out_dtype == SP24_F16)
+            return a_mn_major ? launch_spmm_pair<true, __half>(map_a, map_b, map_e, P, st)
+                              : launch_spmm_pair<false, __half>(map_a, map_b, map_e, P, st);
+        return a_mn_major ? launch_spmm_pair<true, __nv_bfloat16>(map_a, map_b, map_e, P, st)
+                          : launch_spmm_pair<false, __nv_bfloat16>(map_a, map_b, map_e, P, st);
+    }
     int bn = 128, mpt = 2;
     pick_tile(ms, n, sm_count_cached(), bn, mpt);
     P.mblk_per_tile = mpt;

@@ -429,3 +429,27 @@ def test_device_rng_offset_changes_the_draw_without_a_new_seed(S):
     _r.seed(5)
     plain = S.to_sparse_semi_structured(x, MVUE24=True).to_dense()
     assert torch.equal(plain, outs[0])     # counter value 0 == no counter
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("a_col", [False, True])
+@pytest.mark.parametrize("ms,k,n", [(256, 64, 1024), (512, 832, 1100), (768, 3072, 2049), (2304, 768, 4096)])
+def test_cta_pair_kernel_equals_single_cta_kernel(S, monkeypatch, dtype, a_col, ms, k, n):
+    """The two-CTA kernel (cta_group::2, chosen for whole 256-row blocks and at least 1024 tokens) accumulates in
+    the same K order as the single-CTA kernel: results must be bit-equal, with and without a bias, on ragged
+    token counts, and match the fp32 reference within the stated tolerance."""
+    from sparse.spmm import sparse_linear, check_status
+    g = torch.Generator().manual_seed(ms + k + n)
+    w = torch.randn(ms, k, generator=g).to(dtype).to(DEV)
+    x = torch.randn(n, k, generator=g).to(dtype).to(DEV)
+    b = torch.randn(ms, generator=g).to(dtype).to(DEV)
+    sp = S.to_sparse_semi_structured(w.t().contiguous().t() if a_col else w, dtype=dtype)
+    outs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("SP24_SPMM_PAIR", mode)
+        outs[mode] = (sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass),
+                      sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, bias=b))
+        check_status()
+    assert torch.equal(outs["0"][0], outs["1"][0]) and torch.equal(outs["0"][1], outs["1"][1])
+    wm = sp.to_dense().float()
+    check(outs["1"][0], x.float() @ wm.t(), x.float().abs(), wm.abs(), dtype)
