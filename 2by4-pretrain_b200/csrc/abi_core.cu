@@ -1,4 +1,7 @@
 // Library-wide pieces of the C ABI: error strings, version, device check.
+#include <cstdio>
+#include <cstdlib>
+
 #include "sp24_common.cuh"
 
 namespace sp24 {
@@ -17,7 +20,12 @@ int check_device() {
     return ok ? SP24_OK : SP24_ERR_DEVICE;
 }
 
-int launch_status() { return cudaGetLastError() == cudaSuccess ? SP24_OK : SP24_ERR_CUDA; }
+int launch_status() {
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return SP24_OK;
+    if (getenv("SP24_DEBUG")) fprintf(stderr, "sparse24_b200: CUDA error %d: %s\n", (int)e, cudaGetErrorString(e));
+    return SP24_ERR_CUDA;
+}
 
 }  // namespace sp24
 

@@ -19,6 +19,8 @@ struct PcParams {
     int64_t m, k, ld_dense, ld_packed, ld_mask, ld_u;
     uint64_t seed, offset;
     const unsigned long long *offset_dev;   // optional device word added to offset at run time
+    int16_t *tc;                            // optional metadata copy in tensor-core atom order (16-bit outputs)
+    int64_t k_atoms;                        // 128-column atoms per 128-row block
 };
 
 template <typename T, int N> __device__ __forceinline__ void load_elems(const T *p, T (&out)[N]) {
@@ -252,6 +254,9 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_k
     using MetaT = typename VecBytes<MB>::type;
 
     __shared__ __align__(16) MetaT smeta[4][2 * RT];
+    // tensor-core order: line L = 16*(r/16) + 8*(c%2) + r%8 of 16 bytes, int16 slot 2*((c/2)%4) + (r/8)%2; the block's
+    // RT rows x 8 word columns fill RT whole lines of one atom per 128-row block
+    __shared__ __align__(16) uint16_t stc[MB == 2 ? RT * 8 : 8];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t ncols = P.k / CH;
@@ -323,6 +328,17 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_k
         for (int v = 0; v < V; ++v) {
             const int rr = lane * V + v;
             smeta[warp >> 1][(rr / GROUP) * 2 * GROUP + meta_run_pos<MB>(rr % GROUP, warp & 1)] = (MetaT)word[v];
+            if constexpr (MB == 2)
+                if (P.tc) stc[8 * (16 * (rr >> 4) + 8 * (warp & 1) + (rr & 7)) + 2 * (warp >> 1) + ((rr >> 3) & 1)] = (uint16_t)word[v];
+        }
+    } else if constexpr (MB == 2) {
+        // word columns past the matrix (K not a multiple of 128): zeros, the GEMM multiplies them by zero-filled operands
+        if (P.tc && r < P.m) {
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                const int rr = lane * V + v;
+                stc[8 * (16 * (rr >> 4) + 8 * (warp & 1) + (rr & 7)) + 2 * (warp >> 1) + ((rr >> 3) & 1)] = 0;
+            }
         }
     }
     __syncthreads();
@@ -335,6 +351,19 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_k
             char *dst = static_cast<char *>(P.meta) + (cp * 2 * P.m + 2 * r0) * MB + piece * 16;
             *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(
                 reinterpret_cast<const char *>(&smeta[pair][0]) + piece * 16);
+        }
+    }
+    if constexpr (MB == 2) {
+        if (P.tc) {
+            for (int pline = threadIdx.x; pline < RT; pline += 256) {
+                if (pline < rows_here) {
+                    const int64_t gr = r0 + pline;   // line index inside the 128-row block = row index of its first writer
+                    const int64_t off = ((gr >> 7) * P.k_atoms + blockIdx.y) * 2048 + (gr & 127) * 16;
+                    if (off + 16 <= (P.m >> 7) * P.k_atoms * 2048)   // every store is checked against the buffer size
+                        *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(P.tc) + off) =
+                            *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(stc) + pline * 16);
+                }
+            }
         }
     }
 }
@@ -386,7 +415,7 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
                                int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
                                int mode, const void *mask, int64_t ld_mask, const float *uniforms,
                                int64_t ld_uniforms, uint64_t seed, uint64_t offset, const uint64_t *offset_dev,
-                               void *stream) {
+                               void *e_tc, void *stream) {
     using namespace sp24;
     if (!dense || !packed || !meta) return SP24_ERR_ARG;
     const int so = dtype_size(packed_dtype), si = dtype_size(dense_dtype);
@@ -409,7 +438,9 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
         return SP24_ERR_ALIGN;
     if (int rc = check_device()) return rc;
     PcParams P{dense, packed, meta, static_cast<const uint8_t *>(mask), uniforms, m, k, ld_dense, ld_packed, ld_mask,
-               ld_uniforms, seed, offset, reinterpret_cast<const unsigned long long *>(offset_dev)};
+               ld_uniforms, seed, offset, reinterpret_cast<const unsigned long long *>(offset_dev),
+               static_cast<int16_t *>(e_tc), (k + 127) / 128};
+    if (e_tc && (so != 2 || !col_major || m % 128 || !aligned16(e_tc))) return SP24_ERR_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dense_dtype) {
         case SP24_F32: return dispatch_out<float>(P, packed_dtype, mode, col_major, st);
@@ -425,18 +456,21 @@ extern "C" int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m
                                    int mode, const void *mask, int64_t ld_mask, const float *uniforms,
                                    int64_t ld_uniforms, uint64_t seed, uint64_t offset, void *stream) {
     return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode,
-                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, nullptr, stream);
+                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, nullptr, nullptr, stream);
 }
 
-// Same conversion; the Philox offset is `offset` plus the 64-bit word at `offset_dev` (device memory), read when
-// the kernel runs.  A launch recorded once (a CUDA graph) then draws fresh uniforms on every replay if the
-// caller bumps that word between replays.
-extern "C" int sp24_prune_compress_devoffset(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
-                                             int col_major, void *packed, int packed_dtype, int64_t ld_packed,
-                                             void *meta, int mode, const void *mask, int64_t ld_mask,
-                                             const float *uniforms, int64_t ld_uniforms, uint64_t seed, uint64_t offset,
-                                             const uint64_t *offset_dev, void *stream) {
-    if (!offset_dev || (reinterpret_cast<uintptr_t>(offset_dev) & 7u)) return SP24_ERR_ARG;
+// Same conversion with two optional extras (either may be NULL).
+// offset_dev: the Philox offset becomes `offset` plus the 64-bit word at `offset_dev` (device memory), read when the
+//   kernel runs.  A launch recorded once (a CUDA graph) then draws fresh uniforms on every replay if the caller
+//   bumps that word between replays.
+// e_tc: a second copy of the metadata in the order the sparse GEMM reads (sp24_meta_tc_bytes(m, k) bytes), so that
+//   no conversion launch is needed before sp24_spmm.  Column-major storage and 16-bit outputs only, m % 128 == 0.
+extern "C" int sp24_prune_compress_ex(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
+                                      int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
+                                      int mode, const void *mask, int64_t ld_mask, const float *uniforms,
+                                      int64_t ld_uniforms, uint64_t seed, uint64_t offset, const uint64_t *offset_dev,
+                                      void *e_tc, void *stream) {
+    if (offset_dev && (reinterpret_cast<uintptr_t>(offset_dev) & 7u)) return SP24_ERR_ARG;
     return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode,
-                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, offset_dev, stream);
+                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, offset_dev, e_tc, stream);
 }

@@ -993,9 +993,19 @@ int make_map(CUtensorMap *map, const void *base, int dt, int64_t rows, int64_t c
     const cuuint32_t estr[2] = {1, 1};
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return SP24_ERR_CUDA;
-    const CUresult r = encode(map, tmap_dtype(dt), 2, const_cast<void *>(base), dims, strides, box, estr,
-                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode(map, tmap_dtype(dt), 2, const_cast<void *>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_ERROR_INVALID_CONTEXT) {
+        // a host thread that has made no runtime call yet (an autograd worker) has no current context for this
+        // driver entry point: let the runtime bind the primary context, then encode again
+        cudaFree(nullptr);
+        r = encode(map, tmap_dtype(dt), 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (r != CUDA_SUCCESS && getenv("SP24_DEBUG"))
+        fprintf(stderr, "sparse24_b200: cuTensorMapEncodeTiled failed (%d): base %p rows %lld cols %lld ld %lld box %u x %u\n",
+                (int)r, base, (long long)rows, (long long)cols, (long long)ld, box_cols, box_rows);
     return r == CUDA_SUCCESS ? SP24_OK : SP24_ERR_CUDA;
 }
 
@@ -1023,7 +1033,7 @@ int launch_spmm(const CUtensorMap &ma, const CUtensorMap &mb, SpmmParams P, cuda
     const int which = P.activation ? 1 : 0;
     if (dev >= 0 && dev < 64 && !attr_set[dev][which]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
-            return SP24_ERR_CUDA;
+            return launch_status();
         attr_set[dev][which] = true;
     }
     P.idesc |= (uint32_t)(BN >> 3) << 17;
@@ -1041,9 +1051,15 @@ int make_map_e(CUtensorMap *map, const void *e_tc, int64_t n_atoms) {
     const cuuint32_t estr[2] = {1, 1};
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return SP24_ERR_CUDA;
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void *>(e_tc), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void *>(e_tc), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_ERROR_INVALID_CONTEXT) {
+        cudaFree(nullptr);   // see make_map
+        r = encode(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void *>(e_tc), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     return r == CUDA_SUCCESS ? SP24_OK : SP24_ERR_CUDA;
 }
 

@@ -199,6 +199,11 @@ struct DualParams {
     void *packed_w, *packed_t;
     int16_t *meta_w, *meta_t;
     int64_t m, k, ld_w, ld_mask, ld_pw, ld_pt;
+    // optional second copy of the metadata in the order the sparse GEMM reads (2048-byte atoms per 128 rows x 128
+    // columns, int16 index 8*L + 2*q + h with L = 16*(r/16) + 8*(c%2) + r%8, q = (c/2)%4, h = (r/8)%2 for row r of
+    // the 128-row block and metadata word column c); requires m % 128 == 0 and k % 128 == 0
+    int16_t *tc_w, *tc_t;
+    int64_t tc_w_bytes, tc_t_bytes;   // sizes of the two copies: every store is checked against them
 };
 
 // four elements of a row as two registers of packed 16-bit output values (low half = lower column)
@@ -222,6 +227,8 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
     __shared__ __align__(16) uint16_t smeta_t[256];     // 1 column pair x (128 rows x 2)
     __shared__ __align__(4) uint8_t nib_t[8][128];      // [block row][W column]
     __shared__ uint32_t lut[64];
+    __shared__ __align__(16) uint16_t stc_w[32 * 8];    // tensor-core order: 32 rows x 8 words of one atom
+    __shared__ __align__(4) uint16_t stc_t[128 * 2];    // tensor-core order of W^T: [L][h] of one word-column pair
     load_select_lut(lut);
 
     // A block covers 64 rows x 128 columns as two 32-row halves.  Both halves are loaded up front so that
@@ -294,6 +301,15 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
             smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 1, mc & 1)] = (uint16_t)(nib01 >> 16);
             smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 2, mc & 1)] = (uint16_t)nib23;
             smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 3, mc & 1)] = (uint16_t)(nib23 >> 16);
+            if (P.tc_w) {
+                // rows rr = warp*4 .. warp*4+3 of this 32-row half: L = 16*(rr/16) + 8*(mc%2) + rr%8, h = (rr/8)%2
+                const uint32_t vals[4] = {nib01 & 0xFFFFu, nib01 >> 16, nib23 & 0xFFFFu, nib23 >> 16};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int rr = warp * 4 + i;
+                    stc_w[8 * (16 * (rr >> 4) + 8 * (mc & 1) + (rr & 7)) + 2 * (mc >> 1) + ((rr >> 3) & 1)] = (uint16_t)vals[i];
+                }
+            }
         }
         // columns of W (= rows of W^T): transpose the 4x4 block of 16-bit values, then the same table lookup
         {
@@ -326,6 +342,8 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
             const uint8_t *nb = &nib_t[0][0] + (par * 4) * 128 + col;
             const uint32_t word = (uint32_t)nb[0] | ((uint32_t)nb[128] << 4) | ((uint32_t)nb[256] << 8) | ((uint32_t)nb[384] << 12);
             smeta_t[(col / 32) * 64 + meta_run_pos<2>(col % 32, par)] = (uint16_t)word;
+            // W^T row = W column `col` (0..127 of its 128-row block), word column parity `par`
+            if (P.tc_t) stc_t[2 * (16 * (col >> 4) + 8 * par + (col & 7)) + ((col >> 3) & 1)] = (uint16_t)word;
         }
         __syncthreads();
         // write-out: W metadata 4 pairs x 128 B, W^T metadata up to 512 B
@@ -346,6 +364,22 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
                 *reinterpret_cast<uint4 *>(dst) =
                     *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(smeta_t) + piece * 16);
             }
+        }
+        if (P.tc_w && threadIdx.x >= 64 && threadIdx.x < 96) {
+            // 32 lines of 16 bytes, contiguous in the atom of (row block r0/128, column block c0/128)
+            const int piece = threadIdx.x - 64;
+            const int64_t off = ((r0 >> 7) * (P.k >> 7) + (c0 >> 7)) * 2048 + ((r0 & 127) + piece) * 16;
+            if (off >= 0 && off + 16 <= P.tc_w_bytes)
+                *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(P.tc_w) + off) =
+                    *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(stc_w) + piece * 16);
+        }
+        if (P.tc_t && threadIdx.x >= 128) {
+            // W^T: row block c0/128, word columns r0/16 and r0/16 + 1: one 4-byte piece (h = 0, 1) per line L
+            const int L = threadIdx.x - 128;
+            const int64_t wc = r0 >> 4;
+            const int64_t off = ((c0 >> 7) * (P.m >> 7) + (wc >> 3)) * 2048 + L * 16 + ((wc >> 1) & 3) * 4;
+            if (off >= 0 && off + 4 <= P.tc_t_bytes)
+                *reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(P.tc_t) + off) = *reinterpret_cast<const uint32_t *>(&stc_t[2 * L]);
         }
         __syncthreads();  // the staging arrays are rewritten by the next half
 #pragma unroll
@@ -406,27 +440,49 @@ extern "C" int sp24_transposable_select(const void *x, int dtype, int64_t m, int
     return launch_status();
 }
 
-extern "C" int sp24_select_dual_compress(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select,
-                                         void *mask, int64_t ld_mask, void *packed_w, int packed_dtype,
-                                         int64_t ld_packed_w, void *meta_w, void *packed_t, int64_t ld_packed_t,
-                                         void *meta_t, void *stream) {
+static int select_dual_compress_impl(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select, void *mask,
+                                     int64_t ld_mask, void *packed_w, int packed_dtype, int64_t ld_packed_w, void *meta_w,
+                                     void *packed_t, int64_t ld_packed_t, void *meta_t, void *tc_w, void *tc_t,
+                                     void *stream) {
     if (!w || !mask || !packed_w || !meta_w || !packed_t || !meta_t) return SP24_ERR_ARG;
     if (dtype != SP24_F32 && dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
     if (packed_dtype != SP24_F16 && packed_dtype != SP24_BF16) return SP24_ERR_DTYPE;
     if (m <= 0 || k <= 0 || m % 64 || k % 64) return SP24_ERR_SHAPE;
+    if ((tc_w || tc_t) && (m % 128 || k % 128)) return SP24_ERR_SHAPE;
     const int sz = dtype_size(dtype);
     if (ld_w < k || (ld_w * sz) % 16 || ld_mask < k || ld_mask % 16) return SP24_ERR_STRIDE;
     if (ld_packed_w < k / 2 || ld_packed_w % 8 || ld_packed_t < k || ld_packed_t % 8) return SP24_ERR_STRIDE;
     if (!aligned16(w) || !aligned16(mask) || !aligned16(packed_w) || !aligned16(meta_w) || !aligned16(packed_t) ||
-        !aligned16(meta_t))
+        !aligned16(meta_t) || (tc_w && !aligned16(tc_w)) || (tc_t && !aligned16(tc_t)))
         return SP24_ERR_ALIGN;
     if (int rc = check_device()) return rc;
     DualParams P{w, static_cast<uint8_t *>(mask), packed_w, packed_t, static_cast<int16_t *>(meta_w),
-                 static_cast<int16_t *>(meta_t), m, k, ld_w, ld_mask, ld_packed_w, ld_packed_t};
+                 static_cast<int16_t *>(meta_t), m, k, ld_w, ld_mask, ld_packed_w, ld_packed_t,
+                 static_cast<int16_t *>(tc_w), static_cast<int16_t *>(tc_t), (m / 128) * (k / 128) * 2048, (k / 128) * (m / 128) * 2048};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dtype) {
         case SP24_F32: return dispatch_dual<float>(P, packed_dtype, select, st);
         case SP24_F16: return dispatch_dual<__half>(P, packed_dtype, select, st);
         default: return dispatch_dual<__nv_bfloat16>(P, packed_dtype, select, st);
     }
+}
+
+extern "C" int sp24_select_dual_compress(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select,
+                                         void *mask, int64_t ld_mask, void *packed_w, int packed_dtype,
+                                         int64_t ld_packed_w, void *meta_w, void *packed_t, int64_t ld_packed_t,
+                                         void *meta_t, void *stream) {
+    return select_dual_compress_impl(w, dtype, m, k, ld_w, select, mask, ld_mask, packed_w, packed_dtype, ld_packed_w,
+                                     meta_w, packed_t, ld_packed_t, meta_t, nullptr, nullptr, stream);
+}
+
+// Same pass, which also writes the metadata of W (tc_w, sp24_meta_tc_bytes(m, k) bytes) and of W^T (tc_t,
+// sp24_meta_tc_bytes(k, m) bytes) in the order the sparse GEMM reads, so that no conversion launch is needed
+// before sp24_spmm.  Requires m % 128 == 0 and k % 128 == 0.
+extern "C" int sp24_select_dual_compress_tc(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select,
+                                            void *mask, int64_t ld_mask, void *packed_w, int packed_dtype,
+                                            int64_t ld_packed_w, void *meta_w, void *packed_t, int64_t ld_packed_t,
+                                            void *meta_t, void *tc_w, void *tc_t, void *stream) {
+    if (!tc_w || !tc_t) return SP24_ERR_ARG;
+    return select_dual_compress_impl(w, dtype, m, k, ld_w, select, mask, ld_mask, packed_w, packed_dtype, ld_packed_w,
+                                     meta_w, packed_t, ld_packed_t, meta_t, tc_w, tc_t, stream);
 }

@@ -27,8 +27,8 @@ _i64, _i32, _u64, _vp, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_uint64, cty
 _SIGNATURES = {
     "sp24_prune_compress": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _i64, _vp, _i32, _vp, _i64, _vp, _i64,
                             _u64, _u64, _vp],
-    "sp24_prune_compress_devoffset": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _i64, _vp, _i32, _vp, _i64, _vp, _i64,
-                                      _u64, _u64, _vp, _vp],
+    "sp24_prune_compress_ex": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _i64, _vp, _i32, _vp, _i64, _vp, _i64,
+                               _u64, _u64, _vp, _vp, _vp],
     "sp24_to_dense": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _i64, _vp],
     "sp24_mvue24_dense": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _u64, _u64, _vp],
     "sp24_sparse24": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _vp],
@@ -36,6 +36,8 @@ _SIGNATURES = {
     "sp24_transposable_select": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _vp],
     "sp24_select_dual_compress": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i32, _i64, _vp, _vp, _i64,
                                   _vp, _vp],
+    "sp24_select_dual_compress_tc": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i32, _i64, _vp, _vp, _i64,
+                                     _vp, _vp, _vp, _vp],
     "sp24_masked_add": [_vp, _vp, _vp, _i32, _i64, _f32, _vp],
 }
 

@@ -65,19 +65,27 @@ def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, ma
     if not meta.is_contiguous():
         raise RuntimeError("metadata buffer must be contiguous")
     dev_off = _DEVICE_RNG_OFFSET if mode == _ext.PRUNE_MVUE and uniforms is None else None
-    if dev_off is not None:
-        rc = _ext.lib().sp24_prune_compress_devoffset(
+    # column-major 16-bit results with whole 128-row blocks (the dY^T operand of the weight-gradient GEMM) also get
+    # their metadata in the order the GEMM reads, in the same pass
+    e_tc = None
+    if col_major and sparse.element_size() == 2 and m % 128 == 0:
+        from . import spmm as _spmm
+        e_tc = torch.empty(_spmm.tc_bytes(m, k), dtype=torch.uint8, device=meta.device)
+    if dev_off is not None or e_tc is not None:
+        rc = _ext.lib().sp24_prune_compress_ex(
             dense.data_ptr(), _ext.dt(dense.dtype), m, k, ld_d, col_major, sparse.data_ptr(), _ext.dt(sparse.dtype), ld_p,
             meta.data_ptr(), mode, _ext.ptr(mask), ld_m, _ext.ptr(uniforms), ld_u, seed & (2 ** 64 - 1),
-            offset & (2 ** 64 - 1), dev_off.data_ptr(), _ext.stream())
+            offset & (2 ** 64 - 1), _ext.ptr(dev_off), _ext.ptr(e_tc), _ext.stream())
     else:
         rc = _ext.lib().sp24_prune_compress(
             dense.data_ptr(), _ext.dt(dense.dtype), m, k, ld_d, col_major, sparse.data_ptr(), _ext.dt(sparse.dtype), ld_p,
             meta.data_ptr(), mode, _ext.ptr(mask), ld_m, _ext.ptr(uniforms), ld_u, seed & (2 ** 64 - 1),
             offset & (2 ** 64 - 1), _ext.stream())
     _ext.check(rc, "sp24_prune_compress")
-    from .spmm import invalidate_meta
+    from .spmm import invalidate_meta, register_tc_metadata
     invalidate_meta(meta)  # a refilled metadata buffer must not reuse a cached tensor-core copy
+    if e_tc is not None:
+        register_tc_metadata(meta, e_tc)
     return sparse, meta
 
 

@@ -59,21 +59,30 @@ def invalidate_meta(meta):
     _tc_meta_cache.pop(id(meta), None)
 
 
+def tc_bytes(ms: int, k: int) -> int:
+    lib = _ext.lib()
+    lib.sp24_meta_tc_bytes.restype = _i64
+    lib.sp24_meta_tc_bytes.argtypes = [_i64, _i64]
+    return lib.sp24_meta_tc_bytes(ms, k)
+
+
+def register_tc_metadata(meta: torch.Tensor, e_tc: torch.Tensor) -> None:
+    """Attach a tensor-core-order copy that a compression kernel wrote together with ``meta``."""
+    key = id(meta)
+    _tc_meta_cache[key] = (weakref.ref(meta, lambda _r, key=key: _tc_meta_cache.pop(key, None)), e_tc)
+
+
 def tc_metadata(meta: torch.Tensor, ms: int, k: int) -> torch.Tensor:
     """Metadata in the order the tensor cores consume (cached per metadata tensor object)."""
     hit = _tc_meta_cache.get(id(meta))
     e = hit[1] if hit is not None and hit[0]() is meta else None
     if e is None:
         lib = _ext.lib()
-        lib.sp24_meta_tc_bytes.restype = _i64
-        lib.sp24_meta_tc_bytes.argtypes = [_i64, _i64]
-        nbytes = lib.sp24_meta_tc_bytes(ms, k)
-        e = torch.empty(nbytes, dtype=torch.uint8, device=meta.device)
+        e = torch.empty(tc_bytes(ms, k), dtype=torch.uint8, device=meta.device)
         src = meta if meta.is_contiguous() else meta.contiguous()
         _ext.check(lib.sp24_meta_to_tc(src.data_ptr(), src.element_size(), ms, k, e.data_ptr(), _ext.stream()),
                    "sp24_meta_to_tc")
-        key = id(meta)
-        _tc_meta_cache[key] = (weakref.ref(meta, lambda _r, key=key: _tc_meta_cache.pop(key, None)), e)
+        register_tc_metadata(meta, e)
     return e
 
 

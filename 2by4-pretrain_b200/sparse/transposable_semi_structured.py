@@ -86,9 +86,22 @@ def select_and_compress(weight: Tensor, mask: Tensor = None, dtype: torch.dtype 
     meta_w = buf_w[m * k // 2:].view(torch.int16).view(m, k // 16)
     packed_t = buf_t[: m * k // 2].view(m // 2, k).t()
     meta_t = buf_t[m * k // 2:].view(torch.int16).view(k, m // 16)
-    rc = _ext.lib().sp24_select_dual_compress(
-        w.data_ptr(), _ext.dt(w.dtype), m, k, _ext.layout_of(w)[1], 1 if select else 0, mask.data_ptr(),
-        _ext.layout_of(mask)[1], packed_w.data_ptr(), _ext.dt(dtype), k // 2, meta_w.data_ptr(), packed_t.data_ptr(), k,
-        meta_t.data_ptr(), _ext.stream())
-    _ext.check(rc, "sp24_select_dual_compress")
+    if m % 128 == 0 and k % 128 == 0:
+        # whole tensor-core blocks: the kernel also writes both metadata copies in the order the GEMM reads
+        from . import spmm as _spmm
+        tc_w = torch.empty(_spmm.tc_bytes(m, k), dtype=torch.uint8, device=w.device)
+        tc_t = torch.empty(_spmm.tc_bytes(k, m), dtype=torch.uint8, device=w.device)
+        rc = _ext.lib().sp24_select_dual_compress_tc(
+            w.data_ptr(), _ext.dt(w.dtype), m, k, _ext.layout_of(w)[1], 1 if select else 0, mask.data_ptr(),
+            _ext.layout_of(mask)[1], packed_w.data_ptr(), _ext.dt(dtype), k // 2, meta_w.data_ptr(), packed_t.data_ptr(), k,
+            meta_t.data_ptr(), tc_w.data_ptr(), tc_t.data_ptr(), _ext.stream())
+        _ext.check(rc, "sp24_select_dual_compress_tc")
+        _spmm.register_tc_metadata(meta_w, tc_w)
+        _spmm.register_tc_metadata(meta_t, tc_t)
+    else:
+        rc = _ext.lib().sp24_select_dual_compress(
+            w.data_ptr(), _ext.dt(w.dtype), m, k, _ext.layout_of(w)[1], 1 if select else 0, mask.data_ptr(),
+            _ext.layout_of(mask)[1], packed_w.data_ptr(), _ext.dt(dtype), k // 2, meta_w.data_ptr(), packed_t.data_ptr(), k,
+            meta_t.data_ptr(), _ext.stream())
+        _ext.check(rc, "sp24_select_dual_compress")
     return mask, (packed_w, meta_w), (packed_t, meta_t)

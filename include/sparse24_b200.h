@@ -86,16 +86,20 @@ int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m, int64_t k
                         uint64_t seed, uint64_t offset, void *stream);
 
 /*
- * sp24_prune_compress with a Philox offset that is read on the device: the stream is keyed by
- * (seed, offset + *offset_dev), *offset_dev being a 64-bit word in device memory (8-byte aligned, not NULL) read
- * when the kernel runs.  A launch that is recorded once and replayed (a CUDA graph of the training step) draws
- * fresh uniforms on every replay if the caller bumps that word between replays.  The reference draws a new
- * host seed per call (sparse/_semi_structured_conversions.py:1076) and has no replayable form.
+ * sp24_prune_compress with two optional extras (either may be NULL); no counterpart in the reference.
+ *   offset_dev  the Philox stream is keyed by (seed, offset + *offset_dev), *offset_dev being a 64-bit word in
+ *               device memory (8-byte aligned) read when the kernel runs.  A launch that is recorded once and
+ *               replayed (a CUDA graph of the training step) draws fresh uniforms on every replay if the caller
+ *               bumps that word between replays.  The reference draws a new host seed per call
+ *               (sparse/_semi_structured_conversions.py:1076) and has no replayable form.
+ *   e_tc        a second copy of the metadata in the order sp24_spmm reads (sp24_meta_tc_bytes(m, k) bytes, 16-byte
+ *               aligned), which saves the sp24_meta_to_tc launch.  Column-major storage, 16-bit packed types and
+ *               m % 128 == 0 only (the weight-gradient operand dY^T of the training layer).
  */
-int sp24_prune_compress_devoffset(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
-                                  int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta, int mode,
-                                  const void *mask, int64_t ld_mask, const float *uniforms, int64_t ld_uniforms,
-                                  uint64_t seed, uint64_t offset, const uint64_t *offset_dev, void *stream);
+int sp24_prune_compress_ex(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense, int col_major,
+                           void *packed, int packed_dtype, int64_t ld_packed, void *meta, int mode, const void *mask,
+                           int64_t ld_mask, const float *uniforms, int64_t ld_uniforms, uint64_t seed, uint64_t offset,
+                           const uint64_t *offset_dev, void *e_tc, void *stream);
 
 /*
  * 2:4 compressed -> dense (zeros at pruned positions).  Replaces
@@ -159,6 +163,16 @@ int sp24_transposable_select(const void *x, int dtype, int64_t m, int64_t k, int
 int sp24_select_dual_compress(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select, void *mask,
                               int64_t ld_mask, void *packed_w, int packed_dtype, int64_t ld_packed_w, void *meta_w,
                               void *packed_t, int64_t ld_packed_t, void *meta_t, void *stream);
+
+/*
+ * sp24_select_dual_compress, which also writes the metadata of W (tc_w, sp24_meta_tc_bytes(m, k) bytes) and of
+ * W^T (tc_t, sp24_meta_tc_bytes(k, m) bytes) in the order sp24_spmm reads, so that neither operand needs an
+ * sp24_meta_to_tc launch.  m % 128 == 0 and k % 128 == 0.  No counterpart in the reference.
+ */
+int sp24_select_dual_compress_tc(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select, void *mask,
+                                 int64_t ld_mask, void *packed_w, int packed_dtype, int64_t ld_packed_w, void *meta_w,
+                                 void *packed_t, int64_t ld_packed_t, void *meta_t, void *tc_w, void *tc_t,
+                                 void *stream);
 
 /*
  * Masked decay, in place: grad[i] += p[i] * alpha where mask[i] == 0 (two roundings, no fused

@@ -453,3 +453,49 @@ def test_cta_pair_kernel_equals_single_cta_kernel(S, monkeypatch, dtype, a_col, 
     assert torch.equal(outs["0"][0], outs["1"][0]) and torch.equal(outs["0"][1], outs["1"][1])
     wm = sp.to_dense().float()
     check(outs["1"][0], x.float() @ wm.t(), x.float().abs(), wm.abs(), dtype)
+
+
+def _tc_reference(meta, ms, k):
+    """Tensor-core-order copy made by the stand-alone conversion kernel."""
+    from sparse import _ext
+    from sparse.spmm import tc_bytes
+    e = torch.empty(tc_bytes(ms, k), dtype=torch.uint8, device=meta.device)
+    src = meta.contiguous()
+    _ext.check(_ext.lib().sp24_meta_to_tc(src.data_ptr(), src.element_size(), ms, k, e.data_ptr(), _ext.stream()), "meta_to_tc")
+    return e
+
+
+@pytest.mark.parametrize("m,k", [(128, 128), (256, 384), (768, 3072), (2304, 768)])
+@pytest.mark.parametrize("select", [True, False])
+def test_fused_compress_writes_the_tensor_core_metadata_order(S, m, k, select):
+    """The metadata copies the compression kernels write for the GEMM equal what the conversion kernel makes from
+    the reference-layout metadata, bit for bit: W and W^T from the fused select + dual compress, dY^T from the
+    column-major compress (MVUE, magnitude and given-mask modes, K a multiple of 64 only)."""
+    from sparse.spmm import _tc_meta_cache
+    from sparse._semi_structured_conversions import prune_compress
+    from sparse import _ext
+    g = torch.Generator().manual_seed(m + k)
+    w = (torch.randn(m, k, generator=g) * 0.02).to(DEV)
+    mask0 = None
+    if not select:
+        _, mask0 = S.mask_select(w)
+    mask, (pw, mw), (pt, mt) = S.select_and_compress(w, mask=mask0, dtype=torch.bfloat16)
+    for meta, (rows, cols) in ((mw, (m, k)), (mt, (k, m))):
+        fused = _tc_meta_cache[id(meta)][1]
+        assert torch.equal(fused, _tc_reference(meta, rows, cols))
+    # column-major compress of a (rows, tokens) matrix, tokens = 64 * odd exercises the half-filled last atom
+    for mode, tokens in ((_ext.PRUNE_MVUE, 320), (_ext.PRUNE_MSE, 512), (_ext.PRUNE_MASK, 192)):
+        x = torch.randn(tokens, m, generator=g).bfloat16().to(DEV).t()          # (m, tokens), column-major
+        packed = torch.empty(tokens // 2, m, dtype=torch.bfloat16, device=DEV).t()
+        meta = torch.empty(m, tokens // 16, dtype=torch.int16, device=DEV)
+        mk = random_mask(tokens, m, g).to(DEV).t() if mode == _ext.PRUNE_MASK else None
+        prune_compress(x, packed, meta, mode=mode, mask=mk, seed=3)
+        fused = _tc_meta_cache[id(meta)][1]
+        ref = _tc_reference(meta, m, tokens)
+        full_atoms = tokens // 128
+        fv, rv = fused.view(m // 128, -1, 2048), ref.view(m // 128, -1, 2048)
+        assert torch.equal(fv[:, :full_atoms], rv[:, :full_atoms])
+        if tokens % 128:
+            # the last atom holds four word columns (slots 2q + h, q < 2); the others are never read with data
+            lines = fv[:, full_atoms].reshape(-1, 128, 8, 2)[:, :, :4], rv[:, full_atoms].reshape(-1, 128, 8, 2)[:, :, :4]
+            assert torch.equal(*lines)
