@@ -929,6 +929,199 @@ spmm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------
+// Two-CTA form of the weight-gradient GEMM: D (ms x n, fp32) += A_sparse (ms x k) * B (k x n, stored row-major).
+// ------------------------------------------------------------------------------------------------
+// Tiles of 256 sparse rows x 256 dense columns per CTA pair (M = 256, N = 256 per instruction); a CTA stages its 128
+// rows of A (16 KB), its 128 columns of B as two 64-column boxes of 128 K-rows (32 KB) and 2 KB of metadata per K
+// step of 128: 50 KB for 8.4 dense-equivalent MFLOP, four stages.  K is cut into slices (work unit = tile x slice)
+// so that the units fill the pairs; every unit adds its partial product with fp32 vector reductions.  One
+// accumulator of 256 columns per CTA: a pair that owns more than one unit drains it before the next unit's MMAs.
+namespace two {
+constexpr int BN3 = 256;
+constexpr int B3_BYTES = (BN3 / 2) * 256;                  // 128 columns x 128 K-rows x 2 bytes
+constexpr int STAGE3_BYTES = A_STAGE_BYTES + B3_BYTES + 2048;   // 51200
+constexpr int STAGES3 = 4;
+constexpr int SMEM3 = STAGES3 * STAGE3_BYTES + 1024;
+static_assert(STAGE3_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+static_assert(SMEM3 <= 227 * 1024, "shared memory budget");
+}  // namespace two
+
+template <bool A_MN>
+__global__ void __launch_bounds__(320, 1)
+spmm_pair_acc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_e, SpmmParams P) {
+    using namespace two;
+    constexpr int BN = BN3;
+    constexpr int STAGES = STAGES3;
+    constexpr int OFF_B = A_STAGE_BYTES, OFF_E = OFF_B + B3_BYTES;
+    constexpr int KSTEPS = 4;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr int E_COL0 = BN, E_SLOT = 4;       // one accumulator, then two metadata slots
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 2];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int n_tiles_n = (int)((P.n + BN - 1) / BN);
+    const int n_tiles_m = (int)(P.ms / (2 * BM));
+    const int n_tiles = n_tiles_n * n_tiles_m;
+    const int n_units = n_tiles * P.k_splits;     // unit u = (tile u % n_tiles, K slice u / n_tiles)
+    const int k_iters = (int)((P.k + 127) / 128);
+
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t tmem_full = smem_u32(&bars[2 * STAGES]), tmem_empty = smem_u32(&bars[2 * STAGES + 1]);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty, 16);            // used in the leader only: eight epilogue warps of each CTA
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(&tmem_base_smem), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (one per CTA)
+        if (lane == 0) {
+            int g = 0;
+            bool ok = true;
+            constexpr uint32_t cta_tx = A_STAGE_BYTES + 2048 + B3_BYTES;
+            for (int unit = pair; unit < n_units && ok; unit += n_pairs) {
+                const int tile = unit % n_tiles, ks = unit / n_tiles;
+                const int it0 = (int)((int64_t)ks * k_iters / P.k_splits), it1 = (int)((int64_t)(ks + 1) * k_iters / P.k_splits);
+                const int mblk = (tile % n_tiles_m) * 2 + (int)rank;
+                const int mrow = mblk * BM;
+                const int bcol = (tile / n_tiles_m) * BN + (int)rank * (BN / 2);
+                for (int it = it0; it < it1; ++it, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (g / STAGES) & 1;
+                    if (g >= STAGES && !mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, P.status, 1)) { ok = false; break; }
+                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE3_BYTES);
+                    const uint32_t sb = sa + OFF_B;
+                    const uint32_t full_leader = map_to_cta(full0 + 8 * s, 0);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * cta_tx);
+                    if constexpr (!A_MN) {
+                        tma_load_2d_pair(sa, &map_a, it * 64, mrow, full_leader);
+                    } else {
+                        tma_load_2d_pair(sa, &map_a, mrow, it * 64, full_leader);
+                        tma_load_2d_pair(sa + 8192, &map_a, mrow + 64, it * 64, full_leader);
+                    }
+                    tma_load_2d_pair(sa + OFF_E, &map_e, 0, (int)(((int64_t)mblk * P.k_atoms + it) * 2), full_leader);
+                    // this CTA's 128 columns of B: two boxes of 64 columns x 128 K-rows
+                    tma_load_2d_pair(sb, &map_b, bcol, it * 128, full_leader);
+                    tma_load_2d_pair(sb + 16384, &map_b, bcol + 64, it * 128, full_leader);
+                }
+            }
+            if (abort_flag && rank == 0) {
+                for (int q = (g > STAGES ? g - STAGES : 0); q < g; ++q) {
+                    const int s = q % STAGES;
+                    const uint32_t ph = (q / STAGES) & 1;
+                    for (uint32_t w = 0; w < WAIT_LIMIT; ++w)
+                        if (mbar_try_wait(full0 + 8 * s, ph)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t A_LBO = A_MN ? 8192 : 16, A_KSTEP = A_MN ? 2048 : 32;
+            const uint32_t idesc0 = P.idesc;   // M = 256, N = 256, B MN-major set by the launcher
+            int g = 0, tl = 0;
+            bool ok = true;
+            for (int unit = pair; unit < n_units && ok; unit += n_pairs, ++tl) {
+                const int ks = unit / n_tiles;
+                const int it0 = (int)((int64_t)ks * k_iters / P.k_splits), it1 = (int)((int64_t)(ks + 1) * k_iters / P.k_splits);
+                // the epilogues of both CTAs must have drained the accumulator of the previous unit
+                ok = mbar_wait(tmem_empty, (tl & 1) ^ 1, &abort_flag, P.status, 4);
+                for (int it = it0; it < it1 && ok; ++it, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (g / STAGES) & 1;
+                    ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, P.status, 2);
+                    if (!ok) break;
+                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE3_BYTES);
+                    const uint32_t sb = sa + OFF_B;
+                    tc_fence_after();
+                    const uint32_t e_cols = E_COL0 + (g & 1) * E_SLOT;
+                    tc_cp_128x128b_pair(tmem_base + e_cols, make_desc(sa + OFF_E, 16, 128, 0));
+#pragma unroll
+                    for (int j = 0; j < KSTEPS; ++j) {
+                        const uint64_t adesc = make_desc(sa + j * A_KSTEP, A_LBO, 1024, 2);
+                        // MN-major B: 64-column blocks 16384 bytes apart, 32 K-rows (4096 bytes) per MMA
+                        const uint64_t bdesc = make_desc(sb + j * 4096, 16384, 1024, 2);
+                        const uint32_t ecol = e_cols + j;
+                        mma_sp_pair(tmem_base, adesc, bdesc, tmem_base + (ecol & ~1u), idesc0 | (ecol & 1u),
+                                    (it > it0 || j > 0) ? 1u : 0u);
+                    }
+                    tc_commit_pair(empty0 + 8 * s);
+                }
+                tc_commit_pair(tmem_full);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..9 of both CTAs)
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        constexpr int HC = BN / 2;                     // 128 columns per warp
+        float *out = static_cast<float *>(P.out);
+        const uint32_t empty_leader = map_to_cta(tmem_empty, 0);
+        int tl = 0;
+        for (int unit = pair; unit < n_units; unit += n_pairs, ++tl) {
+            const int tile = unit % n_tiles;
+            const int mrow = ((tile % n_tiles_m) * 2 + (int)rank) * BM + quad * 32 + lane;
+            const int64_t col0 = (int64_t)(tile / n_tiles_m) * BN + half * HC;
+            const bool ok = mbar_wait(tmem_full, tl & 1, &abort_flag, P.status, 3);
+            tc_fence_after();
+            const bool run = ok && !abort_flag;
+            if (run) {
+                const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + half * HC;
+                float *row = out + (int64_t)mrow * P.ld_out + col0;
+#pragma unroll 1
+                for (int c = 0; c < HC / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(acc + c * 32, v);
+                    tmem_ld_wait();
+                    const int64_t nb = col0 + c * 32;
+                    if (nb + 32 <= P.n) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            red_add_v4(row + c * 32 + q * 4, __uint_as_float(v[q * 4]), __uint_as_float(v[q * 4 + 1]),
+                                       __uint_as_float(v[q * 4 + 2]), __uint_as_float(v[q * 4 + 3]));
+                    } else {
+                        for (int i = 0; i < 32; ++i)
+                            if (nb + i < P.n) atomicAdd(row + c * 32 + i, __uint_as_float(v[i]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(empty_leader);
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // metadata: reference (reordered) layout -> tensor-core atom order
 // ------------------------------------------------------------------------------------------------
 // 16-bit types: atom = 128 rows x 128 logical columns = 2048 bytes, byte 16*L + 4*q + 2*h with
@@ -1092,6 +1285,45 @@ int launch_spmm_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtenso
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, kern, ma, mb, me, P) != cudaSuccess) return SP24_ERR_CUDA;
+    return launch_status();
+}
+
+template <bool A_MN>
+int launch_spmm_pair_acc(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &me, SpmmParams P, int k_splits,
+                         cudaStream_t st) {
+    auto kern = spmm_pair_acc_kernel<A_MN>;
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, two::SMEM3) != cudaSuccess)
+            return launch_status();
+        attr_set[dev] = true;
+    }
+    // M = 256 over the CTA pair, N = 256
+    P.idesc = (P.idesc & ~(0x1Fu << 24)) | ((uint32_t)(256 >> 4) << 24) | ((uint32_t)(two::BN3 >> 3) << 17);
+    const int64_t tiles = ((P.n + two::BN3 - 1) / two::BN3) * (P.ms / 256);
+    const int64_t pairs_max = sm_count_cached() / 2;
+    const int64_t k_iters = (P.k + 127) / 128;
+    int64_t splits = k_splits ? k_splits : pairs_max / tiles;
+    if (splits < 1) splits = 1;
+    if (splits > k_iters) splits = k_iters;
+    P.k_splits = (int)splits;
+    const int64_t units = tiles * splits;
+    const unsigned pairs = (unsigned)(units < pairs_max ? units : pairs_max);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(320, 1, 1);
+    cfg.dynamicSmemBytes = two::SMEM3;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, ma, mb, me, P) != cudaSuccess) return launch_status();
     return launch_status();
 }
 
@@ -1336,6 +1568,17 @@ extern "C" int sp24_spmm_accumulate_f32(const void *a_packed, int dtype, int a_m
     const uint32_t fmt = dtype == SP24_BF16 ? 1u : 0u;
     P.idesc = (1u << 2) | (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) | (1u << 16) |
               ((uint32_t)(BM >> 4) << 24);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // CTA-pair kernel for whole 256-row blocks and at least one full tile of columns
+    bool pair_form = ms % 256 == 0 && n >= 256;
+    if (const char *env = getenv("SP24_SPMM_PAIR")) pair_form = pair_form && atoi(env) != 0;
+    if (pair_form) {
+        CUtensorMap map_e;
+        rc = make_map_e(&map_e, e_tc, (ms / 128) * P.k_atoms);
+        if (rc) return rc;
+        return a_mn_major ? launch_spmm_pair_acc<true>(map_a, map_b, map_e, P, k_splits, st)
+                          : launch_spmm_pair_acc<false>(map_a, map_b, map_e, P, k_splits, st);
+    }
     // widest tile (least operand traffic per output), then as many K slices as idle SMs allow
     const int sms = sm_count_cached();
     const bool wide = n >= 192;
@@ -1347,7 +1590,6 @@ extern "C" int sp24_spmm_accumulate_f32(const void *a_packed, int dtype, int a_m
     if (splits < 1) splits = 1;
     if (splits > k_iters) splits = k_iters;
     P.k_splits = (int)splits;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     // fp16 and bf16 operands share these kernels: the element type only enters through the tensor maps and the
     // instruction descriptor
     if (a_mn_major) return wide ? launch_spmm<192, false, true, true, false, float>(map_a, map_b, P, st)

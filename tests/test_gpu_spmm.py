@@ -361,7 +361,8 @@ def test_token_count_need_not_be_a_multiple_of_eight(S, n):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("a_col", [False, True])
-@pytest.mark.parametrize("ms,k,n,splits", [(128, 64, 8, 0), (256, 1024, 200, 0), (384, 2048, 192, 1), (512, 4096, 328, 5)])
+@pytest.mark.parametrize("ms,k,n,splits", [(128, 64, 8, 0), (256, 1024, 200, 0), (384, 2048, 192, 1), (512, 4096, 328, 5),
+                                            (768, 8192, 768, 0), (1280, 1024, 520, 3), (256, 192, 256, 0)])
 def test_accumulating_split_k_gemm(S, dtype, a_col, ms, k, n, splits):
     """D += A_sparse B with fp32 reductions: equals the fp32 matmul of the masked operands to fp32 rounding
     (1e-5 of the largest entry), on a zeroed output and on top of an existing gradient."""
