@@ -395,7 +395,7 @@ def run_case(name):
             packed = torch.empty(m, k // 2, dtype=torch.bfloat16, device=dev)
             meta = torch.empty(m, k // 16, dtype=torch.int16, device=dev)
         fn = lambda: prune_compress(g, packed, meta, mode=mode, seed=1)
-    elif name in ("spmm_fwd", "spmm_dx", "spmm_dw"):
+    elif name in ("spmm_fwd", "spmm_dx", "spmm_dw", "spmm_dw_acc"):
         T, K, N = 16384, 768, 3072
         dt = torch.float16
         x = torch.randn(T, K, device=dev).to(dt)
@@ -409,8 +409,12 @@ def run_case(name):
             fn = lambda: torch.mm(x, ws.t())
         elif name == "spmm_dx":
             fn = lambda: torch.mm(dy, wt.t())
-        else:
+        elif name == "spmm_dw":
             fn = lambda: torch.mm(dys, x)
+        else:   # the form the training layer uses: fp32 gradient buffer, split-K, vector reductions
+            from sparse.spmm import sparse_mm_accumulate_
+            gw = torch.zeros(N, K, dtype=torch.float32, device=dev)
+            fn = lambda: sparse_mm_accumulate_(gw, dys.sparse_tensor_cutlass, dys.meta_tensor_cutlass, x)
     elif name == "soft":
         g = (torch.randn(16384, 4096, device=dev) * 1e-3).bfloat16()
         fn = lambda: sparse.soft_threshold24_triton(g)
