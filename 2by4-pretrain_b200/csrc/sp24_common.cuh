@@ -229,6 +229,7 @@ inline int dtype_size(int dt) {
         case SP24_F32: return 4;
         case SP24_F16: case SP24_BF16: return 2;
         case SP24_E4M3: case SP24_E5M2: case SP24_I8: return 1;
+        case SP24_I32: return 4;
         default: return 0;
     }
 }

@@ -97,13 +97,21 @@ __device__ __forceinline__ void tc_cp_128x128b(uint32_t taddr, uint64_t sdesc) {
 }
 template <bool F8>
 __device__ __forceinline__ void mma_sp(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t e_tmem, uint32_t idesc,
-                                       uint32_t accumulate) {
+                                       uint32_t accumulate, int int8 = 0) {
     if constexpr (F8) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
-            "tcgen05.mma.sp.cta_group::1.kind::f8f6f4 [%0], %1, %2, [%3], %4, p;\n\t}" ::"r"(d_tmem),
-            "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
-            : "memory");
+        if (int8) {   // signed 8-bit integers, 32-bit integer accumulators; same operand geometry as fp8
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                "tcgen05.mma.sp.cta_group::1.kind::i8 [%0], %1, %2, [%3], %4, p;\n\t}" ::"r"(d_tmem),
+                "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+                : "memory");
+        } else {
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                "tcgen05.mma.sp.cta_group::1.kind::f8f6f4 [%0], %1, %2, [%3], %4, p;\n\t}" ::"r"(d_tmem),
+                "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+                : "memory");
+        }
     } else {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
@@ -160,6 +168,7 @@ struct SpmmParams {
     uint32_t idesc;         // instruction descriptor without the metadata selector bits
     int activation;         // 0 none, 1 relu, 2 silu, 3 gelu (tanh form)
     unsigned long long *trace;  // optional timing trace of CTA 0 (debugging aid), else null
+    int int8;               // 8-bit operands are signed integers (kind::i8, int32 accumulators and output)
     int k_splits;           // work units per tile along K (> 1 only for the accumulating fp32 output)
     int mblk_per_tile;      // 128-row blocks per tile: 2 (B staged once per 256 rows) or 1 (more, smaller tiles)
 };
@@ -168,10 +177,12 @@ template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
 template <> __device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ int32_t to_out<int32_t>(float v) { return __float_as_int(v); }
 template <typename OutT> __device__ __forceinline__ float from_out(OutT v);
 template <> __device__ __forceinline__ float from_out<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float from_out<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float from_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ float from_out<int32_t>(int32_t) { return 0.f; }   // no bias for integer GEMMs
 
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == 1) return v > 0.f ? v : 0.f;
@@ -188,6 +199,18 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 template <bool ACT> __device__ __forceinline__ float finish(float v, int act) {
     if constexpr (ACT) return apply_act(v, act);
     return v;
+}
+
+// One accumulator word -> one output value.  Integer accumulators pass through untouched: no float operation may
+// see their bits (an add of 0.0f would rewrite -0.0 and signalling-NaN patterns, which are ordinary integers).
+template <typename OutT, bool ACT> __device__ __forceinline__ OutT emit(uint32_t acc_bits, float bias, int act) {
+    if constexpr (std::is_same<OutT, int32_t>::value) return (int32_t)acc_bits;
+    else return to_out<OutT>(finish<ACT>(__uint_as_float(acc_bits) + bias, act));
+}
+// the same, as the 32-bit container of a 4-byte output type
+template <typename OutT, bool ACT> __device__ __forceinline__ uint32_t emit_bits(uint32_t acc_bits, float bias, int act) {
+    if constexpr (std::is_same<OutT, int32_t>::value) return acc_bits;
+    else return __float_as_uint(finish<ACT>(__uint_as_float(acc_bits) + bias, act));
 }
 
 __device__ __forceinline__ unsigned long long globaltimer() {
@@ -387,7 +410,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             // 16-bit types: the instruction takes the even column of a pair plus a 1-bit selector
                             const uint32_t e_addr = tmem_base + (F8 ? ecol : (ecol & ~1u));
                             const uint32_t idesc = P.idesc | (F8 ? 0u : (ecol & 1u));
-                            mma_sp<F8>(tmem_base + mb * BN, adesc, bdesc, e_addr, idesc, (it > it0 || j > 0) ? 1u : 0u);
+                            mma_sp<F8>(tmem_base + mb * BN, adesc, bdesc, e_addr, idesc, (it > it0 || j > 0) ? 1u : 0u, P.int8);
                         }
                     }
                     tc_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
@@ -443,7 +466,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             Vec<OutT, 8> o;
 #pragma unroll
                             for (int i = 0; i < 8; ++i)
-                                o.v[i] = to_out<OutT>(finish<ACT>(__uint_as_float(v[q * 8 + i]) + bias0, P.activation));
+                                o.v[i] = emit<OutT, ACT>(v[q * 8 + i], bias0, P.activation);
                             const int piece = (half * HC + c * 32) / 8 + q;
                             *reinterpret_cast<uint4 *>(stg_row + ((piece ^ swz) << 4)) = *reinterpret_cast<const uint4 *>(&o);
                         }
@@ -462,8 +485,8 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
                                 Vec<OutT, 2> o;
-                                o.v[0] = to_out<OutT>(finish<ACT>(__uint_as_float(v[2 * i]) + bias1, P.activation));
-                                o.v[1] = to_out<OutT>(finish<ACT>(__uint_as_float(v[2 * i + 1]) + bias1, P.activation));
+                                o.v[0] = emit<OutT, ACT>(v[2 * i], bias1, P.activation);
+                                o.v[1] = emit<OutT, ACT>(v[2 * i + 1], bias1, P.activation);
                                 held[c * 16 + i] = *reinterpret_cast<const uint32_t *>(&o);
                             }
                         }
@@ -555,10 +578,10 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
                                     for (int q = 0; q < 8; ++q) {
                                         float4 o;
-                                        o.x = finish<ACT>(__uint_as_float(v[q * 4 + 0]) + bias, P.activation);
-                                        o.y = finish<ACT>(__uint_as_float(v[q * 4 + 1]) + bias, P.activation);
-                                        o.z = finish<ACT>(__uint_as_float(v[q * 4 + 2]) + bias, P.activation);
-                                        o.w = finish<ACT>(__uint_as_float(v[q * 4 + 3]) + bias, P.activation);
+                                        o.x = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 0], bias, P.activation));
+                                        o.y = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 1], bias, P.activation));
+                                        o.z = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 2], bias, P.activation));
+                                        o.w = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 3], bias, P.activation));
                                         *reinterpret_cast<float4 *>(stg_row + (col + q * 4) * 4) = o;
                                     }
                                 }
@@ -619,13 +642,13 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                         Vec<OutT, PER> o;
 #pragma unroll
                                         for (int i = 0; i < PER; ++i)
-                                            o.v[i] = to_out<OutT>(finish<ACT>(__uint_as_float(v[q * PER + i]) + bias, P.activation));
+                                            o.v[i] = emit<OutT, ACT>(v[q * PER + i], bias, P.activation);
                                         store_vec<OutT, PER>(row + q * PER, o);
                                     }
                                 } else {
                                     for (int i = 0; i < 32; ++i)
                                         if (nb + i < P.n)
-                                            row[i] = to_out<OutT>(finish<ACT>(__uint_as_float(v[i]) + bias, P.activation));
+                                            row[i] = emit<OutT, ACT>(v[i], bias, P.activation);
                                 }
                             }
                         }
@@ -1386,10 +1409,12 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
                          int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype,
                          int trans_out, int64_t ld_out, const void *bias, int activation, int *status, void *stream) {
     if (!a_packed || !e_tc || !b || !out) return SP24_ERR_ARG;
-    const bool f8 = dtype == SP24_E4M3 || dtype == SP24_E5M2;
+    const bool i8 = dtype == SP24_I8;
+    const bool f8 = dtype == SP24_E4M3 || dtype == SP24_E5M2 || i8;   // 8-bit operand geometry
     if (!f8 && dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
-    if (f8 ? out_dtype != SP24_F32 : out_dtype != dtype) return SP24_ERR_DTYPE;
+    if (i8 ? out_dtype != SP24_I32 : (f8 ? out_dtype != SP24_F32 : out_dtype != dtype)) return SP24_ERR_DTYPE;
     if (f8 && (a_mn_major || b_mn_major)) return SP24_ERR_DTYPE;  // 8-bit operands are K-major only
+    if (i8 && (bias || activation)) return SP24_ERR_ARG;          // integer GEMM: plain product only
     if (activation < 0 || activation > 3) return SP24_ERR_ARG;
     const int esz = f8 ? 1 : 2;
     if (ms <= 0 || n <= 0 || k <= 0 || ms % 128 || k % (f8 ? 128 : 64)) return SP24_ERR_SHAPE;
@@ -1414,9 +1439,12 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     P.trace = nullptr;
     P.k_splits = 1;
     if (const char *env = getenv("SP24_SPMM_TRACE_PTR")) P.trace = reinterpret_cast<unsigned long long *>(strtoull(env, nullptr, 0));
-    const uint32_t fmt = (dtype == SP24_BF16 || dtype == SP24_E5M2) ? 1u : 0u;
-    // sparse flag, fp32 accumulate, operand formats, operand majors, M = 128 (N is added by the launcher)
-    P.idesc = (1u << 2) | (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) |
+    // operand format codes: f16 0 / bf16 1; e4m3 0 / e5m2 1; unsigned 0 / signed 1 for the integer kind
+    const uint32_t fmt = (dtype == SP24_BF16 || dtype == SP24_E5M2 || i8) ? 1u : 0u;
+    // sparse flag, accumulator format (fp32 = 1, int32 = 2), operand formats, operand majors, M = 128 (N is added
+    // by the launcher)
+    P.int8 = i8 ? 1 : 0;
+    P.idesc = (1u << 2) | ((i8 ? 2u : 1u) << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) |
               ((uint32_t)(b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BM >> 4) << 24);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // CTA-pair kernel: 16-bit types, token-major B and output, whole 256-row blocks, no activation
@@ -1438,6 +1466,10 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     pick_tile(ms, n, sm_count_cached(), bn, mpt);
     P.mblk_per_tile = mpt;
 #define SP24_GO(F8_, AMN_, BMN_, TR_, OT_) return dispatch_bn<F8_, AMN_, BMN_, TR_, OT_>(bn, b, dtype, n, k, ld_b, map_a, P, st)
+    if (i8) {
+        if (trans_out) SP24_GO(true, false, false, true, int32_t);
+        SP24_GO(true, false, false, false, int32_t);
+    }
     if (f8) {
         if (trans_out) SP24_GO(true, false, false, true, float);
         SP24_GO(true, false, false, false, float);

@@ -12,10 +12,10 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libsparse24_b200.so")
 
-F32, F16, BF16, E4M3, E5M2, I8 = 0, 1, 2, 3, 4, 5
+F32, F16, BF16, E4M3, E5M2, I8, I32 = 0, 1, 2, 3, 4, 5, 6
 PRUNE_MSE, PRUNE_MASK, PRUNE_MVUE = 0, 1, 2
 
-_DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int8: I8}
+_DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int8: I8, torch.int32: I32}
 if hasattr(torch, "float8_e4m3fn"):
     _DT[torch.float8_e4m3fn] = E4M3
     _DT[torch.float8_e5m2] = E5M2

@@ -113,7 +113,11 @@ def sparse_linear(input, weight, meta, bias=None, activation=None):
     # layout_of: 0 = rows contiguous along k (K-major for the GEMM), 1 = k strided (the caller passed B.t())
     b_mn, ld_b = lay_b
     f8 = weight.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
-    out_dtype = torch.float32 if f8 else weight.dtype
+    # fp8 operands give fp32, int8 operands int32 (the reference's table,
+    # sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:594-637,729,772), 16-bit operands their own type
+    out_dtype = torch.float32 if f8 else (torch.int32 if weight.dtype == torch.int8 else weight.dtype)
+    if weight.dtype == torch.int8 and (bias is not None or activation not in (None, "none")):
+        raise RuntimeError("_sparse_semi_structured_linear: the int8 GEMM on sm_100a takes no bias and no activation")
     if bias is not None:
         if bias.dim() != 1 or bias.shape[0] != ms:
             raise RuntimeError(f"_sparse_semi_structured_linear: Expected bias argument to have {ms} elements, but got {bias.numel()}")

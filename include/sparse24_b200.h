@@ -31,7 +31,8 @@ enum {
     SP24_BF16 = 2,
     SP24_E4M3 = 3, /* float8_e4m3fn */
     SP24_E5M2 = 4, /* float8_e5m2 */
-    SP24_I8 = 5
+    SP24_I8 = 5,
+    SP24_I32 = 6   /* output of the int8 sparse GEMM only */
 };
 
 /* pruning rule of the dense -> 2:4 conversion */
@@ -197,7 +198,8 @@ int64_t sp24_meta_tc_bytes(int64_t m, int64_t k);
 int sp24_meta_to_tc(const void *meta, int meta_itemsize, int64_t m, int64_t k, void *e_tc, void *stream);
 
 /*
- * 2:4 sparse GEMM  D (ms x n) = A_sparse (ms x k) * B (k x n) [+ bias[row]] [activation], fp32 accumulate.
+ * 2:4 sparse GEMM  D (ms x n) = A_sparse (ms x k) * B (k x n) [+ bias[row]] [activation], fp32 accumulate
+ * (int32 for int8 operands).
  * Replaces my_sparse_semi_structured_linear and its CUTLASS SparseGemm instantiations
  * (sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:498-817, :34-233; caller
  * sparse/sparse_semi_structured_linear.py:4-5).
@@ -209,7 +211,11 @@ int sp24_meta_to_tc(const void *meta, int meta_itemsize, int64_t m, int64_t k, v
  *              activations X (tokens, k)), 1: stored as (k, n) row-major
  *   out        trans_out = 0: (ms, n) row-major; 1: (n, ms) row-major, i.e. already transposed back to
  *              (tokens, features); leading dimension ld_out
- *   dtype      F16 / BF16 (out_dtype = dtype) or E4M3 / E5M2 (out_dtype = F32, K-major operands only)
+ *   dtype      F16 / BF16 (out_dtype = dtype), E4M3 / E5M2 (out_dtype = F32) or I8 (out_dtype = I32, no bias, no
+ *              activation); the 8-bit types take K-major operands only.  The same table as the reference's
+ *              (sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:594-637, 729, 772).
+ *              16-bit GEMMs with b_mn_major = 0, trans_out = 1, ms % 256 == 0, n >= 1024 and no activation run on
+ *              pairs of CTAs (tcgen05 cta_group::2); the result is bit-equal to the single-CTA kernel's.
  *   bias       ms values in the output type or NULL; activation 0 none, 1 relu, 2 silu, 3 gelu (tanh form; not in the reference)
  *   status     optional device int: set to a non-zero code if a bounded on-device wait gave up
  * Shape rules: ms % 128 == 0, k % 64 == 0 (16-bit) or k % 128 == 0 (8-bit); n % 8 == 0 unless B is stored (n, k)

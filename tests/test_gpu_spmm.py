@@ -500,3 +500,30 @@ def test_fused_compress_writes_the_tensor_core_metadata_order(S, m, k, select):
             # the last atom holds four word columns (slots 2q + h, q < 2); the others are never read with data
             lines = fv[:, full_atoms].reshape(-1, 128, 8, 2)[:, :, :4], rv[:, full_atoms].reshape(-1, 128, 8, 2)[:, :, :4]
             assert torch.equal(*lines)
+
+
+@pytest.mark.parametrize("ms,k,n", [(128, 128, 16), (256, 896, 208), (384, 4096, 1000)])
+@pytest.mark.parametrize("view", [False, True])
+def test_spmm_int8_is_exact(S, monkeypatch, ms, k, n, view):
+    """int8 operands, int32 accumulators and output (tcgen05 kind::i8): integer arithmetic, so the result must
+    equal the int64 matmul of the pruned operands exactly, in both output orders; extreme values included
+    (int32 bit patterns that would be -0.0 or NaN as floats must pass through untouched)."""
+    from sparse import spmm as spmm_mod
+    from sparse.spmm import sparse_linear, check_status
+    g = torch.Generator().manual_seed(ms + k + n)
+    w = torch.randint(-128, 128, (ms, k), generator=g, dtype=torch.int32).to(torch.int8).to(DEV)
+    x = torch.randint(-128, 128, (n, k), generator=g, dtype=torch.int32).to(torch.int8).to(DEV)
+    w[0, :] = -128                      # row 0: large negative sums
+    x[0, :] = 127
+    sp = S.to_sparse_semi_structured(w, dtype=torch.int8)
+    assert sp.meta_tensor_cutlass.dtype == torch.int32
+    monkeypatch.setattr(spmm_mod, "RETURN_TRANSPOSED_VIEW", view)
+    y = sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass)
+    check_status()
+    assert y.dtype == torch.int32 and y.shape == (n, ms)
+    wd = sp.to_dense()
+    ref = (x.cpu().long() @ wd.cpu().long().t())
+    assert int(ref.abs().max()) < 2 ** 31
+    assert torch.equal(y.cpu().long(), ref)
+    with pytest.raises(RuntimeError):
+        sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, bias=torch.zeros(ms, dtype=torch.int32, device=DEV))
