@@ -391,3 +391,83 @@ extern "C" int sp24_masked_add(void *grad, const void *p, const void *mask, int 
     else masked_add_kernel<4><<<blocks, 256, 0, st>>>(g, q, mask, n, alpha);
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Masked decay + AdamW in one pass over a flat fp32 parameter range
+// ---------------------------------------------------------------------------------------------
+namespace sp24 {
+namespace {
+
+struct AdamParams {
+    float *p, *g, *m, *v;
+    const uint8_t *mask;       // may be null: no masked decay
+    int64_t n;
+    float lr, beta1, beta2, eps, weight_decay, alpha;
+    float step;                // optimizer step number (1, 2, ...) when step_dev is null
+    const float *step_dev;     // optional: step number read on the device (replayed launches)
+};
+
+__device__ __forceinline__ void adam_one(float &p, float g, float &m, float &v, bool keep, const AdamParams &P, float inv_bc1,
+                                         float inv_sqrt_bc2) {
+    // masked decay first, with the two roundings of the stand-alone kernel: grad + (p * alpha) on pruned positions
+    if (!keep) g = __fadd_rn(g, __fmul_rn(p, P.alpha));
+    p = p * (1.f - P.lr * P.weight_decay);
+    m = m + (g - m) * (1.f - P.beta1);
+    v = v * P.beta2 + (1.f - P.beta2) * g * g;
+    const float denom = sqrtf(v) * inv_sqrt_bc2 + P.eps;
+    p = p - (P.lr * inv_bc1) * (m / denom);
+}
+
+__global__ void __launch_bounds__(256) adamw_masked_decay_kernel(AdamParams P) {
+    const float t = P.step_dev ? *P.step_dev : P.step;
+    const float inv_bc1 = 1.f / (1.f - powf(P.beta1, t));
+    const float inv_sqrt_bc2 = 1.f / sqrtf(1.f - powf(P.beta2, t));
+    const int64_t n4 = P.n / 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        float4 p = reinterpret_cast<const float4 *>(P.p)[i];
+        const float4 g = reinterpret_cast<const float4 *>(P.g)[i];
+        float4 m = reinterpret_cast<const float4 *>(P.m)[i];
+        float4 v = reinterpret_cast<const float4 *>(P.v)[i];
+        uint32_t mk = 0x01010101u;
+        if (P.mask) mk = reinterpret_cast<const uint32_t *>(P.mask)[i];
+        adam_one(p.x, g.x, m.x, v.x, (mk & 0xFFu) != 0, P, inv_bc1, inv_sqrt_bc2);
+        adam_one(p.y, g.y, m.y, v.y, (mk & 0xFF00u) != 0, P, inv_bc1, inv_sqrt_bc2);
+        adam_one(p.z, g.z, m.z, v.z, (mk & 0xFF0000u) != 0, P, inv_bc1, inv_sqrt_bc2);
+        adam_one(p.w, g.w, m.w, v.w, (mk & 0xFF000000u) != 0, P, inv_bc1, inv_sqrt_bc2);
+        reinterpret_cast<float4 *>(P.p)[i] = p;
+        reinterpret_cast<float4 *>(P.m)[i] = m;
+        reinterpret_cast<float4 *>(P.v)[i] = v;
+    }
+    // tail (n not a multiple of 4)
+    const int64_t i = n4 * 4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < P.n) {
+        const bool keep = P.mask ? P.mask[i] != 0 : true;
+        adam_one(P.p[i], P.g[i], P.m[i], P.v[i], keep, P, inv_bc1, inv_sqrt_bc2);
+    }
+}
+
+}  // namespace
+}  // namespace sp24
+
+extern "C" int sp24_adamw_masked_decay(void *p, const void *grad, const void *mask, void *exp_avg, void *exp_avg_sq, int64_t n,
+                                       float lr, float beta1, float beta2, float eps, float weight_decay, float alpha,
+                                       float step, const float *step_dev, void *stream) {
+    using namespace sp24;
+    if (!p || !grad || !exp_avg || !exp_avg_sq) return SP24_ERR_ARG;
+    if (n < 0) return SP24_ERR_SHAPE;
+    if (n == 0) return SP24_OK;
+    if (!step_dev && !(step >= 1.f)) return SP24_ERR_ARG;
+    if (!aligned16(p) || !aligned16(grad) || !aligned16(exp_avg) || !aligned16(exp_avg_sq) ||
+        (mask && (reinterpret_cast<uintptr_t>(mask) & 3u)))
+        return SP24_ERR_ALIGN;
+    if (int rc = check_device()) return rc;
+    AdamParams P{static_cast<float *>(p), const_cast<float *>(static_cast<const float *>(grad)), static_cast<float *>(exp_avg),
+                 static_cast<float *>(exp_avg_sq), static_cast<const uint8_t *>(mask), n, lr, beta1, beta2, eps, weight_decay,
+                 alpha, step, step_dev};
+    const int64_t n4 = n / 4;
+    int64_t blocks = (n4 + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    adamw_masked_decay_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
+    return launch_status();
+}

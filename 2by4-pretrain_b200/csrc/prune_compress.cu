@@ -436,11 +436,11 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
     if (!aligned16(dense) || !aligned16(packed) || !aligned16(meta) || (mask && !aligned16(mask)) ||
         (uniforms && !aligned16(uniforms)))
         return SP24_ERR_ALIGN;
+    if (e_tc && (so != 2 || !col_major || m % 128 || !aligned16(e_tc))) return SP24_ERR_ARG;
     if (int rc = check_device()) return rc;
     PcParams P{dense, packed, meta, static_cast<const uint8_t *>(mask), uniforms, m, k, ld_dense, ld_packed, ld_mask,
                ld_uniforms, seed, offset, reinterpret_cast<const unsigned long long *>(offset_dev),
                static_cast<int16_t *>(e_tc), (k + 127) / 128};
-    if (e_tc && (so != 2 || !col_major || m % 128 || !aligned16(e_tc))) return SP24_ERR_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dense_dtype) {
         case SP24_F32: return dispatch_out<float>(P, packed_dtype, mode, col_major, st);

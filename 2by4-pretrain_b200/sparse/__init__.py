@@ -5,7 +5,7 @@ classes the reference only lists in its README (``SparseLinearTranspose``,
 ``sparse_linear_transpose``, ``mask_select``).
 """
 from .triton_ops import MVUE24_approx_triton, sparse24_triton, soft_threshold24_triton
-from .decay import masked_add_
+from .decay import masked_add_, adamw_masked_decay_
 from .transposable_semi_structured import TransposableSparse, select_and_compress
 from .semi_structured import to_sparse_semi_structured, SparseSemiStructuredTensor
 from .sparse_ops import (MyLinear, SparseLinear, SparseLinearTranspose, sparse_linear_transpose, sparse_state,
@@ -23,6 +23,7 @@ __all__ = [
     'sparse24_triton',
     'soft_threshold24_triton',
     'masked_add_',
+    'adamw_masked_decay_',
     'TransposableSparse',
     'mask_select',
     'select_and_compress',

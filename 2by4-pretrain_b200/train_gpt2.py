@@ -14,9 +14,9 @@ Masks need no communication: the weights are identical on all ranks after the re
 recomputes the same transposable mask.  MVUE seeds come from Python's ``random``, seeded per rank.
 
 ``--graphs`` replays the step from CUDA graphs instead of launching ~2000 kernels from Python: one graph for
-forward + backward on a mask-refresh step, one for the other steps, one for masked decay + AdamW.  Gradients
-live in one flat fp32 buffer that is all-reduced with a single NCCL call between the graphs (no collective
-is captured).  The MVUE seeds recorded in a graph stay fixed, so the kernels add a device counter, bumped
+forward + backward on a mask-refresh step, one for the other steps, one for masked decay + AdamW (one fused
+kernel launch per parameter segment).  Parameters, gradients and moments live in flat fp32 buffers; the gradient
+buffer is all-reduced with a single NCCL call between the graphs (no collective is captured).  The MVUE seeds recorded in a graph stay fixed, so the kernels add a device counter, bumped
 inside the graph, to their Philox offset: every replay draws fresh uniforms.
 """
 import argparse
@@ -201,17 +201,35 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
     sparse_params = [p for p in params if hasattr(p, "mask") and p.mode == "sparse"]
     for p in sparse_params:
         p.freq = freq
-    # one flat fp32 gradient buffer; every p.grad is a view of it for the whole run
-    flat = torch.zeros(sum(p.numel() for p in params), dtype=torch.float32, device=dev)
-    off = 0
-    for p in params:
-        p.grad = flat[off:off + p.numel()].view_as(p)
-        off += p.numel()
-    decay, no_decay = [], []
-    for n_, p in model.named_parameters():
-        (no_decay if p.dim() < 2 or hasattr(p, "mask") else decay).append(p)
-    opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": no_decay, "weight_decay": 0.0}],
-                            lr=lr, betas=(0.9, 0.95), fused=True, capturable=True)
+    # Flat fp32 buffers for parameters, gradients and AdamW moments, ordered in three segments: (a) weights with
+    # weight decay, (b) sparse weights (no weight decay, masked decay instead), (c) everything else.  Every p.data /
+    # p.grad is a view for the whole run; the update is one fused launch per segment, the all-reduce one call.
+    sparse_ids = {id(p) for p in sparse_params}
+    seg_decay = [p for p in params if p.dim() >= 2 and not hasattr(p, "mask")]
+    seg_sparse = [p for p in params if id(p) in sparse_ids]
+    seg_other = [p for p in params if p.dim() < 2 or (hasattr(p, "mask") and id(p) not in sparse_ids)]
+    order = seg_decay + seg_sparse + seg_other
+    pad = lambda n: (n + 3) // 4 * 4     # keep every tensor (and segment) 16-byte aligned
+    total = sum(pad(p.numel()) for p in order)
+    flat_p = torch.zeros(total, dtype=torch.float32, device=dev)
+    flat = torch.zeros(total, dtype=torch.float32, device=dev)
+    flat_m, flat_v = torch.zeros_like(flat), torch.zeros_like(flat)
+    flat_mask = torch.ones(sum(pad(p.numel()) for p in seg_sparse), dtype=torch.bool, device=dev)
+    off, bounds = 0, []
+    for seg in (seg_decay, seg_sparse, seg_other):
+        start = off
+        for p in seg:
+            n_ = p.numel()
+            flat_p[off:off + n_].copy_(p.data.reshape(-1))
+            p.data = flat_p[off:off + n_].view_as(p)
+            p.grad = flat[off:off + n_].view_as(p)
+            if seg is seg_sparse:
+                m_off = off - start
+                flat_mask[m_off:m_off + n_].copy_(p.mask.reshape(-1))
+                p.mask = flat_mask[m_off:m_off + n_].view_as(p)     # the select kernel refreshes it in place
+            off += pad(n_)
+        bounds.append((start, off))
+    step_dev = torch.zeros(1, dtype=torch.float32, device=dev)
     rng_counter = torch.zeros(1, dtype=torch.int64, device=dev)
     set_device_rng_offset(rng_counter if mode == "sparse" else None)
     static_tok = torch.zeros((batch, seq + 1), dtype=torch.long, device=dev)
@@ -234,11 +252,13 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         return loss.detach()
 
     def update():
-        if mode == "sparse":
-            with torch.no_grad():
-                for p in sparse_params:
-                    sparse.masked_add_(p.grad, p.data, p.mask, alpha=alpha)
-        opt.step()
+        step_dev.add_(1)
+        for (a, b), wd, use_mask in zip(bounds, (0.1, 0.0, 0.0), (False, True, False)):
+            if b > a:
+                sparse.adamw_masked_decay_(flat_p[a:b], flat[a:b], flat_m[a:b], flat_v[a:b], step=step_dev, lr=lr,
+                                           betas=(0.9, 0.95), eps=1e-8, weight_decay=wd,
+                                           mask=flat_mask if (use_mask and mode == "sparse") else None,
+                                           alpha=alpha if use_mask else 0.0)
 
     def next_tokens():
         tok = torch.randint(0, vocab, (batch, seq + 1), generator=gen).pin_memory()
@@ -316,7 +336,7 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         from sparse.spmm import check_status
         check_status()
     set_device_rng_offset(None)
-    del graphs, g_upd, opt, model, flat
+    del graphs, g_upd, model, flat, flat_p, flat_m, flat_v
     torch.cuda.empty_cache()
     if own_group:
         dist.destroy_process_group()

@@ -185,6 +185,19 @@ int sp24_masked_add(void *grad, const void *p, const void *mask, int mask_itemsi
                     void *stream);
 
 /*
+ * Masked decay and the AdamW update in one pass over a flat float32 range (step 2 of the reference recipe,
+ * README.md:205-214 of the reference, followed by torch.optim.AdamW; the reference runs them as separate passes):
+ *   g = grad + p * alpha on pruned positions (mask byte 0; same two roundings as sp24_masked_add), grad elsewhere;
+ *   p *= 1 - lr * weight_decay;  m += (g - m) * (1 - beta1);  v = v * beta2 + (1 - beta2) * g * g;
+ *   p -= lr / (1 - beta1^t) * m / (sqrt(v) / sqrt(1 - beta2^t) + eps).
+ * mask: n bytes or NULL (no decay).  t: `step` (>= 1), or the float at `step_dev` (device memory) when that is not
+ * NULL, for launches that are recorded once and replayed.  All arrays 16-byte aligned.  grad is not modified.
+ */
+int sp24_adamw_masked_decay(void *p, const void *grad, const void *mask, void *exp_avg, void *exp_avg_sq, int64_t n,
+                            float lr, float beta1, float beta2, float eps, float weight_decay, float alpha, float step,
+                            const float *step_dev, void *stream);
+
+/*
  * Metadata re-layout for the tensor cores: the reference's reordered metadata (m*k/16 int16 or m*k/32
  * int32) -> the order tcgen05.mma.sp consumes from tensor memory.  The result is a sequence of 2048-byte
  * atoms, one per (128-row block, 128-column block), row blocks outermost; 16-bit types: atom byte

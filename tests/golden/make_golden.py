@@ -1,9 +1,8 @@
 """Regenerates the golden fixtures in this folder from the reference project's own code.
 
-Run in a container that has the reference checkout (default /root/reference,
-override with REFERENCE_ROOT) and no GPU:
+Run where a checkout of the reference project is available (its path in REFERENCE_ROOT), no GPU needed:
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py
+    REFERENCE_ROOT=<checkout of huyz2023/2by4-pretrain> TRITON_INTERPRET=1 python tests/golden/make_golden.py
 
 What is executed is the reference, not this repository:
   * its pure-PyTorch converter ``_sparse_semi_structured_from_dense`` /
@@ -32,7 +31,9 @@ import torch  # noqa: E402
 import triton  # noqa: E402
 import triton.language as tl  # noqa: E402
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF or not os.path.isdir(os.path.join(REF, "sparse")):
+    raise SystemExit("make_golden.py: set REFERENCE_ROOT to a checkout of the reference project (the folder holding sparse/)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

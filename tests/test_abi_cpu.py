@@ -77,6 +77,25 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.sp24_masked_add(p, q, r, 1, 0, 0.5, None) == 0  # empty input is a no-op
     assert lib.sp24_sparse24(p, F16, 32, 12, 12, 0, q, 12, r, 12, None) == -1
     assert lib.sp24_to_dense(p, F32, 32, 64, 32, q, r, 64, None) == -3
+    # the newer entry points validate in the same way
+    from sparse import spmm  # noqa: F401  (binds the GEMM signatures)
+    I8, I32, BF16 = 5, 6, 2
+    st = ctypes.c_void_p(base + 12288)
+    # sparse GEMM: rows of the sparse operand not a multiple of 128; int8 wants an int32 output and no bias
+    assert lib.sp24_spmm(p, F16, 0, 64, q, 64, 128, r, 0, 128, 8, st, F16, 1, 64, None, 0, None, None) == -1
+    assert lib.sp24_spmm(p, I8, 0, 64, q, 128, 128, r, 0, 128, 8, st, F32, 1, 128, None, 0, None, None) == -3
+    assert lib.sp24_spmm(p, I8, 0, 64, q, 128, 128, r, 0, 128, 8, st, I32, 1, 128, r, 0, None, None) == -5
+    # accumulating form: fp8 is not accepted, n must keep 16-byte rows
+    assert lib.sp24_spmm_accumulate_f32(p, 3, 0, 64, q, 128, 128, r, 8, 8, st, 8, 0, st, None) == -3
+    assert lib.sp24_spmm_accumulate_f32(p, BF16, 0, 64, q, 128, 128, r, 12, 12, st, 12, 0, st, None) == -1
+    # fused optimizer: null moments, unaligned mask, step 0
+    assert lib.sp24_adamw_masked_decay(p, q, None, None, r, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 1.0, None, None) == -5
+    assert lib.sp24_adamw_masked_decay(p, q, ctypes.c_void_p(base + 1), r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 1.0, None,
+                                       None) == -4
+    assert lib.sp24_adamw_masked_decay(p, q, None, r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 0.0, None, None) == -5
+    # tensor-core metadata copies need whole 128-row / 128-column blocks
+    assert lib.sp24_select_dual_compress_tc(p, F16, 64, 128, 128, 1, q, 128, q, F16, 64, r, q, 128, r, st, st, None) == -1
+    assert lib.sp24_prune_compress_ex(p, F16, 128, 64, 64, 0, q, F16, 32, r, 0, None, 0, None, 0, 0, 0, None, st, None) == -5
 
 
 def test_missing_library_fails_loudly(monkeypatch):

@@ -467,3 +467,48 @@ def test_large_matrix_round_trip(S):
     sl = x[:, :256].t().contiguous().cpu()                                       # first 256 rows of x^T
     wp, wm = O.prune_compress(sl, torch.bfloat16)
     assert same_bits(db[:256].cpu(), O.to_dense(wp, wm))
+
+
+@pytest.mark.parametrize("n", [4096 * 3, 1001])
+def test_fused_masked_decay_adamw_matches_the_two_pass_recipe(S, n):
+    """masked_add_ followed by torch.optim.AdamW (the reference recipe) against the one-pass kernel, five steps:
+    same parameters and moments to float32 rounding of the differently ordered arithmetic."""
+    g = torch.Generator().manual_seed(n)
+    p0 = torch.randn(n, generator=g) * 0.02
+    mask = (torch.rand(n, generator=g) < 0.5)
+    grads = [torch.randn(n, generator=g) * 1e-3 for _ in range(5)]
+    lr, betas, eps, wd, alpha = 6e-4, (0.9, 0.95), 1e-8, 0.1, 2e-4
+    # reference: two passes
+    pr = torch.nn.Parameter(p0.clone().to(DEV))
+    opt = torch.optim.AdamW([pr], lr=lr, betas=betas, eps=eps, weight_decay=wd)
+    for gr in grads:
+        pr.grad = gr.clone().to(DEV)
+        S.masked_add_(pr.grad, pr.data, mask.to(DEV), alpha=alpha)
+        opt.step()
+    # one pass, host step number and device step number
+    for dev_step in (False, True):
+        p = p0.clone().to(DEV)
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        mk = mask.to(DEV)
+        st = torch.zeros(1, device=DEV)
+        for i, gr in enumerate(grads):
+            gd = gr.clone().to(DEV)
+            keep = gd.clone()
+            st += 1
+            S.adamw_masked_decay_(p, gd, m, v, step=st if dev_step else i + 1, lr=lr, betas=betas, eps=eps, weight_decay=wd,
+                                  mask=mk, alpha=alpha)
+            assert torch.equal(gd, keep)          # the gradient is read only
+        state = opt.state[pr]
+        assert torch.allclose(p, pr.data, rtol=2e-5, atol=1e-8)
+        assert torch.allclose(m, state["exp_avg"], rtol=2e-5, atol=1e-10)
+        assert torch.allclose(v, state["exp_avg_sq"], rtol=2e-5, atol=1e-14)
+    # without a mask it is plain AdamW
+    p = p0.clone().to(DEV)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    pr2 = torch.nn.Parameter(p0.clone().to(DEV))
+    opt2 = torch.optim.AdamW([pr2], lr=lr, betas=betas, eps=eps, weight_decay=wd)
+    for i, gr in enumerate(grads):
+        pr2.grad = gr.clone().to(DEV)
+        opt2.step()
+        S.adamw_masked_decay_(p, gr.clone().to(DEV), m, v, step=i + 1, lr=lr, betas=betas, eps=eps, weight_decay=wd)
+    assert torch.allclose(p, pr2.data, rtol=2e-5, atol=1e-8)
