@@ -220,15 +220,17 @@ template <typename T, typename TOut> __device__ __forceinline__ void pack_row(co
     }
 }
 
-template <typename T, typename TOut, bool SELECT>
+template <typename T, typename TOut, bool SELECT, bool TC>
 // three CTAs per SM for 16-bit inputs (80 registers); fp32 inputs need more registers and keep two
 __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(DualParams P) {
     __shared__ __align__(16) uint16_t smeta_w[4][64];   // 4 column pairs x (32 rows x 2)
     __shared__ __align__(16) uint16_t smeta_t[256];     // 1 column pair x (128 rows x 2)
     __shared__ __align__(4) uint8_t nib_t[8][128];      // [block row][W column]
     __shared__ uint32_t lut[64];
-    __shared__ __align__(16) uint16_t stc_w[32 * 8];    // tensor-core order: 32 rows x 8 words of one atom
-    __shared__ __align__(4) uint16_t stc_t[128 * 2];    // tensor-core order of W^T: [L][h] of one word-column pair
+    // tensor-core order (only in the instantiation that writes it): 32 rows x 8 words of one atom of W, and [L][h] of
+    // one word-column pair of W^T
+    __shared__ __align__(16) uint16_t stc_w[TC ? 32 * 8 : 8];
+    __shared__ __align__(4) uint16_t stc_t[TC ? 128 * 2 : 2];
     load_select_lut(lut);
 
     // A block covers 64 rows x 128 columns as two 32-row halves.  Both halves are loaded up front so that
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
             smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 1, mc & 1)] = (uint16_t)(nib01 >> 16);
             smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 2, mc & 1)] = (uint16_t)nib23;
             smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 3, mc & 1)] = (uint16_t)(nib23 >> 16);
-            if (P.tc_w) {
+            if constexpr (TC) {
                 // rows rr = warp*4 .. warp*4+3 of this 32-row half: L = 16*(rr/16) + 8*(mc%2) + rr%8, h = (rr/8)%2
                 const uint32_t vals[4] = {nib01 & 0xFFFFu, nib01 >> 16, nib23 & 0xFFFFu, nib23 >> 16};
 #pragma unroll
@@ -343,7 +345,7 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
             const uint32_t word = (uint32_t)nb[0] | ((uint32_t)nb[128] << 4) | ((uint32_t)nb[256] << 8) | ((uint32_t)nb[384] << 12);
             smeta_t[(col / 32) * 64 + meta_run_pos<2>(col % 32, par)] = (uint16_t)word;
             // W^T row = W column `col` (0..127 of its 128-row block), word column parity `par`
-            if (P.tc_t) stc_t[2 * (16 * (col >> 4) + 8 * par + (col & 7)) + ((col >> 3) & 1)] = (uint16_t)word;
+            if constexpr (TC) stc_t[2 * (16 * (col >> 4) + 8 * par + (col & 7)) + ((col >> 3) & 1)] = (uint16_t)word;
         }
         __syncthreads();
         // write-out: W metadata 4 pairs x 128 B, W^T metadata up to 512 B
@@ -365,7 +367,8 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
                     *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(smeta_t) + piece * 16);
             }
         }
-        if (P.tc_w && threadIdx.x >= 64 && threadIdx.x < 96) {
+        if constexpr (TC) {
+        if (threadIdx.x >= 64 && threadIdx.x < 96) {
             // 32 lines of 16 bytes, contiguous in the atom of (row block r0/128, column block c0/128)
             const int piece = threadIdx.x - 64;
             const int64_t off = ((r0 >> 7) * (P.k >> 7) + (c0 >> 7)) * 2048 + ((r0 & 127) + piece) * 16;
@@ -373,13 +376,14 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
                 *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(P.tc_w) + off) =
                     *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(stc_w) + piece * 16);
         }
-        if (P.tc_t && threadIdx.x >= 128) {
+        if (threadIdx.x >= 128) {
             // W^T: row block c0/128, word columns r0/16 and r0/16 + 1: one 4-byte piece (h = 0, 1) per line L
             const int L = threadIdx.x - 128;
             const int64_t wc = r0 >> 4;
             const int64_t off = ((c0 >> 7) * (P.m >> 7) + (wc >> 3)) * 2048 + L * 16 + ((wc >> 1) & 3) * 4;
             if (off >= 0 && off + 4 <= P.tc_t_bytes)
                 *reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(P.tc_t) + off) = *reinterpret_cast<const uint32_t *>(&stc_t[2 * L]);
+        }
         }
         __syncthreads();  // the staging arrays are rewritten by the next half
 #pragma unroll
@@ -393,8 +397,14 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
 
 template <typename T, typename TOut> int launch_dual(const DualParams &P, int select, cudaStream_t st) {
     dim3 grid((unsigned)((P.k + 127) / 128), (unsigned)(P.m / 64));
-    if (select) ts_dual_kernel<T, TOut, true><<<grid, 256, 0, st>>>(P);
-    else ts_dual_kernel<T, TOut, false><<<grid, 256, 0, st>>>(P);
+    const bool tc = P.tc_w != nullptr;
+    if (select) {
+        if (tc) ts_dual_kernel<T, TOut, true, true><<<grid, 256, 0, st>>>(P);
+        else ts_dual_kernel<T, TOut, true, false><<<grid, 256, 0, st>>>(P);
+    } else {
+        if (tc) ts_dual_kernel<T, TOut, false, true><<<grid, 256, 0, st>>>(P);
+        else ts_dual_kernel<T, TOut, false, false><<<grid, 256, 0, st>>>(P);
+    }
     return launch_status();
 }
 
