@@ -223,14 +223,12 @@ template <typename T, typename TOut> __device__ __forceinline__ void pack_row(co
 template <typename T, typename TOut, bool SELECT, bool TC>
 // three CTAs per SM for 16-bit inputs (80 registers); fp32 inputs need more registers and keep two
 __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(DualParams P) {
-    __shared__ __align__(16) uint16_t smeta_w[4][64];   // 4 column pairs x (32 rows x 2)
-    __shared__ __align__(16) uint16_t smeta_t[256];     // 1 column pair x (128 rows x 2)
+    // Metadata words are staged in the order they are produced (one cheap store per producer); the few threads
+    // that write them out gather them into the reference's run order (and the tensor-core order) afterwards.
+    __shared__ __align__(8) uint16_t wlin[8 * 8 * 4];   // W: [warp = 4-row group][word column][row in group]
+    __shared__ __align__(4) uint16_t tlin[2 * 128];     // W^T: [word column parity][W column]
     __shared__ __align__(4) uint8_t nib_t[8][128];      // [block row][W column]
     __shared__ uint32_t lut[64];
-    // tensor-core order (only in the instantiation that writes it): 32 rows x 8 words of one atom of W, and [L][h] of
-    // one word-column pair of W^T
-    __shared__ __align__(16) uint16_t stc_w[TC ? 32 * 8 : 8];
-    __shared__ __align__(4) uint16_t stc_t[TC ? 128 * 2 : 2];
     load_select_lut(lut);
 
     // A block covers 64 rows x 128 columns as two 32-row halves.  Both halves are loaded up front so that
@@ -297,22 +295,8 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
         nib23 |= __shfl_xor_sync(0xFFFFFFFFu, nib23, 1);
         nib01 |= __shfl_xor_sync(0xFFFFFFFFu, nib01, 2);
         nib23 |= __shfl_xor_sync(0xFFFFFFFFu, nib23, 2);
-        if ((lane & 3) == 0) {
-            const int mc = lane >> 2;  // metadata column inside the tile (0..7)
-            smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 0, mc & 1)] = (uint16_t)nib01;
-            smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 1, mc & 1)] = (uint16_t)(nib01 >> 16);
-            smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 2, mc & 1)] = (uint16_t)nib23;
-            smeta_w[mc >> 1][meta_run_pos<2>(warp * 4 + 3, mc & 1)] = (uint16_t)(nib23 >> 16);
-            if constexpr (TC) {
-                // rows rr = warp*4 .. warp*4+3 of this 32-row half: L = 16*(rr/16) + 8*(mc%2) + rr%8, h = (rr/8)%2
-                const uint32_t vals[4] = {nib01 & 0xFFFFu, nib01 >> 16, nib23 & 0xFFFFu, nib23 >> 16};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int rr = warp * 4 + i;
-                    stc_w[8 * (16 * (rr >> 4) + 8 * (mc & 1) + (rr & 7)) + 2 * (mc >> 1) + ((rr >> 3) & 1)] = (uint16_t)vals[i];
-                }
-            }
-        }
+        if ((lane & 3) == 0)   // word column lane / 4, rows warp*4 .. warp*4+3: (row 0, row 1) and (row 2, row 3)
+            *reinterpret_cast<uint2 *>(&wlin[(warp * 8 + (lane >> 2)) * 4]) = make_uint2(nib01, nib23);
         // columns of W (= rows of W^T): transpose the 4x4 block of 16-bit values, then the same table lookup
         {
             uint32_t pj[4], nibs = 0;
@@ -343,47 +327,62 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
             const int col = threadIdx.x >> 1, par = threadIdx.x & 1;
             const uint8_t *nb = &nib_t[0][0] + (par * 4) * 128 + col;
             const uint32_t word = (uint32_t)nb[0] | ((uint32_t)nb[128] << 4) | ((uint32_t)nb[256] << 8) | ((uint32_t)nb[384] << 12);
-            smeta_t[(col / 32) * 64 + meta_run_pos<2>(col % 32, par)] = (uint16_t)word;
-            // W^T row = W column `col` (0..127 of its 128-row block), word column parity `par`
-            if constexpr (TC) stc_t[2 * (16 * (col >> 4) + 8 * par + (col & 7)) + ((col >> 3) & 1)] = (uint16_t)word;
+            tlin[par * 128 + col] = (uint16_t)word;
         }
         __syncthreads();
-        // write-out: W metadata 4 pairs x 128 B, W^T metadata up to 512 B
+        // Write-out.  In the reference layout the 64 words of (32 rows x one word-column pair) form one 128-byte
+        // run; its 16-byte piece p holds, in this order, the words (row, parity) = (p,0) (8+p,0) (p,1) (8+p,1)
+        // (16+p,0) (24+p,0) (16+p,1) (24+p,1).
         if (threadIdx.x < 32) {
+            // W: 4 word-column pairs x 8 pieces
             const int pair = threadIdx.x >> 3, piece = threadIdx.x & 7;
             const int64_t cp = c0 / 32 + pair;
             if (cp * 2 < P.k / 16) {
+                auto wd = [&](int q, int par) { return (uint32_t)wlin[((2 * q + (piece >> 2)) * 8 + pair * 2 + par) * 4 + (piece & 3)]; };
+                uint4 o;
+                o.x = wd(0, 0) | (wd(1, 0) << 16); o.y = wd(0, 1) | (wd(1, 1) << 16);
+                o.z = wd(2, 0) | (wd(3, 0) << 16); o.w = wd(2, 1) | (wd(3, 1) << 16);
                 char *dst = reinterpret_cast<char *>(P.meta_w) + (cp * 2 * P.m + 2 * r0) * 2 + piece * 16;
-                *reinterpret_cast<uint4 *>(dst) =
-                    *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(&smeta_w[pair][0]) + piece * 16);
+                *reinterpret_cast<uint4 *>(dst) = o;
             }
         } else if (threadIdx.x < 64) {
-            const int piece = threadIdx.x - 32;
+            // W^T: 4 groups of 32 W columns x 8 pieces, one word-column pair (the 32 rows of this half)
+            const int grp = (threadIdx.x - 32) >> 3, piece = threadIdx.x & 7;
             const int64_t cols_here = (P.k - c0 < 128) ? (P.k - c0) : 128;
-            if (piece * 8 < cols_here * 2) {
+            if (grp * 32 < cols_here) {
+                auto wd = [&](int q, int par) { return (uint32_t)tlin[par * 128 + grp * 32 + q * 8 + piece]; };
+                uint4 o;
+                o.x = wd(0, 0) | (wd(1, 0) << 16); o.y = wd(0, 1) | (wd(1, 1) << 16);
+                o.z = wd(2, 0) | (wd(3, 0) << 16); o.w = wd(2, 1) | (wd(3, 1) << 16);
                 const int64_t cp = r0 / 32;  // column pair of the (k, m) metadata matrix
-                char *dst = reinterpret_cast<char *>(P.meta_t) + (cp * 2 * P.k + 2 * c0) * 2 + piece * 16;
-                *reinterpret_cast<uint4 *>(dst) =
-                    *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(smeta_t) + piece * 16);
+                char *dst = reinterpret_cast<char *>(P.meta_t) + (cp * 2 * P.k + 2 * c0) * 2 + (grp * 8 + piece) * 16;
+                *reinterpret_cast<uint4 *>(dst) = o;
             }
         }
         if constexpr (TC) {
-        if (threadIdx.x >= 64 && threadIdx.x < 96) {
-            // 32 lines of 16 bytes, contiguous in the atom of (row block r0/128, column block c0/128)
-            const int piece = threadIdx.x - 64;
-            const int64_t off = ((r0 >> 7) * (P.k >> 7) + (c0 >> 7)) * 2048 + ((r0 & 127) + piece) * 16;
-            if (off >= 0 && off + 16 <= P.tc_w_bytes)
-                *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(P.tc_w) + off) =
-                    *reinterpret_cast<const uint4 *>(reinterpret_cast<const char *>(stc_w) + piece * 16);
-        }
-        if (threadIdx.x >= 128) {
-            // W^T: row block c0/128, word columns r0/16 and r0/16 + 1: one 4-byte piece (h = 0, 1) per line L
-            const int L = threadIdx.x - 128;
-            const int64_t wc = r0 >> 4;
-            const int64_t off = ((c0 >> 7) * (P.m >> 7) + (wc >> 3)) * 2048 + L * 16 + ((wc >> 1) & 3) * 4;
-            if (off >= 0 && off + 4 <= P.tc_t_bytes)
-                *reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(P.tc_t) + off) = *reinterpret_cast<const uint32_t *>(&stc_t[2 * L]);
-        }
+            // tensor-core order: line L = 16*(r/16) + 8*(c%2) + r%8 of 16 bytes holds the int16 slots 2*((c/2)%4) + (r/8)%2
+            if (threadIdx.x >= 64 && threadIdx.x < 96) {
+                // W: 32 lines, contiguous in the atom of (row block r0/128, column block c0/128)
+                const int L = threadIdx.x - 64, par = (L >> 3) & 1;
+                auto wd = [&](int q, int hh) {
+                    const int rr = 16 * (L >> 4) + 8 * hh + (L & 7);
+                    return (uint32_t)wlin[((rr >> 2) * 8 + 2 * q + par) * 4 + (rr & 3)];
+                };
+                uint4 o;
+                o.x = wd(0, 0) | (wd(0, 1) << 16); o.y = wd(1, 0) | (wd(1, 1) << 16);
+                o.z = wd(2, 0) | (wd(2, 1) << 16); o.w = wd(3, 0) | (wd(3, 1) << 16);
+                const int64_t off = ((r0 >> 7) * (P.k >> 7) + (c0 >> 7)) * 2048 + ((r0 & 127) + L) * 16;
+                if (off >= 0 && off + 16 <= P.tc_w_bytes) *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(P.tc_w) + off) = o;
+            }
+            if (threadIdx.x >= 128) {
+                // W^T: row block c0/128, word columns r0/16 and r0/16 + 1: one 4-byte piece (h = 0, 1) per line L
+                const int L = threadIdx.x - 128, par = (L >> 3) & 1;
+                const int col = 16 * (L >> 4) + (L & 7);
+                const uint32_t o = (uint32_t)tlin[par * 128 + col] | ((uint32_t)tlin[par * 128 + col + 8] << 16);
+                const int64_t wc = r0 >> 4;
+                const int64_t off = ((c0 >> 7) * (P.m >> 7) + (wc >> 3)) * 2048 + L * 16 + ((wc >> 1) & 3) * 4;
+                if (off >= 0 && off + 4 <= P.tc_t_bytes) *reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(P.tc_t) + off) = o;
+            }
         }
         __syncthreads();  // the staging arrays are rewritten by the next half
 #pragma unroll

@@ -383,6 +383,10 @@ def run_case(name):
     elif name == "select":
         w = (torch.randn(8192, 8192, device=dev) * 0.02).half()
         fn = lambda: sparse.mask_select(w)
+    elif name == "dual_given_mask":   # the refresh between mask selections: mask read, both compressions written
+        w = (torch.randn(8192, 8192, device=dev) * 0.02).half()
+        _, mk = sparse.mask_select(w)
+        fn = lambda: sparse.select_and_compress(w, mask=mk)
     elif name in ("mvue_row", "mse_row", "mvue_col", "mse_col"):
         m, k = 16384, 4096
         g = (torch.randn(m, k, device=dev) * 1e-3).bfloat16()
