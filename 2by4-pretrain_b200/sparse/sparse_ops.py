@@ -127,10 +127,12 @@ class sparse_linear_transpose(autograd.Function):
 
 class _fst_linear(autograd.Function):
     """What ``sparse_linear_transpose`` computes, on the raw compressed buffers: no tensor-subclass objects,
-    no cast of the (unused) fp32 weight.  ``weight`` only routes the gradient."""
+    no cast of the (unused) fp32 weight.  ``weight`` only routes the gradient.  With ``into_grad`` the weight
+    gradient is accumulated by the GEMM itself into the existing fp32 ``weight.grad`` (D += A B) and autograd
+    receives no gradient for the weight: no zero-filled temporary, no separate add."""
 
     @staticmethod
-    def forward(ctx, input, weight, pw, mw, pt, mt, bias):
+    def forward(ctx, input, weight, pw, mw, pt, mt, bias, into_grad=False):
         x = input.reshape(-1, input.shape[-1])
         if x.dtype != pw.dtype:
             x = x.to(pw.dtype)
@@ -139,6 +141,7 @@ class _fst_linear(autograd.Function):
         ctx.shape = input.shape
         ctx.has_bias = bias is not None
         ctx.fp32_grad = weight.dtype == torch.float32 and x.shape[1] % 8 == 0
+        ctx.grad_target = weight if (into_grad and ctx.fp32_grad) else None
         output = _spmm(x, pw, mw, bias=b)     # bias added in the GEMM epilogue
         return output.view(*input.shape[:-1], -1)
 
@@ -155,7 +158,11 @@ class _fst_linear(autograd.Function):
             grad_input = _spmm(g, pt, mt).view(ctx.shape)
         if ctx.needs_input_grad[1]:
             gs = to_sparse_semi_structured(g.t(), MVUE24=True, dtype=g.dtype)
-            if ctx.fp32_grad:
+            target = ctx.grad_target
+            if target is not None and target.grad is not None and target.grad.dtype == torch.float32 \
+                    and target.grad.is_contiguous():
+                _spmm_acc(target.grad, gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass, x)
+            elif ctx.fp32_grad:
                 # split-K GEMM with fp32 accumulation: the gradient arrives in the dtype of the master weight
                 grad_weight = torch.zeros((g.shape[1], x.shape[1]), dtype=torch.float32, device=g.device)
                 _spmm_acc(grad_weight, gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass, x)
@@ -163,7 +170,7 @@ class _fst_linear(autograd.Function):
                 grad_weight = _spmm(x.t(), gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass).t()
         if ctx.has_bias and ctx.needs_input_grad[6]:
             grad_bias = g.sum(0)
-        return grad_input, grad_weight, None, None, None, None, grad_bias
+        return grad_input, grad_weight, None, None, None, None, grad_bias, None
 
 
 class SparseLinearTranspose(nn.Linear):
@@ -183,6 +190,9 @@ class SparseLinearTranspose(nn.Linear):
     """
 
     materialize_sparse_tensors = False
+    # True: the weight-gradient GEMM adds straight into an existing fp32 ``weight.grad`` (a trainer that owns flat
+    # gradient buffers and needs no autograd hook on the weight, e.g. the graph-replayed one); False: autograd gets it
+    accumulate_into_grad = False
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, func=lambda step: 'dense', **kwargs):
         super().__init__(in_features, out_features, bias=bias, **kwargs)
@@ -238,7 +248,7 @@ class SparseLinearTranspose(nn.Linear):
             elif w.compressed is None:   # state restored in the middle of an accumulation window
                 self._refresh(reselect=False)
             pw, mw, pt, mt = w.compressed
-            x = _fst_linear.apply(x, w, pw, mw, pt, mt, self.bias)
+            x = _fst_linear.apply(x, w, pw, mw, pt, mt, self.bias, self.accumulate_into_grad)
 
         if self.training:
             if w.cnt == 0:

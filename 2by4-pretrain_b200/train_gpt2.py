@@ -197,6 +197,9 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         own_group = True
     random.seed(1234 + rank)
     model = build(mode, dev, layers, d, heads, seq, vocab)
+    for mod in model.modules():   # weight gradients are added into the flat buffer by the GEMM itself
+        if hasattr(mod, "accumulate_into_grad"):
+            mod.accumulate_into_grad = True
     params = [p for p in model.parameters()]
     sparse_params = [p for p in params if hasattr(p, "mask") and p.mode == "sparse"]
     for p in sparse_params:

@@ -527,3 +527,25 @@ def test_spmm_int8_is_exact(S, monkeypatch, ms, k, n, view):
     assert torch.equal(y.cpu().long(), ref)
     with pytest.raises(RuntimeError):
         sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, bias=torch.zeros(ms, dtype=torch.int32, device=DEV))
+
+
+def test_weight_gradient_accumulates_into_an_existing_grad_buffer(S):
+    """accumulate_into_grad: the dW GEMM adds into weight.grad itself (two backward passes add up) and autograd
+    receives nothing for the weight; same values as the autograd route with the same MVUE seeds."""
+    torch.manual_seed(3)
+    a = S.SparseLinearTranspose(256, 384, bias=True).to(DEV)
+    b = S.SparseLinearTranspose(256, 384, bias=True).to(DEV)
+    b.load_state_dict(a.state_dict())
+    b.accumulate_into_grad = True
+    b.weight.grad = torch.zeros_like(b.weight)
+    buf = b.weight.grad
+    x = torch.randn(4, 64, 256, device=DEV)
+    for _ in range(2):
+        for layer in (a, b):
+            random.seed(77)
+            layer.weight.cnt = 0
+            layer(x).float().square().sum().backward()
+    assert b.weight.grad is buf                      # same buffer, filled by the GEMM
+    ga, gb = a.weight.grad, b.weight.grad
+    assert float((ga - gb).abs().max() / ga.abs().max()) < 1e-5
+    assert torch.allclose(a.bias.grad, b.bias.grad)
