@@ -549,3 +549,32 @@ def test_weight_gradient_accumulates_into_an_existing_grad_buffer(S):
     ga, gb = a.weight.grad, b.weight.grad
     assert float((ga - gb).abs().max() / ga.abs().max()) < 1e-5
     assert torch.allclose(a.bias.grad, b.bias.grad)
+
+
+def test_spmm_random_shapes_agree_with_the_reference(S):
+    """Thirty seeded random problems (rows, K, tokens, dtype, operand storage orders, bias): every one within the
+    stated tolerance of the fp32 matmul of the pruned operands, whichever kernel the dispatcher picks."""
+    from sparse.spmm import sparse_linear, check_status
+    rng = random.Random(20240611)
+    g = torch.Generator().manual_seed(99)
+    for case in range(30):
+        ms = 128 * rng.randint(1, 10)
+        k = 64 * rng.randint(1, 40)
+        n = rng.choice([1, 7, 8, 100, 191, 192, 193, 1000, 1024, 1500, 2048 + rng.randint(0, 63)])
+        dtype = rng.choice([torch.float16, torch.bfloat16])
+        a_col, use_bias = rng.random() < 0.5, rng.random() < 0.5
+        w = torch.randn(ms, k, generator=g).to(dtype).to(DEV)
+        mask = random_mask(ms, k, g).to(DEV)
+        x = torch.randn(n, k, generator=g).to(dtype).to(DEV)
+        b = torch.randn(ms, generator=g).to(dtype).to(DEV) if use_bias else None
+        src, mk = (w.t().contiguous().t(), mask.t().contiguous().t()) if a_col else (w, mask)
+        sp = S.to_sparse_semi_structured(src, mask=mk, dtype=dtype)
+        y = sparse_linear(x, sp.sparse_tensor_cutlass, sp.meta_tensor_cutlass, bias=b)
+        wm = torch.where(mask, w, torch.zeros((), dtype=dtype, device=DEV)).float()
+        ref = x.float() @ wm.t() + (b.float() if use_bias else 0.0)
+        bound = x.float().abs() @ wm.abs().t() + (b.float().abs() if use_bias else 0.0)
+        tol = TOL[dtype]
+        err = (y.float() - ref).abs()
+        assert float(err.max() / ref.abs().max()) <= tol, (case, ms, k, n, dtype, a_col, use_bias)
+        assert bool((err <= tol * bound + 1e-30).all()), (case, ms, k, n, dtype, a_col, use_bias)
+    check_status()
