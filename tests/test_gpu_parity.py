@@ -512,3 +512,38 @@ def test_fused_masked_decay_adamw_matches_the_two_pass_recipe(S, n):
         opt2.step()
         S.adamw_masked_decay_(p, gr.clone().to(DEV), m, v, step=i + 1, lr=lr, betas=betas, eps=eps, weight_decay=wd)
     assert torch.allclose(p, pr2.data, rtol=2e-5, atol=1e-8)
+
+
+def test_prune_compress_random_shapes_match_the_oracle(S):
+    """Twenty-four seeded random conversions (shape, dtype pair, storage order, pruning rule): packed values and
+    reordered metadata equal the oracle's bit for bit."""
+    import random as _r
+    from sparse._semi_structured_conversions import prune_compress
+    from sparse import _ext
+    rng = _r.Random(4242)
+    g = torch.Generator().manual_seed(17)
+    for case in range(24):
+        m = 32 * rng.randint(1, 9)
+        k = 64 * rng.randint(1, 9)
+        din = rng.choice([torch.float32, torch.float16, torch.bfloat16])
+        dout = rng.choice([torch.float16, torch.bfloat16])
+        col = rng.random() < 0.5
+        mode = rng.choice(["mse", "mask", "mvue"])
+        x = (torch.randn(m, k, generator=g) * rng.choice([1e-3, 1.0, 50.0])).to(din)
+        xin = x.t().contiguous().t() if col else x
+        packed = (torch.empty(k // 2, m, dtype=dout, device=DEV).t() if col else torch.empty(m, k // 2, dtype=dout, device=DEV))
+        meta = torch.empty(m, k // 16, dtype=torch.int16, device=DEV)
+        kwargs, okw = {}, {}
+        if mode == "mask":
+            pats = torch.tensor([[1, 1, 0, 0], [1, 0, 1, 0], [1, 0, 0, 1], [0, 1, 1, 0], [0, 1, 0, 1], [0, 0, 1, 1]], dtype=torch.bool)
+            mk = pats[torch.randint(0, 6, (m, k // 4), generator=g)].reshape(m, k)
+            kwargs["mask"] = (mk.t().contiguous().t() if col else mk).to(DEV)
+            okw["mask"] = mk
+        if mode == "mvue":
+            kwargs["seed"], kwargs["offset"] = 1000 + case, case
+            okw.update(mvue=True, seed=1000 + case, offset=case)
+        code = {"mse": _ext.PRUNE_MSE, "mask": _ext.PRUNE_MASK, "mvue": _ext.PRUNE_MVUE}[mode]
+        prune_compress(xin.to(DEV), packed, meta, mode=code, **kwargs)
+        op, om = O.prune_compress(x, dout, **okw)[:2]
+        assert same_bits(packed.cpu().contiguous(), op), (case, m, k, din, dout, col, mode)
+        assert torch.equal(meta.cpu(), om), (case, m, k, din, dout, col, mode)
