@@ -232,6 +232,31 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
                 reinterpret_cast<const char *>(&smeta[pair][0]) + piece * 16);
         }
     }
+    if constexpr (MB == 2) {
+        if (P.tc && threadIdx.x < 128) {
+            // Second copy in tensor-core order, gathered from the staged runs: the tile's 32 rows x 32 word columns
+            // are 32 whole 16-byte lines in each of four atoms.  Line L holds rows 16*(L/16) + 8*h + L%8 (h = 0, 1) of
+            // word columns 2*q + (L/8)%2 (q = 0..3) at int16 slot 2*q + h.
+            const int atom = threadIdx.x >> 5, L = threadIdx.x & 31, par = (L >> 3) & 1;
+            const int64_t atom_col = (int64_t)blockIdx.x * 4 + atom;
+            if (atom_col < P.k_atoms) {
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int wc = atom * 8 + 2 * q + par;                  // word column inside the tile
+                    uint32_t lo = 0, hi = 0;
+                    if ((int64_t)blockIdx.x * 32 + wc < ncols) {
+                        lo = (uint16_t)smeta[wc >> 1][meta_run_pos<MB>(16 * (L >> 4) + (L & 7), wc & 1)];
+                        hi = (uint16_t)smeta[wc >> 1][meta_run_pos<MB>(16 * (L >> 4) + 8 + (L & 7), wc & 1)];
+                    }
+                    o[q] = lo | (hi << 16);
+                }
+                const int64_t off = ((r0 >> 7) * P.k_atoms + atom_col) * 2048 + ((r0 & 127) + L) * 16;
+                if (off + 16 <= (P.m >> 7) * P.k_atoms * 2048)   // every store is checked against the buffer size
+                    *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(P.tc) + off) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -436,7 +461,7 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
     if (!aligned16(dense) || !aligned16(packed) || !aligned16(meta) || (mask && !aligned16(mask)) ||
         (uniforms && !aligned16(uniforms)))
         return SP24_ERR_ALIGN;
-    if (e_tc && (so != 2 || !col_major || m % 128 || !aligned16(e_tc))) return SP24_ERR_ARG;
+    if (e_tc && (so != 2 || m % 128 || !aligned16(e_tc))) return SP24_ERR_ARG;
     if (int rc = check_device()) return rc;
     PcParams P{dense, packed, meta, static_cast<const uint8_t *>(mask), uniforms, m, k, ld_dense, ld_packed, ld_mask,
                ld_uniforms, seed, offset, reinterpret_cast<const unsigned long long *>(offset_dev),
@@ -464,7 +489,7 @@ extern "C" int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m
 //   kernel runs.  A launch recorded once (a CUDA graph) then draws fresh uniforms on every replay if the caller
 //   bumps that word between replays.
 // e_tc: a second copy of the metadata in the order the sparse GEMM reads (sp24_meta_tc_bytes(m, k) bytes), so that
-//   no conversion launch is needed before sp24_spmm.  Column-major storage and 16-bit outputs only, m % 128 == 0.
+//   no conversion launch is needed before sp24_spmm.  16-bit outputs only, m % 128 == 0.
 extern "C" int sp24_prune_compress_ex(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
                                       int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
                                       int mode, const void *mask, int64_t ld_mask, const float *uniforms,

@@ -65,10 +65,9 @@ def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, ma
     if not meta.is_contiguous():
         raise RuntimeError("metadata buffer must be contiguous")
     dev_off = _DEVICE_RNG_OFFSET if mode == _ext.PRUNE_MVUE and uniforms is None else None
-    # column-major 16-bit results with whole 128-row blocks (the dY^T operand of the weight-gradient GEMM) also get
-    # their metadata in the order the GEMM reads, in the same pass
+    # 16-bit results with whole 128-row blocks also get their metadata in the order the GEMM reads, in the same pass
     e_tc = None
-    if col_major and sparse.element_size() == 2 and m % 128 == 0:
+    if sparse.element_size() == 2 and m % 128 == 0:
         from . import spmm as _spmm
         e_tc = torch.empty(_spmm.tc_bytes(m, k), dtype=torch.uint8, device=meta.device)
     if dev_off is not None or e_tc is not None:

@@ -94,8 +94,7 @@ int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m, int64_t k
  *               bumps that word between replays.  The reference draws a new host seed per call
  *               (sparse/_semi_structured_conversions.py:1076) and has no replayable form.
  *   e_tc        a second copy of the metadata in the order sp24_spmm reads (sp24_meta_tc_bytes(m, k) bytes, 16-byte
- *               aligned), which saves the sp24_meta_to_tc launch.  Column-major storage, 16-bit packed types and
- *               m % 128 == 0 only (the weight-gradient operand dY^T of the training layer).
+ *               aligned), which saves the sp24_meta_to_tc launch.  16-bit packed types and m % 128 == 0 only.
  */
 int sp24_prune_compress_ex(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense, int col_major,
                            void *packed, int packed_dtype, int64_t ld_packed, void *meta, int mode, const void *mask,

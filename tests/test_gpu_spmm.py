@@ -500,6 +500,19 @@ def test_fused_compress_writes_the_tensor_core_metadata_order(S, m, k, select):
             # the last atom holds four word columns (slots 2q + h, q < 2); the others are never read with data
             lines = fv[:, full_atoms].reshape(-1, 128, 8, 2)[:, :, :4], rv[:, full_atoms].reshape(-1, 128, 8, 2)[:, :, :4]
             assert torch.equal(*lines)
+    # row-major compress (the plain to_sparse_semi_structured route)
+    for mode, cols in ((_ext.PRUNE_MSE, 640), (_ext.PRUNE_MVUE, 192)):
+        x = torch.randn(m, cols, generator=g).bfloat16().to(DEV)
+        packed = torch.empty(m, cols // 2, dtype=torch.bfloat16, device=DEV)
+        meta = torch.empty(m, cols // 16, dtype=torch.int16, device=DEV)
+        prune_compress(x, packed, meta, mode=mode, seed=5)
+        fused, ref = _tc_meta_cache[id(meta)][1], _tc_reference(meta, m, cols)
+        full_atoms = cols // 128
+        fv, rv = fused.view(m // 128, -1, 2048), ref.view(m // 128, -1, 2048)
+        assert torch.equal(fv[:, :full_atoms], rv[:, :full_atoms])
+        if cols % 128:
+            lines = fv[:, full_atoms].reshape(-1, 128, 8, 2)[:, :, :4], rv[:, full_atoms].reshape(-1, 128, 8, 2)[:, :, :4]
+            assert torch.equal(*lines)
 
 
 @pytest.mark.parametrize("ms,k,n", [(128, 128, 16), (256, 896, 208), (384, 4096, 1000)])
