@@ -51,10 +51,10 @@ __device__ __forceinline__ uint32_t do_group(const TIn (&in)[4], uint32_t given_
     if constexpr (MODE == SP24_PRUNE_MVUE) {
         float x[4] = {Elem<TIn>::to_f32(in[0]), Elem<TIn>::to_f32(in[1]), Elem<TIn>::to_f32(in[2]),
                       Elem<TIn>::to_f32(in[3])};
-        keep = mvue24_group(x, u0, u1);
+        keep = mvue24_group<false>(x, u0, u1);     // quotients of the two stored positions in x[0], x[1]
         const uint32_t nib = encode_nibble(keep);
-        o0 = Elem<TOut>::from_f32(pick4(nib & 3u, x[0], x[1], x[2], x[3]));
-        o1 = Elem<TOut>::from_f32(pick4(nib >> 2, x[0], x[1], x[2], x[3]));
+        o0 = Elem<TOut>::from_f32(x[0]);
+        o1 = Elem<TOut>::from_f32(x[1]);
         return nib;
     } else {
         if constexpr (MODE == SP24_PRUNE_MASK) {

@@ -180,6 +180,7 @@ __device__ __forceinline__ void mvue_uniform_pairs(uint64_t pair, uint64_t seed,
 // MVUE24 (approximate): float32, one rounding per operation, left-to-right sums, IEEE division.
 // x[] is overwritten with x_i / p_i; returns the keep mask as bits 0..3.
 // ---------------------------------------------------------------------------------------------
+template <bool ALL_FOUR = true>
 __device__ __forceinline__ uint32_t mvue24_group(float (&x)[4], float u0, float u1) {
     const float eps = 1.19209e-07f;
     float a[4], t[4], kk[4];
@@ -211,13 +212,27 @@ __device__ __forceinline__ uint32_t mvue24_group(float (&x)[4], float u0, float 
     const bool e1 = (tt <= d01) && !e0;
     const bool e2 = (tt <= d012) && !e1 && !e0;
     const bool e3 = !e2 && !e1 && !e0;
+    const uint32_t keep = (uint32_t)(m0 || e0) | ((uint32_t)(m1 || e1) << 1) | ((uint32_t)(m2 || e2) << 2) |
+                          ((uint32_t)(m3 || e3) << 3);
+    if constexpr (ALL_FOUR) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float p = __fadd_rn(t[i], __fmul_rn(a[i], __fsub_rn(ks, kk[i])));
-        x[i] = __fdiv_rn(x[i], p);
+        for (int i = 0; i < 4; ++i) {
+            const float p = __fadd_rn(t[i], __fmul_rn(a[i], __fsub_rn(ks, kk[i])));
+            x[i] = __fdiv_rn(x[i], p);
+        }
+    } else {
+        // compressed output: only the two stored positions are divided (the same two quotients the full form
+        // would pick); they come back in x[0], x[1]
+        float p[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = __fadd_rn(t[i], __fmul_rn(a[i], __fsub_rn(ks, kk[i])));
+        const uint32_t nib = encode_nibble(keep);
+        const float q0 = __fdiv_rn(pick4(nib & 3u, x[0], x[1], x[2], x[3]), pick4(nib & 3u, p[0], p[1], p[2], p[3]));
+        const float q1 = __fdiv_rn(pick4(nib >> 2, x[0], x[1], x[2], x[3]), pick4(nib >> 2, p[0], p[1], p[2], p[3]));
+        x[0] = q0;
+        x[1] = q1;
     }
-    return (uint32_t)(m0 || e0) | ((uint32_t)(m1 || e1) << 1) | ((uint32_t)(m2 || e2) << 2) |
-           ((uint32_t)(m3 || e3) << 3);
+    return keep;
 }
 
 // ---------------------------------------------------------------------------------------------
