@@ -35,7 +35,7 @@ def set_device_rng_offset(counter: Optional[Tensor]) -> None:
 
 
 def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, mask: Optional[Tensor] = None,
-                   uniforms: Optional[Tensor] = None, seed: int = 0, offset: int = 0):
+                   uniforms: Optional[Tensor] = None, seed: int = 0, offset: int = 0, emit_tc: Optional[bool] = None):
     """Low-level entry: fills ``sparse`` (packed values) and ``meta`` (reordered metadata) in place.
 
     ``dense`` is a logical (m, k) matrix in row- or column-major storage; ``sparse`` must be an
@@ -65,9 +65,12 @@ def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, ma
     if not meta.is_contiguous():
         raise RuntimeError("metadata buffer must be contiguous")
     dev_off = _DEVICE_RNG_OFFSET if mode == _ext.PRUNE_MVUE and uniforms is None else None
-    # 16-bit results with whole 128-row blocks also get their metadata in the order the GEMM reads, in the same pass
+    # 16-bit results with whole 128-row blocks can also get their metadata in the order the GEMM reads, in the same
+    # pass.  Default: for column-major results (the dY^T operand of the weight-gradient GEMM, consumed at once);
+    # row-major results (weights converted once) get it on request, else lazily at their first GEMM.
     e_tc = None
-    if sparse.element_size() == 2 and m % 128 == 0:
+    want_tc = bool(col_major) if emit_tc is None else emit_tc
+    if want_tc and sparse.element_size() == 2 and m % 128 == 0:
         from . import spmm as _spmm
         e_tc = torch.empty(_spmm.tc_bytes(m, k), dtype=torch.uint8, device=meta.device)
     if dev_off is not None or e_tc is not None:

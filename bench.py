@@ -481,8 +481,22 @@ def side_measurements(dev):
     del packed, meta, packed_t, meta_t
     Wf = [torch.randn(4096, 4096, device=dev) * 0.02 for _ in range(nb)]
     rec("transposable select fp32 4096x4096 (sparse+mask)", timeit(lambda i: sparse.mask_select(Wf[i]), nb), 4096 * 4096 * 9)
-    rec("select+dual compress fp32->fp16 4096x4096", timeit(lambda i: sparse.select_and_compress(Wf[i]), nb),
-        4096 * 4096 * (4 + 1 + 2.25))
+    # fp32 master weights -> fp16 compressed copies, through the C ABI with caller-allocated outputs (as a trainer
+    # with a fixed memory plan would call it; the Python wrapper adds five allocations per call)
+    lib = _ext.lib()
+    mm = kk = 4096
+    d_mask = [torch.empty(mm, kk, dtype=torch.bool, device=dev) for _ in range(nb)]
+    d_bw = [torch.empty(mm * kk * 9 // 16, dtype=torch.float16, device=dev) for _ in range(nb)]
+    d_bt = [torch.empty(mm * kk * 9 // 16, dtype=torch.float16, device=dev) for _ in range(nb)]
+
+    def dual_f32(i):
+        rc = lib.sp24_select_dual_compress(Wf[i].data_ptr(), _ext.F32, mm, kk, kk, 1, d_mask[i].data_ptr(), kk,
+                                           d_bw[i].data_ptr(), _ext.F16, kk // 2, d_bw[i].data_ptr() + mm * kk,
+                                           d_bt[i].data_ptr(), kk, d_bt[i].data_ptr() + mm * kk, _ext.stream())
+        _ext.check(rc, "sp24_select_dual_compress")
+
+    rec("select+dual compress fp32->fp16 4096x4096", timeit(dual_f32, nb), 4096 * 4096 * (4 + 1 + 2.25))
+    del d_mask, d_bw, d_bt
     p = [torch.randn(m, k, device=dev) * 0.02 for _ in range(2)]
     gr = [torch.randn(m, k, device=dev) * 1e-3 for _ in range(2)]
     mk = [torch.rand(m, k, device=dev) < 0.5 for _ in range(2)]

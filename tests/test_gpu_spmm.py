@@ -505,7 +505,7 @@ def test_fused_compress_writes_the_tensor_core_metadata_order(S, m, k, select):
         x = torch.randn(m, cols, generator=g).bfloat16().to(DEV)
         packed = torch.empty(m, cols // 2, dtype=torch.bfloat16, device=DEV)
         meta = torch.empty(m, cols // 16, dtype=torch.int16, device=DEV)
-        prune_compress(x, packed, meta, mode=mode, seed=5)
+        prune_compress(x, packed, meta, mode=mode, seed=5, emit_tc=True)
         fused, ref = _tc_meta_cache[id(meta)][1], _tc_reference(meta, m, cols)
         full_atoms = cols // 128
         fv, rv = fused.view(m // 128, -1, 2048), ref.view(m // 128, -1, 2048)
