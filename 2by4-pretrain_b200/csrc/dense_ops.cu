@@ -63,7 +63,9 @@ template <typename T, int OP, bool HAS_U> __global__ void __launch_bounds__(256)
 #pragma unroll
     for (int it = 0; it < ITEMS; ++it) {
         const int64_t idx = base + it * 256;
-        rr[it] = idx / per_row;
+        // 64-bit division is emulated (dozens of instructions); matrices below 2^31 items take the 32-bit one
+        if (total <= 0x7FFFFFFF) rr[it] = (int64_t)((uint32_t)idx / (uint32_t)per_row);
+        else rr[it] = idx / per_row;
         cc[it] = (idx - rr[it] * per_row) * 8;
         if (idx < total) {
             T tmp[8];
