@@ -45,6 +45,16 @@ METRIC = "prune/compress HBM GB/s (transposable select + dual 2:4 compress)"
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 74.3e6
 
 
+def measured_tensor_peak():
+    """Dense bf16 GEMM peak (TFLOP/s) measured on this pool (burst figure: a kernel timed alone), else the fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -617,6 +627,7 @@ def spmm_measurements(dev):
     T, K, N = 16384, 768, 3072
     flops = 2.0 * T * N * K
     res = {}
+    tensor_peak, tensor_peak_kind = measured_tensor_peak()
     for dtype, tag in ((torch.float16, "fp16"), (torch.bfloat16, "bf16")):
         nb = 3
         xs = [torch.randn(T, K, device=dev).to(dtype) for _ in range(nb)]
@@ -682,6 +693,10 @@ def spmm_measurements(dev):
             "per_gemm_TFLOPs": {"fwd": flops / t_fwd / 1e12, "dx": flops / t_dx / 1e12,
                                 "dw_gemm_only": flops / t_dw_gemm_only / 1e12,
                                 "dw_splitk_fp32_gemm_and_memset_only": flops / t_dw_splitk_gemm / 1e12},
+            # dense-equivalent rate over twice the dense tensor peak (2:4 sparse MMAs run at twice the dense rate)
+            "roofline": {"bound": "tensor", "peak": 2 * tensor_peak, "peak_kind": tensor_peak_kind, "unit": "TFLOP/s",
+                         "frac": {"fwd": flops / t_fwd / 1e12 / (2 * tensor_peak), "dx": flops / t_dx / 1e12 / (2 * tensor_peak),
+                                  "dw_gemm": flops / t_dw_splitk_gemm / 1e12 / (2 * tensor_peak)}},
         }
         del xs, dys, pre
     # fp8 e4m3 forward (per-tensor scales applied outside the GEMM), fp32 output
