@@ -39,6 +39,7 @@ BATCH = 8
 BYTES_PER_ELEM = 2 + 1 + 2 * (2 / 2 + 1 / 8)  # read fp16 W, write bool mask, write 2 x (fp16 values/2 + 4 bits/4 elems)
 ALG_BYTES_PER_MATRIX = M * K * BYTES_PER_ELEM
 METRIC = "prune/compress HBM GB/s (transposable select + dual 2:4 compress)"
+WORKLOAD = f"cfg2: transposable select + dual 2:4 compress, {M}x{K} fp16 N(0,0.02) seed 2+i"
 # dram__bytes_read.sum + dram__bytes_write.sum of one ts_dual_kernel launch on this workload, from the
 # ncu capture summarised in profiles/ts_dual_kernel_8192x8192_fp16.md: (134.2 + 162.9) MB for an 8192 x 8192
 # matrix, scaled by the element count (1/4) to one 4096 x 4096 launch
@@ -181,7 +182,7 @@ def run_reference(args, rank):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / len(per_step) * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"transposable select + dual 2:4 compress, {M}x{K} fp16 N(0,0.02)",
+        "config": {"workload": WORKLOAD, "alg_bytes_per_elem": BYTES_PER_ELEM,
                    "step": "one matrix per step (bounded sample of the GPU arm's 8-matrix batch)"},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"{len(per_step)} steps x one {M}x{K} matrix; CPU restatement of the reference "
@@ -351,7 +352,7 @@ def main():
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"cfg2: transposable select + dual 2:4 compress, {M}x{K} fp16 N(0,0.02) seed 2+i",
+            "config": {"workload": WORKLOAD,
                        "batch_per_step_per_gpu": BATCH, "alg_bytes_per_elem": BYTES_PER_ELEM,
                        "l2": "inputs+outputs per step = 672 MiB > 126 MB L2, no flush",
                        "parallelism": f"independent matrices x{world}"},
