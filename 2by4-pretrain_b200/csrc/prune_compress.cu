@@ -21,6 +21,7 @@ struct PcParams {
     const unsigned long long *offset_dev;   // optional device word added to offset at run time
     int16_t *tc;                            // optional metadata copy in tensor-core atom order (16-bit outputs)
     int64_t k_atoms;                        // 128-column atoms per 128-row block
+    float *row_sums;                        // optional (column-major only): row_sums[r] += sum over k of dense[r, k]
 };
 
 template <typename T, int N> __device__ __forceinline__ void load_elems(const T *p, T (&out)[N]) {
@@ -282,6 +283,7 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_k
     // tensor-core order: line L = 16*(r/16) + 8*(c%2) + r%8 of 16 bytes, int16 slot 2*((c/2)%4) + (r/8)%2; the block's
     // RT rows x 8 word columns fill RT whole lines of one atom per 128-row block
     __shared__ __align__(16) uint16_t stc[MB == 2 ? RT * 8 : 8];
+    __shared__ float ssum[8][RT];           // per-warp partial row sums (only used when row sums are asked for)
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t ncols = P.k / CH;
@@ -291,6 +293,10 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_k
     const TIn *dense = static_cast<const TIn *>(P.dense);
     TOut *packed = static_cast<TOut *>(P.packed);
 
+    if (P.row_sums) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) ssum[warp][lane * V + v] = 0.f;
+    }
     if (r < P.m && c < ncols) {
         uint32_t word[V];
 #pragma unroll
@@ -304,6 +310,16 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_k
                 const int64_t kk = c * CH + half * 16 + j;
                 load_elems<TIn, V>(dense + kk * P.ld_dense + r, in[j]);
                 if constexpr (MODE == SP24_PRUNE_MASK) load_elems<uint8_t, V>(P.mask + kk * P.ld_mask + r, mk[j]);
+            }
+            if (P.row_sums) {   // sums of the unpruned values, fp32; parked in shared memory at once so that
+                                // no register stays live across the pruning arithmetic
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) a += Elem<TIn>::to_f32(in[j][v]);
+                    ssum[warp][lane * V + v] += a;
+                }
             }
 #pragma unroll
             for (int g2 = 0; g2 < 2; ++g2) {
@@ -367,6 +383,17 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_k
         }
     }
     __syncthreads();
+    if (P.row_sums) {
+        // the eight warps hold eight K ranges of the same rows: one reduction per row and block
+        for (int t = threadIdx.x; t < RT; t += 256) {
+            if (r0 + t < P.m) {
+                float a = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) a += ssum[w][t];
+                atomicAdd(P.row_sums + r0 + t, a);
+            }
+        }
+    }
     const int64_t rows_here = (P.m - r0 < RT) ? (P.m - r0) : RT;
     const int pieces = (int)(rows_here * 2 * MB / 16);
     for (int i = threadIdx.x; i < 4 * (2 * RT * MB / 16); i += 256) {
@@ -440,7 +467,7 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
                                int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
                                int mode, const void *mask, int64_t ld_mask, const float *uniforms,
                                int64_t ld_uniforms, uint64_t seed, uint64_t offset, const uint64_t *offset_dev,
-                               void *e_tc, void *stream) {
+                               void *e_tc, float *row_sums, void *stream) {
     using namespace sp24;
     if (!dense || !packed || !meta) return SP24_ERR_ARG;
     const int so = dtype_size(packed_dtype), si = dtype_size(dense_dtype);
@@ -462,10 +489,11 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
         (uniforms && !aligned16(uniforms)))
         return SP24_ERR_ALIGN;
     if (e_tc && (so != 2 || m % 128 || !aligned16(e_tc))) return SP24_ERR_ARG;
+    if (row_sums && (!col_major || (reinterpret_cast<uintptr_t>(row_sums) & 3u))) return SP24_ERR_ARG;
     if (int rc = check_device()) return rc;
     PcParams P{dense, packed, meta, static_cast<const uint8_t *>(mask), uniforms, m, k, ld_dense, ld_packed, ld_mask,
                ld_uniforms, seed, offset, reinterpret_cast<const unsigned long long *>(offset_dev),
-               static_cast<int16_t *>(e_tc), (k + 127) / 128};
+               static_cast<int16_t *>(e_tc), (k + 127) / 128, row_sums};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dense_dtype) {
         case SP24_F32: return dispatch_out<float>(P, packed_dtype, mode, col_major, st);
@@ -481,21 +509,24 @@ extern "C" int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m
                                    int mode, const void *mask, int64_t ld_mask, const float *uniforms,
                                    int64_t ld_uniforms, uint64_t seed, uint64_t offset, void *stream) {
     return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode,
-                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, nullptr, nullptr, stream);
+                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, nullptr, nullptr, nullptr, stream);
 }
 
-// Same conversion with two optional extras (either may be NULL).
+// Same conversion with three optional extras (each may be NULL).
 // offset_dev: the Philox offset becomes `offset` plus the 64-bit word at `offset_dev` (device memory), read when the
 //   kernel runs.  A launch recorded once (a CUDA graph) then draws fresh uniforms on every replay if the caller
 //   bumps that word between replays.
 // e_tc: a second copy of the metadata in the order the sparse GEMM reads (sp24_meta_tc_bytes(m, k) bytes), so that
 //   no conversion launch is needed before sp24_spmm.  16-bit outputs only, m % 128 == 0.
+// row_sums: m floats; row_sums[r] += sum over k of dense[r, k] (the values before pruning, fp32 partial sums added
+//   with atomics: the caller zeroes the array or passes a gradient buffer).  Column-major storage only: for dY^T this
+//   is the bias gradient, taken from the pass that reads dY anyway.
 extern "C" int sp24_prune_compress_ex(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
                                       int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
                                       int mode, const void *mask, int64_t ld_mask, const float *uniforms,
                                       int64_t ld_uniforms, uint64_t seed, uint64_t offset, const uint64_t *offset_dev,
-                                      void *e_tc, void *stream) {
+                                      void *e_tc, float *row_sums, void *stream) {
     if (offset_dev && (reinterpret_cast<uintptr_t>(offset_dev) & 7u)) return SP24_ERR_ARG;
     return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode,
-                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, offset_dev, e_tc, stream);
+                               mask, ld_mask, uniforms, ld_uniforms, seed, offset, offset_dev, e_tc, row_sums, stream);
 }

@@ -35,7 +35,8 @@ def set_device_rng_offset(counter: Optional[Tensor]) -> None:
 
 
 def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, mask: Optional[Tensor] = None,
-                   uniforms: Optional[Tensor] = None, seed: int = 0, offset: int = 0, emit_tc: Optional[bool] = None):
+                   uniforms: Optional[Tensor] = None, seed: int = 0, offset: int = 0, emit_tc: Optional[bool] = None,
+                   row_sums: Optional[Tensor] = None):
     """Low-level entry: fills ``sparse`` (packed values) and ``meta`` (reordered metadata) in place.
 
     ``dense`` is a logical (m, k) matrix in row- or column-major storage; ``sparse`` must be an
@@ -73,11 +74,14 @@ def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, ma
     if want_tc and sparse.element_size() == 2 and m % 128 == 0:
         from . import spmm as _spmm
         e_tc = torch.empty(_spmm.tc_bytes(m, k), dtype=torch.uint8, device=meta.device)
-    if dev_off is not None or e_tc is not None:
+    if row_sums is not None:
+        if not col_major or row_sums.dtype != torch.float32 or row_sums.numel() != m or not row_sums.is_contiguous():
+            raise RuntimeError("row_sums: column-major input and a contiguous float32 vector of one value per row")
+    if dev_off is not None or e_tc is not None or row_sums is not None:
         rc = _ext.lib().sp24_prune_compress_ex(
             dense.data_ptr(), _ext.dt(dense.dtype), m, k, ld_d, col_major, sparse.data_ptr(), _ext.dt(sparse.dtype), ld_p,
             meta.data_ptr(), mode, _ext.ptr(mask), ld_m, _ext.ptr(uniforms), ld_u, seed & (2 ** 64 - 1),
-            offset & (2 ** 64 - 1), _ext.ptr(dev_off), _ext.ptr(e_tc), _ext.stream())
+            offset & (2 ** 64 - 1), _ext.ptr(dev_off), _ext.ptr(e_tc), _ext.ptr(row_sums), _ext.stream())
     else:
         rc = _ext.lib().sp24_prune_compress(
             dense.data_ptr(), _ext.dt(dense.dtype), m, k, ld_d, col_major, sparse.data_ptr(), _ext.dt(sparse.dtype), ld_p,

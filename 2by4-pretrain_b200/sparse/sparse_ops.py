@@ -6,11 +6,15 @@ a transposable 2:4 mask, backward dX = dY W_s through the separately compressed 
 dW = MVUE24(dY^T) X with the gradient compressed on the fly.  ``MyLinear`` / ``SparseLinear`` are the
 older dense-GEMM variants of sparse/sparse_ops.py:8-87 of the reference.
 """
+import random
+
 import torch
 import torch.nn.functional as F
 from torch import autograd, nn
 from torch.amp import custom_fwd, custom_bwd
 
+from . import _ext
+from ._semi_structured_conversions import prune_compress
 from .semi_structured import SparseSemiStructuredTensor, to_sparse_semi_structured
 from .transposable_semi_structured import TransposableSparse, select_and_compress
 from .triton_ops import MVUE24_approx_triton
@@ -125,6 +129,20 @@ class sparse_linear_transpose(autograd.Function):
         return grad_input, grad_weight, None, None, grad_bias
 
 
+def _mvue_compress_t(g, row_sums):
+    """MVUE 2:4 compression of ``g.t()`` (features x tokens, column-major) into buffers carved like
+    ``SparseSemiStructuredTensor`` carves them, with the per-feature sums of ``g`` added to ``row_sums``
+    by the same pass.  Returns (packed values, reordered metadata)."""
+    tokens, features = g.shape
+    if not g.is_contiguous() or features % 32 or tokens % 64:
+        raise RuntimeError(f"gradient of shape {tuple(g.shape)}: contiguous, features % 32 == 0, tokens % 64 == 0")
+    buf = torch.empty((features * tokens * 9 // 16,), dtype=g.dtype, device=g.device)
+    packed = buf[: features * tokens // 2].view(-1, features).t()
+    meta = buf[features * tokens // 2:].view(torch.int16).view(features, -1)
+    prune_compress(g.t(), packed, meta, mode=_ext.PRUNE_MVUE, seed=random.randint(0, 2 ** 31 - 1), row_sums=row_sums)
+    return packed, meta
+
+
 class _fst_linear(autograd.Function):
     """What ``sparse_linear_transpose`` computes, on the raw compressed buffers: no tensor-subclass objects,
     no cast of the (unused) fp32 weight.  ``weight`` only routes the gradient.  With ``into_grad`` the weight
@@ -142,6 +160,7 @@ class _fst_linear(autograd.Function):
         ctx.has_bias = bias is not None
         ctx.fp32_grad = weight.dtype == torch.float32 and x.shape[1] % 8 == 0
         ctx.grad_target = weight if (into_grad and ctx.fp32_grad) else None
+        ctx.bias_target = bias if (ctx.grad_target is not None and bias is not None) else None
         output = _spmm(x, pw, mw, bias=b)     # bias added in the GEMM epilogue
         return output.view(*input.shape[:-1], -1)
 
@@ -156,19 +175,32 @@ class _fst_linear(autograd.Function):
             g = g.to(pt.dtype)
         if ctx.needs_input_grad[0]:
             grad_input = _spmm(g, pt, mt).view(ctx.shape)
+        bias_done = False
         if ctx.needs_input_grad[1]:
-            gs = to_sparse_semi_structured(g.t(), MVUE24=True, dtype=g.dtype)
             target = ctx.grad_target
-            if target is not None and target.grad is not None and target.grad.dtype == torch.float32 \
-                    and target.grad.is_contiguous():
-                _spmm_acc(target.grad, gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass, x)
+            into = target is not None and target.grad is not None and target.grad.dtype == torch.float32 \
+                and target.grad.is_contiguous()
+            bias_grad = None
+            if into and ctx.has_bias and ctx.needs_input_grad[6] and g.dtype in (torch.float16, torch.bfloat16):
+                bg = ctx.bias_target.grad
+                if bg is not None and bg.dtype == torch.float32 and bg.is_contiguous():
+                    bias_grad = bg
+            if bias_grad is not None:
+                # the pass that compresses dY^T also adds its row sums (= grad_output.sum(0)) to bias.grad
+                gp, gm = _mvue_compress_t(g, bias_grad)
+                bias_done = True
+            else:
+                gs = to_sparse_semi_structured(g.t(), MVUE24=True, dtype=g.dtype)
+                gp, gm = gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass
+            if into:
+                _spmm_acc(target.grad, gp, gm, x)
             elif ctx.fp32_grad:
                 # split-K GEMM with fp32 accumulation: the gradient arrives in the dtype of the master weight
                 grad_weight = torch.zeros((g.shape[1], x.shape[1]), dtype=torch.float32, device=g.device)
-                _spmm_acc(grad_weight, gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass, x)
+                _spmm_acc(grad_weight, gp, gm, x)
             else:
-                grad_weight = _spmm(x.t(), gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass).t()
-        if ctx.has_bias and ctx.needs_input_grad[6]:
+                grad_weight = _spmm(x.t(), gp, gm).t()
+        if ctx.has_bias and ctx.needs_input_grad[6] and not bias_done:
             grad_bias = g.sum(0)
         return grad_input, grad_weight, None, None, None, None, grad_bias, None
 

@@ -87,7 +87,7 @@ int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m, int64_t k
                         uint64_t seed, uint64_t offset, void *stream);
 
 /*
- * sp24_prune_compress with two optional extras (either may be NULL); no counterpart in the reference.
+ * sp24_prune_compress with three optional extras (each may be NULL); no counterpart in the reference.
  *   offset_dev  the Philox stream is keyed by (seed, offset + *offset_dev), *offset_dev being a 64-bit word in
  *               device memory (8-byte aligned) read when the kernel runs.  A launch that is recorded once and
  *               replayed (a CUDA graph of the training step) draws fresh uniforms on every replay if the caller
@@ -95,11 +95,15 @@ int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m, int64_t k
  *               (sparse/_semi_structured_conversions.py:1076) and has no replayable form.
  *   e_tc        a second copy of the metadata in the order sp24_spmm reads (sp24_meta_tc_bytes(m, k) bytes, 16-byte
  *               aligned), which saves the sp24_meta_to_tc launch.  16-bit packed types and m % 128 == 0 only.
+ *   row_sums    m floats: row_sums[r] += sum over k of dense[r, k] (values before pruning; fp32 partial sums added
+ *               with atomics, so zero the array first or pass a gradient buffer to add to).  Column-major storage
+ *               only.  For dY^T these are the bias gradients of the layer (grad_output.sum(0), README.md:197-198 of
+ *               the reference), taken from the pass that reads dY anyway.
  */
 int sp24_prune_compress_ex(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense, int col_major,
                            void *packed, int packed_dtype, int64_t ld_packed, void *meta, int mode, const void *mask,
                            int64_t ld_mask, const float *uniforms, int64_t ld_uniforms, uint64_t seed, uint64_t offset,
-                           const uint64_t *offset_dev, void *e_tc, void *stream);
+                           const uint64_t *offset_dev, void *e_tc, float *row_sums, void *stream);
 
 /*
  * 2:4 compressed -> dense (zeros at pruned positions).  Replaces

@@ -547,3 +547,34 @@ def test_prune_compress_random_shapes_match_the_oracle(S):
         op, om = O.prune_compress(x, dout, **okw)[:2]
         assert same_bits(packed.cpu().contiguous(), op), (case, m, k, din, dout, col, mode)
         assert torch.equal(meta.cpu(), om), (case, m, k, din, dout, col, mode)
+
+
+@pytest.mark.parametrize("din", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("mode", ["mse", "mvue"])
+def test_row_sums_come_out_of_the_column_major_compress(S, din, mode):
+    """The optional row-sum output of the column-major conversion: fp32 sums of the unpruned values added to what
+    the buffer held (rtol 1e-5 on sum|x|, the order of the fp32 additions is free), packed values and metadata
+    bit-identical to the call without it; row counts that leave the last CTA ragged; row-major input refused."""
+    from sparse._semi_structured_conversions import prune_compress
+    from sparse import _ext
+    g = torch.Generator().manual_seed(91)
+    code = {"mse": _ext.PRUNE_MSE, "mvue": _ext.PRUNE_MVUE}[mode]
+    for m, k in [(32, 64), (96, 640), (160, 1088), (2048, 64), (736, 4096)]:
+        x = torch.randn(k, m, generator=g).to(din).to(DEV).t()         # (m, k) column-major
+        outs = []
+        for with_sums in (False, True):
+            packed = torch.empty(k // 2, m, dtype=torch.float16, device=DEV).t()
+            meta = torch.empty(m, k // 16, dtype=torch.int16, device=DEV)
+            sums = torch.full((m,), 3.0, dtype=torch.float32, device=DEV) if with_sums else None
+            prune_compress(x, packed, meta, mode=code, seed=5, offset=9, row_sums=sums)
+            outs.append((packed.clone(), meta.clone(), sums))
+        assert torch.equal(outs[0][0].view(torch.int16), outs[1][0].view(torch.int16))
+        assert torch.equal(outs[0][1], outs[1][1])
+        want = x.double().sum(1) + 3.0
+        err = (outs[1][2].double() - want).abs()
+        assert bool((err <= 1e-5 * (x.double().abs().sum(1) + 3.0)).all()), (m, k, float(err.max()))
+    x = torch.randn(64, 128, generator=g).half().to(DEV)
+    with pytest.raises(RuntimeError):
+        prune_compress(x, torch.empty(64, 64, dtype=torch.float16, device=DEV),
+                       torch.empty(64, 8, dtype=torch.int16, device=DEV), mode=_ext.PRUNE_MSE,
+                       row_sums=torch.zeros(64, device=DEV))
