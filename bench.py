@@ -277,7 +277,7 @@ def main():
     launches = args.steps * BATCH * world
     total_bytes = ALG_BYTES_PER_MATRIX * BATCH * args.steps * world
     value = total_bytes / (ms * 1e-3) / 1e9
-    per_launch_s = ms * 1e-3 / launches
+    per_launch_s = ms * 1e-3 / (args.steps * BATCH)   # one GPU's launches: the roofline is per kernel launch, not per job
     achieved = ALG_BYTES_PER_MATRIX / per_launch_s / 1e9
 
     # end-to-end through the public API with host buffers
