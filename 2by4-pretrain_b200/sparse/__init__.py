@@ -4,6 +4,7 @@ Public names follow sparse/__init__.py of the reference for everything on that p
 classes the reference only lists in its README (``SparseLinearTranspose``,
 ``sparse_linear_transpose``, ``mask_select``).
 """
+from .legacy import MVUE24_approx_torch, sparse24_torch, soft_threshold24_torch
 from .triton_ops import MVUE24_approx_triton, sparse24_triton, soft_threshold24_triton
 from .decay import masked_add_, adamw_masked_decay_
 from .transposable_semi_structured import TransposableSparse, select_and_compress
@@ -19,6 +20,9 @@ __all__ = [
     'SparseLinear',
     'SparseLinearTranspose',
     'sparse_linear_transpose',
+    'MVUE24_approx_torch',
+    'sparse24_torch',
+    'soft_threshold24_torch',
     'MVUE24_approx_triton',
     'sparse24_triton',
     'soft_threshold24_triton',
