@@ -16,7 +16,9 @@ recomputes the same transposable mask.  MVUE seeds come from Python's ``random``
 ``--graphs`` replays the step from CUDA graphs instead of launching ~2000 kernels from Python: one graph for
 forward + backward on a mask-refresh step, one for the other steps, one for masked decay + AdamW (one fused
 kernel launch per parameter segment).  Parameters, gradients and moments live in flat fp32 buffers; the gradient
-buffer is all-reduced with a single NCCL call between the graphs (no collective is captured).  The MVUE seeds recorded in a graph stay fixed, so the kernels add a device counter, bumped
+buffer is all-reduced by a few NCCL calls issued from the host on a second stream (no collective is captured): one
+per group of transformer blocks, each released by an event-record node inside the backward graph, so that all
+but the last group's exchange overlaps the rest of the backward pass.  The MVUE seeds recorded in a graph stay fixed, so the kernels add a device counter, bumped
 inside the graph, to their Philox offset: every replay draws fresh uniforms.
 """
 import argparse
@@ -62,6 +64,9 @@ class GPT2(nn.Module):
         self.wpe = nn.Embedding(seq, d)
         self.blocks = nn.ModuleList(Block(d, heads, linear) for _ in range(layers))
         self.ln_f = nn.LayerNorm(d)
+        # block index -> callable run when the gradient with respect to that block's input exists, i.e. when the
+        # backward pass has left the block (used to start gradient all-reduces early)
+        self.input_grad_hooks = {}
         self.apply(self._init)
 
     @staticmethod
@@ -74,7 +79,9 @@ class GPT2(nn.Module):
     def forward(self, idx, targets):
         b, t = idx.shape
         x = self.wte(idx) + self.wpe(torch.arange(t, device=idx.device))
-        for blk in self.blocks:
+        for i, blk in enumerate(self.blocks):
+            if i in self.input_grad_hooks and x.requires_grad:
+                x.register_hook(lambda g, f=self.input_grad_hooks[i]: f())
             x = blk(x)
         logits = F.linear(self.ln_f(x), self.wte.weight)  # tied output head
         return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.reshape(-1))
@@ -181,8 +188,13 @@ def run(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12,
 
 
 def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12, d=768, heads=12, alpha=2e-4,
-               lr=6e-4, freq=40, verbose=False, return_losses=False):
-    """The same step as ``run`` replayed from CUDA graphs.  Returns the same dict."""
+               lr=6e-4, freq=40, verbose=False, return_losses=False, comm_groups=4):
+    """The same step as ``run`` replayed from CUDA graphs.  Returns the same dict.
+
+    With more than one rank and ``comm_groups`` > 1 the gradient all-reduce is split into that many groups of
+    transformer blocks, last blocks first; each group's all-reduce starts on a second stream as soon as the
+    backward pass (still running inside the graph) has left the group, signalled by an event-record node in the
+    graph.  ``comm_groups`` = 1 is one all-reduce of the whole flat gradient after the graph."""
     import torch.distributed as dist
     import sparse
     from sparse._semi_structured_conversions import set_device_rng_offset
@@ -267,9 +279,51 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         tok = torch.randint(0, vocab, (batch, seq + 1), generator=gen).pin_memory()
         static_tok.copy_(tok, non_blocking=True)
 
+    # Gradient exchange.  Group 0 = the last blocks (+ the final layer norm), ..., the last group = the first blocks
+    # and the embeddings, whose gradients are complete only when the backward pass ends.  A group's slices of the
+    # flat buffer are contiguous inside each segment because parameters keep the model's order there.
+    n_groups = max(1, min(comm_groups, layers)) if world > 1 else 1
+    per = (layers + n_groups - 1) // n_groups
+    group_of = {}
+    for i, blk in enumerate(model.blocks):
+        for p in blk.parameters():
+            group_of[id(p)] = n_groups - 1 - min(i // per, n_groups - 1)
+    for p in model.ln_f.parameters():
+        group_of[id(p)] = 0
+    slices = [[] for _ in range(n_groups)]
+    o = 0
+    for p in order:
+        g_ = group_of.get(id(p), n_groups - 1)
+        a, b = o, o + pad(p.numel())
+        if slices[g_] and slices[g_][-1][1] == a:
+            slices[g_][-1][1] = b
+        else:
+            slices[g_].append([a, b])
+        o = b
+    comm = torch.cuda.Stream() if n_groups > 1 else None
+    ready = [torch.cuda.Event(external=True) for _ in range(n_groups - 1)]
+    tail = torch.cuda.Event()
+    if n_groups > 1:
+        for g_ in range(n_groups - 1):
+            # lowest block of group g_ is (n_groups - 1 - g_) * per; its gradients are all accumulated once the
+            # backward pass has also left the block below it
+            below = (n_groups - 1 - g_) * per - 1
+            model.input_grad_hooks[below] = ready[g_].record
+
     def reduce_grads():
-        if world > 1:
+        if world == 1:
+            return
+        if n_groups == 1:
             dist.all_reduce(flat, op=dist.ReduceOp.AVG)
+            return
+        main = torch.cuda.current_stream()
+        tail.record(main)
+        with torch.cuda.stream(comm):
+            for g_ in range(n_groups):
+                comm.wait_event(ready[g_] if g_ < n_groups - 1 else tail)
+                for a, b in slices[g_]:
+                    dist.all_reduce(flat[a:b], op=dist.ReduceOp.AVG)
+        main.wait_stream(comm)
 
     # eager warm-up on a side stream (allocator, cuBLAS workspaces, optimizer state, kernel attributes)
     side = torch.cuda.Stream()

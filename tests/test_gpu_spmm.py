@@ -406,6 +406,21 @@ def test_graph_replayed_step_matches_the_eager_step():
     assert all(abs(v - math.log(512)) < 0.6 for v in sp["losses"])   # random tokens: stays near ln(vocab)
 
 
+def test_grouped_all_reduce_released_inside_the_graph_equals_the_single_one():
+    """Two ranks (skipped with fewer GPUs): see tests/_two_rank_overlap.py."""
+    import os, socket, subprocess, sys
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    here = os.path.dirname(os.path.abspath(__file__))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(here, "_two_rank_overlap.py")],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "OVERLAP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_device_rng_offset_changes_the_draw_without_a_new_seed(S):
     from sparse._semi_structured_conversions import set_device_rng_offset
     g = torch.Generator().manual_seed(21)
