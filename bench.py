@@ -532,8 +532,9 @@ def gpt2_measurements(world):
                "loss_finite": sp["loss_finite"], "n_gpus": world,
                "sparse_eager_ddp_tokens_per_s": sp_eager["tokens_per_s"],
                "sparse_eager_ddp_host_enqueue_ms_per_step": sp_eager["host_enqueue_ms_per_step"],
-               "note": "step replayed from CUDA graphs (forward+backward, then one NCCL all-reduce of the flat fp32 "
-                       "gradient, then masked decay + AdamW); 50 timed sparse steps, mean, including the mask "
+               "note": "step replayed from CUDA graphs (forward+backward; the flat fp32 gradient all-reduced by NCCL "
+                       "in four block groups released by event nodes inside the backward graph; then masked "
+                       "decay + AdamW); 50 timed sparse steps, mean, including the mask "
                        "refresh every 40 steps; eager = Python-launched step with DistributedDataParallel"}
     except Exception as exc:  # the headline line must still be printed
         out = {"error": repr(exc)[:300]}
