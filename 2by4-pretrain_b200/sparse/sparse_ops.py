@@ -134,8 +134,9 @@ def _mvue_compress_t(g, row_sums):
     ``SparseSemiStructuredTensor`` carves them, with the per-feature sums of ``g`` added to ``row_sums``
     by the same pass.  Returns (packed values, reordered metadata)."""
     tokens, features = g.shape
-    if not g.is_contiguous() or features % 32 or tokens % 64:
-        raise RuntimeError(f"gradient of shape {tuple(g.shape)}: contiguous, features % 32 == 0, tokens % 64 == 0")
+    if features % 32 or tokens % 64:
+        raise RuntimeError(f"gradient of shape {tuple(g.shape)}: features % 32 == 0 and tokens % 64 == 0 required")
+    g = g.contiguous()
     buf = torch.empty((features * tokens * 9 // 16,), dtype=g.dtype, device=g.device)
     packed = buf[: features * tokens // 2].view(-1, features).t()
     meta = buf[features * tokens // 2:].view(torch.int16).view(features, -1)
