@@ -274,7 +274,7 @@ template <typename TIn> struct ColVec {
 };
 
 template <typename TIn, typename TOut, int MODE, bool HAS_U, int V>
-__global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_col_kernel(PcParams P) {
+__global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 4 : 1) pc_col_kernel(PcParams P) {
     const uint64_t rng_offset = P.offset + (P.offset_dev ? *P.offset_dev : 0ull);
     constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;
     constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;
