@@ -220,9 +220,9 @@ template <typename T, typename TOut> __device__ __forceinline__ void pack_row(co
     }
 }
 
+// Work of one block: 64 rows x 128 columns at block coordinates (bx, by) of the matrix P describes.
 template <typename T, typename TOut, bool SELECT, bool TC>
-// three CTAs per SM for 16-bit inputs (80 registers); fp32 inputs need more registers and keep two
-__global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(DualParams P) {
+__device__ __forceinline__ void ts_dual_block(const DualParams &P, const unsigned bx, const unsigned by) {
     // Metadata words are staged in the order they are produced (one cheap store per producer); the few threads
     // that write them out gather them into the reference's run order (and the tensor-core order) afterwards.
     __shared__ __align__(8) uint16_t wlin[8 * 8 * 4];   // W: [warp = 4-row group][word column][row in group]
@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
     // A block covers 64 rows x 128 columns as two 32-row halves.  Both halves are loaded up front so that
     // the second half's global loads are in flight while the first half is being searched.
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t c0 = (int64_t)blockIdx.x * 128, c = c0 + lane * 4;
+    const int64_t c0 = (int64_t)bx * 128, c = c0 + lane * 4;
     const bool active = c < P.k;
     const T *w_ptr = static_cast<const T *>(P.w);
     uint16_t *pw = static_cast<uint16_t *>(P.packed_w);
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
     T w[4][4], w_next[4][4];
     uint32_t mw[4] = {0, 0, 0, 0}, mw_next[4] = {0, 0, 0, 0};
     if (active) {
-        const int64_t ra = (int64_t)blockIdx.y * 64 + warp * 4;
+        const int64_t ra = (int64_t)by * 64 + warp * 4;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             load_row4<T>(w_ptr + (ra + i) * P.ld_w + c, w[i]);
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
 
 #pragma unroll 1
     for (int half = 0; half < 2; ++half) {
-        const int64_t r0 = (int64_t)blockIdx.y * 64 + half * 32;
+        const int64_t r0 = (int64_t)by * 64 + half * 32;
         const int64_t r = r0 + warp * 4;
         uint32_t bits = 0;
         uint32_t h[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // the block as packed 16-bit output values
@@ -394,6 +394,31 @@ __global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(Du
     }
 }
 
+template <typename T, typename TOut, bool SELECT, bool TC>
+// three CTAs per SM for 16-bit inputs (80 registers); fp32 inputs need more registers and keep two
+__global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_kernel(DualParams P) {
+    ts_dual_block<T, TOut, SELECT, TC>(P, blockIdx.x, blockIdx.y);
+}
+
+// Several matrices in one launch (the per-step recompression of all the layers of a model: each matrix alone is
+// too small to fill the GPU).  Blocks are numbered through the matrices one after the other; first[i] is the first
+// block of matrix i.
+constexpr int kDualBatchMax = 48;
+struct DualBatch {
+    DualParams p[kDualBatchMax];
+    unsigned first[kDualBatchMax + 1];
+    int count;
+};
+template <typename T, typename TOut, bool SELECT, bool TC>
+__global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) ts_dual_batch_kernel(const __grid_constant__ DualBatch B) {
+    int i = 0;
+    while (i + 1 < B.count && blockIdx.x >= B.first[i + 1]) ++i;
+    const DualParams &P = B.p[i];
+    const unsigned local = blockIdx.x - B.first[i];
+    const unsigned ncb = (unsigned)((P.k + 127) / 128);
+    ts_dual_block<T, TOut, SELECT, TC>(P, local % ncb, local / ncb);
+}
+
 template <typename T, typename TOut> int launch_dual(const DualParams &P, int select, cudaStream_t st) {
     dim3 grid((unsigned)((P.k + 127) / 128), (unsigned)(P.m / 64));
     const bool tc = P.tc_w != nullptr;
@@ -405,6 +430,24 @@ template <typename T, typename TOut> int launch_dual(const DualParams &P, int se
         else ts_dual_kernel<T, TOut, false, false><<<grid, 256, 0, st>>>(P);
     }
     return launch_status();
+}
+
+template <typename T, typename TOut> int launch_dual_batch(const DualBatch &B, int select, bool tc, cudaStream_t st) {
+    const unsigned grid = B.first[B.count];
+    if (select) {
+        if (tc) ts_dual_batch_kernel<T, TOut, true, true><<<grid, 256, 0, st>>>(B);
+        else ts_dual_batch_kernel<T, TOut, true, false><<<grid, 256, 0, st>>>(B);
+    } else {
+        if (tc) ts_dual_batch_kernel<T, TOut, false, true><<<grid, 256, 0, st>>>(B);
+        else ts_dual_batch_kernel<T, TOut, false, false><<<grid, 256, 0, st>>>(B);
+    }
+    return launch_status();
+}
+
+template <typename T> int dispatch_dual_batch(const DualBatch &B, int packed_dtype, int select, bool tc, cudaStream_t st) {
+    if (packed_dtype == SP24_F16) return launch_dual_batch<T, __half>(B, select, tc, st);
+    if (packed_dtype == SP24_BF16) return launch_dual_batch<T, __nv_bfloat16>(B, select, tc, st);
+    return SP24_ERR_DTYPE;
 }
 
 template <typename T> int dispatch_dual(const DualParams &P, int packed_dtype, int select, cudaStream_t st) {
@@ -449,10 +492,10 @@ extern "C" int sp24_transposable_select(const void *x, int dtype, int64_t m, int
     return launch_status();
 }
 
-static int select_dual_compress_impl(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select, void *mask,
-                                     int64_t ld_mask, void *packed_w, int packed_dtype, int64_t ld_packed_w, void *meta_w,
-                                     void *packed_t, int64_t ld_packed_t, void *meta_t, void *tc_w, void *tc_t,
-                                     void *stream) {
+// Argument checks of one matrix; fills P.  No CUDA call.
+static int make_dual_params(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, void *mask, int64_t ld_mask,
+                            void *packed_w, int packed_dtype, int64_t ld_packed_w, void *meta_w, void *packed_t,
+                            int64_t ld_packed_t, void *meta_t, void *tc_w, void *tc_t, DualParams *P) {
     if (!w || !mask || !packed_w || !meta_w || !packed_t || !meta_t) return SP24_ERR_ARG;
     if (dtype != SP24_F32 && dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
     if (packed_dtype != SP24_F16 && packed_dtype != SP24_BF16) return SP24_ERR_DTYPE;
@@ -464,16 +507,68 @@ static int select_dual_compress_impl(const void *w, int dtype, int64_t m, int64_
     if (!aligned16(w) || !aligned16(mask) || !aligned16(packed_w) || !aligned16(meta_w) || !aligned16(packed_t) ||
         !aligned16(meta_t) || (tc_w && !aligned16(tc_w)) || (tc_t && !aligned16(tc_t)))
         return SP24_ERR_ALIGN;
+    *P = DualParams{w, static_cast<uint8_t *>(mask), packed_w, packed_t, static_cast<int16_t *>(meta_w),
+                    static_cast<int16_t *>(meta_t), m, k, ld_w, ld_mask, ld_packed_w, ld_packed_t,
+                    static_cast<int16_t *>(tc_w), static_cast<int16_t *>(tc_t), (m / 128) * (k / 128) * 2048,
+                    (k / 128) * (m / 128) * 2048};
+    return SP24_OK;
+}
+
+static int select_dual_compress_impl(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select, void *mask,
+                                     int64_t ld_mask, void *packed_w, int packed_dtype, int64_t ld_packed_w, void *meta_w,
+                                     void *packed_t, int64_t ld_packed_t, void *meta_t, void *tc_w, void *tc_t,
+                                     void *stream) {
+    DualParams P;
+    if (int rc = make_dual_params(w, dtype, m, k, ld_w, mask, ld_mask, packed_w, packed_dtype, ld_packed_w, meta_w,
+                                  packed_t, ld_packed_t, meta_t, tc_w, tc_t, &P))
+        return rc;
     if (int rc = check_device()) return rc;
-    DualParams P{w, static_cast<uint8_t *>(mask), packed_w, packed_t, static_cast<int16_t *>(meta_w),
-                 static_cast<int16_t *>(meta_t), m, k, ld_w, ld_mask, ld_packed_w, ld_packed_t,
-                 static_cast<int16_t *>(tc_w), static_cast<int16_t *>(tc_t), (m / 128) * (k / 128) * 2048, (k / 128) * (m / 128) * 2048};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dtype) {
         case SP24_F32: return dispatch_dual<float>(P, packed_dtype, select, st);
         case SP24_F16: return dispatch_dual<__half>(P, packed_dtype, select, st);
         default: return dispatch_dual<__nv_bfloat16>(P, packed_dtype, select, st);
     }
+}
+
+// Same conversion for `count` matrices of one element type in as few launches as possible (48 matrices per launch).
+// Either every descriptor carries both tensor-core metadata pointers or none does.
+extern "C" int sp24_select_dual_compress_batch(const sp24_dual_desc *descs, int count, int dtype, int packed_dtype,
+                                               int select, void *stream) {
+    if (!descs || count <= 0) return SP24_ERR_ARG;
+    const bool tc = descs[0].tc_w != nullptr;
+    for (int i = 0; i < count; ++i)
+        if ((descs[i].tc_w != nullptr) != tc || (descs[i].tc_t != nullptr) != tc) return SP24_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    bool device_checked = false;
+    for (int base = 0; base < count; base += kDualBatchMax) {
+        DualBatch B;
+        B.count = count - base < kDualBatchMax ? count - base : kDualBatchMax;
+        uint64_t blocks = 0;
+        for (int i = 0; i < B.count; ++i) {
+            const sp24_dual_desc &d = descs[base + i];
+            if (int rc = make_dual_params(d.w, dtype, d.m, d.k, d.ld_w, d.mask, d.ld_mask, d.packed_w, packed_dtype,
+                                          d.ld_packed_w, d.meta_w, d.packed_t, d.ld_packed_t, d.meta_t, d.tc_w, d.tc_t,
+                                          &B.p[i]))
+                return rc;
+            B.first[i] = (unsigned)blocks;
+            blocks += (uint64_t)((d.k + 127) / 128) * (uint64_t)(d.m / 64);
+            if (blocks > 0x7FFFFFFFull) return SP24_ERR_TOO_LARGE;
+        }
+        B.first[B.count] = (unsigned)blocks;
+        if (!device_checked) {
+            if (int rc = check_device()) return rc;
+            device_checked = true;
+        }
+        int rc;
+        switch (dtype) {
+            case SP24_F32: rc = dispatch_dual_batch<float>(B, packed_dtype, select, tc, st); break;
+            case SP24_F16: rc = dispatch_dual_batch<__half>(B, packed_dtype, select, tc, st); break;
+            default: rc = dispatch_dual_batch<__nv_bfloat16>(B, packed_dtype, select, tc, st);
+        }
+        if (rc) return rc;
+    }
+    return SP24_OK;
 }
 
 extern "C" int sp24_select_dual_compress(const void *w, int dtype, int64_t m, int64_t k, int64_t ld_w, int select,

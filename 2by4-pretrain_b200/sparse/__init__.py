@@ -7,10 +7,10 @@ classes the reference only lists in its README (``SparseLinearTranspose``,
 from .legacy import MVUE24_approx_torch, sparse24_torch, soft_threshold24_torch
 from .triton_ops import MVUE24_approx_triton, sparse24_triton, soft_threshold24_triton
 from .decay import masked_add_, adamw_masked_decay_
-from .transposable_semi_structured import TransposableSparse, select_and_compress
+from .transposable_semi_structured import TransposableSparse, select_and_compress, select_and_compress_many
 from .semi_structured import to_sparse_semi_structured, SparseSemiStructuredTensor
 from .sparse_ops import (MyLinear, SparseLinear, SparseLinearTranspose, sparse_linear_transpose, sparse_state,
-                         load_sparse_state)
+                         load_sparse_state, refresh_sparse_layers)
 from .sste import SoftThreshold, SoftThresholdLinear
 
 mask_select = TransposableSparse()
@@ -31,6 +31,8 @@ __all__ = [
     'TransposableSparse',
     'mask_select',
     'select_and_compress',
+    'select_and_compress_many',
+    'refresh_sparse_layers',
     'to_sparse_semi_structured',
     'SparseSemiStructuredTensor',
     'SoftThreshold',

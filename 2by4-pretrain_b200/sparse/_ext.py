@@ -24,6 +24,13 @@ _lib = None
 
 _i64, _i32, _u64, _vp, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_float
 
+class DualDesc(ctypes.Structure):
+    """``sp24_dual_desc`` of the C header: one matrix of a batched select + dual compress call."""
+    _fields_ = [("w", _vp), ("m", _i64), ("k", _i64), ("ld_w", _i64), ("mask", _vp), ("ld_mask", _i64),
+                ("packed_w", _vp), ("ld_packed_w", _i64), ("meta_w", _vp), ("packed_t", _vp), ("ld_packed_t", _i64),
+                ("meta_t", _vp), ("tc_w", _vp), ("tc_t", _vp)]
+
+
 _SIGNATURES = {
     "sp24_prune_compress": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _i64, _vp, _i32, _vp, _i64, _vp, _i64,
                             _u64, _u64, _vp],
@@ -39,6 +46,7 @@ _SIGNATURES = {
                                   _vp, _vp],
     "sp24_select_dual_compress_tc": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i32, _i64, _vp, _vp, _i64,
                                      _vp, _vp, _vp, _vp],
+    "sp24_select_dual_compress_batch": [ctypes.POINTER(DualDesc), _i32, _i32, _i32, _i32, _vp],
     "sp24_masked_add": [_vp, _vp, _vp, _i32, _i64, _f32, _vp],
 }
 

@@ -277,7 +277,10 @@ class SparseLinearTranspose(nn.Linear):
             if w.mask.device != w.device:
                 w.mask = w.mask.to(device=w.device)
             if w.cnt == 0:
-                self._refresh(reselect=(w.counter % w.freq == 0))
+                if getattr(w, 'refreshed', False):
+                    w.refreshed = False      # refresh_sparse_layers has just rebuilt the copies of this step
+                else:
+                    self._refresh(reselect=(w.counter % w.freq == 0))
             elif w.compressed is None:   # state restored in the middle of an accumulation window
                 self._refresh(reselect=False)
             pw, mw, pt, mt = w.compressed
@@ -289,6 +292,50 @@ class SparseLinearTranspose(nn.Linear):
             w.step += 1
             w.cnt += 1
         return x
+
+
+def refresh_sparse_layers(model: nn.Module) -> int:
+    """What every ``SparseLinearTranspose`` of ``model`` would do at the start of its next forward pass when a
+    refresh is due (``cnt`` == 0): reselect the mask if ``counter % freq == 0`` and rebuild the compressed copies
+    of W and W^T; done here for all those layers with one kernel launch per 48 weights instead of one per layer.
+    Call it right before the forward pass, under the same autocast context.  Layers whose shapes are not
+    multiples of 128 are left to refresh themselves.  Returns the number of layers refreshed."""
+    from .transposable_semi_structured import select_and_compress_many
+    dtype = torch.float16
+    if torch.is_autocast_enabled('cuda') and torch.get_autocast_dtype('cuda') == torch.bfloat16:
+        dtype = torch.bfloat16
+    groups = {}
+    for mod in model.modules():
+        if not isinstance(mod, SparseLinearTranspose):
+            continue
+        w = mod.weight
+        if w.mode != 'sparse' or w.cnt != 0 or not w.is_cuda or w.shape[0] % 128 or w.shape[1] % 128:
+            continue
+        if w.mask.device != w.device:
+            w.mask = w.mask.to(device=w.device)
+        if w.mask.dtype != torch.bool or not w.mask.is_contiguous():
+            w.mask = w.mask.to(torch.bool).contiguous()
+        groups.setdefault((w.counter % w.freq == 0, w.dtype, w.device), []).append(mod)
+    done = 0
+    for (reselect, _, _), mods in groups.items():
+        res = select_and_compress_many([m.weight for m in mods], [m.weight.mask for m in mods], dtype=dtype,
+                                       reselect=reselect)
+        for mod, (mask, (pw, mw), (pt, mt)) in zip(mods, res):
+            w = mod.weight
+            w.compressed = (pw, mw, pt, mt)
+            w.refreshed = True
+            if mod.materialize_sparse_tensors:
+                out_f, in_f = w.shape
+                w.weight_sparse = SparseSemiStructuredTensor(
+                    None, original_shape=torch.Size([out_f, in_f]), sparse_tensor_cutlass=pw, meta_tensor_cutlass=mw,
+                    dtype=dtype)
+                w.weight_sparse_T = SparseSemiStructuredTensor(
+                    None, original_shape=torch.Size([in_f, out_f]), sparse_tensor_cutlass=pt, meta_tensor_cutlass=mt,
+                    dtype=dtype)
+            else:
+                w.weight_sparse = w.weight_sparse_T = None
+            done += 1
+    return done
 
 
 def sparse_state(model: nn.Module) -> dict:

@@ -105,3 +105,53 @@ def select_and_compress(weight: Tensor, mask: Tensor = None, dtype: torch.dtype 
             meta_t.data_ptr(), _ext.stream())
         _ext.check(rc, "sp24_select_dual_compress")
     return mask, (packed_w, meta_w), (packed_t, meta_t)
+
+
+def select_and_compress_many(weights, masks, dtype: torch.dtype = torch.float16, reselect: bool = False):
+    """``select_and_compress`` for a list of weights of one dtype in one kernel launch per 48 matrices (the
+    per-step recompression of all layers of a model, each too small to fill the GPU alone).  ``masks``: one
+    contiguous bool (m, k) tensor per weight; read when ``reselect`` is false, overwritten with the newly
+    selected mask when it is true.  Every shape must be a multiple of 128 in both dimensions.  Returns a list of
+    (mask, (packed_w, meta_w), (packed_t, meta_t)) like the single call."""
+    from . import spmm as _spmm
+    if len(weights) == 0:
+        return []
+    if len(masks) != len(weights):
+        raise RuntimeError("select_and_compress_many: one mask per weight")
+    _ext.require_cuda(*weights, *masks)
+    descs = (_ext.DualDesc * len(weights))()
+    out, keep = [], []
+    for i, (weight, mask) in enumerate(zip(weights, masks)):
+        m, k = weight.shape
+        if m % 128 or k % 128:
+            raise RuntimeError(f"select_and_compress_many: shape {(m, k)} is not a multiple of 128 x 128")
+        if weight.dtype != weights[0].dtype or weight.device != weights[0].device:
+            raise RuntimeError("select_and_compress_many: all weights must share dtype and device")
+        if mask.dtype != torch.bool or tuple(mask.shape) != (m, k) or not mask.is_contiguous():
+            raise RuntimeError("select_and_compress_many: masks must be contiguous bool tensors of the weights' shapes")
+        w = _ext.as_layout(weight.detach(), 0)
+        buf_w = torch.empty(m * k * 9 // 16, dtype=dtype, device=w.device)
+        buf_t = torch.empty(m * k * 9 // 16, dtype=dtype, device=w.device)
+        packed_w = buf_w[: m * k // 2].view(m, k // 2)
+        meta_w = buf_w[m * k // 2:].view(torch.int16).view(m, k // 16)
+        packed_t = buf_t[: m * k // 2].view(m // 2, k).t()
+        meta_t = buf_t[m * k // 2:].view(torch.int16).view(k, m // 16)
+        tc_w = torch.empty(_spmm.tc_bytes(m, k), dtype=torch.uint8, device=w.device)
+        tc_t = torch.empty(_spmm.tc_bytes(k, m), dtype=torch.uint8, device=w.device)
+        d = descs[i]
+        d.w, d.m, d.k, d.ld_w = w.data_ptr(), m, k, _ext.layout_of(w)[1]
+        d.mask, d.ld_mask = mask.data_ptr(), k
+        d.packed_w, d.ld_packed_w, d.meta_w = packed_w.data_ptr(), k // 2, meta_w.data_ptr()
+        d.packed_t, d.ld_packed_t, d.meta_t = packed_t.data_ptr(), k, meta_t.data_ptr()
+        d.tc_w, d.tc_t = tc_w.data_ptr(), tc_t.data_ptr()
+        keep.append(w)
+        out.append((mask, (packed_w, meta_w), (packed_t, meta_t), (tc_w, tc_t)))
+    rc = _ext.lib().sp24_select_dual_compress_batch(descs, len(weights), _ext.dt(weights[0].dtype), _ext.dt(dtype),
+                                                    1 if reselect else 0, _ext.stream())
+    _ext.check(rc, "sp24_select_dual_compress_batch")
+    res = []
+    for mask, (pw, mw), (pt, mt), (tc_w, tc_t) in out:
+        _spmm.register_tc_metadata(mw, tc_w)
+        _spmm.register_tc_metadata(mt, tc_t)
+        res.append((mask, (pw, mw), (pt, mt)))
+    return res

@@ -262,6 +262,8 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         rng_counter.add_(1)
         x, y = static_tok[:, :-1], static_tok[:, 1:]
         with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+            if mode == "sparse":
+                sparse.refresh_sparse_layers(model)     # all layers' W / W^T copies in one launch
             loss = model(x, y)
         loss.backward()
         return loss.detach()

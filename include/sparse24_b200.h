@@ -179,6 +179,29 @@ int sp24_select_dual_compress_tc(const void *w, int dtype, int64_t m, int64_t k,
                                  void *stream);
 
 /*
+ * sp24_select_dual_compress(_tc) for several matrices of one element type in one launch per 48 matrices: the
+ * per-step recompression of every layer of a model (README.md:148-155 of the reference, once per layer), where
+ * one matrix alone is too small to fill the GPU.  Fields as the arguments of the same name above; tc_w / tc_t
+ * are either both set in every descriptor or NULL in every descriptor.  The descriptors are read on the host
+ * during the call.  No counterpart in the reference.
+ */
+typedef struct sp24_dual_desc {
+    const void *w;
+    int64_t m, k, ld_w;
+    void *mask;
+    int64_t ld_mask;
+    void *packed_w;
+    int64_t ld_packed_w;
+    void *meta_w;
+    void *packed_t;
+    int64_t ld_packed_t;
+    void *meta_t;
+    void *tc_w, *tc_t;
+} sp24_dual_desc;
+int sp24_select_dual_compress_batch(const sp24_dual_desc *descs, int count, int dtype, int packed_dtype, int select,
+                                    void *stream);
+
+/*
  * Masked decay, in place: grad[i] += p[i] * alpha where mask[i] == 0 (two roundings, no fused
  * multiply-add).  Replaces masked_add_ / masked_add_kernel (sparse/decay.py:7-37).
  * grad, p: float32, n elements, contiguous; mask_itemsize 1 (bool / uint8), 2 (f16 / bf16) or 4 (f32),

@@ -96,6 +96,18 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     # tensor-core metadata copies need whole 128-row / 128-column blocks
     assert lib.sp24_select_dual_compress_tc(p, F16, 64, 128, 128, 1, q, 128, q, F16, 64, r, q, 128, r, st, st, None) == -1
     assert lib.sp24_prune_compress_ex(p, F16, 64, 64, 64, 0, q, F16, 32, r, 0, None, 0, None, 0, 0, 0, None, st, None, None) == -5
+    # batched select + dual compress: empty batch, descriptors that disagree about the tensor-core copies, bad shape
+    from sparse._ext import DualDesc
+    descs = (DualDesc * 2)()
+    for d in descs:
+        d.w, d.m, d.k, d.ld_w, d.mask, d.ld_mask = base, 128, 128, 128, base, 128
+        d.packed_w, d.ld_packed_w, d.meta_w, d.packed_t, d.ld_packed_t, d.meta_t = base, 64, base, base, 128, base
+    assert lib.sp24_select_dual_compress_batch(descs, 0, F16, F16, 0, None) == -5
+    descs[1].tc_w = descs[1].tc_t = base
+    assert lib.sp24_select_dual_compress_batch(descs, 2, F16, F16, 0, None) == -5
+    descs[1].tc_w = descs[1].tc_t = None
+    descs[1].m = 96
+    assert lib.sp24_select_dual_compress_batch(descs, 2, F16, F16, 0, None) == -1
     # row sums exist for column-major storage only
     assert lib.sp24_prune_compress_ex(p, F16, 128, 64, 64, 0, q, F16, 32, r, 0, None, 0, None, 0, 0, 0, None, None, st, None) == -5
 

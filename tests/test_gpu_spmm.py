@@ -620,3 +620,59 @@ def test_spmm_random_shapes_agree_with_the_reference(S):
         assert float(err.max() / ref.abs().max()) <= tol, (case, ms, k, n, dtype, a_col, use_bias)
         assert bool((err <= tol * bound + 1e-30).all()), (case, ms, k, n, dtype, a_col, use_bias)
     check_status()
+
+
+@pytest.mark.parametrize("reselect", [False, True])
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+def test_batched_select_and_compress_equals_the_single_calls(S, reselect, wdt):
+    """One launch over many matrices (52 of them: two launches) writes what the per-matrix calls write, bit for
+    bit: masks, packed values, reordered metadata and the tensor-core metadata copies."""
+    from sparse.spmm import tc_metadata as _tcm
+    tc_metadata = lambda meta: _tcm(meta, meta.shape[0], meta.shape[1] * 16)   # the copy registered by the kernels
+    g = torch.Generator().manual_seed(41)
+    shapes = [(128, 128), (256, 384), (768, 256), (128, 640)] * 13
+    ws = [(torch.randn(m, k, generator=g) * 0.02).to(wdt).to(DEV) for m, k in shapes]
+    singles, masks = [], []
+    for w in ws:
+        mk, (pw, mw), (pt, mt) = S.select_and_compress(w, None, torch.bfloat16)
+        if not reselect:   # second pass reading the mask, the form the batch call is compared with
+            mk, (pw, mw), (pt, mt) = S.select_and_compress(w, mk, torch.bfloat16)
+        singles.append((mk.clone(), pw.clone(), mw.clone(), pt.clone(), mt.clone(), tc_metadata(mw).clone(), tc_metadata(mt).clone()))
+        masks.append(torch.zeros_like(mk) if reselect else mk.clone())
+    res = S.select_and_compress_many(ws, masks, dtype=torch.bfloat16, reselect=reselect)
+    assert len(res) == len(ws)
+    for (mk, (pw, mw), (pt, mt)), ref, given in zip(res, singles, masks):
+        assert mk is given
+        assert torch.equal(mk, ref[0])
+        assert torch.equal(pw.view(torch.int16), ref[1].view(torch.int16)) and torch.equal(mw, ref[2])
+        assert torch.equal(pt.view(torch.int16), ref[3].view(torch.int16)) and torch.equal(mt, ref[4])
+        assert torch.equal(tc_metadata(mw), ref[5]) and torch.equal(tc_metadata(mt), ref[6])
+    with pytest.raises(RuntimeError):
+        S.select_and_compress_many([ws[0][:64]], [masks[0][:64].contiguous()], dtype=torch.bfloat16)
+
+
+def test_model_wide_refresh_equals_the_per_layer_refresh(S):
+    """refresh_sparse_layers before the forward pass: same outputs and gradients as layers refreshing themselves
+    (same seeds), counters advance the same way, and a second forward in the same accumulation window does not
+    refresh again."""
+    def make():
+        torch.manual_seed(9)
+        return torch.nn.Sequential(S.SparseLinearTranspose(256, 384), torch.nn.GELU(), S.SparseLinearTranspose(384, 128)).to(DEV)
+    a, b = make(), make()
+    x = torch.randn(128, 256, device=DEV)
+    outs = []
+    for net, batched in ((a, False), (b, True)):
+        random.seed(5)
+        if batched:
+            assert S.refresh_sparse_layers(net) == 2
+        y = net(x)
+        y.float().square().sum().backward()
+        if batched:
+            assert S.refresh_sparse_layers(net) == 0      # cnt != 0 now: nothing is due
+        outs.append((y.detach().clone(), [p.grad.clone() for p in net.parameters()],
+                     [(m.weight.cnt, m.weight.counter) for m in net if hasattr(m, 'weight')]))
+    assert torch.equal(outs[0][0], outs[1][0])
+    for ga, gb in zip(outs[0][1], outs[1][1]):
+        assert torch.equal(ga, gb)
+    assert outs[0][2] == outs[1][2]
+    assert torch.equal(a[0].weight.mask, b[0].weight.mask) and torch.equal(a[2].weight.mask, b[2].weight.mask)
