@@ -117,6 +117,7 @@ def run(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12,
         lr=6e-4, verbose=False):
     """Returns a dict with tokens/s (whole job) and ms per step, timed on the device, max over ranks."""
     import torch.distributed as dist
+    import sparse
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -144,6 +145,8 @@ def run(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12,
         tok = tok.pin_memory().to(dev, non_blocking=True)
         x, y = tok[:, :-1], tok[:, 1:]
         with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+            if mode == "sparse":
+                sparse.refresh_sparse_layers(model)     # all layers' W / W^T copies in one launch
             loss = net(x, y)
         loss.backward()
         if mode == "sparse":
