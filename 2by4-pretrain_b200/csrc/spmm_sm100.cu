@@ -167,7 +167,7 @@ struct SpmmParams {
     int *status;
     uint32_t idesc;         // instruction descriptor without the metadata selector bits
     int activation;         // 0 none, 1 relu, 2 silu, 3 gelu (tanh form)
-    unsigned long long *trace;  // optional timing trace of CTA 0 (debugging aid), else null
+    unsigned long long *trace;  // timing trace of CTA 0: only developer builds (-DSP24_TRACE_BUILD) ever set it
     int int8;               // 8-bit operands are signed integers (kind::i8, int32 accumulators and output)
     int k_splits;           // work units per tile along K (> 1 only for the accumulating fp32 output)
     int mblk_per_tile;      // 128-row blocks per tile: 2 (B staged once per 256 rows) or 1 (more, smaller tiles)
@@ -218,8 +218,13 @@ __device__ __forceinline__ unsigned long long globaltimer() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// trace layout: 3 roles x 256 slots of nanosecond timestamps, CTA 0 only
+// trace layout: 3 roles x 256 slots of nanosecond timestamps, CTA 0 only.  Compiled out of the shipped library:
+// a developer build (-DSP24_TRACE_BUILD) stores through P.trace, which that build takes from the environment.
+#ifdef SP24_TRACE_BUILD
 #define SP24_TRACE(role, slot) do { if (P.trace && blockIdx.x == 0 && (slot) < 256) P.trace[(role) * 256 + (slot)] = globaltimer(); } while (0)
+#else
+#define SP24_TRACE(role, slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
@@ -1225,6 +1230,15 @@ int make_map(CUtensorMap *map, const void *base, int dt, int64_t rows, int64_t c
     return r == CUDA_SUCCESS ? SP24_OK : SP24_ERR_CUDA;
 }
 
+// SP24_SPMM_PAIR=0 in the environment keeps every GEMM on the single-CTA kernels (read once per process)
+bool pair_kernels_enabled() {
+    static const bool enabled = [] {
+        const char *env = getenv("SP24_SPMM_PAIR");
+        return !(env && atoi(env) == 0);
+    }();
+    return enabled;
+}
+
 int sm_count_cached() {
     static int cached[64];
     int dev = 0;
@@ -1405,10 +1419,11 @@ extern "C" int64_t sp24_meta_tc_bytes(int64_t m, int64_t k) {
     return ((m + 127) / 128) * ((k + 127) / 128) * 2048;
 }
 
-extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms,
-                         int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype,
-                         int trans_out, int64_t ld_out, const void *bias, int activation, int *status, void *stream) {
-    if (!a_packed || !e_tc || !b || !out) return SP24_ERR_ARG;
+// Argument checks of sp24_spmm (everything except the metadata pointer); no CUDA call.
+static int validate_spmm_args(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, int64_t ms, int64_t k,
+                              const void *b, int b_mn_major, int64_t ld_b, int64_t n, const void *out, int out_dtype,
+                              int trans_out, int64_t ld_out, const void *bias, int activation) {
+    if (!a_packed || !b || !out) return SP24_ERR_ARG;
     const bool i8 = dtype == SP24_I8;
     const bool f8 = dtype == SP24_E4M3 || dtype == SP24_E5M2 || i8;   // 8-bit operand geometry
     if (!f8 && dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
@@ -1424,7 +1439,20 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     const int64_t a_inner = a_mn_major ? ms : k / 2, b_inner = b_mn_major ? n : k, o_inner = trans_out ? ms : n;
     if (ld_a < a_inner || (ld_a * esz) % 16 || ld_b < b_inner || (ld_b * esz) % 16 || ld_out < o_inner) return SP24_ERR_STRIDE;
     if ((ld_out * dtype_size(out_dtype)) % 16) return SP24_ERR_STRIDE;
-    if (!aligned16(a_packed) || !aligned16(e_tc) || !aligned16(b) || !aligned16(out)) return SP24_ERR_ALIGN;
+    if (!aligned16(a_packed) || !aligned16(b) || !aligned16(out)) return SP24_ERR_ALIGN;
+    return SP24_OK;
+}
+
+extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms,
+                         int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype,
+                         int trans_out, int64_t ld_out, const void *bias, int activation, int *status, void *stream) {
+    if (!e_tc) return SP24_ERR_ARG;
+    if (int rc = validate_spmm_args(a_packed, dtype, a_mn_major, ld_a, ms, k, b, b_mn_major, ld_b, n, out, out_dtype,
+                                    trans_out, ld_out, bias, activation))
+        return rc;
+    if (!aligned16(e_tc)) return SP24_ERR_ALIGN;
+    const bool i8 = dtype == SP24_I8;
+    const bool f8 = dtype == SP24_E4M3 || dtype == SP24_E5M2 || i8;   // 8-bit operand geometry
     if (int rc = check_device()) return rc;
 
     CUtensorMap map_a;
@@ -1438,7 +1466,9 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     P.k_atoms = (k + 127) / 128; P.status = status; P.activation = activation;
     P.trace = nullptr;
     P.k_splits = 1;
+#ifdef SP24_TRACE_BUILD
     if (const char *env = getenv("SP24_SPMM_TRACE_PTR")) P.trace = reinterpret_cast<unsigned long long *>(strtoull(env, nullptr, 0));
+#endif
     // operand format codes: f16 0 / bf16 1; e4m3 0 / e5m2 1; unsigned 0 / signed 1 for the integer kind
     const uint32_t fmt = (dtype == SP24_BF16 || dtype == SP24_E5M2 || i8) ? 1u : 0u;
     // sparse flag, accumulator format (fp32 = 1, int32 = 2), operand formats, operand majors, M = 128 (N is added
@@ -1449,7 +1479,7 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // CTA-pair kernel: 16-bit types, token-major B and output, whole 256-row blocks, no activation
     bool pair_form = !f8 && !b_mn_major && trans_out && ms % 256 == 0 && activation == 0 && n >= 1024;
-    if (const char *env = getenv("SP24_SPMM_PAIR")) pair_form = pair_form && atoi(env) != 0;
+    pair_form = pair_form && pair_kernels_enabled();
     if (pair_form) {
         CUtensorMap map_b, map_e;
         rc = make_map(&map_b, b, dtype, n, k, ld_b, 64, two::BN2 / 2);
@@ -1556,9 +1586,14 @@ extern "C" int sp24_spmm_noalloc(const void *a_packed, int dtype, int a_mn_major
                                  int64_t ms, int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out,
                                  int out_dtype, int trans_out, int64_t ld_out, const void *bias, int activation,
                                  int *status, void *stream) {
+    // every check of sp24_spmm comes first: a rejected call launches nothing and leaves the shared array alone
     if (!meta) return SP24_ERR_ARG;
-    const bool f8 = dtype == SP24_E4M3 || dtype == SP24_E5M2;
-    if (ms <= 0 || k <= 0 || ms % 128 || k % (f8 ? 128 : 64)) return SP24_ERR_SHAPE;
+    if (int rc = validate_spmm_args(a_packed, dtype, a_mn_major, ld_a, ms, k, b, b_mn_major, ld_b, n, out, out_dtype,
+                                    trans_out, ld_out, bias, activation))
+        return rc;
+    if (!aligned16(meta)) return SP24_ERR_ALIGN;
+    // fp8 and int8 operands carry 32-bit metadata words, the 16-bit types 16-bit words
+    const bool f8 = dtype == SP24_E4M3 || dtype == SP24_E5M2 || dtype == SP24_I8;
     if (sp24_meta_tc_bytes(ms, k) > NOALLOC_SCRATCH_BYTES) return SP24_ERR_TOO_LARGE;
     if (int rc = check_device()) return rc;
     void *scratch = nullptr;
@@ -1603,7 +1638,7 @@ extern "C" int sp24_spmm_accumulate_f32(const void *a_packed, int dtype, int a_m
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // CTA-pair kernel for whole 256-row blocks and at least one full tile of columns
     bool pair_form = ms % 256 == 0 && n >= 256;
-    if (const char *env = getenv("SP24_SPMM_PAIR")) pair_form = pair_form && atoi(env) != 0;
+    pair_form = pair_form && pair_kernels_enabled();
     if (pair_form) {
         CUtensorMap map_e;
         rc = make_map_e(&map_e, e_tc, (ms / 128) * P.k_atoms);

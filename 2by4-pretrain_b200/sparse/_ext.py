@@ -109,9 +109,20 @@ def ptr(t):
 
 
 def require_cuda(*tensors):
+    """Every tensor (``None`` entries skipped) must be a CUDA tensor on the CURRENT device: the kernels run on the
+    current device's current stream and dereference raw addresses, so a tensor of another GPU would be an illegal
+    address on the device instead of a Python error.  Select the device first (``torch.cuda.device(t.device)``)."""
+    current = None
     for t in tensors:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise RuntimeError(f"Error tensor.device= {t.device} is not supported! Only CUDA tensors are currently supported.")
+        if current is None:
+            current = torch.cuda.current_device()
+        if t.device.index != current:
+            raise RuntimeError(f"tensor on {t.device} but the current CUDA device is cuda:{current}: the sparse24 kernels "
+                               "launch on the current device; wrap the call in torch.cuda.device(tensor.device)")
 
 
 def layout_of(t: torch.Tensor):

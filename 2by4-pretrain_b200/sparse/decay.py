@@ -10,6 +10,7 @@ def masked_add_(grad: torch.Tensor, p_data: torch.Tensor, p_mask: torch.Tensor, 
     grad.add_(p.data * (1 - p.mask), alpha=decay)
     '''
     assert grad.is_cuda and p_data.is_cuda and p_mask.is_cuda
+    _ext.require_cuda(grad, p_data, p_mask)
     assert (grad.layout, p_data.layout, p_mask.layout) == (torch.strided, torch.strided, torch.strided)
     assert grad.stride() == p_data.stride() == p_mask.stride()
     if grad.dtype != torch.float32 or p_data.dtype != torch.float32:

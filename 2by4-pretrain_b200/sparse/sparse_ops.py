@@ -21,70 +21,43 @@ from .triton_ops import MVUE24_approx_triton
 from .spmm import sparse_linear as _spmm, sparse_mm_accumulate_ as _spmm_acc
 
 
-class my_linear(autograd.Function):
-    @staticmethod
-    @custom_fwd(device_type='cuda')
-    def forward(ctx, input, weight, bias):
-        ctx.save_for_backward(input, weight, bias)
-        ctx.shape = input.shape
-        input = input.view(-1, input.shape[-1])
-        output = torch.mm(input, weight.t())
-        if bias is None:
-            return output.view(*ctx.shape[:-1], -1)
-        return output.view(*ctx.shape[:-1], -1) + bias
+def _dense_linear(name, dx_weight, doc):
+    """Builds the autograd function of a dense linear layer, y = x W^T (+ b), whose input gradient is
+    dY @ ``dx_weight(W)``.  The two dense layers of the reference differ only in that factor
+    (sparse/sparse_ops.py:8-87 of the reference): W itself, or a fresh MVUE 2:4 estimate of it."""
 
-    @staticmethod
-    @custom_bwd(device_type='cuda')
+    def forward(ctx, input, weight, bias):
+        ctx.save_for_backward(input, weight)
+        ctx.lead = input.shape[:-1]
+        y = input.reshape(-1, input.shape[-1]).mm(weight.t()).view(*ctx.lead, weight.shape[0])
+        return y if bias is None else y + bias
+
     def backward(ctx, grad_output):
-        input, weight, bias = ctx.saved_tensors
-        grad_input = grad_weight = grad_bias = None
-        if ctx.needs_input_grad[0]:
-            grad_output = grad_output.reshape(-1, grad_output.shape[-1])
-            grad_input = torch.mm(grad_output, weight).view(ctx.shape)
-        if ctx.needs_input_grad[1]:
-            input = input.view(-1, input.shape[-1])
-            grad_output = grad_output.reshape(-1, grad_output.shape[-1])
-            grad_weight = torch.mm(grad_output.t(), input)
-        if ctx.needs_input_grad[2]:
-            grad_bias = grad_output.reshape(-1, grad_output.shape[-1]).sum(0)
-        return grad_input, grad_weight, grad_bias
+        input, weight = ctx.saved_tensors
+        want_x, want_w, want_b = ctx.needs_input_grad
+        g = grad_output.reshape(-1, weight.shape[0])
+        gx = g.mm(dx_weight(weight)).view(*ctx.lead, weight.shape[1]) if want_x else None
+        gw = g.t().mm(input.reshape(-1, weight.shape[1])) if want_w else None
+        gb = g.sum(0) if want_b else None
+        return gx, gw, gb
+
+    return type(name, (autograd.Function,), {
+        "__doc__": doc,
+        "forward": staticmethod(custom_fwd(device_type='cuda')(forward)),
+        "backward": staticmethod(custom_bwd(device_type='cuda')(backward)),
+    })
+
+
+my_linear = _dense_linear("my_linear", lambda w: w, "Plain dense linear layer as a custom autograd function.")
+sparse_linear = _dense_linear(
+    "sparse_linear", lambda w: MVUE24_approx_triton(w.t()).t(),
+    "Dense GEMMs; the input gradient multiplies dY with an MVUE 2:4 estimate of the weight, drawn along its "
+    "output-feature axis on every backward pass.")
 
 
 class MyLinear(nn.Linear):
     def forward(self, x):
         return my_linear.apply(x, self.weight, self.bias)
-
-
-class sparse_linear(autograd.Function):
-    """Dense GEMMs; the backward pass multiplies dY with an MVUE 2:4 estimate of the weight
-    (sparse/sparse_ops.py:58-87 of the reference)."""
-
-    @staticmethod
-    @custom_fwd(device_type='cuda')
-    def forward(ctx, input, weight, bias):
-        ctx.save_for_backward(input, weight, bias)
-        ctx.shape = input.shape
-        input = input.view(-1, input.shape[-1])
-        output = torch.mm(input, weight.t())
-        if bias is None:
-            return output.view(*ctx.shape[:-1], -1)
-        return output.view(*ctx.shape[:-1], -1) + bias
-
-    @staticmethod
-    @custom_bwd(device_type='cuda')
-    def backward(ctx, grad_output):
-        input, weight, bias = ctx.saved_tensors
-        grad_input = grad_weight = grad_bias = None
-        if ctx.needs_input_grad[0]:
-            grad_output = grad_output.reshape(-1, grad_output.shape[-1])
-            grad_input = torch.mm(grad_output, MVUE24_approx_triton(weight.t()).t()).view(ctx.shape)
-        if ctx.needs_input_grad[1]:
-            input = input.view(-1, input.shape[-1])
-            grad_output = grad_output.reshape(-1, grad_output.shape[-1])
-            grad_weight = torch.mm(grad_output.t(), input)
-        if ctx.needs_input_grad[2]:
-            grad_bias = grad_output.reshape(-1, grad_output.shape[-1]).sum(0)
-        return grad_input, grad_weight, grad_bias
 
 
 class SparseLinear(nn.Linear):

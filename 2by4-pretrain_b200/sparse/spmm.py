@@ -33,7 +33,10 @@ _ACT = {None: 0, "none": 0, "relu": 1, "silu": 2, "gelu": 3}  # gelu (tanh form)
 # returns (sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:813-815 of the reference), a transposed view
 # of the (features, tokens) product; downstream element-wise ops and the next sparse GEMM accept it as is.
 RETURN_TRANSPOSED_VIEW = False
-_tc_meta_cache = {}  # id(meta tensor) -> (weak reference to it, tensor-core copy); tensors do not hash by value
+# id(meta tensor) -> (weak reference to it, tensor-core copy, (data_ptr, _version) of the metadata when the copy was
+# made); tensors do not hash by value.  An in-place write to the metadata (copy_ on a checkpoint restore, a write
+# through another view of the same storage) bumps its version counter, and the copy is then rebuilt on the next use.
+_tc_meta_cache = {}
 _status = {}
 
 
@@ -56,7 +59,13 @@ def check_status(device=None):
 
 
 def invalidate_meta(meta):
+    """Drop the cached tensor-core copy of ``meta``.  Only needed by code that rewrites the metadata behind torch's
+    back (a raw-pointer kernel launch): writes through torch are seen through the tensor's version counter."""
     _tc_meta_cache.pop(id(meta), None)
+
+
+def _stamp(meta):
+    return (meta.data_ptr(), meta._version)
 
 
 def tc_bytes(ms: int, k: int) -> int:
@@ -69,13 +78,13 @@ def tc_bytes(ms: int, k: int) -> int:
 def register_tc_metadata(meta: torch.Tensor, e_tc: torch.Tensor) -> None:
     """Attach a tensor-core-order copy that a compression kernel wrote together with ``meta``."""
     key = id(meta)
-    _tc_meta_cache[key] = (weakref.ref(meta, lambda _r, key=key: _tc_meta_cache.pop(key, None)), e_tc)
+    _tc_meta_cache[key] = (weakref.ref(meta, lambda _r, key=key: _tc_meta_cache.pop(key, None)), e_tc, _stamp(meta))
 
 
 def tc_metadata(meta: torch.Tensor, ms: int, k: int) -> torch.Tensor:
     """Metadata in the order the tensor cores consume (cached per metadata tensor object)."""
     hit = _tc_meta_cache.get(id(meta))
-    e = hit[1] if hit is not None and hit[0]() is meta else None
+    e = hit[1] if hit is not None and hit[0]() is meta and hit[2] == _stamp(meta) else None
     if e is None:
         lib = _ext.lib()
         e = torch.empty(tc_bytes(ms, k), dtype=torch.uint8, device=meta.device)

@@ -85,6 +85,15 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.sp24_spmm(p, F16, 0, 64, q, 64, 128, r, 0, 128, 8, st, F16, 1, 64, None, 0, None, None) == -1
     assert lib.sp24_spmm(p, I8, 0, 64, q, 128, 128, r, 0, 128, 8, st, F32, 1, 128, None, 0, None, None) == -3
     assert lib.sp24_spmm(p, I8, 0, 64, q, 128, 128, r, 0, 128, 8, st, I32, 1, 128, r, 0, None, None) == -5
+    # the allocation-free GEMM runs the same checks before it touches its scratch array or the device
+    noalloc = lib.sp24_spmm_noalloc
+    noalloc.restype = ctypes.c_int
+    noalloc.argtypes = lib.sp24_spmm.argtypes
+    assert noalloc(p, F16, 0, 64, q, 64, 128, r, 0, 128, 8, st, F16, 1, 64, None, 0, None, None) == -1
+    assert noalloc(p, I8, 0, 64, q, 128, 128, r, 0, 128, 8, st, F32, 1, 128, None, 0, None, None) == -3
+    assert noalloc(p, F16, 0, 64, q, 128, 128, r, 0, 128, 8, None, F16, 1, 128, None, 0, None, None) == -5
+    assert noalloc(p, F16, 0, 64, None, 128, 128, r, 0, 128, 8, st, F16, 1, 128, None, 0, None, None) == -5
+    assert noalloc(p, F16, 0, 4096, q, 8192, 8192, r, 0, 8192, 8, st, F16, 1, 8192, None, 0, None, None) == -8
     # accumulating form: fp8 is not accepted, n must keep 16-byte rows
     assert lib.sp24_spmm_accumulate_f32(p, 3, 0, 64, q, 128, 128, r, 8, 8, st, 8, 0, st, None) == -3
     assert lib.sp24_spmm_accumulate_f32(p, BF16, 0, 64, q, 128, 128, r, 12, 12, st, 12, 0, st, None) == -1
