@@ -20,6 +20,19 @@ int check_device() {
     return ok ? SP24_OK : SP24_ERR_DEVICE;
 }
 
+// Number of SMs of the current device (cached per device ordinal; 148 if the query fails).
+int sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 int launch_status() {
     const cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) return SP24_OK;
@@ -44,4 +57,4 @@ extern "C" const char *sp24_strerror(int code) {
     }
 }
 
-extern "C" int sp24_abi_version(void) { return 1; }
+extern "C" int sp24_abi_version(void) { return 2; }

@@ -6,7 +6,8 @@
 namespace sp24 {
 namespace {
 
-enum { OP_MVUE = 0, OP_SPARSE24 = 1, OP_SOFT = 2 };
+enum { OP_MVUE = 0, OP_SPARSE24 = 1, OP_SOFT = 2, OP_MVUE_FAST = 3 };
+constexpr bool op_is_mvue(int op) { return op == OP_MVUE || op == OP_MVUE_FAST; }
 
 struct DenseParams {
     const void *x;
@@ -25,8 +26,10 @@ __device__ __forceinline__ void dense_group(const T (&in)[4], float u0, float u1
                                             T (&mk)[4]) {
     const T zero = Elem<T>::from_f32(0.f), one = Elem<T>::from_f32(1.f);
     float x[4] = {Elem<T>::to_f32(in[0]), Elem<T>::to_f32(in[1]), Elem<T>::to_f32(in[2]), Elem<T>::to_f32(in[3])};
-    if constexpr (OP == OP_MVUE) {
-        const uint32_t keep = mvue24_group(x, u0, u1);
+    if constexpr (op_is_mvue(OP)) {
+        uint32_t keep;
+        if constexpr (OP == OP_MVUE) keep = mvue24_group(x, u0, u1);
+        else keep = mvue24_group_fast(x, u0, u1);
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[i] = ((keep >> i) & 1u) ? Elem<T>::from_f32(x[i]) : zero;
     } else {
@@ -85,7 +88,7 @@ template <typename T, int OP, bool HAS_U> __global__ void __launch_bounds__(256)
         const int64_t idx = base + it * 256;
         if (idx >= total) continue;
         float u[4] = {0.f, 0.f, 0.f, 0.f};
-        if constexpr (OP == OP_MVUE) {
+        if constexpr (op_is_mvue(OP)) {
             if constexpr (HAS_U) {
                 const float *up = P.uniforms + rr[it] * P.ld_u + cc[it];
                 const float2 ua = *reinterpret_cast<const float2 *>(up);
@@ -93,7 +96,8 @@ template <typename T, int OP, bool HAS_U> __global__ void __launch_bounds__(256)
                 u[0] = ua.x; u[1] = ua.y; u[2] = ub.x; u[3] = ub.y;
             } else {
                 const uint64_t gi = (uint64_t)rr[it] * (uint64_t)(P.k / 4) + (uint64_t)(cc[it] / 4);
-                mvue_uniform_pairs(gi >> 1, P.seed, P.offset, u[0], u[1], u[2], u[3]);
+                if constexpr (OP == OP_MVUE_FAST) mvue_uniform_pairs_fast(gi >> 1, P.seed, P.offset, u[0], u[1], u[2], u[3]);
+                else mvue_uniform_pairs(gi >> 1, P.seed, P.offset, u[0], u[1], u[2], u[3]);
             }
         }
         T s[8], mk[8];
@@ -103,16 +107,16 @@ template <typename T, int OP, bool HAS_U> __global__ void __launch_bounds__(256)
             T so[4], mo4[4];
             dense_group<T, OP>(grp, u[2 * h], u[2 * h + 1], P, so, mo4);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { s[4 * h + i] = so[i]; if constexpr (OP != OP_MVUE) mk[4 * h + i] = mo4[i]; }
+            for (int i = 0; i < 4; ++i) { s[4 * h + i] = so[i]; if constexpr (!op_is_mvue(OP)) mk[4 * h + i] = mo4[i]; }
         }
         constexpr int PER = 16 / sizeof(T);
 #pragma unroll
         for (int v = 0; v < 8 / PER; ++v) {
             Vec<T, PER> vs, vm;
 #pragma unroll
-            for (int j = 0; j < PER; ++j) { vs.v[j] = s[v * PER + j]; if constexpr (OP != OP_MVUE) vm.v[j] = mk[v * PER + j]; }
+            for (int j = 0; j < PER; ++j) { vs.v[j] = s[v * PER + j]; if constexpr (!op_is_mvue(OP)) vm.v[j] = mk[v * PER + j]; }
             store_vec<T, PER>(sp + rr[it] * P.ld_s + cc[it] + v * PER, vs);
-            if constexpr (OP != OP_MVUE) store_vec<T, PER>(mo + rr[it] * P.ld_m + cc[it] + v * PER, vm);
+            if constexpr (!op_is_mvue(OP)) store_vec<T, PER>(mo + rr[it] * P.ld_m + cc[it] + v * PER, vm);
         }
     }
 }
@@ -130,7 +134,7 @@ template <typename T, int OP, bool HAS_U> __global__ void __launch_bounds__(256)
 #pragma unroll
     for (int j = 0; j < 8; ++j) in[j] = load_vec<T, V>(x + (c8 + j) * P.ld_x + r);
     float u[V][4];
-    if constexpr (OP == OP_MVUE) {
+    if constexpr (op_is_mvue(OP)) {
         if constexpr (HAS_U) {
             constexpr int FV = 4;
 #pragma unroll
@@ -149,7 +153,8 @@ template <typename T, int OP, bool HAS_U> __global__ void __launch_bounds__(256)
 #pragma unroll
             for (int v = 0; v < V; ++v) {
                 const uint64_t gi = (uint64_t)(r + v) * (uint64_t)(P.k / 4) + (uint64_t)(c8 / 4);
-                mvue_uniform_pairs(gi >> 1, P.seed, P.offset, u[v][0], u[v][1], u[v][2], u[v][3]);
+                if constexpr (OP == OP_MVUE_FAST) mvue_uniform_pairs_fast(gi >> 1, P.seed, P.offset, u[v][0], u[v][1], u[v][2], u[v][3]);
+                else mvue_uniform_pairs(gi >> 1, P.seed, P.offset, u[v][0], u[v][1], u[v][2], u[v][3]);
             }
         }
     }
@@ -161,15 +166,15 @@ template <typename T, int OP, bool HAS_U> __global__ void __launch_bounds__(256)
             const T grp[4] = {in[4 * h].v[v], in[4 * h + 1].v[v], in[4 * h + 2].v[v], in[4 * h + 3].v[v]};
             T s4[4], m4[4];
             float ua = 0.f, ub = 0.f;
-            if constexpr (OP == OP_MVUE) { ua = u[v][2 * h]; ub = u[v][2 * h + 1]; }
+            if constexpr (op_is_mvue(OP)) { ua = u[v][2 * h]; ub = u[v][2 * h + 1]; }
             dense_group<T, OP>(grp, ua, ub, P, s4, m4);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { so[i].v[v] = s4[i]; if constexpr (OP != OP_MVUE) mk[i].v[v] = m4[i]; }
+            for (int i = 0; i < 4; ++i) { so[i].v[v] = s4[i]; if constexpr (!op_is_mvue(OP)) mk[i].v[v] = m4[i]; }
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             store_vec<T, V>(sp + (c8 + 4 * h + i) * P.ld_s + r, so[i]);
-            if constexpr (OP != OP_MVUE) store_vec<T, V>(mo + (c8 + 4 * h + i) * P.ld_m + r, mk[i]);
+            if constexpr (!op_is_mvue(OP)) store_vec<T, V>(mo + (c8 + 4 * h + i) * P.ld_m + r, mk[i]);
         }
     }
 }
@@ -334,6 +339,15 @@ extern "C" int sp24_mvue24_dense(const void *x, int dtype, int64_t m, int64_t k,
     }
     DenseParams P{x, out, nullptr, uniforms, m, k, ld_x, ld_out, 0, ld_uniforms, seed, offset, 1.f, 0};
     return dispatch_dense<OP_MVUE>(P, dtype, col_major, static_cast<cudaStream_t>(stream));
+}
+
+// The same estimator with the fast arithmetic of SP24_PRUNE_MVUE_FAST (seeded only): what the compressing kernel
+// stores for (seed, offset) in that mode is what this one writes at the kept positions, bit for bit.
+extern "C" int sp24_mvue24_dense_fast(const void *x, int dtype, int64_t m, int64_t k, int64_t ld_x, int col_major, void *out,
+                                      int64_t ld_out, uint64_t seed, uint64_t offset, void *stream) {
+    if (int rc = check_dense_args(x, dtype, m, k, ld_x, col_major, out, ld_out, nullptr, 0, false)) return rc;
+    DenseParams P{x, out, nullptr, nullptr, m, k, ld_x, ld_out, 0, 0, seed, offset, 1.f, 0};
+    return dispatch_dense<OP_MVUE_FAST>(P, dtype, col_major, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int sp24_sparse24(const void *x, int dtype, int64_t m, int64_t k, int64_t ld_x, int col_major, void *sparse,

@@ -44,12 +44,48 @@ template <typename T, int N> __device__ __forceinline__ void store_elems(T *p, c
     }
 }
 
+constexpr bool is_mvue(int mode) { return mode == SP24_PRUNE_MVUE || mode == SP24_PRUNE_MVUE_FAST; }
+// uniform pairs of the two groups of one Philox block, in the stream of the pruning mode
+template <int MODE>
+__device__ __forceinline__ void mode_uniform_pairs(uint64_t pair, uint64_t seed, uint64_t offset, float &u0a, float &u1a,
+                                                   float &u0b, float &u1b) {
+    if constexpr (MODE == SP24_PRUNE_MVUE_FAST) mvue_uniform_pairs_fast(pair, seed, offset, u0a, u1a, u0b, u1b);
+    else mvue_uniform_pairs(pair, seed, offset, u0a, u1a, u0b, u1b);
+}
+
+// Fast MVUE, after the arithmetic: q[] holds all four quotients, keep the keep mask.  Emits the two stored values
+// and returns the 4-bit code.  16-bit outputs: round all four, then one table lookup (keep_lut = words 64..79 of the
+// group table, in shared memory) and one byte permute gather the two stored ones.
+template <typename TOut>
+__device__ __forceinline__ uint32_t emit_fast(const float (&q)[4], uint32_t keep, TOut &o0, TOut &o1, const uint32_t *keep_lut) {
+    if constexpr (sizeof(TOut) == 2) {
+        const uint32_t e = keep_lut[keep];
+        const uint32_t o = __byte_perm(Elem<TOut>::pack2(q[0], q[1]), Elem<TOut>::pack2(q[2], q[3]), e >> 8);
+        const uint16_t lo = (uint16_t)(o & 0xFFFFu), hi = (uint16_t)(o >> 16);
+        o0 = *reinterpret_cast<const TOut *>(&lo);
+        o1 = *reinterpret_cast<const TOut *>(&hi);
+        return e & 0xFu;
+    } else {
+        const uint32_t nib = encode_nibble(keep);
+        o0 = Elem<TOut>::from_f32(pick4(nib & 3u, q[0], q[1], q[2], q[3]));
+        o1 = Elem<TOut>::from_f32(pick4(nib >> 2, q[0], q[1], q[2], q[3]));
+        return nib;
+    }
+}
+
 // One group of four: decide the keep mask, emit the two stored values and the 4-bit code.
+// keep_lut: words 64..79 of the group table (indexed by a 4-bit keep mask) in shared memory; only the fast MVUE
+// mode with 16-bit outputs reads it.
 template <typename TIn, typename TOut, int MODE>
 __device__ __forceinline__ uint32_t do_group(const TIn (&in)[4], uint32_t given_mask, float u0, float u1, TOut &o0,
-                                             TOut &o1) {
+                                             TOut &o1, const uint32_t *keep_lut = nullptr) {
     uint32_t keep;
-    if constexpr (MODE == SP24_PRUNE_MVUE) {
+    if constexpr (MODE == SP24_PRUNE_MVUE_FAST) {
+        float x[4] = {Elem<TIn>::to_f32(in[0]), Elem<TIn>::to_f32(in[1]), Elem<TIn>::to_f32(in[2]),
+                      Elem<TIn>::to_f32(in[3])};
+        keep = mvue24_group_fast(x, u0, u1);         // all four quotients in x[]
+        return emit_fast<TOut>(x, keep, o0, o1, keep_lut);
+    } else if constexpr (MODE == SP24_PRUNE_MVUE) {
         float x[4] = {Elem<TIn>::to_f32(in[0]), Elem<TIn>::to_f32(in[1]), Elem<TIn>::to_f32(in[2]),
                       Elem<TIn>::to_f32(in[3])};
         keep = mvue24_group<false>(x, u0, u1);     // quotients of the two stored positions in x[0], x[1]
@@ -129,7 +165,7 @@ template <typename T> __device__ __forceinline__ uint32_t mse_lookup(uint32_t lo
 // Tile = 32 rows x 32 metadata columns; 8 warps, lane = metadata column, warp w owns rows 4w..4w+3.
 // ---------------------------------------------------------------------------------------------
 template <typename TIn, typename TOut, int MODE, bool HAS_U>
-__global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_kernel(PcParams P) {
+__global__ void __launch_bounds__(256, is_mvue(MODE) ? 3 : 1) pc_row_kernel(PcParams P) {
     const uint64_t rng_offset = P.offset + (P.offset_dev ? *P.offset_dev : 0ull);
     constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;  // dense elements per metadata word
     constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;    // bytes per metadata word
@@ -137,13 +173,18 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
     using MetaT = typename VecBytes<MB>::type;
     // rows in flight per thread; MVUE is arithmetic-bound, so it trades memory-level parallelism for
     // fewer registers (more resident warps)
-    constexpr int RPI = (MODE == SP24_PRUNE_MVUE || CH * sizeof(TIn) >= 128) ? 1 : (CH * sizeof(TIn) >= 64 ? 2 : 4);
+    constexpr int RPI = (is_mvue(MODE) || CH * sizeof(TIn) >= 128) ? 1 : (CH * sizeof(TIn) >= 64 ? 2 : 4);
 
     __shared__ __align__(16) MetaT smeta[16][64];
-    constexpr bool PACKED = MODE != SP24_PRUNE_MVUE && std::is_same<TIn, TOut>::value && sizeof(TIn) == 2;
-    __shared__ uint32_t glut[PACKED ? 80 : 1];
+    constexpr bool PACKED = !is_mvue(MODE) && std::is_same<TIn, TOut>::value && sizeof(TIn) == 2;
+    constexpr bool KEEP_LUT = MODE == SP24_PRUNE_MVUE_FAST && sizeof(TOut) == 2;   // words 64..79 only
+    __shared__ uint32_t glut[PACKED ? 80 : (KEEP_LUT ? 16 : 1)];
     if constexpr (PACKED) {
         if (threadIdx.x < 80) glut[threadIdx.x] = kGroupLut.v[threadIdx.x];
+        __syncthreads();
+    }
+    if constexpr (KEEP_LUT) {
+        if (threadIdx.x < 16) glut[threadIdx.x] = kGroupLut.v[64 + threadIdx.x];
         __syncthreads();
     }
 
@@ -155,7 +196,7 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
     TOut *packed = static_cast<TOut *>(P.packed);
 
     if (c < ncols) {
-#pragma unroll(MODE == SP24_PRUNE_MVUE ? 1 : 4)
+#pragma unroll(is_mvue(MODE) ? 1 : 4)
         for (int it = 0; it < 4 / RPI; ++it) {
             TIn in[RPI][CH];
             uint8_t mk[RPI][CH];
@@ -191,7 +232,7 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
 #pragma unroll
                 for (int g2 = 0; g2 < CH / 8; ++g2) {
                     float u[4] = {0.f, 0.f, 0.f, 0.f};
-                    if constexpr (MODE == SP24_PRUNE_MVUE) {
+                    if constexpr (is_mvue(MODE)) {
                         if constexpr (HAS_U) {
                             const float *up = P.uniforms + r * P.ld_u + c * CH + g2 * 8;
                             const float2 ua = *reinterpret_cast<const float2 *>(up);
@@ -199,7 +240,7 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
                             u[0] = ua.x; u[1] = ua.y; u[2] = ub.x; u[3] = ub.y;
                         } else {
                             const uint64_t gi = (uint64_t)r * (uint64_t)(P.k / 4) + (uint64_t)(c * (CH / 4) + g2 * 2);
-                            mvue_uniform_pairs(gi >> 1, P.seed, rng_offset, u[0], u[1], u[2], u[3]);
+                            mode_uniform_pairs<MODE>(gi >> 1, P.seed, rng_offset, u[0], u[1], u[2], u[3]);
                         }
                     }
 #pragma unroll
@@ -212,7 +253,7 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
                                     ((mk[j][4 * g + 3] != 0) << 3);
                         }
                         const uint32_t nib =
-                            do_group<TIn, TOut, MODE>(grp, given, u[2 * h], u[2 * h + 1], out[2 * g], out[2 * g + 1]);
+                            do_group<TIn, TOut, MODE>(grp, given, u[2 * h], u[2 * h + 1], out[2 * g], out[2 * g + 1], glut);
                         word |= nib << (4 * g);
                     }
                 }
@@ -267,14 +308,19 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 3 : 1) pc_row_k
 // ---------------------------------------------------------------------------------------------
 template <typename TIn> struct ColVec {
     static constexpr int wide = sizeof(TIn) == 1 ? 8 : 16 / sizeof(TIn);   // streaming modes: 16-byte (8 for int8) loads
-    // MVUE is bound by instruction issue, not by load width: one row per thread makes blocks of 32 rows, twice as
-    // many as with two rows, which balances the SMs better on short matrices (768 x 8192 bf16: 24.7 -> 20.8 us)
-    // and is never slower on long ones
+    // Exact MVUE is bound by instruction issue, not by load width: one row per thread makes blocks of 32 rows, which
+    // balances the SMs better on short matrices and is never slower on long ones.
     static constexpr int narrow = 1;
+    // Fast MVUE has a third of the arithmetic, so its loads and stores weigh more: four rows per thread (8-byte
+    // accesses for 16-bit inputs) is the fastest from 768 x 8192 to 4096 x 8192 (one / two rows: +7 % / +3 %).
+    static constexpr int fast = 4;
 };
 
+// resident blocks per SM the register budget is set for
+constexpr int col_min_blocks(int mode) { return mode == SP24_PRUNE_MVUE_FAST ? 3 : (mode == SP24_PRUNE_MVUE ? 4 : 1); }
+
 template <typename TIn, typename TOut, int MODE, bool HAS_U, int V>
-__global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 4 : 1) pc_col_kernel(PcParams P) {
+__global__ void __launch_bounds__(256, col_min_blocks(MODE)) pc_col_kernel(PcParams P) {
     const uint64_t rng_offset = P.offset + (P.offset_dev ? *P.offset_dev : 0ull);
     constexpr int CH = sizeof(TOut) == 2 ? 16 : 32;
     constexpr int MB = sizeof(TOut) == 2 ? 2 : 4;
@@ -287,86 +333,93 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 4 : 1) pc_col_k
     // RT rows x 8 word columns fill RT whole lines of one atom per 128-row block
     __shared__ __align__(16) uint16_t stc[MB == 2 ? RT * 8 : 8];
     __shared__ float ssum[8][RT];           // per-warp partial row sums (only used when row sums are asked for)
+    constexpr bool KEEP_LUT = MODE == SP24_PRUNE_MVUE_FAST && sizeof(TOut) == 2;
+    __shared__ uint32_t glut[KEEP_LUT ? 16 : 1];
+    if constexpr (KEEP_LUT) {
+        if (threadIdx.x < 16) glut[threadIdx.x] = kGroupLut.v[64 + threadIdx.x];
+        __syncthreads();
+    }
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t ncols = P.k / CH;
     const int64_t r0 = (int64_t)blockIdx.x * RT;
     const int64_t r = r0 + lane * V;
     const int64_t c = (int64_t)blockIdx.y * 8 + warp;
-    const TIn *dense = static_cast<const TIn *>(P.dense);
     TOut *packed = static_cast<TOut *>(P.packed);
 
-    if (P.row_sums) {
-#pragma unroll
-        for (int v = 0; v < V; ++v) ssum[warp][lane * V + v] = 0.f;
-    }
     if (r < P.m && c < ncols) {
         uint32_t word[V];
+        float rsum[V];
 #pragma unroll
-        for (int v = 0; v < V; ++v) word[v] = 0;
+        for (int v = 0; v < V; ++v) { word[v] = 0; rsum[v] = 0.f; }
+        // one running pointer per array: the eight storage rows of a step are ld apart
+        const TIn *src = static_cast<const TIn *>(P.dense) + (c * CH) * P.ld_dense + r;
+        const uint8_t *msrc = MODE == SP24_PRUNE_MASK ? P.mask + (c * CH) * P.ld_mask + r : nullptr;
+        TOut *dst = packed + (c * (CH / 2)) * P.ld_packed + r;
+        // a step = 8 consecutive storage rows = two groups of four per logical row = one Philox block
 #pragma unroll
-        for (int half = 0; half < CH / 16; ++half) {
-            TIn in[16][V];
-            uint8_t mk[16][V];
+        for (int step = 0; step < CH / 8; ++step) {
+            Vec<TIn, V> in[8];
+            Vec<uint8_t, V> mk[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int64_t kk = c * CH + half * 16 + j;
-                load_elems<TIn, V>(dense + kk * P.ld_dense + r, in[j]);
-                if constexpr (MODE == SP24_PRUNE_MASK) load_elems<uint8_t, V>(P.mask + kk * P.ld_mask + r, mk[j]);
+            for (int j = 0; j < 8; ++j) {
+                in[j] = load_vec<TIn, V>(src + j * P.ld_dense);
+                if constexpr (MODE == SP24_PRUNE_MASK) mk[j] = load_vec<uint8_t, V>(msrc + j * P.ld_mask);
             }
-            if (P.row_sums) {   // sums of the unpruned values, fp32; parked in shared memory at once so that
-                                // no register stays live across the pruning arithmetic
+            src += 8 * P.ld_dense;
+            if constexpr (MODE == SP24_PRUNE_MASK) msrc += 8 * P.ld_mask;
+            if (P.row_sums) {   // sums of the unpruned values, fp32
 #pragma unroll
                 for (int v = 0; v < V; ++v) {
                     float a = 0.f;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) a += Elem<TIn>::to_f32(in[j][v]);
-                    ssum[warp][lane * V + v] += a;
+                    for (int j = 0; j < 8; ++j) a += Elem<TIn>::to_f32(in[j].v[v]);
+                    rsum[v] += a;
                 }
             }
+            float u[V][4];
+            if constexpr (is_mvue(MODE)) {
+                const int64_t gcol = c * (CH / 4) + step * 2;  // first of the two groups
+                if constexpr (HAS_U) {
+                    float t0[V], t1[V], t2[V], t3[V];
+                    load_elems<float, V>(P.uniforms + (gcol * 4 + 0) * P.ld_u + r, t0);
+                    load_elems<float, V>(P.uniforms + (gcol * 4 + 1) * P.ld_u + r, t1);
+                    load_elems<float, V>(P.uniforms + (gcol * 4 + 4) * P.ld_u + r, t2);
+                    load_elems<float, V>(P.uniforms + (gcol * 4 + 5) * P.ld_u + r, t3);
 #pragma unroll
-            for (int g2 = 0; g2 < 2; ++g2) {
-                float u[V][4];
-                if constexpr (MODE == SP24_PRUNE_MVUE) {
-                    const int64_t gcol = c * (CH / 4) + half * 4 + g2 * 2;  // first of the two groups
-                    if constexpr (HAS_U) {
-                        float t0[V], t1[V], t2[V], t3[V];
-                        load_elems<float, V>(P.uniforms + (gcol * 4 + 0) * P.ld_u + r, t0);
-                        load_elems<float, V>(P.uniforms + (gcol * 4 + 1) * P.ld_u + r, t1);
-                        load_elems<float, V>(P.uniforms + (gcol * 4 + 4) * P.ld_u + r, t2);
-                        load_elems<float, V>(P.uniforms + (gcol * 4 + 5) * P.ld_u + r, t3);
-#pragma unroll
-                        for (int v = 0; v < V; ++v) { u[v][0] = t0[v]; u[v][1] = t1[v]; u[v][2] = t2[v]; u[v][3] = t3[v]; }
-                    } else {
-#pragma unroll
-                        for (int v = 0; v < V; ++v) {
-                            const uint64_t gi = (uint64_t)(r + v) * (uint64_t)(P.k / 4) + (uint64_t)gcol;
-                            mvue_uniform_pairs(gi >> 1, P.seed, rng_offset, u[v][0], u[v][1], u[v][2], u[v][3]);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int g = g2 * 2 + h;  // group inside this half (0..3)
-                    TOut o0[V], o1[V];
+                    for (int v = 0; v < V; ++v) { u[v][0] = t0[v]; u[v][1] = t1[v]; u[v][2] = t2[v]; u[v][3] = t3[v]; }
+                } else {
 #pragma unroll
                     for (int v = 0; v < V; ++v) {
-                        const TIn grp[4] = {in[4 * g][v], in[4 * g + 1][v], in[4 * g + 2][v], in[4 * g + 3][v]};
-                        uint32_t given = 0;
-                        if constexpr (MODE == SP24_PRUNE_MASK) {
-                            given = (mk[4 * g][v] != 0) | ((mk[4 * g + 1][v] != 0) << 1) | ((mk[4 * g + 2][v] != 0) << 2) |
-                                    ((mk[4 * g + 3][v] != 0) << 3);
-                        }
-                        float ua = 0.f, ub = 0.f;
-                        if constexpr (MODE == SP24_PRUNE_MVUE) { ua = u[v][2 * h]; ub = u[v][2 * h + 1]; }
-                        const uint32_t nib = do_group<TIn, TOut, MODE>(grp, given, ua, ub, o0[v], o1[v]);
-                        word[v] |= nib << (4 * (half * 4 + g));
+                        const uint64_t gi = (uint64_t)(r + v) * (uint64_t)(P.k / 4) + (uint64_t)gcol;
+                        mode_uniform_pairs<MODE>(gi >> 1, P.seed, rng_offset, u[v][0], u[v][1], u[v][2], u[v][3]);
                     }
-                    const int64_t prow = c * (CH / 2) + (half * 4 + g) * 2;
-                    store_elems<TOut, V>(packed + prow * P.ld_packed + r, o0);
-                    store_elems<TOut, V>(packed + (prow + 1) * P.ld_packed + r, o1);
                 }
             }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                Vec<TOut, V> o0, o1;
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    const TIn grp[4] = {in[4 * h].v[v], in[4 * h + 1].v[v], in[4 * h + 2].v[v], in[4 * h + 3].v[v]};
+                    uint32_t given = 0;
+                    if constexpr (MODE == SP24_PRUNE_MASK) {
+                        given = (mk[4 * h].v[v] != 0) | ((mk[4 * h + 1].v[v] != 0) << 1) | ((mk[4 * h + 2].v[v] != 0) << 2) |
+                                ((mk[4 * h + 3].v[v] != 0) << 3);
+                    }
+                    float ua = 0.f, ub = 0.f;
+                    if constexpr (is_mvue(MODE)) { ua = u[v][2 * h]; ub = u[v][2 * h + 1]; }
+                    const uint32_t nib = do_group<TIn, TOut, MODE>(grp, given, ua, ub, o0.v[v], o1.v[v], glut);
+                    word[v] |= nib << (4 * (step * 2 + h));
+                }
+                store_vec<TOut, V>(dst, o0);
+                store_vec<TOut, V>(dst + P.ld_packed, o1);
+                dst += 2 * P.ld_packed;
+            }
+        }
+        if (P.row_sums) {
+#pragma unroll
+            for (int v = 0; v < V; ++v) ssum[warp][lane * V + v] = rsum[v];
         }
 #pragma unroll
         for (int v = 0; v < V; ++v) {
@@ -375,13 +428,19 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 4 : 1) pc_col_k
             if constexpr (MB == 2)
                 if (P.tc) stc[8 * (16 * (rr >> 4) + 8 * (warp & 1) + (rr & 7)) + 2 * (warp >> 1) + ((rr >> 3) & 1)] = (uint16_t)word[v];
         }
-    } else if constexpr (MB == 2) {
-        // word columns past the matrix (K not a multiple of 128): zeros, the GEMM multiplies them by zero-filled operands
-        if (P.tc && r < P.m) {
+    } else {
+        if (P.row_sums) {
 #pragma unroll
-            for (int v = 0; v < V; ++v) {
-                const int rr = lane * V + v;
-                stc[8 * (16 * (rr >> 4) + 8 * (warp & 1) + (rr & 7)) + 2 * (warp >> 1) + ((rr >> 3) & 1)] = 0;
+            for (int v = 0; v < V; ++v) ssum[warp][lane * V + v] = 0.f;
+        }
+        if constexpr (MB == 2) {
+            // word columns past the matrix (K not a multiple of 128): zeros, the GEMM multiplies them by zero-filled operands
+            if (P.tc && r < P.m) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    const int rr = lane * V + v;
+                    stc[8 * (16 * (rr >> 4) + 8 * (warp & 1) + (rr & 7)) + 2 * (warp >> 1) + ((rr >> 3) & 1)] = 0;
+                }
             }
         }
     }
@@ -403,8 +462,8 @@ __global__ void __launch_bounds__(256, MODE == SP24_PRUNE_MVUE ? 4 : 1) pc_col_k
         const int pair = i / (2 * RT * MB / 16), piece = i % (2 * RT * MB / 16);
         const int64_t cp = (int64_t)blockIdx.y * 4 + pair;
         if (piece < pieces && cp * 2 < ncols) {
-            char *dst = static_cast<char *>(P.meta) + (cp * 2 * P.m + 2 * r0) * MB + piece * 16;
-            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(
+            char *dstm = static_cast<char *>(P.meta) + (cp * 2 * P.m + 2 * r0) * MB + piece * 16;
+            *reinterpret_cast<uint4 *>(dstm) = *reinterpret_cast<const uint4 *>(
                 reinterpret_cast<const char *>(&smeta[pair][0]) + piece * 16);
         }
     }
@@ -430,7 +489,7 @@ int launch(const PcParams &P, int col_major, cudaStream_t st) {
         dim3 grid((unsigned)((P.k / CH + 31) / 32), (unsigned)(P.m / 32));
         pc_row_kernel<TIn, TOut, MODE, HAS_U><<<grid, 256, 0, st>>>(P);
     } else {
-        constexpr int V = MODE == SP24_PRUNE_MVUE ? ColVec<TIn>::narrow : ColVec<TIn>::wide;
+        constexpr int V = MODE == SP24_PRUNE_MVUE_FAST ? ColVec<TIn>::fast : (MODE == SP24_PRUNE_MVUE ? ColVec<TIn>::narrow : ColVec<TIn>::wide);
         constexpr int RT = 32 * V;
         dim3 grid((unsigned)((P.m + RT - 1) / RT), (unsigned)((P.k / CH + 7) / 8));
         pc_col_kernel<TIn, TOut, MODE, HAS_U, V><<<grid, 256, 0, st>>>(P);
@@ -449,6 +508,9 @@ template <typename TIn, typename TOut> int dispatch_mode(const PcParams &P, int 
                 return P.uniforms ? launch<TIn, TOut, SP24_PRUNE_MVUE, true>(P, col_major, st)
                                   : launch<TIn, TOut, SP24_PRUNE_MVUE, false>(P, col_major, st);
             }
+        case SP24_PRUNE_MVUE_FAST:
+            if constexpr (std::is_same<TIn, int8_t>::value) return SP24_ERR_DTYPE;
+            else return launch<TIn, TOut, SP24_PRUNE_MVUE_FAST, false>(P, col_major, st);
         default: return SP24_ERR_ARG;
     }
 }
@@ -482,7 +544,7 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
     if (mode == SP24_PRUNE_MASK && !mask) return SP24_ERR_ARG;
     if (mode != SP24_PRUNE_MASK && mask) return SP24_ERR_ARG;
     if (mode != SP24_PRUNE_MVUE && uniforms) return SP24_ERR_ARG;
-    if (mode < SP24_PRUNE_MSE || mode > SP24_PRUNE_MVUE) return SP24_ERR_ARG;
+    if (mode < SP24_PRUNE_MSE || mode > SP24_PRUNE_MVUE_FAST) return SP24_ERR_ARG;
     const int64_t inner = col_major ? m : k, inner_p = col_major ? m : k / 2;
     if (ld_dense < inner || (ld_dense * si) % 16) return SP24_ERR_STRIDE;
     if (ld_packed < inner_p || (ld_packed * so) % 16) return SP24_ERR_STRIDE;

@@ -30,11 +30,20 @@ template <> struct Elem<__half> {
     static constexpr int code = SP24_F16;
     __device__ static float to_f32(__half v) { return __half2float(v); }
     __device__ static __half from_f32(float v) { return __float2half_rn(v); }
+    // two values rounded and packed into one register (lo in bits 0..15): one conversion instruction
+    __device__ static uint32_t pack2(float lo, float hi) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
 };
 template <> struct Elem<__nv_bfloat16> {
     static constexpr int code = SP24_BF16;
     __device__ static float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ static __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+    __device__ static uint32_t pack2(float lo, float hi) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
 };
 template <> struct Elem<e4m3_t> {
     static constexpr int code = SP24_E4M3;
@@ -151,10 +160,12 @@ template <int META_BYTES> __device__ __forceinline__ int meta_run_pos(int rr, in
 // ---------------------------------------------------------------------------------------------
 // Philox4x32-10 and the uniform pair of a group
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+// Philox4x32 with ROUNDS rounds: 10 for the exact MVUE mode; 7 (the fewest rounds Salmon et al. report as passing
+// BigCrush) for the fast mode.  The reference draws with five (tl.rand4x(..., n_rounds=5)).
+template <int ROUNDS = 10> __device__ __forceinline__ uint4 philox4x32(uint4 c, uint2 k) {
     constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
 #pragma unroll
-    for (int i = 0; i < 10; ++i) {
+    for (int i = 0; i < ROUNDS; ++i) {
         const uint32_t hi0 = __umulhi(M0, c.x), lo0 = M0 * c.x;
         const uint32_t hi1 = __umulhi(M1, c.z), lo1 = M1 * c.z;
         c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
@@ -167,9 +178,10 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
 __device__ __forceinline__ float u32_to_uniform(uint32_t x) { return (float)(x >> 8) * 5.9604644775390625e-08f; }
 
 // Uniform pairs of the two groups 2*pair and 2*pair+1 (linear group index over the logical matrix).
+template <int ROUNDS = 10>
 __device__ __forceinline__ void mvue_uniform_pairs(uint64_t pair, uint64_t seed, uint64_t offset, float &u0a,
                                                    float &u1a, float &u0b, float &u1b) {
-    const uint4 r = philox4x32_10(make_uint4((uint32_t)pair, (uint32_t)(pair >> 32), (uint32_t)offset,
+    const uint4 r = philox4x32<ROUNDS>(make_uint4((uint32_t)pair, (uint32_t)(pair >> 32), (uint32_t)offset,
                                              (uint32_t)(offset >> 32)),
                                   make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
     u0a = u32_to_uniform(r.x); u1a = u32_to_uniform(r.y);
@@ -236,6 +248,79 @@ __device__ __forceinline__ uint32_t mvue24_group(float (&x)[4], float u0, float 
 }
 
 // ---------------------------------------------------------------------------------------------
+// MVUE24, fast arithmetic (seeded mode only).  The same estimator - sample two of four without replacement with
+// probability proportional to a_i = |x_i| + eps, store x_i / p_i with p_i the inclusion probability - arranged for
+// the instruction mix of the SM instead of for bit-equality with the reference formulas:
+//   * every division is a reciprocal approximation (MUFU) and a multiply;
+//   * S - a_i and K - k_i are taken as the sum of the other three terms, not as a difference: no cancellation when one
+//     magnitude dominates its group, so p_i is good to a few float32 ulps everywhere (the reference order loses up to
+//     ~1e-4 relative there);
+//   * a draw is a count of thresholds below the scaled uniform instead of a cascade of dependent predicates;
+//   * all four quotients are formed (two more reciprocals) so that the two stored ones can be gathered with one
+//     table-driven byte permute instead of select chains.
+// Every operation is an explicit intrinsic (no compiler contraction), so all kernels that call this function produce
+// the same bits for the same inputs.  As in the reference, a second uniform of exactly zero repeats a first pick of
+// position 0 (one kept value in that group, probability ~2^-25).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float rcp_fast(float v) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+constexpr int kMvueFastRounds = 7;
+
+// 23 random bits -> float32 uniform on [0, 1) with 2^-23 spacing (mantissa of a float in [1, 2), minus one)
+__device__ __forceinline__ float u32_to_uniform23(uint32_t x) {
+    return __fadd_rn(__uint_as_float((x & 0x007FFFFFu) | 0x3F800000u), -1.f);
+}
+
+// Uniform pairs of groups 2*pair and 2*pair+1 for the fast mode: Philox4x32-7, 23-bit uniforms.
+__device__ __forceinline__ void mvue_uniform_pairs_fast(uint64_t pair, uint64_t seed, uint64_t offset, float &u0a,
+                                                        float &u1a, float &u0b, float &u1b) {
+    const uint4 r = philox4x32<kMvueFastRounds>(make_uint4((uint32_t)pair, (uint32_t)(pair >> 32), (uint32_t)offset,
+                                                           (uint32_t)(offset >> 32)),
+                                                make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+    u0a = u32_to_uniform23(r.x); u1a = u32_to_uniform23(r.y);
+    u0b = u32_to_uniform23(r.z); u1b = u32_to_uniform23(r.w);
+}
+
+// number of thresholds c0 <= c1 <= c2 strictly below w: 0..3
+__device__ __forceinline__ uint32_t count_below(float w, float c0, float c1, float c2) {
+    return (uint32_t)(w > c0) + (uint32_t)(w > c1) + (uint32_t)(w > c2);
+}
+
+// x[] is overwritten with x_i / p_i for ALL four positions; returns the keep mask as bits 0..3.
+__device__ __forceinline__ uint32_t mvue24_group_fast(float (&x)[4], float u0, float u1) {
+    const float eps = 1.19209e-07f;
+    const float a0 = __fadd_rn(fabsf(x[0]), eps), a1 = __fadd_rn(fabsf(x[1]), eps);
+    const float a2 = __fadd_rn(fabsf(x[2]), eps), a3 = __fadd_rn(fabsf(x[3]), eps);
+    const float a01 = __fadd_rn(a0, a1), a23 = __fadd_rn(a2, a3);
+    const float s = __fadd_rn(a01, a23), a012 = __fadd_rn(a01, a2);
+    // sums of the other three
+    const float s0 = __fadd_rn(a1, a23), s1 = __fadd_rn(a0, a23), s2 = __fadd_rn(a01, a3);
+    const float rs = rcp_fast(s);
+    const float t0 = __fmul_rn(a0, rs), t1 = __fmul_rn(a1, rs), t2 = __fmul_rn(a2, rs), t3 = __fmul_rn(a3, rs);
+    const float k0 = __fmul_rn(t0, rcp_fast(s0)), k1 = __fmul_rn(t1, rcp_fast(s1));
+    const float k2 = __fmul_rn(t2, rcp_fast(s2)), k3 = __fmul_rn(t3, rcp_fast(a012));
+    const float k01 = __fadd_rn(k0, k1), k23 = __fadd_rn(k2, k3);
+    const float p0 = __fmaf_rn(a0, __fadd_rn(k1, k23), t0), p1 = __fmaf_rn(a1, __fadd_rn(k0, k23), t1);
+    const float p2 = __fmaf_rn(a2, __fadd_rn(k01, k3), t2), p3 = __fmaf_rn(a3, __fadd_rn(k01, k2), t3);
+    // first pick: the interval of the cumulative sums (a0, a01, a012, s) that u0 * s falls into
+    const float w = __fmul_rn(u0, s);
+    const bool b0 = w > a0, b2 = w > a012;
+    const uint32_t f = (uint32_t)b0 + (uint32_t)(w > a01) + (uint32_t)b2;
+    // second pick among the other three: the same walk over the cumulative sums with the first pick's weight zeroed
+    const float d0 = b0 ? a0 : 0.f, d1 = f == 1u ? 0.f : a1, d2 = f == 2u ? 0.f : a2, d3 = b2 ? 0.f : a3;
+    const float d01 = __fadd_rn(d0, d1), d012 = __fadd_rn(d01, d2);
+    const uint32_t g = count_below(__fmul_rn(u1, __fadd_rn(d012, d3)), d0, d01, d012);
+    x[0] = __fmul_rn(x[0], rcp_fast(p0));
+    x[1] = __fmul_rn(x[1], rcp_fast(p1));
+    x[2] = __fmul_rn(x[2], rcp_fast(p2));
+    x[3] = __fmul_rn(x[3], rcp_fast(p3));
+    return (1u << f) | (1u << g);
+}
+
+// ---------------------------------------------------------------------------------------------
 // host-side helpers
 // ---------------------------------------------------------------------------------------------
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -250,5 +335,6 @@ inline int dtype_size(int dt) {
 }
 int check_device();            // SP24_OK when the current device is compute capability 10.x
 int launch_status();           // maps cudaGetLastError() to SP24_OK / SP24_ERR_CUDA
+int sm_count();                // SMs of the current device
 
 }  // namespace sp24

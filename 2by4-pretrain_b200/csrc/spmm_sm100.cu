@@ -1239,18 +1239,7 @@ bool pair_kernels_enabled() {
     return enabled;
 }
 
-int sm_count_cached() {
-    static int cached[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return 148;
-    if (!cached[dev]) {
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
-    }
-    return cached[dev];
-}
+int sm_count_cached() { return sm_count(); }
 
 template <int BN, bool F8, bool A_MN, bool B_MN, bool TRANS, typename OutT>
 int launch_spmm(const CUtensorMap &ma, const CUtensorMap &mb, SpmmParams P, cudaStream_t st) {

@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libsparse24_b200.so")
 
 F32, F16, BF16, E4M3, E5M2, I8, I32 = 0, 1, 2, 3, 4, 5, 6
-PRUNE_MSE, PRUNE_MASK, PRUNE_MVUE = 0, 1, 2
+PRUNE_MSE, PRUNE_MASK, PRUNE_MVUE, PRUNE_MVUE_FAST = 0, 1, 2, 3
 
 _DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int8: I8, torch.int32: I32}
 if hasattr(torch, "float8_e4m3fn"):
@@ -39,6 +39,7 @@ _SIGNATURES = {
     "sp24_adamw_masked_decay": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp],
     "sp24_to_dense": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _i64, _vp],
     "sp24_mvue24_dense": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _u64, _u64, _vp],
+    "sp24_mvue24_dense_fast": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _u64, _u64, _vp],
     "sp24_sparse24": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _vp],
     "sp24_soft_threshold24": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _i32, _f32, _vp],
     "sp24_transposable_select": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _vp],

@@ -65,7 +65,7 @@ def prune_compress(dense: Tensor, sparse: Tensor, meta: Tensor, *, mode: int, ma
         ld_u = _ext.layout_of(uniforms)[1]
     if not meta.is_contiguous():
         raise RuntimeError("metadata buffer must be contiguous")
-    dev_off = _DEVICE_RNG_OFFSET if mode == _ext.PRUNE_MVUE and uniforms is None else None
+    dev_off = _DEVICE_RNG_OFFSET if mode in (_ext.PRUNE_MVUE, _ext.PRUNE_MVUE_FAST) and uniforms is None else None
     # 16-bit results with whole 128-row blocks can also get their metadata in the order the GEMM reads, in the same
     # pass.  Default: for column-major results (the dY^T operand of the weight-gradient GEMM, consumed at once);
     # row-major results (weights converted once) get it on request, else lazily at their first GEMM.
@@ -101,7 +101,7 @@ def sparse_semi_structured_from_dense_triton(dense, sparse, meta, MVUE24: bool =
     if mask is not None:
         mode = _ext.PRUNE_MASK
     elif MVUE24:
-        mode = _ext.PRUNE_MVUE
+        mode = _ext.PRUNE_MVUE_FAST   # production arithmetic; PRUNE_MVUE (exact) is reached through prune_compress
     else:
         mode = _ext.PRUNE_MSE
     seed = random.randint(0, 2 ** 31 - 1)

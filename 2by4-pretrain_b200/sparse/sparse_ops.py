@@ -113,7 +113,7 @@ def _mvue_compress_t(g, row_sums):
     buf = torch.empty((features * tokens * 9 // 16,), dtype=g.dtype, device=g.device)
     packed = buf[: features * tokens // 2].view(-1, features).t()
     meta = buf[features * tokens // 2:].view(torch.int16).view(features, -1)
-    prune_compress(g.t(), packed, meta, mode=_ext.PRUNE_MVUE, seed=random.randint(0, 2 ** 31 - 1), row_sums=row_sums)
+    prune_compress(g.t(), packed, meta, mode=_ext.PRUNE_MVUE_FAST, seed=random.randint(0, 2 ** 31 - 1), row_sums=row_sums)
     return packed, meta
 
 

@@ -26,19 +26,34 @@ def _like(dense, col_major):
     return torch.empty((m, k), dtype=dense.dtype, device=dense.device)
 
 
-def MVUE24_approx_triton(dense, *, uniforms: Optional[torch.Tensor] = None, seed: Optional[int] = None, offset: int = 0):
+def MVUE24_approx_triton(dense, *, uniforms: Optional[torch.Tensor] = None, seed: Optional[int] = None, offset: int = 0,
+                         exact: Optional[bool] = None):
     """Minimum-variance unbiased 2:4 estimate of ``dense`` (same shape, zeros where dropped).
     ``uniforms`` / ``seed`` / ``offset`` are optional extras for reproducibility; by default the seed
-    comes from Python's ``random`` like the reference (sparse/triton_ops.py:58)."""
+    comes from Python's ``random`` like the reference (sparse/triton_ops.py:58).
+
+    ``exact``: True = IEEE arithmetic and the 10-round Philox stream, bit-exact against the reference formulas
+    (always the case with ``uniforms``); False = the production arithmetic (reciprocal approximations, 7-round
+    stream), which is what ``to_sparse_semi_structured(MVUE24=True)`` stores for the same seed.  Default: exact
+    only when ``uniforms`` is given."""
     dense, col_major, ld = _prep(dense)
     m, k = dense.shape
     out = _like(dense, col_major)
+    if exact is None:
+        exact = uniforms is not None
+    if uniforms is not None and not exact:
+        raise RuntimeError("MVUE24_approx_triton: supplied uniforms drive the exact arithmetic only")
+    if seed is None:
+        seed = random.randint(0, 2 ** 31 - 1)
+    if not exact:
+        rc = _ext.lib().sp24_mvue24_dense_fast(dense.data_ptr(), _ext.dt(dense.dtype), m, k, ld, col_major, out.data_ptr(),
+                                               _ext.layout_of(out)[1], seed, offset, _ext.stream())
+        _ext.check(rc, "sp24_mvue24_dense_fast")
+        return out
     ld_u = 0
     if uniforms is not None:
         uniforms = _ext.as_layout(uniforms.float(), col_major)
         ld_u = _ext.layout_of(uniforms)[1]
-    if seed is None:
-        seed = random.randint(0, 2 ** 31 - 1)
     rc = _ext.lib().sp24_mvue24_dense(dense.data_ptr(), _ext.dt(dense.dtype), m, k, ld, col_major, out.data_ptr(),
                                       _ext.layout_of(out)[1], _ext.ptr(uniforms), ld_u, seed, offset, _ext.stream())
     _ext.check(rc, "sp24_mvue24_dense")

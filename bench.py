@@ -398,10 +398,10 @@ def run_case(name):
         w = (torch.randn(8192, 8192, device=dev) * 0.02).half()
         _, mk = sparse.mask_select(w)
         fn = lambda: sparse.select_and_compress(w, mask=mk)
-    elif name in ("mvue_row", "mse_row", "mvue_col", "mse_col"):
+    elif name in ("mvue_row", "mse_row", "mvue_col", "mse_col", "mvue_fast_row", "mvue_fast_col"):
         m, k = 16384, 4096
         g = (torch.randn(m, k, device=dev) * 1e-3).bfloat16()
-        mode = 2 if name.startswith("mvue") else 0
+        mode = 3 if name.startswith("mvue_fast") else (2 if name.startswith("mvue") else 0)
         if name.endswith("col"):
             g = g.t()
             packed = torch.empty(m // 2, k, dtype=torch.bfloat16, device=dev).t()
@@ -477,18 +477,25 @@ def side_measurements(dev):
     def rec(name, secs, nbytes):
         res[name] = {"ms": secs * 1e3, "GB/s": nbytes / secs / 1e9, "frac_of_hbm_peak": nbytes / secs / 1e9 / peak}
 
-    rec("cfg3 mvue compress row bf16 8192x4096",
+    rec("cfg3 mvue compress row bf16 8192x4096 (exact arithmetic)",
         timeit(lambda i: prune_compress(G[i], packed[i], meta[i], mode=2, seed=1, offset=i), nb), n * (2 + 1 + 0.125))
+    rec("cfg3 mvue compress row bf16 8192x4096 (fast arithmetic, the training path)",
+        timeit(lambda i: prune_compress(G[i], packed[i], meta[i], mode=3, seed=1, offset=i), nb), n * (2 + 1 + 0.125))
     rec("cfg3 magnitude compress row bf16 8192x4096",
         timeit(lambda i: prune_compress(G[i], packed[i], meta[i], mode=0), nb), n * (2 + 1 + 0.125))
     Gt = [g.t() for g in G]  # column-major view of a (4096, 8192) logical matrix
     packed_t = [torch.empty(m // 2, k, dtype=torch.bfloat16, device=dev).t() for _ in range(nb)]
     meta_t = [torch.empty(k, m // 16, dtype=torch.int16, device=dev) for _ in range(nb)]
-    rec("mvue compress col-major bf16 (dY^T form) 4096x8192",
+    rec("mvue compress col-major bf16 (dY^T form) 4096x8192 (exact arithmetic)",
         timeit(lambda i: prune_compress(Gt[i], packed_t[i], meta_t[i], mode=2, seed=1, offset=i), nb), n * (2 + 1 + 0.125))
+    rec("mvue compress col-major bf16 (dY^T form) 4096x8192 (fast arithmetic, the training path)",
+        timeit(lambda i: prune_compress(Gt[i], packed_t[i], meta_t[i], mode=3, seed=1, offset=i), nb), n * (2 + 1 + 0.125))
     rec("cfg3 soft_threshold24 bf16 8192x4096", timeit(lambda i: sparse.soft_threshold24_triton(G[i]), nb), n * 6)
     rec("sparse24 bf16 8192x4096", timeit(lambda i: sparse.sparse24_triton(G[i]), nb), n * 6)
-    rec("mvue24 dense bf16 8192x4096", timeit(lambda i: sparse.MVUE24_approx_triton(G[i], seed=3, offset=i), nb), n * 4)
+    rec("mvue24 dense bf16 8192x4096 (exact arithmetic)",
+        timeit(lambda i: sparse.MVUE24_approx_triton(G[i], seed=3, offset=i, exact=True), nb), n * 4)
+    rec("mvue24 dense bf16 8192x4096 (fast arithmetic)",
+        timeit(lambda i: sparse.MVUE24_approx_triton(G[i], seed=3, offset=i, exact=False), nb), n * 4)
     del packed, meta, packed_t, meta_t
     Wf = [torch.randn(4096, 4096, device=dev) * 0.02 for _ in range(nb)]
     rec("transposable select fp32 4096x4096 (sparse+mask)", timeit(lambda i: sparse.mask_select(Wf[i]), nb), 4096 * 4096 * 9)

@@ -39,7 +39,11 @@ enum {
 enum {
     SP24_PRUNE_MSE = 0,  /* keep the two largest magnitudes of every four (ties keep the higher index) */
     SP24_PRUNE_MASK = 1, /* keep what a supplied 0/1 byte mask says */
-    SP24_PRUNE_MVUE = 2  /* minimum-variance unbiased 2-of-4 sampling, rescaled */
+    SP24_PRUNE_MVUE = 2, /* minimum-variance unbiased 2-of-4 sampling, rescaled; IEEE arithmetic, bit-exact
+                            against the reference formulas given the uniforms */
+    SP24_PRUNE_MVUE_FAST = 3 /* the same estimator for production use: seeded only (no uniforms argument),
+                                reciprocal-approximation arithmetic and a 7-round Philox stream; unbiased to
+                                float32 rounding, not bit-comparable with SP24_PRUNE_MVUE */
 };
 
 /* error codes */
@@ -74,10 +78,14 @@ int sp24_abi_version(void);
  *              reordered layout (row interleave by 8 within groups of 32 / 16 rows, 2x2 swizzle,
  *              column-major interleaved by 2)
  *   mode       SP24_PRUNE_*; mask (bytes, non-zero = keep, logical (m, k)) only for SP24_PRUNE_MASK
- *   uniforms   optional, MVUE only: float32 logical (m, k); group g of row r uses [r,4g] and [r,4g+1].
+ *   uniforms   optional, SP24_PRUNE_MVUE only: float32 logical (m, k); group g of row r uses [r,4g] and [r,4g+1].
  *              When NULL the kernel draws from Philox4x32-10 keyed by (seed, offset):
  *              group index gi = r*(k/4)+g, counter = (gi>>1, offset), key = seed, even groups take
  *              words 0,1 and odd groups words 2,3, u = (word >> 8) * 2^-24.
+ *              SP24_PRUNE_MVUE_FAST takes no uniforms and draws the same way from Philox4x32-7; its arithmetic
+ *              replaces the ten IEEE divisions per group by seven reciprocal approximations (the reference's
+ *              own GPU kernel also divides approximately), so kept positions and stored values can differ from
+ *              SP24_PRUNE_MVUE's in the last float32 bits; it is the mode the training layer uses.
  * Shape rules (sparse/semi_structured.py:24-30,188-200): m % 32 == 0; k % 64 == 0 (16-bit) or
  * k % 128 == 0 (8-bit).  Leading dimensions must keep every row/column start 16-byte aligned.
  */
@@ -123,6 +131,15 @@ int sp24_to_dense(const void *packed, int dtype, int64_t m, int64_t k, int64_t l
 int sp24_mvue24_dense(const void *x, int dtype, int64_t m, int64_t k, int64_t ld_x, int col_major, void *out,
                       int64_t ld_out, const float *uniforms, int64_t ld_uniforms, uint64_t seed, uint64_t offset,
                       void *stream);
+
+/*
+ * sp24_mvue24_dense with the arithmetic and the 7-round Philox stream of SP24_PRUNE_MVUE_FAST (seeded only): at the
+ * kept positions it writes exactly what sp24_prune_compress stores in that mode for the same (seed, offset).  The
+ * reference's own GPU kernel divides with the compiler's approximate division (sparse/utils.py:6-59 as launched
+ * from sparse/triton_ops.py:55-81); this is the counterpart of that production path.
+ */
+int sp24_mvue24_dense_fast(const void *x, int dtype, int64_t m, int64_t k, int64_t ld_x, int col_major, void *out,
+                           int64_t ld_out, uint64_t seed, uint64_t offset, void *stream);
 
 /*
  * Magnitude 2:4 pruning, dense-shaped: sparse = x where kept else +0, mask = 1 / 0 in x's dtype.

@@ -188,9 +188,9 @@ _PH_W0 = np.uint32(0x9E3779B9)
 _PH_W1 = np.uint32(0xBB67AE85)
 
 
-def philox4x32_10(c0, c1, c2, c3, k0, k1):
-    """Philox-4x32 with 10 rounds (Salmon et al., SC'11), vectorised over numpy
-    uint32 arrays.  This is the project's own stream definition: the reference
+def philox4x32_10(c0, c1, c2, c3, k0, k1, rounds: int = 10):
+    """Philox-4x32 (Salmon et al., SC'11), vectorised over numpy uint32 arrays; 10 rounds for the exact MVUE
+    mode, 7 for the fast one.  This is the project's own stream definition: the reference
     draws from Triton's ``tl.rand4x(..., n_rounds=5)``
     (sparse/_semi_structured_conversions.py:535-551), which is deliberately not
     reproduced stream-for-stream."""
@@ -199,7 +199,7 @@ def philox4x32_10(c0, c1, c2, c3, k0, k1):
     k1 = np.uint32(k1)
     mask32 = np.uint64(0xFFFFFFFF)
     with np.errstate(over="ignore"):
-        for _ in range(10):
+        for _ in range(rounds):
             p0 = _PH_M0 * c0.astype(np.uint64)
             p1 = _PH_M1 * c2.astype(np.uint64)
             hi0 = (p0 >> np.uint64(32)).astype(np.uint32)
@@ -217,23 +217,35 @@ def u32_to_uniform(x: np.ndarray) -> np.ndarray:
     return (x >> np.uint32(8)).astype(np.float32) * np.float32(2.0 ** -24)
 
 
-def mvue_uniforms(m: int, k: int, seed: int, offset: int) -> Tuple[np.ndarray, np.ndarray]:
-    """The (u0, u1) pair of every group of 4 of a logical (m, k) matrix.
+def u32_to_uniform23(x: np.ndarray) -> np.ndarray:
+    """Low 23 bits as the mantissa of a float in [1, 2), minus one: uniform on [0, 1) with 2^-23 spacing (the
+    conversion of the kernels' fast MVUE mode)."""
+    bits = (x & np.uint32(0x007FFFFF)) | np.uint32(0x3F800000)
+    return bits.view(np.float32) - np.float32(1.0)
+
+
+def mvue_uniforms(m: int, k: int, seed: int, offset: int, rounds: int = 10, fast: bool = False
+                  ) -> Tuple[np.ndarray, np.ndarray]:
+    """The (u0, u1) pair of every group of 4 of a logical (m, k) matrix.  ``fast``: the stream of the kernels'
+    fast mode (Philox4x32-7 and the 23-bit conversion), otherwise Philox4x32-``rounds`` and 24 bits.
 
     Group ``g`` of row ``r`` has linear index ``gi = r*(k/4) + g`` whatever the
     storage order.  One Philox block serves two groups: counter =
     (lo32(gi>>1), hi32(gi>>1), lo32(offset), hi32(offset)), key = (lo32(seed),
     hi32(seed)); the even group takes words 0,1 and the odd group words 2,3.
     """
+    if fast:
+        rounds = 7
+    conv = u32_to_uniform23 if fast else u32_to_uniform
     gi = np.arange(m * (k // 4), dtype=np.uint64)
     pair = gi >> np.uint64(1)
     x0, x1, x2, x3 = philox4x32_10(
         (pair & np.uint64(0xFFFFFFFF)).astype(np.uint32), (pair >> np.uint64(32)).astype(np.uint32),
         np.uint32(offset & 0xFFFFFFFF), np.uint32((offset >> 32) & 0xFFFFFFFF),
-        seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+        seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF, rounds=rounds)
     odd = (gi & np.uint64(1)).astype(bool)
-    u0 = u32_to_uniform(np.where(odd, x2, x0)).reshape(m, k // 4)
-    u1 = u32_to_uniform(np.where(odd, x3, x1)).reshape(m, k // 4)
+    u0 = conv(np.ascontiguousarray(np.where(odd, x2, x0))).reshape(m, k // 4)
+    u1 = conv(np.ascontiguousarray(np.where(odd, x3, x1))).reshape(m, k // 4)
     return u0, u1
 
 
@@ -278,6 +290,45 @@ def mvue24_groups(x4: np.ndarray, u0: np.ndarray, u1: np.ndarray):
     return vals.astype(f), mask
 
 
+def mvue24_groups_f64(x4: np.ndarray, u0: np.ndarray, u1: np.ndarray):
+    """The same estimator (sparse/utils.py:6-59) evaluated in float64: the yardstick for the kernels' fast
+    arithmetic, whose float32 operations are ordered differently from the reference's.  Returns
+    (values float64 (..., 4) = x_i / p_i, mask bool (..., 4))."""
+    d = np.float64
+    x = [np.ascontiguousarray(x4[..., i]).astype(d) for i in range(4)]
+    u0 = u0.astype(d)
+    u1 = u1.astype(d)
+    with np.errstate(all="ignore"):
+        a = [np.abs(xi) + d(MVUE_EPS) for xi in x]
+        s = a[0] + a[1] + a[2] + a[3]
+        t = [ai / s for ai in a]
+        kk = [t[i] / (s - a[i]) for i in range(4)]
+        ks = kk[0] + kk[1] + kk[2] + kk[3]
+        p = [t[i] + a[i] * (ks - kk[i]) for i in range(4)]
+        m0 = u0 <= t[0]
+        m1 = (u0 <= t[0] + t[1]) & ~m0
+        m2 = (u0 <= t[0] + t[1] + t[2]) & ~m1 & ~m0
+        m = [m0, m1, m2, ~m2 & ~m1 & ~m0]
+        dd = [np.where(m[i], 0.0, a[i]) for i in range(4)]
+        tt = u1 * (dd[0] + dd[1] + dd[2] + dd[3])
+        e0 = tt <= dd[0]
+        e1 = (tt <= dd[0] + dd[1]) & ~e0
+        e2 = (tt <= dd[0] + dd[1] + dd[2]) & ~e1 & ~e0
+        e = [e0, e1, e2, ~e2 & ~e1 & ~e0]
+        vals = np.stack([x[i] / p[i] for i in range(4)], axis=-1)
+        mask = np.stack([m[i] | e[i] for i in range(4)], axis=-1)
+    return vals, mask
+
+
+def mvue24_dense_f64(x: torch.Tensor, seed: int, offset: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Float64 evaluation of the estimator on the uniforms of the kernels' fast mode for (seed, offset):
+    (values x_i / p_i at every position, keep mask), both shaped like ``x``."""
+    m, k = x.shape
+    u0, u1 = mvue_uniforms(m, k, seed, offset, fast=True)
+    vals, mask = mvue24_groups_f64(x.double().reshape(m, k // 4, 4).numpy(), u0, u1)
+    return torch.from_numpy(vals).reshape(m, k), torch.from_numpy(mask).reshape(m, k)
+
+
 def mvue24_probabilities(x4: np.ndarray) -> np.ndarray:
     """Inclusion probabilities p_i of sparse/utils.py:31-34 (float32 (..., 4)): the estimator stores
     x_i / p_i with probability p_i, which is what makes it unbiased."""
@@ -297,21 +348,23 @@ def _uniform_pairs_from_tensor(U: torch.Tensor):
     return np.ascontiguousarray(u[..., 0]), np.ascontiguousarray(u[..., 1])
 
 
-def _mvue(x: torch.Tensor, U: Optional[torch.Tensor], seed: int, offset: int):
+def _mvue(x: torch.Tensor, U: Optional[torch.Tensor], seed: int, offset: int, rounds: int = 10):
     m, k = x.shape
     if U is not None:
         u0, u1 = _uniform_pairs_from_tensor(U)
     else:
-        u0, u1 = mvue_uniforms(m, k, seed, offset)
+        u0, u1 = mvue_uniforms(m, k, seed, offset, rounds)
     x4 = x.float().reshape(m, k // 4, 4).numpy()
     vals, mask = mvue24_groups(x4, u0, u1)
     return torch.from_numpy(vals).reshape(m, k), torch.from_numpy(mask).reshape(m, k)
 
 
-def mvue24_dense(x: torch.Tensor, U: Optional[torch.Tensor] = None, seed: int = 0, offset: int = 0
-                 ) -> torch.Tensor:
-    """sparse/triton_ops.py:10-81: dense-shaped MVUE, zeros where dropped, stored in x's dtype."""
-    vals, mask = _mvue(x, U, seed, offset)
+def mvue24_dense(x: torch.Tensor, U: Optional[torch.Tensor] = None, seed: int = 0, offset: int = 0,
+                 rounds: int = 10) -> torch.Tensor:
+    """sparse/triton_ops.py:10-81: dense-shaped MVUE, zeros where dropped, stored in x's dtype.
+    ``rounds`` = 7 gives the stream of the kernels' fast mode (with this function's exact arithmetic: the
+    yardstick the fast arithmetic is measured against)."""
+    vals, mask = _mvue(x, U, seed, offset, rounds)
     return torch.where(mask, cast_store(vals, x.dtype), torch.zeros((), dtype=x.dtype))
 
 
