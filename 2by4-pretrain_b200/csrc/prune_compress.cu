@@ -22,6 +22,8 @@ struct PcParams {
     int16_t *tc;                            // optional metadata copy in tensor-core atom order (16-bit outputs)
     int64_t k_atoms;                        // 128-column atoms per 128-row block
     float *row_sums;                        // optional (column-major only): row_sums[r] += sum over k of dense[r, k]
+    int packed_rm;                          // column-major input, 8-bit output: packed is written row-major (m, k/2)
+    float out_scale;                        // 8-bit outputs: stored value = value * out_scale (1 = none)
 };
 
 template <typename T, int N> __device__ __forceinline__ void load_elems(const T *p, T (&out)[N]) {
@@ -57,7 +59,8 @@ __device__ __forceinline__ void mode_uniform_pairs(uint64_t pair, uint64_t seed,
 // and returns the 4-bit code.  16-bit outputs: round all four, then one table lookup (keep_lut = words 64..79 of the
 // group table, in shared memory) and one byte permute gather the two stored ones.
 template <typename TOut>
-__device__ __forceinline__ uint32_t emit_fast(const float (&q)[4], uint32_t keep, TOut &o0, TOut &o1, const uint32_t *keep_lut) {
+__device__ __forceinline__ uint32_t emit_fast(const float (&q)[4], uint32_t keep, TOut &o0, TOut &o1, const uint32_t *keep_lut,
+                                              float scale = 1.f) {
     if constexpr (sizeof(TOut) == 2) {
         const uint32_t e = keep_lut[keep];
         const uint32_t o = __byte_perm(Elem<TOut>::pack2(q[0], q[1]), Elem<TOut>::pack2(q[2], q[3]), e >> 8);
@@ -66,9 +69,10 @@ __device__ __forceinline__ uint32_t emit_fast(const float (&q)[4], uint32_t keep
         o1 = *reinterpret_cast<const TOut *>(&hi);
         return e & 0xFu;
     } else {
+        // 8-bit outputs: the caller's quantisation scale is applied before the cast (one more float32 rounding)
         const uint32_t nib = encode_nibble(keep);
-        o0 = Elem<TOut>::from_f32(pick4(nib & 3u, q[0], q[1], q[2], q[3]));
-        o1 = Elem<TOut>::from_f32(pick4(nib >> 2, q[0], q[1], q[2], q[3]));
+        o0 = Elem<TOut>::from_f32(__fmul_rn(pick4(nib & 3u, q[0], q[1], q[2], q[3]), scale));
+        o1 = Elem<TOut>::from_f32(__fmul_rn(pick4(nib >> 2, q[0], q[1], q[2], q[3]), scale));
         return nib;
     }
 }
@@ -78,20 +82,22 @@ __device__ __forceinline__ uint32_t emit_fast(const float (&q)[4], uint32_t keep
 // mode with 16-bit outputs reads it.
 template <typename TIn, typename TOut, int MODE>
 __device__ __forceinline__ uint32_t do_group(const TIn (&in)[4], uint32_t given_mask, float u0, float u1, TOut &o0,
-                                             TOut &o1, const uint32_t *keep_lut = nullptr) {
+                                             TOut &o1, const uint32_t *keep_lut = nullptr, float scale = 1.f) {
+    // `scale` only acts on 8-bit outputs (float8 quantisation); 16-bit outputs ignore it
+    constexpr bool SCALED = sizeof(TOut) == 1 && !std::is_same<TOut, int8_t>::value;
     uint32_t keep;
     if constexpr (MODE == SP24_PRUNE_MVUE_FAST) {
         float x[4] = {Elem<TIn>::to_f32(in[0]), Elem<TIn>::to_f32(in[1]), Elem<TIn>::to_f32(in[2]),
                       Elem<TIn>::to_f32(in[3])};
         keep = mvue24_group_fast(x, u0, u1);         // all four quotients in x[]
-        return emit_fast<TOut>(x, keep, o0, o1, keep_lut);
+        return emit_fast<TOut>(x, keep, o0, o1, keep_lut, scale);
     } else if constexpr (MODE == SP24_PRUNE_MVUE) {
         float x[4] = {Elem<TIn>::to_f32(in[0]), Elem<TIn>::to_f32(in[1]), Elem<TIn>::to_f32(in[2]),
                       Elem<TIn>::to_f32(in[3])};
         keep = mvue24_group<false>(x, u0, u1);     // quotients of the two stored positions in x[0], x[1]
         const uint32_t nib = encode_nibble(keep);
-        o0 = Elem<TOut>::from_f32(x[0]);
-        o1 = Elem<TOut>::from_f32(x[1]);
+        o0 = Elem<TOut>::from_f32(SCALED ? __fmul_rn(x[0], scale) : x[0]);
+        o1 = Elem<TOut>::from_f32(SCALED ? __fmul_rn(x[1], scale) : x[1]);
         return nib;
     } else {
         if constexpr (MODE == SP24_PRUNE_MASK) {
@@ -101,8 +107,13 @@ __device__ __forceinline__ uint32_t do_group(const TIn (&in)[4], uint32_t given_
                                    Elem<TIn>::to_f32(in[3]));
         }
         const uint32_t nib = encode_nibble(keep);
-        o0 = convert<TOut>(pick4(nib & 3u, in[0], in[1], in[2], in[3]));
-        o1 = convert<TOut>(pick4(nib >> 2, in[0], in[1], in[2], in[3]));
+        if constexpr (SCALED) {
+            o0 = Elem<TOut>::from_f32(__fmul_rn(Elem<TIn>::to_f32(pick4(nib & 3u, in[0], in[1], in[2], in[3])), scale));
+            o1 = Elem<TOut>::from_f32(__fmul_rn(Elem<TIn>::to_f32(pick4(nib >> 2, in[0], in[1], in[2], in[3])), scale));
+        } else {
+            o0 = convert<TOut>(pick4(nib & 3u, in[0], in[1], in[2], in[3]));
+            o1 = convert<TOut>(pick4(nib >> 2, in[0], in[1], in[2], in[3]));
+        }
         return nib;
     }
 }
@@ -253,7 +264,7 @@ __global__ void __launch_bounds__(256, is_mvue(MODE) ? 3 : 1) pc_row_kernel(PcPa
                                     ((mk[j][4 * g + 3] != 0) << 3);
                         }
                         const uint32_t nib =
-                            do_group<TIn, TOut, MODE>(grp, given, u[2 * h], u[2 * h + 1], out[2 * g], out[2 * g + 1], glut);
+                            do_group<TIn, TOut, MODE>(grp, given, u[2 * h], u[2 * h + 1], out[2 * g], out[2 * g + 1], glut, P.out_scale);
                         word |= nib << (4 * g);
                     }
                 }
@@ -356,6 +367,10 @@ __global__ void __launch_bounds__(256, col_min_blocks(MODE)) pc_col_kernel(PcPar
         const TIn *src = static_cast<const TIn *>(P.dense) + (c * CH) * P.ld_dense + r;
         const uint8_t *msrc = MODE == SP24_PRUNE_MASK ? P.mask + (c * CH) * P.ld_mask + r : nullptr;
         TOut *dst = packed + (c * (CH / 2)) * P.ld_packed + r;
+        // 8-bit outputs can also leave row-major (the K-major operand order of the 8-bit sparse GEMM): a thread's
+        // 32 logical columns are 16 contiguous packed bytes of its row
+        constexpr bool CAN_RM = sizeof(TOut) == 1;
+        TOut orow[CAN_RM ? V : 1][CAN_RM ? CH / 2 : 1];
         // a step = 8 consecutive storage rows = two groups of four per logical row = one Philox block
 #pragma unroll
         for (int step = 0; step < CH / 8; ++step) {
@@ -409,12 +424,24 @@ __global__ void __launch_bounds__(256, col_min_blocks(MODE)) pc_col_kernel(PcPar
                     }
                     float ua = 0.f, ub = 0.f;
                     if constexpr (is_mvue(MODE)) { ua = u[v][2 * h]; ub = u[v][2 * h + 1]; }
-                    const uint32_t nib = do_group<TIn, TOut, MODE>(grp, given, ua, ub, o0.v[v], o1.v[v], glut);
+                    const uint32_t nib = do_group<TIn, TOut, MODE>(grp, given, ua, ub, o0.v[v], o1.v[v], glut, P.out_scale);
                     word[v] |= nib << (4 * (step * 2 + h));
+                    if constexpr (CAN_RM) {
+                        orow[v][(step * 2 + h) * 2] = o0.v[v];
+                        orow[v][(step * 2 + h) * 2 + 1] = o1.v[v];
+                    }
                 }
-                store_vec<TOut, V>(dst, o0);
-                store_vec<TOut, V>(dst + P.ld_packed, o1);
-                dst += 2 * P.ld_packed;
+                if (!CAN_RM || !P.packed_rm) {
+                    store_vec<TOut, V>(dst, o0);
+                    store_vec<TOut, V>(dst + P.ld_packed, o1);
+                    dst += 2 * P.ld_packed;
+                }
+            }
+        }
+        if constexpr (CAN_RM) {
+            if (P.packed_rm) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) store_elems<TOut, CH / 2>(packed + (r + v) * P.ld_packed + c * (CH / 2), orow[v]);
             }
         }
         if (P.row_sums) {
@@ -532,7 +559,7 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
                                int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
                                int mode, const void *mask, int64_t ld_mask, const float *uniforms,
                                int64_t ld_uniforms, uint64_t seed, uint64_t offset, const uint64_t *offset_dev,
-                               void *e_tc, float *row_sums, void *stream) {
+                               void *e_tc, float *row_sums, void *stream, int packed_rm = 0, float out_scale = 1.f) {
     using namespace sp24;
     if (!dense || !packed || !meta) return SP24_ERR_ARG;
     const int so = dtype_size(packed_dtype), si = dtype_size(dense_dtype);
@@ -545,7 +572,9 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
     if (mode != SP24_PRUNE_MASK && mask) return SP24_ERR_ARG;
     if (mode != SP24_PRUNE_MVUE && uniforms) return SP24_ERR_ARG;
     if (mode < SP24_PRUNE_MSE || mode > SP24_PRUNE_MVUE_FAST) return SP24_ERR_ARG;
-    const int64_t inner = col_major ? m : k, inner_p = col_major ? m : k / 2;
+    if (packed_rm && (!col_major || so != 1)) return SP24_ERR_ARG;
+    if (!(out_scale > 0.f) || (out_scale != 1.f && (so != 1 || packed_dtype == SP24_I8))) return SP24_ERR_ARG;
+    const int64_t inner = col_major ? m : k, inner_p = (col_major && !packed_rm) ? m : k / 2;
     if (ld_dense < inner || (ld_dense * si) % 16) return SP24_ERR_STRIDE;
     if (ld_packed < inner_p || (ld_packed * so) % 16) return SP24_ERR_STRIDE;
     if (mask && (ld_mask < inner || ld_mask % 16)) return SP24_ERR_STRIDE;
@@ -558,7 +587,7 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
     if (int rc = check_device()) return rc;
     PcParams P{dense, packed, meta, static_cast<const uint8_t *>(mask), uniforms, m, k, ld_dense, ld_packed, ld_mask,
                ld_uniforms, seed, offset, reinterpret_cast<const unsigned long long *>(offset_dev),
-               static_cast<int16_t *>(e_tc), (k + 127) / 128, row_sums};
+               static_cast<int16_t *>(e_tc), (k + 127) / 128, row_sums, packed_rm, out_scale};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dense_dtype) {
         case SP24_F32: return dispatch_out<float>(P, packed_dtype, mode, col_major, st);
@@ -594,4 +623,19 @@ extern "C" int sp24_prune_compress_ex(const void *dense, int dense_dtype, int64_
     if (offset_dev && (reinterpret_cast<uintptr_t>(offset_dev) & 7u)) return SP24_ERR_ARG;
     return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode,
                                mask, ld_mask, uniforms, ld_uniforms, seed, offset, offset_dev, e_tc, row_sums, stream);
+}
+
+// Float8 quantising form of the conversion: packed is ALWAYS row-major (m, k/2), the K-major operand order the 8-bit
+// sparse GEMM requires, whatever the storage order of dense (col_major = 1: a transposed view such as W.T of a
+// row-major weight or dY.T of a row-major gradient, converted without a transpose pass).  Stored values are
+// value * out_scale rounded to the float8 type (the caller's per-tensor quantisation scale; 1 for none).  mask follows
+// the storage order of dense.  Metadata: m*k/32 int32 in the reference's reordered layout, as for any 8-bit output.
+extern "C" int sp24_prune_compress_q8(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense, int col_major,
+                                      void *packed, int packed_dtype, int64_t ld_packed, void *meta, int mode,
+                                      const void *mask, int64_t ld_mask, float out_scale, uint64_t seed, uint64_t offset,
+                                      void *stream) {
+    if (packed_dtype != SP24_E4M3 && packed_dtype != SP24_E5M2) return SP24_ERR_DTYPE;
+    return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode, mask,
+                               ld_mask, nullptr, 0, seed, offset, nullptr, nullptr, nullptr, stream, col_major ? 1 : 0,
+                               out_scale);
 }

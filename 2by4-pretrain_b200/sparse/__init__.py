@@ -12,6 +12,7 @@ from .semi_structured import to_sparse_semi_structured, SparseSemiStructuredTens
 from .sparse_ops import (MyLinear, SparseLinear, SparseLinearTranspose, sparse_linear_transpose, sparse_state,
                          load_sparse_state, refresh_sparse_layers)
 from .sste import SoftThreshold, SoftThresholdLinear
+from . import fp8  # noqa: F401  (float8 form of the FST layer: sparse.fp8.sparse_linear_transpose_fp8)
 
 mask_select = TransposableSparse()
 

@@ -5,8 +5,10 @@
 
 Prints ONE JSON line (rank 0).  Default workload ``select_dual_compress``: one mask refresh of a
 training layer — transposable 4x4 mask select plus 2:4 compression of W and W^T — on 4096 x 4096
-fp16 weights ~N(0, 0.02), seed 2 (+ matrix index).  One step processes a batch of 8 such matrices
-(distinct buffers, 672 MiB of traffic per step, larger than the 126 MB L2, so no flush is needed).
+fp16 weights ~N(0, 0.02), seeded per matrix.  One step is the mask refresh of a 48-layer model: 48 such
+matrices (distinct buffers, 4 GB of traffic per step, far larger than the 126 MB L2, so no flush is needed)
+converted by ONE launch of the batched entry point ``sp24_select_dual_compress_batch`` (what
+``sparse.refresh_sparse_layers`` calls once per optimizer step).
 
   value      algorithmic GB/s with inputs resident in HBM (CUDA events on the launching stream)
   e2e        the same metric through the public Python API from pinned HOST buffers: H2D copy of W,
@@ -35,15 +37,28 @@ sys.path.insert(0, os.path.join(ROOT, "2by4-pretrain_b200"))
 import torch  # noqa: E402
 
 M = K = 4096
-BATCH = 8
+BATCH = 48          # matrices per step = per launch of the batched kernel (its descriptor array holds 48)
+E2E_BATCH = 8       # matrices per step of the host-buffer leg (PCIe-bound: 9 ms per step)
 BYTES_PER_ELEM = 2 + 1 + 2 * (2 / 2 + 1 / 8)  # read fp16 W, write bool mask, write 2 x (fp16 values/2 + 4 bits/4 elems)
 ALG_BYTES_PER_MATRIX = M * K * BYTES_PER_ELEM
 METRIC = "prune/compress HBM GB/s (transposable select + dual 2:4 compress)"
 WORKLOAD = f"cfg2: transposable select + dual 2:4 compress, {M}x{K} fp16 N(0,0.02) seed 2+i"
-# dram__bytes_read.sum + dram__bytes_write.sum of one ts_dual_kernel launch on this workload, from the
-# ncu capture summarised in profiles/ts_dual_kernel_8192x8192_fp16.md: (134.2 + 162.9) MB for an 8192 x 8192
-# matrix, scaled by the element count (1/4) to one 4096 x 4096 launch
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 74.3e6
+
+
+def ncu_traffic_per_launch():
+    """DRAM bytes (read + write) of one launch of the benchmark kernel, taken from the committed ncu summary of that
+    kernel (the line ``dram_bytes_per_matrix_4096x4096: N`` of the profile text) times the matrices per launch;
+    None when the summary carries no such line."""
+    import glob
+    import re
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "ts_dual*"))):
+        try:
+            m = re.search(r"dram_bytes_per_matrix_4096x4096:\s*([0-9.eE+]+)", open(path).read())
+        except OSError:
+            m = None
+        if m:
+            return float(m.group(1)) * BATCH
+    return None
 
 
 def measured_tensor_peak():
@@ -183,7 +198,7 @@ def run_reference(args, rank):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / len(per_step) * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "alg_bytes_per_elem": BYTES_PER_ELEM,
-                   "step": "one matrix per step (bounded sample of the GPU arm's 8-matrix batch)"},
+                   "step": "one matrix per step (bounded sample of the GPU arm's 48-matrix batch)"},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"{len(per_step)} steps x one {M}x{K} matrix; CPU restatement of the reference "
                                    "path (matmul-form mask select + pure-torch compress)"},
@@ -196,7 +211,7 @@ def run_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -232,24 +247,32 @@ def main():
     from sparse import _ext
 
     lib = _ext.lib()
-    ws_cpu = make_weights(BATCH, "cpu", seed0=2 + rank * BATCH)
-    ws = [w.to(dev) for w in ws_cpu]
+    # device-resident inputs: 48 distinct matrices drawn on the device (seed 2 + matrix index, rank-disjoint)
+    ws = []
+    for i in range(BATCH):
+        g = torch.Generator(device=dev).manual_seed(2 + rank * BATCH + i)
+        ws.append((torch.randn(M, K, device=dev, generator=g) * 0.02).half())
+    ws_cpu = make_weights(E2E_BATCH, "cpu", seed0=2 + rank * E2E_BATCH)      # host copies for the end-to-end leg
+    descs = (_ext.DualDesc * BATCH)()
     outs = []
-    for _ in range(BATCH):
+    for i in range(BATCH):
         mask = torch.empty(M, K, dtype=torch.bool, device=dev)
         bw = torch.empty(M * K * 9 // 16, dtype=torch.float16, device=dev)
         bt = torch.empty(M * K * 9 // 16, dtype=torch.float16, device=dev)
         outs.append((mask, bw, bt))
+        d = descs[i]
+        d.w, d.m, d.k, d.ld_w = ws[i].data_ptr(), M, K, K
+        d.mask, d.ld_mask = mask.data_ptr(), K
+        d.packed_w, d.ld_packed_w, d.meta_w = bw.data_ptr(), K // 2, bw.data_ptr() + M * K
+        d.packed_t, d.ld_packed_t, d.meta_t = bt.data_ptr(), K, bt.data_ptr() + M * K
+        d.tc_w = d.tc_t = None
     stream = torch.cuda.current_stream()
 
     def step_device():
-        sp = stream.cuda_stream
-        for w, (mask, bw, bt) in zip(ws, outs):
-            rc = lib.sp24_select_dual_compress(
-                w.data_ptr(), _ext.F16, M, K, K, 1, mask.data_ptr(), K, bw.data_ptr(), _ext.F16, K // 2,
-                bw.data_ptr() + M * K, bt.data_ptr(), K, bt.data_ptr() + M * K, sp)
-            if rc:
-                _ext.check(rc, "sp24_select_dual_compress")
+        # one launch: select + dual compress of all 48 matrices
+        rc = lib.sp24_select_dual_compress_batch(descs, BATCH, _ext.F16, _ext.F16, 1, stream.cuda_stream)
+        if rc:
+            _ext.check(rc, "sp24_select_dual_compress_batch")
 
     def barrier():
         if world > 1:
@@ -274,18 +297,20 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    launches = args.steps * BATCH * world
+    launches = args.steps * world
     total_bytes = ALG_BYTES_PER_MATRIX * BATCH * args.steps * world
     value = total_bytes / (ms * 1e-3) / 1e9
-    per_launch_s = ms * 1e-3 / (args.steps * BATCH)   # one GPU's launches: the roofline is per kernel launch, not per job
-    achieved = ALG_BYTES_PER_MATRIX / per_launch_s / 1e9
+    per_launch_s = ms * 1e-3 / args.steps   # one GPU's launches: the roofline is per kernel launch, not per job
+    achieved = ALG_BYTES_PER_MATRIX * BATCH / per_launch_s / 1e9
+    del ws, outs, descs
+    torch.cuda.empty_cache()
 
     # end-to-end through the public API with host buffers
     pinned = [w.pin_memory() for w in ws_cpu]
     host_out = [(torch.empty(M, K, dtype=torch.bool).pin_memory(),
                  torch.empty(M, K // 2, dtype=torch.float16).pin_memory(), torch.empty(M, K // 16, dtype=torch.int16).pin_memory(),
                  torch.empty(M // 2, K, dtype=torch.float16).pin_memory(), torch.empty(K, M // 16, dtype=torch.int16).pin_memory())
-                for _ in range(BATCH)]
+                for _ in range(E2E_BATCH)]
 
     # Three streams: uploads, the kernels, downloads.  PCIe is full duplex, so matrix i+1 goes up while matrix i is
     # compressed and matrix i-1 comes down; events order the three stages of every matrix.
@@ -328,9 +353,9 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
-    e2e_val = ALG_BYTES_PER_MATRIX * BATCH * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
-    h2d = BATCH * M * K * 2
-    d2h = BATCH * (M * K + 2 * (M * K + M * K // 8))
+    e2e_val = ALG_BYTES_PER_MATRIX * E2E_BATCH * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
+    h2d = E2E_BATCH * M * K * 2
+    d2h = E2E_BATCH * (M * K + 2 * (M * K + M * K // 8))
 
     extra = None
     spmm_extra = None
@@ -353,14 +378,14 @@ def main():
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD,
-                       "batch_per_step_per_gpu": BATCH, "alg_bytes_per_elem": BYTES_PER_ELEM,
-                       "l2": "inputs+outputs per step = 672 MiB > 126 MB L2, no flush",
+                       "batch_per_step_per_gpu": BATCH, "launches_per_step": 1, "alg_bytes_per_elem": BYTES_PER_ELEM,
+                       "l2": "inputs+outputs per step = 4.0 GB > 126 MB L2, no flush",
                        "parallelism": f"independent matrices x{world}"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind, "kernel": "ts_dual_kernel",
-                         "alg_bytes_per_launch": ALG_BYTES_PER_MATRIX},
+                         "traffic": ncu_traffic_per_launch(), "peak_kind": peak_kind, "kernel": "ts_dual_batch_kernel",
+                         "alg_bytes_per_launch": ALG_BYTES_PER_MATRIX * BATCH},
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps, "matrices_per_step": E2E_BATCH,
                     "streams": "pinned host buffers; uploads, kernels and downloads on three streams, ordered per matrix by events"},
             "gpu_launches": launches, "clocks": clocks,
         }

@@ -114,6 +114,22 @@ int sp24_prune_compress_ex(const void *dense, int dense_dtype, int64_t m, int64_
                            const uint64_t *offset_dev, void *e_tc, float *row_sums, void *stream);
 
 /*
+ * Float8 quantising form of sp24_prune_compress: packed_dtype E4M3 or E5M2, stored value = value * out_scale (the
+ * caller's per-tensor quantisation scale, > 0; saturating cast), and packed is ALWAYS row-major (m, k/2) with pitch
+ * ld_packed, whatever the storage order of dense.  With col_major = 1 (W.T of a row-major weight, dY.T of a row-major
+ * gradient) this gives the K-major sparse operand the 8-bit GEMM requires without a transpose pass.  The reference
+ * cannot run its backward pass in float8: its 8-bit kernels take row-major A only
+ * (sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:735-738, :778-781) while its conversion of a transposed view
+ * writes column-major packed values (sparse/semi_structured.py:231-243), and its MVUE branch for 8-bit outputs is
+ * incomplete (sparse/_semi_structured_conversions.py:822-839); this entry point defines that path: eight groups per
+ * int32 metadata word, one Philox block per two groups as for 16-bit outputs.  mode: MSE, MASK, MVUE (seeded) or
+ * MVUE_FAST; mask follows the storage order of dense.
+ */
+int sp24_prune_compress_q8(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense, int col_major,
+                           void *packed, int packed_dtype, int64_t ld_packed, void *meta, int mode, const void *mask,
+                           int64_t ld_mask, float out_scale, uint64_t seed, uint64_t offset, void *stream);
+
+/*
  * 2:4 compressed -> dense (zeros at pruned positions).  Replaces
  * _sparse_semi_structured_to_dense_triton / _sparse_semi_structured_to_dense
  * (sparse/_semi_structured_conversions.py:1163-1274, :217-328).

@@ -373,8 +373,8 @@ def mvue24_dense(x: torch.Tensor, U: Optional[torch.Tensor] = None, seed: int = 
 # ---------------------------------------------------------------------------
 def prune_compress(dense: torch.Tensor, out_dtype: torch.dtype = torch.float16, *,
                    mask: Optional[torch.Tensor] = None, mvue: bool = False,
-                   U: Optional[torch.Tensor] = None, seed: int = 0, offset: int = 0
-                   ) -> Tuple[torch.Tensor, torch.Tensor]:
+                   U: Optional[torch.Tensor] = None, seed: int = 0, offset: int = 0,
+                   out_scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """sparse/_semi_structured_conversions.py:431-661 / :664-1069 with
     PRUNE = 'mask' | 'mvue' | 'mse' (launcher :1072-1132).
 
@@ -384,12 +384,15 @@ def prune_compress(dense: torch.Tensor, out_dtype: torch.dtype = torch.float16, 
     """
     if mask is not None and mvue:
         raise RuntimeError("Error using MVUE24 with mask is not supported! ")  # semi_structured.py:207-210
+    # float8 quantisation (no counterpart in the reference): the value that would be stored is multiplied by
+    # ``out_scale`` in float32 (one rounding) before the cast; the pruning decision is taken on the unscaled input
+    q = (lambda v: v) if out_scale is None else (lambda v: v.float() * torch.tensor(out_scale, dtype=torch.float32))
     if mask is not None:
-        return compress_with_mask(dense, mask, out_dtype)
+        return compress_with_mask(q(dense), mask, out_dtype)
     if mvue:
         vals, mk = _mvue(dense, U, seed, offset)
-        return compress_with_mask(vals, mk, out_dtype)
-    return compress_with_mask(dense, magnitude_mask24(dense), out_dtype)
+        return compress_with_mask(q(vals), mk, out_dtype)
+    return compress_with_mask(q(dense), magnitude_mask24(dense), out_dtype)
 
 
 def to_dense(packed: torch.Tensor, meta: torch.Tensor) -> torch.Tensor:

@@ -211,21 +211,93 @@ def test_config4_forward_backward_full_size(S, dtype):
     check_status()
 
 
-def test_config4_fp8_forward(S):
+def test_config4_fp8_forward_and_backward(S):
+    """cfg4 in e4m3 with per-tensor scales: the three GEMMs of the FST layer on 8-bit operands.  Tolerance 1e-5
+    (max error over max magnitude) against fp32 matmuls of the same quantised, pruned operands: only the summation
+    order differs.  The reference has no float8 backward (its 8-bit GEMMs reject the column-major packed W^T and
+    dY^T, and its MVUE-to-8-bit branch is incomplete), so the K-major conversions are checked against the oracle."""
+    from oracle import sp24_oracle as O
+    from sparse import _ext, fp8
+    from sparse._semi_structured_conversions import sparse_semi_structured_to_dense as to_dense
     T, K, N = 16384, 768, 3072
     x = torch.randn(T, K, generator=torch.Generator().manual_seed(7)).to(DEV)
     w = (torch.randn(N, K, generator=torch.Generator().manual_seed(8)) * 0.02).to(DEV)
+    dy = (torch.randn(T, N, generator=torch.Generator().manual_seed(9)) * 1e-2).to(DEV).half()
     _, mask = S.mask_select(w)
-    sx, sw = x.abs().max() / 448, w.abs().max() / 448
-    xq = (x / sx).to(torch.float8_e4m3fn)
-    ws = S.to_sparse_semi_structured(w / sw, mask=mask, dtype=torch.float8_e4m3fn)
-    y = torch.mm(xq, ws.t()) * (sx * sw)
-    wq = torch.where(mask, (w / sw).to(torch.float8_e4m3fn).float(), torch.zeros((), device=DEV))
-    ref = (xq.float() @ wq.t()) * (sx * sw)
+    w8 = fp8.Fp8SparseWeight(w, mask)
+    xq, sx = fp8.quantize(x)
+    gq, sg = fp8.quantize(dy)
+    # both compressed copies hold the same quantised values: W^T's K-major copy is the transpose of W's
+    wq = to_dense(w8.pw, w8.mw).float()
+    assert torch.equal(to_dense(w8.pt, w8.mt).float(), wq.t())
+    assert torch.equal(wq != 0, mask & (wq != 0)) and w8.pt.is_contiguous() and tuple(w8.pt.shape) == (K, N // 2)
+    # forward
+    y = fp8.fst_fp8_forward(xq, sx, w8)
+    ref = (xq.float() @ wq.t()) * (sx * w8.scale)
     assert float((y - ref).abs().max() / ref.abs().max()) <= 1e-5
-    # and the quantised result tracks the unquantised masked product to fp8 accuracy
     full = x @ torch.where(mask, w, torch.zeros((), device=DEV)).t()
-    assert float((y - full).norm() / full.norm()) < 0.08
+    assert float((y - full).norm() / full.norm()) < 0.08          # and tracks the unquantised product to fp8 accuracy
+    # input gradient through the K-major W^T
+    dx = fp8.fst_fp8_input_grad(gq, sg, w8)
+    ref = (gq.float() @ wq) * (sg * w8.scale)
+    assert float((dx - ref).abs().max() / ref.abs().max()) <= 1e-5
+    # weight gradient: MVUE of dY^T quantised on store, times Xq
+    xq_t = xq.t().contiguous()
+    pg, mg = fp8.compress_q8(dy.t(), mode=_ext.PRUNE_MVUE_FAST, scale=sg, seed=11)
+    gd = to_dense(pg, mg).float()                                  # (N, T), two kept per group of four tokens
+    assert int((gd.reshape(N, -1, 4) != 0).sum(-1).max()) <= 2
+    dw = fp8.fst_fp8_weight_grad(dy, sg, xq_t, sx, seed=11)
+    ref = (gd @ xq.float()) * (sg * sx)
+    assert float((dw - ref).abs().max() / ref.abs().max()) <= 1e-5
+    # the same draw without quantisation (dense-shaped MVUE of dY^T with the same seed, times X): float8 accuracy apart
+    mv = S.MVUE24_approx_triton(dy.t(), seed=11, exact=False).float()
+    unq = mv @ x
+    assert float((dw - unq).norm() / unq.norm()) < 0.08
+    # conversions against the oracle on a slab (exact-arithmetic MVUE, mask mode), values and metadata bit for bit
+    rows = slice(256, 384)
+    pg2, mg2 = fp8.compress_q8(dy.t()[rows], mode=_ext.PRUNE_MVUE, scale=sg, seed=5, offset=3)
+    inv = float(torch.tensor(1.0 / sg, dtype=torch.float32))
+    op, om = O.prune_compress(dy.t()[rows].cpu().contiguous(), torch.float8_e4m3fn, mvue=True, seed=5, offset=3, out_scale=inv)
+    assert torch.equal(pg2.cpu().view(torch.uint8), op.view(torch.uint8)) and torch.equal(mg2.cpu(), om)
+    inv = float(torch.tensor(1.0 / w8.scale, dtype=torch.float32))
+    op, om = O.prune_compress(w.t()[rows].cpu().contiguous(), torch.float8_e4m3fn, mask=mask.t()[rows].cpu().contiguous(),
+                              out_scale=inv)
+    pt2, mt2 = fp8.compress_q8(w.t()[rows], mode=_ext.PRUNE_MASK, mask=mask.t()[rows], scale=w8.scale)
+    assert torch.equal(pt2.cpu().view(torch.uint8), op.view(torch.uint8)) and torch.equal(mt2.cpu(), om)
+    from sparse.spmm import check_status
+    check_status()
+
+
+def test_fp8_layer_function_trains_like_the_fp32_masked_layer(S):
+    """sparse_linear_transpose_fp8: output and input gradient within float8 accuracy of the fp32 masked linear layer,
+    weight gradient an unbiased estimate (averaged over draws it approaches the exact one)."""
+    from sparse import fp8
+    g = torch.Generator().manual_seed(21)
+    T, K, N = 1024, 256, 384
+    x = torch.randn(T, K, generator=g).to(DEV).requires_grad_(True)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(DEV).requires_grad_(True)
+    b = torch.randn(N, generator=g).to(DEV).requires_grad_(True)
+    dy = (torch.randn(T, N, generator=g) * 1e-2).to(DEV)
+    _, mask = S.mask_select(w.detach())
+    w8 = fp8.Fp8SparseWeight(w, mask)
+    y = fp8.sparse_linear_transpose_fp8.apply(x, w, w8, b)
+    y.backward(dy)
+    wm = torch.where(mask, w.detach(), torch.zeros((), device=DEV))
+    y_ref = x.detach() @ wm.t() + b.detach()
+    assert float((y.detach() - y_ref).norm() / y_ref.norm()) < 0.08
+    dx_ref = dy @ wm
+    assert float((x.grad - dx_ref).norm() / dx_ref.norm()) < 0.08
+    assert torch.allclose(b.grad, dy.sum(0), rtol=1e-4, atol=1e-5)
+    dw_ref = dy.t() @ x.detach()
+    acc = torch.zeros_like(dw_ref)
+    n = 24
+    for _ in range(n):
+        w.grad = None
+        fp8.sparse_linear_transpose_fp8.apply(x.detach(), w, w8, None).backward(dy)
+        acc += w.grad
+    one = float((w.grad - dw_ref).norm() / dw_ref.norm())
+    avg = float((acc / n - dw_ref).norm() / dw_ref.norm())
+    assert avg < 0.5 * one and avg < 0.25, (one, avg)
 
 
 def test_gpt2_training_steps_tiny(S):
