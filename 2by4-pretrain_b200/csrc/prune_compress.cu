@@ -24,7 +24,12 @@ struct PcParams {
     float *row_sums;                        // optional (column-major only): row_sums[r] += sum over k of dense[r, k]
     int packed_rm;                          // column-major input, 8-bit output: packed is written row-major (m, k/2)
     float out_scale;                        // 8-bit outputs: stored value = value * out_scale (1 = none)
+    float soft_scale;                       // soft-threshold mode: kept values are also multiplied by this ...
+    int soft_use_scale;                     // ... when this is set (one more rounding in the input type)
 };
+
+// internal mode code of the fused soft-threshold + compress entry point (not part of the public enum)
+constexpr int PRUNE_SOFT = 4;
 
 template <typename T, int N> __device__ __forceinline__ void load_elems(const T *p, T (&out)[N]) {
     constexpr int PER = (sizeof(T) * N >= 16) ? 16 / sizeof(T) : N;
@@ -98,6 +103,26 @@ __device__ __forceinline__ uint32_t do_group(const TIn (&in)[4], uint32_t given_
         const uint32_t nib = encode_nibble(keep);
         o0 = Elem<TOut>::from_f32(SCALED ? __fmul_rn(x[0], scale) : x[0]);
         o1 = Elem<TOut>::from_f32(SCALED ? __fmul_rn(x[1], scale) : x[1]);
+        return nib;
+    } else if constexpr (MODE == PRUNE_SOFT) {
+        // S-STE: magnitude 2:4 mask; the two kept values move toward zero by the group's second-smallest magnitude
+        // (one rounding in the input type), then optionally times the frozen scale (one more rounding in the input
+        // type), then the cast to the packed type.  u0 carries the scale, u1 != 0 says whether to apply it.
+        const float x0 = Elem<TIn>::to_f32(in[0]), x1 = Elem<TIn>::to_f32(in[1]), x2 = Elem<TIn>::to_f32(in[2]),
+                    x3 = Elem<TIn>::to_f32(in[3]);
+        keep = magnitude_mask4(x0, x1, x2, x3);
+        const float a0 = fabsf(x0), a1 = fabsf(x1), a2 = fabsf(x2), a3 = fabsf(x3);
+        const float thr = fminf(fmaxf(fminf(a0, a1), fminf(a2, a3)), fminf(fmaxf(a0, a1), fmaxf(a2, a3)));
+        const uint32_t nib = encode_nibble(keep);
+        float kv[2] = {pick4(nib & 3u, x0, x1, x2, x3), pick4(nib >> 2, x0, x1, x2, x3)};
+        TIn t[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            t[i] = Elem<TIn>::from_f32(kv[i] > 0.f ? __fsub_rn(kv[i], thr) : __fadd_rn(kv[i], thr));
+            if (u1 != 0.f) t[i] = Elem<TIn>::from_f32(__fmul_rn(Elem<TIn>::to_f32(t[i]), u0));
+        }
+        o0 = convert<TOut>(t[0]);
+        o1 = convert<TOut>(t[1]);
         return nib;
     } else {
         if constexpr (MODE == SP24_PRUNE_MASK) {
@@ -187,7 +212,7 @@ __global__ void __launch_bounds__(256, is_mvue(MODE) ? 3 : 1) pc_row_kernel(PcPa
     constexpr int RPI = (is_mvue(MODE) || CH * sizeof(TIn) >= 128) ? 1 : (CH * sizeof(TIn) >= 64 ? 2 : 4);
 
     __shared__ __align__(16) MetaT smeta[16][64];
-    constexpr bool PACKED = !is_mvue(MODE) && std::is_same<TIn, TOut>::value && sizeof(TIn) == 2;
+    constexpr bool PACKED = !is_mvue(MODE) && MODE != PRUNE_SOFT && std::is_same<TIn, TOut>::value && sizeof(TIn) == 2;
     constexpr bool KEEP_LUT = MODE == SP24_PRUNE_MVUE_FAST && sizeof(TOut) == 2;   // words 64..79 only
     __shared__ uint32_t glut[PACKED ? 80 : (KEEP_LUT ? 16 : 1)];
     if constexpr (PACKED) {
@@ -243,6 +268,7 @@ __global__ void __launch_bounds__(256, is_mvue(MODE) ? 3 : 1) pc_row_kernel(PcPa
 #pragma unroll
                 for (int g2 = 0; g2 < CH / 8; ++g2) {
                     float u[4] = {0.f, 0.f, 0.f, 0.f};
+                    if constexpr (MODE == PRUNE_SOFT) { u[0] = u[2] = P.soft_scale; u[1] = u[3] = P.soft_use_scale ? 1.f : 0.f; }
                     if constexpr (is_mvue(MODE)) {
                         if constexpr (HAS_U) {
                             const float *up = P.uniforms + r * P.ld_u + c * CH + g2 * 8;
@@ -424,6 +450,7 @@ __global__ void __launch_bounds__(256, col_min_blocks(MODE)) pc_col_kernel(PcPar
                     }
                     float ua = 0.f, ub = 0.f;
                     if constexpr (is_mvue(MODE)) { ua = u[v][2 * h]; ub = u[v][2 * h + 1]; }
+                    if constexpr (MODE == PRUNE_SOFT) { ua = P.soft_scale; ub = P.soft_use_scale ? 1.f : 0.f; }
                     const uint32_t nib = do_group<TIn, TOut, MODE>(grp, given, ua, ub, o0.v[v], o1.v[v], glut, P.out_scale);
                     word[v] |= nib << (4 * (step * 2 + h));
                     if constexpr (CAN_RM) {
@@ -538,6 +565,9 @@ template <typename TIn, typename TOut> int dispatch_mode(const PcParams &P, int 
         case SP24_PRUNE_MVUE_FAST:
             if constexpr (std::is_same<TIn, int8_t>::value) return SP24_ERR_DTYPE;
             else return launch<TIn, TOut, SP24_PRUNE_MVUE_FAST, false>(P, col_major, st);
+        case PRUNE_SOFT:
+            if constexpr (std::is_same<TIn, int8_t>::value || sizeof(TOut) != 2) return SP24_ERR_DTYPE;
+            else return launch<TIn, TOut, PRUNE_SOFT, false>(P, col_major, st);
         default: return SP24_ERR_ARG;
     }
 }
@@ -559,7 +589,8 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
                                int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
                                int mode, const void *mask, int64_t ld_mask, const float *uniforms,
                                int64_t ld_uniforms, uint64_t seed, uint64_t offset, const uint64_t *offset_dev,
-                               void *e_tc, float *row_sums, void *stream, int packed_rm = 0, float out_scale = 1.f) {
+                               void *e_tc, float *row_sums, void *stream, int packed_rm = 0, float out_scale = 1.f,
+                               int soft_use_scale = 0, float soft_scale = 1.f) {
     using namespace sp24;
     if (!dense || !packed || !meta) return SP24_ERR_ARG;
     const int so = dtype_size(packed_dtype), si = dtype_size(dense_dtype);
@@ -571,7 +602,7 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
     if (mode == SP24_PRUNE_MASK && !mask) return SP24_ERR_ARG;
     if (mode != SP24_PRUNE_MASK && mask) return SP24_ERR_ARG;
     if (mode != SP24_PRUNE_MVUE && uniforms) return SP24_ERR_ARG;
-    if (mode < SP24_PRUNE_MSE || mode > SP24_PRUNE_MVUE_FAST) return SP24_ERR_ARG;
+    if (mode < SP24_PRUNE_MSE || mode > PRUNE_SOFT) return SP24_ERR_ARG;
     if (packed_rm && (!col_major || so != 1)) return SP24_ERR_ARG;
     if (!(out_scale > 0.f) || (out_scale != 1.f && (so != 1 || packed_dtype == SP24_I8))) return SP24_ERR_ARG;
     const int64_t inner = col_major ? m : k, inner_p = (col_major && !packed_rm) ? m : k / 2;
@@ -587,7 +618,7 @@ static int prune_compress_impl(const void *dense, int dense_dtype, int64_t m, in
     if (int rc = check_device()) return rc;
     PcParams P{dense, packed, meta, static_cast<const uint8_t *>(mask), uniforms, m, k, ld_dense, ld_packed, ld_mask,
                ld_uniforms, seed, offset, reinterpret_cast<const unsigned long long *>(offset_dev),
-               static_cast<int16_t *>(e_tc), (k + 127) / 128, row_sums, packed_rm, out_scale};
+               static_cast<int16_t *>(e_tc), (k + 127) / 128, row_sums, packed_rm, out_scale, soft_scale, soft_use_scale};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (dense_dtype) {
         case SP24_F32: return dispatch_out<float>(P, packed_dtype, mode, col_major, st);
@@ -602,6 +633,7 @@ extern "C" int sp24_prune_compress(const void *dense, int dense_dtype, int64_t m
                                    int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
                                    int mode, const void *mask, int64_t ld_mask, const float *uniforms,
                                    int64_t ld_uniforms, uint64_t seed, uint64_t offset, void *stream) {
+    if (mode > SP24_PRUNE_MVUE_FAST) return SP24_ERR_ARG;
     return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode,
                                mask, ld_mask, uniforms, ld_uniforms, seed, offset, nullptr, nullptr, nullptr, stream);
 }
@@ -621,6 +653,7 @@ extern "C" int sp24_prune_compress_ex(const void *dense, int dense_dtype, int64_
                                       int64_t ld_uniforms, uint64_t seed, uint64_t offset, const uint64_t *offset_dev,
                                       void *e_tc, float *row_sums, void *stream) {
     if (offset_dev && (reinterpret_cast<uintptr_t>(offset_dev) & 7u)) return SP24_ERR_ARG;
+    if (mode > SP24_PRUNE_MVUE_FAST) return SP24_ERR_ARG;
     return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode,
                                mask, ld_mask, uniforms, ld_uniforms, seed, offset, offset_dev, e_tc, row_sums, stream);
 }
@@ -635,7 +668,21 @@ extern "C" int sp24_prune_compress_q8(const void *dense, int dense_dtype, int64_
                                       const void *mask, int64_t ld_mask, float out_scale, uint64_t seed, uint64_t offset,
                                       void *stream) {
     if (packed_dtype != SP24_E4M3 && packed_dtype != SP24_E5M2) return SP24_ERR_DTYPE;
+    if (mode > SP24_PRUNE_MVUE_FAST) return SP24_ERR_ARG;
     return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta, mode, mask,
                                ld_mask, nullptr, 0, seed, offset, nullptr, nullptr, nullptr, stream, col_major ? 1 : 0,
                                out_scale);
+}
+
+// S-STE forward in one pass: magnitude 2:4 mask, soft threshold of the kept values (one rounding in the input type),
+// optional frozen scale (one more rounding in the input type), cast to the packed 16-bit type, metadata - what
+// sp24_soft_threshold24 followed by a cast and sp24_prune_compress (mask mode) produce in three passes over W.
+// e_tc (optional): the metadata also in the order sp24_spmm reads (m % 128 == 0).
+extern "C" int sp24_soft_threshold24_compress(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense,
+                                              int col_major, void *packed, int packed_dtype, int64_t ld_packed, void *meta,
+                                              int use_scale, float scale, void *e_tc, void *stream) {
+    if (packed_dtype != SP24_F16 && packed_dtype != SP24_BF16) return SP24_ERR_DTYPE;
+    return prune_compress_impl(dense, dense_dtype, m, k, ld_dense, col_major, packed, packed_dtype, ld_packed, meta,
+                               sp24::PRUNE_SOFT, nullptr, 0, nullptr, 0, 0, 0, nullptr, e_tc, nullptr, stream, 0, 1.f,
+                               use_scale ? 1 : 0, scale);
 }

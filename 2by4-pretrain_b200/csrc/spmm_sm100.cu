@@ -171,6 +171,7 @@ struct SpmmParams {
     int int8;               // 8-bit operands are signed integers (kind::i8, int32 accumulators and output)
     int k_splits;           // work units per tile along K (> 1 only for the accumulating fp32 output)
     int mblk_per_tile;      // 128-row blocks per tile: 2 (B staged once per 256 rows) or 1 (more, smaller tiles)
+    float alpha;            // float32 outputs: D = alpha * (A * B) (+ bias); 16-bit and integer outputs ignore it
 };
 
 template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
@@ -203,14 +204,16 @@ template <bool ACT> __device__ __forceinline__ float finish(float v, int act) {
 
 // One accumulator word -> one output value.  Integer accumulators pass through untouched: no float operation may
 // see their bits (an add of 0.0f would rewrite -0.0 and signalling-NaN patterns, which are ordinary integers).
-template <typename OutT, bool ACT> __device__ __forceinline__ OutT emit(uint32_t acc_bits, float bias, int act) {
+// float32 outputs are scaled first: alpha * acc + bias in one fused multiply-add (alpha = 1 gives acc + bias exactly).
+template <typename OutT, bool ACT> __device__ __forceinline__ OutT emit(uint32_t acc_bits, float bias, int act, float alpha) {
     if constexpr (std::is_same<OutT, int32_t>::value) return (int32_t)acc_bits;
+    else if constexpr (std::is_same<OutT, float>::value) return finish<ACT>(fmaf(__uint_as_float(acc_bits), alpha, bias), act);
     else return to_out<OutT>(finish<ACT>(__uint_as_float(acc_bits) + bias, act));
 }
 // the same, as the 32-bit container of a 4-byte output type
-template <typename OutT, bool ACT> __device__ __forceinline__ uint32_t emit_bits(uint32_t acc_bits, float bias, int act) {
+template <typename OutT, bool ACT> __device__ __forceinline__ uint32_t emit_bits(uint32_t acc_bits, float bias, int act, float alpha) {
     if constexpr (std::is_same<OutT, int32_t>::value) return acc_bits;
-    else return __float_as_uint(finish<ACT>(__uint_as_float(acc_bits) + bias, act));
+    else return __float_as_uint(finish<ACT>(fmaf(__uint_as_float(acc_bits), alpha, bias), act));
 }
 
 __device__ __forceinline__ unsigned long long globaltimer() {
@@ -471,7 +474,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             Vec<OutT, 8> o;
 #pragma unroll
                             for (int i = 0; i < 8; ++i)
-                                o.v[i] = emit<OutT, ACT>(v[q * 8 + i], bias0, P.activation);
+                                o.v[i] = emit<OutT, ACT>(v[q * 8 + i], bias0, P.activation, P.alpha);
                             const int piece = (half * HC + c * 32) / 8 + q;
                             *reinterpret_cast<uint4 *>(stg_row + ((piece ^ swz) << 4)) = *reinterpret_cast<const uint4 *>(&o);
                         }
@@ -490,8 +493,8 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
                                 Vec<OutT, 2> o;
-                                o.v[0] = emit<OutT, ACT>(v[2 * i], bias1, P.activation);
-                                o.v[1] = emit<OutT, ACT>(v[2 * i + 1], bias1, P.activation);
+                                o.v[0] = emit<OutT, ACT>(v[2 * i], bias1, P.activation, P.alpha);
+                                o.v[1] = emit<OutT, ACT>(v[2 * i + 1], bias1, P.activation, P.alpha);
                                 held[c * 16 + i] = *reinterpret_cast<const uint32_t *>(&o);
                             }
                         }
@@ -583,10 +586,10 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
                                     for (int q = 0; q < 8; ++q) {
                                         float4 o;
-                                        o.x = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 0], bias, P.activation));
-                                        o.y = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 1], bias, P.activation));
-                                        o.z = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 2], bias, P.activation));
-                                        o.w = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 3], bias, P.activation));
+                                        o.x = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 0], bias, P.activation, P.alpha));
+                                        o.y = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 1], bias, P.activation, P.alpha));
+                                        o.z = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 2], bias, P.activation, P.alpha));
+                                        o.w = __uint_as_float(emit_bits<OutT, ACT>(v[q * 4 + 3], bias, P.activation, P.alpha));
                                         *reinterpret_cast<float4 *>(stg_row + (col + q * 4) * 4) = o;
                                     }
                                 }
@@ -647,13 +650,13 @@ spmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                         Vec<OutT, PER> o;
 #pragma unroll
                                         for (int i = 0; i < PER; ++i)
-                                            o.v[i] = emit<OutT, ACT>(v[q * PER + i], bias, P.activation);
+                                            o.v[i] = emit<OutT, ACT>(v[q * PER + i], bias, P.activation, P.alpha);
                                         store_vec<OutT, PER>(row + q * PER, o);
                                     }
                                 } else {
                                     for (int i = 0; i < 32; ++i)
                                         if (nb + i < P.n)
-                                            row[i] = emit<OutT, ACT>(v[i], bias, P.activation);
+                                            row[i] = emit<OutT, ACT>(v[i], bias, P.activation, P.alpha);
                                 }
                             }
                         }
@@ -1432,9 +1435,9 @@ static int validate_spmm_args(const void *a_packed, int dtype, int a_mn_major, i
     return SP24_OK;
 }
 
-extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms,
-                         int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype,
-                         int trans_out, int64_t ld_out, const void *bias, int activation, int *status, void *stream) {
+static int spmm_impl(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms,
+                     int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype,
+                     int trans_out, int64_t ld_out, const void *bias, int activation, float alpha, int *status, void *stream) {
     if (!e_tc) return SP24_ERR_ARG;
     if (int rc = validate_spmm_args(a_packed, dtype, a_mn_major, ld_a, ms, k, b, b_mn_major, ld_b, n, out, out_dtype,
                                     trans_out, ld_out, bias, activation))
@@ -1455,6 +1458,7 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     P.k_atoms = (k + 127) / 128; P.status = status; P.activation = activation;
     P.trace = nullptr;
     P.k_splits = 1;
+    P.alpha = alpha;
 #ifdef SP24_TRACE_BUILD
     if (const char *env = getenv("SP24_SPMM_TRACE_PTR")) P.trace = reinterpret_cast<unsigned long long *>(strtoull(env, nullptr, 0));
 #endif
@@ -1506,6 +1510,25 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
     if (trans_out) SP24_GO(false, true, true, true, __nv_bfloat16);
     SP24_GO(false, true, true, false, __nv_bfloat16);
 #undef SP24_GO
+}
+
+
+extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms,
+                         int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype,
+                         int trans_out, int64_t ld_out, const void *bias, int activation, int *status, void *stream) {
+    return spmm_impl(a_packed, dtype, a_mn_major, ld_a, e_tc, ms, k, b, b_mn_major, ld_b, n, out, out_dtype, trans_out, ld_out,
+                     bias, activation, 1.f, status, stream);
+}
+
+// The float8 GEMM with the dequantisation folded into the epilogue: D = alpha * (A_sparse * B) [+ bias] [activation],
+// alpha = the product of the operands' per-tensor scales.  Float8 operands (float32 output) only.
+extern "C" int sp24_spmm_scaled(const void *a_packed, int dtype, int64_t ld_a, const void *e_tc, int64_t ms, int64_t k,
+                                const void *b, int64_t ld_b, int64_t n, float *out, int trans_out, int64_t ld_out,
+                                const float *bias, int activation, float alpha, int *status, void *stream) {
+    if (dtype != SP24_E4M3 && dtype != SP24_E5M2) return SP24_ERR_DTYPE;
+    if (!(alpha == alpha)) return SP24_ERR_ARG;
+    return spmm_impl(a_packed, dtype, 0, ld_a, e_tc, ms, k, b, 0, ld_b, n, out, SP24_F32, trans_out, ld_out, bias, activation,
+                     alpha, status, stream);
 }
 
 
@@ -1621,6 +1644,7 @@ extern "C" int sp24_spmm_accumulate_f32(const void *a_packed, int dtype, int a_m
     SpmmParams P{};
     P.e_tc = e_tc; P.out = out; P.bias = nullptr; P.ms = ms; P.n = n; P.k = k; P.ld_out = ld_out;
     P.k_atoms = (k + 127) / 128; P.status = status; P.activation = 0; P.trace = nullptr;
+    P.alpha = 1.f;
     const uint32_t fmt = dtype == SP24_BF16 ? 1u : 0u;
     P.idesc = (1u << 2) | (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) | (1u << 16) |
               ((uint32_t)(BM >> 4) << 24);

@@ -12,7 +12,7 @@ of ``sparse_linear_transpose`` (README.md:169-200 of the reference) run on the f
     dX = (dYq Wq_s)              * (sg * sw)        dYq = dY / sg
     dW = (MVUE24(dY^T)/sg  Xq)   * (sg * sx)        MVUE drawn on the 16-bit gradient, quantised on store
 
-Scales are per tensor, ``amax / 448``, read back to the host (one synchronisation per quantised tensor): the layer is
+The dequantisation scales are applied in the GEMM epilogue (``sp24_spmm_scaled``).  Scales are per tensor, ``amax / 448``, read back to the host (one synchronisation per quantised tensor): the layer is
 a functional reference of the float8 recipe, not a tuned training loop.
 """
 import random
@@ -89,13 +89,12 @@ class Fp8SparseWeight:
 
 def fst_fp8_forward(xq: torch.Tensor, sx: float, w8: Fp8SparseWeight, bias: Optional[torch.Tensor] = None):
     """Y (tokens, out_features) fp32 = dequantised Xq W_s^T (+ bias)."""
-    y = _spmm(xq, w8.pw, w8.mw) * (sx * w8.scale)
-    return y if bias is None else y + bias.float()
+    return _spmm(xq, w8.pw, w8.mw, bias=None if bias is None else bias.float().contiguous(), alpha=sx * w8.scale)
 
 
 def fst_fp8_input_grad(gq: torch.Tensor, sg: float, w8: Fp8SparseWeight):
     """dX (tokens, in_features) fp32 = dequantised dYq W_s, through the K-major compressed W^T."""
-    return _spmm(gq, w8.pt, w8.mt) * (sg * w8.scale)
+    return _spmm(gq, w8.pt, w8.mt, alpha=sg * w8.scale)
 
 
 def fst_fp8_weight_grad(g: torch.Tensor, sg: float, xq_t: torch.Tensor, sx: float, seed: Optional[int] = None,
@@ -107,7 +106,7 @@ def fst_fp8_weight_grad(g: torch.Tensor, sg: float, xq_t: torch.Tensor, sx: floa
         seed = random.randint(0, 2 ** 31 - 1)
     mode = _ext.PRUNE_MVUE_FAST if fast else _ext.PRUNE_MVUE
     pg, mg = compress_q8(g.t(), mode=mode, scale=sg, seed=seed)                   # (out_features, tokens / 2)
-    return _spmm(xq_t, pg, mg).t() * (sg * sx)
+    return _spmm(xq_t, pg, mg, alpha=sg * sx).t()
 
 
 class sparse_linear_transpose_fp8(autograd.Function):

@@ -22,6 +22,8 @@ _ext.register_signature("sp24_spmm", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _v
 _ext.register_signature("sp24_spmm_noalloc", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _i64, _vp, _i32, _i32,
                                               _i64, _vp, _i32, _vp, _vp])
 
+_ext.register_signature("sp24_spmm_scaled", [_vp, _i32, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _vp, _i32,
+                                             ctypes.c_float, _vp, _vp])
 _ext.register_signature("sp24_selftest_bounded_wait", [_vp, _i32, _vp])
 _ext.register_signature("sp24_spmm_accumulate_f32", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64,
                                                      _i32, _vp, _vp])
@@ -95,7 +97,9 @@ def tc_metadata(meta: torch.Tensor, ms: int, k: int) -> torch.Tensor:
     return e
 
 
-def sparse_linear(input, weight, meta, bias=None, activation=None):
+def sparse_linear(input, weight, meta, bias=None, activation=None, alpha=None):
+    """``alpha`` (float8 operands only, an addition to the reference's contract): the result is
+    alpha * (input @ dense(weight).T) (+ bias) (activation), the dequantisation scale applied in the GEMM epilogue."""
     _ext.require_cuda(input, weight, meta, bias)
     if activation not in _ACT:
         raise RuntimeError(f"_sparse_semi_structured_linear: Invalid activation {activation}")
@@ -146,10 +150,18 @@ def sparse_linear(input, weight, meta, bias=None, activation=None):
     else:
         out = torch.empty((n, ms), dtype=out_dtype, device=weight.device)
         trans_out, ld_out = 1, ms
-    rc = _ext.lib().sp24_spmm(weight.data_ptr(), _ext.dt(weight.dtype), a_mn, ld_a, e_tc.data_ptr(), ms, k, x2.data_ptr(),
-                              b_mn, ld_b, n, out.data_ptr(), _ext.dt(out_dtype), trans_out, ld_out, _ext.ptr(bias),
-                              _ACT[activation], status.data_ptr(), _ext.stream())
-    _ext.check(rc, "sp24_spmm")
+    if alpha is not None:
+        if not f8 or a_mn or b_mn:
+            raise RuntimeError("_sparse_semi_structured_linear: alpha is for float8 operands (both K-major) only")
+        rc = _ext.lib().sp24_spmm_scaled(weight.data_ptr(), _ext.dt(weight.dtype), ld_a, e_tc.data_ptr(), ms, k, x2.data_ptr(),
+                                         ld_b, n, out.data_ptr(), trans_out, ld_out, _ext.ptr(bias), _ACT[activation],
+                                         float(alpha), status.data_ptr(), _ext.stream())
+        _ext.check(rc, "sp24_spmm_scaled")
+    else:
+        rc = _ext.lib().sp24_spmm(weight.data_ptr(), _ext.dt(weight.dtype), a_mn, ld_a, e_tc.data_ptr(), ms, k, x2.data_ptr(),
+                                  b_mn, ld_b, n, out.data_ptr(), _ext.dt(out_dtype), trans_out, ld_out, _ext.ptr(bias),
+                                  _ACT[activation], status.data_ptr(), _ext.stream())
+        _ext.check(rc, "sp24_spmm")
     res = out.t() if as_view else out
     sizes[-1] = ms
     return res.reshape(sizes) if len(sizes) != 2 else res

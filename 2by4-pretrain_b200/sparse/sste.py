@@ -28,32 +28,61 @@ class SoftThreshold(autograd.Function):
         return grad_output, None
 
 
+def soft_threshold24_compress(weight: torch.Tensor, scale=None, dtype: torch.dtype = torch.float16):
+    """One pass over ``weight``: S-STE soft threshold (times ``scale`` if given) and 2:4 compression to ``dtype``.
+    Returns (packed (m, k/2), reordered metadata (m, k/16) int16), the operands of ``sparse_linear``; the
+    tensor-core order of the metadata is written by the same kernel when m is a multiple of 128.  Bit-identical to
+    ``soft_threshold24_triton(weight, scale=scale)``, a cast and ``to_sparse_semi_structured(..., mask=mask)``."""
+    from . import _ext, spmm as _spmm
+    _ext.require_cuda(weight)
+    if weight.dim() != 2:
+        raise RuntimeError(f"Expected 2-dimensional dense tensor, got {weight.dim()}-dimensional tensor")
+    if dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"soft_threshold24_compress: packed dtype must be float16 or bfloat16, got {dtype}")
+    m, k = weight.shape
+    if m % 32 or k % 64:
+        raise RuntimeError(f"soft_threshold24_compress: shape {(m, k)}: rows % 32 == 0 and columns % 64 == 0 required")
+    w = _ext.as_layout(weight.detach(), 0)
+    buf = torch.empty(m * k * 9 // 16, dtype=dtype, device=w.device)
+    packed = buf[: m * k // 2].view(m, k // 2)
+    meta = buf[m * k // 2:].view(torch.int16).view(m, k // 16)
+    e_tc = torch.empty(_spmm.tc_bytes(m, k), dtype=torch.uint8, device=w.device) if m % 128 == 0 else None
+    rc = _ext.lib().sp24_soft_threshold24_compress(w.data_ptr(), _ext.dt(w.dtype), m, k, _ext.layout_of(w)[1], 0,
+                                                   packed.data_ptr(), _ext.dt(dtype), k // 2, meta.data_ptr(),
+                                                   0 if scale is None else 1, 0.0 if scale is None else float(scale),
+                                                   _ext.ptr(e_tc), _ext.stream())
+    _ext.check(rc, "sp24_soft_threshold24_compress")
+    if e_tc is not None:
+        _spmm.register_tc_metadata(meta, e_tc)
+    return packed, meta
+
+
 class _soft_threshold_spmm_linear(autograd.Function):
-    """Forward on the sparse tensor cores; both gradients are dense GEMMs (the soft-threshold mask is
-    not transposable, so W_s^T has no 2:4 structure along its rows)."""
+    """Forward on the sparse tensor cores from a copy of the weight that one kernel soft-thresholds, scales and
+    compresses.  Both gradients are dense GEMMs by construction: the soft-threshold mask is 2:4 along the rows of W
+    only, so W_s^T has no 2:4 structure along its rows and the input gradient dY W_s has no sparse-tensor-core form;
+    the weight gradient is the straight-through dense dY^T X of the recipe (README.md:233-267 of the reference)."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, scale, dtype):
-        from .semi_structured import to_sparse_semi_structured
         from .spmm import sparse_linear
-        w_s, mask = soft_threshold24_triton(weight.detach(), scale=scale)
-        w_s = w_s.to(dtype)
-        comp = to_sparse_semi_structured(w_s, mask=mask != 0, dtype=dtype)
+        packed, meta = soft_threshold24_compress(weight, scale=scale, dtype=dtype)
         x2 = x.reshape(-1, x.shape[-1]).to(dtype)
         b = None if bias is None else bias.to(dtype)
-        y = sparse_linear(x2, comp.sparse_tensor_cutlass, comp.meta_tensor_cutlass, bias=b)
-        ctx.save_for_backward(x2, w_s)
+        y = sparse_linear(x2, packed, meta, bias=b)
+        ctx.save_for_backward(x2, packed, meta)
         ctx.shape = x.shape
         ctx.has_bias = bias is not None
         return y.view(*x.shape[:-1], -1)
 
     @staticmethod
     def backward(ctx, grad_output):
-        x2, w_s = ctx.saved_tensors
-        g = grad_output.reshape(-1, grad_output.shape[-1]).to(w_s.dtype)
+        from ._semi_structured_conversions import sparse_semi_structured_to_dense
+        x2, packed, meta = ctx.saved_tensors
+        g = grad_output.reshape(-1, grad_output.shape[-1]).to(packed.dtype)
         grad_x = grad_w = grad_b = None
         if ctx.needs_input_grad[0]:
-            grad_x = torch.mm(g, w_s).view(ctx.shape)
+            grad_x = torch.mm(g, sparse_semi_structured_to_dense(packed, meta)).view(ctx.shape)
         if ctx.needs_input_grad[1]:
             grad_w = torch.mm(g.t(), x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:

@@ -733,23 +733,41 @@ def spmm_measurements(dev):
                                   "dw_gemm": flops / t_dw_splitk_gemm / 1e12 / (2 * tensor_peak)}},
         }
         del xs, dys, pre
-    # fp8 e4m3 forward (per-tensor scales applied outside the GEMM), fp32 output
+    # fp8 e4m3 with per-tensor scales: forward, input gradient through the K-major W^T, weight gradient with the MVUE
+    # compression of dY^T to e4m3 included; fp32 outputs (scales applied by one multiply on the result)
+    from sparse import fp8, _ext as _e
     x = torch.randn(T, K, device=dev)
     w = torch.randn(N, K, device=dev) * 0.02
+    dy = (torch.randn(T, N, device=dev) * 1e-2).bfloat16()
     _, mask = sparse.mask_select(w)
-    xq = (x / (x.abs().max() / 448)).to(torch.float8_e4m3fn)
-    ws8 = sparse.to_sparse_semi_structured(w / (w.abs().max() / 448), mask=mask, dtype=torch.float8_e4m3fn)
-    for _ in range(3):
-        torch.mm(xq, ws8.t())
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(10):
-        torch.mm(xq, ws8.t())
-    e1.record()
-    torch.cuda.synchronize()
-    t8 = e0.elapsed_time(e1) * 1e-3 / 10
-    res["fp8_e4m3"] = {"fwd_ms": t8 * 1e3, "fwd_TFLOPs_dense_equiv": flops / t8 / 1e12, "note": "fp32 output (201 MB)"}
+    w8 = fp8.Fp8SparseWeight(w, mask)
+    xq, sx = fp8.quantize(x)
+    gq, sg = fp8.quantize(dy)
+    xq_t = xq.t().contiguous()
+
+    def t8(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / reps
+
+    t_f = t8(lambda: fp8.fst_fp8_forward(xq, sx, w8))
+    t_x = t8(lambda: fp8.fst_fp8_input_grad(gq, sg, w8))
+    t_w = t8(lambda: fp8.fst_fp8_weight_grad(dy, sg, xq_t, sx, seed=1))
+    pg, mg = fp8.compress_q8(dy.t(), mode=_e.PRUNE_MVUE_FAST, scale=sg, seed=1)
+    t_wc = t8(lambda: fp8.compress_q8(dy.t(), mode=_e.PRUNE_MVUE_FAST, scale=sg, seed=1))
+    res["fp8_e4m3"] = {"fwd_ms": t_f * 1e3, "dx_ms": t_x * 1e3, "dw_incl_mvue_compress_ms": t_w * 1e3,
+                       "dw_mvue_compress_only_ms": t_wc * 1e3,
+                       "fwd_TFLOPs_dense_equiv": flops / t_f / 1e12, "dx_TFLOPs_dense_equiv": flops / t_x / 1e12,
+                       "dw_TFLOPs_dense_equiv": flops / t_w / 1e12,
+                       "fwd_bwd_TFLOPs_dense_equiv": 3 * flops / (t_f + t_x + t_w) / 1e12,
+                       "note": "fp32 outputs (201 MB for fwd, 50 MB for dX), dequantisation scales applied in the GEMM epilogue"}
     from sparse.spmm import check_status
     check_status()
     return res

@@ -175,6 +175,19 @@ int sp24_soft_threshold24(const void *x, int dtype, int64_t m, int64_t k, int64_
                           int64_t ld_sparse, void *mask, int64_t ld_mask, int use_scale, float scale, void *stream);
 
 /*
+ * The forward pass of the S-STE layer in one pass over W: magnitude 2:4 mask, soft threshold of the two kept values
+ * (one rounding in dense's type), optional multiplication by the frozen scale (one more rounding in dense's type), cast
+ * to the packed 16-bit type, reordered metadata - bit for bit what sp24_soft_threshold24, a cast and sp24_prune_compress
+ * (mask mode) produce in three passes.  Replaces `weight_sparse * scale` of the reference's S-STE recipe
+ * (README.md:233-260; soft_threshold24_triton, sparse/triton_ops.py:157-227) followed by to_sparse_semi_structured
+ * (sparse/semi_structured.py:575-631) when the forward GEMM runs on the sparse tensor cores.
+ * dense: F32 / F16 / BF16, either storage order; packed_dtype F16 / BF16; e_tc optional (as in sp24_prune_compress_ex).
+ */
+int sp24_soft_threshold24_compress(const void *dense, int dense_dtype, int64_t m, int64_t k, int64_t ld_dense, int col_major,
+                                   void *packed, int packed_dtype, int64_t ld_packed, void *meta, int use_scale, float scale,
+                                   void *e_tc, void *stream);
+
+/*
  * Transposable 4x4 mask select: for every 4x4 block the first (in descending lexicographic order of
  * the row-major bit string) of the 90 patterns with two ones per row and per column that maximises
  * the float32 score (s0 + s1) + (s2 + s3), s_i = v[i][a_i] + v[i][b_i], v = |x| when use_abs.
@@ -296,6 +309,17 @@ int sp24_meta_to_tc(const void *meta, int meta_itemsize, int64_t m, int64_t k, v
 int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms, int64_t k,
               const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype, int trans_out,
               int64_t ld_out, const void *bias, int activation, int *status, void *stream);
+
+/*
+ * sp24_spmm for float8 operands with the dequantisation folded into the epilogue:
+ *   D (float32) = alpha * (A_sparse * B) [+ bias[row]] [activation],  alpha = product of the per-tensor scales.
+ * Both operands K-major (a_packed row-major (ms, k/2), b stored (n, k)), as for every 8-bit GEMM.  The reference's
+ * float8 kernels apply no scale (sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:724-809); its callers multiply the
+ * float32 result in a separate pass, which at this output size costs as much as the GEMM.
+ */
+int sp24_spmm_scaled(const void *a_packed, int dtype, int64_t ld_a, const void *e_tc, int64_t ms, int64_t k, const void *b,
+                     int64_t ld_b, int64_t n, float *out, int trans_out, int64_t ld_out, const float *bias, int activation,
+                     float alpha, int *status, void *stream);
 
 /*
  * Weight-gradient form of the sparse GEMM with fp32 accumulation into the output:

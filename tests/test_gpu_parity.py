@@ -630,3 +630,32 @@ def test_row_sums_come_out_of_the_column_major_compress(S, din, mode):
         prune_compress(x, torch.empty(64, 64, dtype=torch.float16, device=DEV),
                        torch.empty(64, 8, dtype=torch.int16, device=DEV), mode=_ext.PRUNE_MSE,
                        row_sums=torch.zeros(64, device=DEV))
+
+
+# ------------------------------------------------------------------------------------------------
+# S-STE forward in one pass: soft threshold (+ frozen scale) fused with the 2:4 compression
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("idt", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("odt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("scale", [None, 1.37])
+def test_soft_threshold_compress_matches_the_three_pass_sequence(S, idt, odt, scale):
+    """sp24_soft_threshold24_compress against the oracle (soft_threshold24, then compress_with_mask with the cast to
+    the packed type) and against the kernels it replaces, values and metadata bit for bit; ties included."""
+    from sparse.sste import soft_threshold24_compress
+    from sparse.spmm import tc_metadata
+    m, k = 256, 320
+    x = with_ties(randn((m, k), 910), 911).to(idt)
+    packed, meta = soft_threshold24_compress(x.to(DEV), scale=scale, dtype=odt)
+    ws, wm = O.soft_threshold24(x, scale=scale)
+    op, om = O.compress_with_mask(ws, wm != 0, odt)
+    assert same_bits(packed.cpu().contiguous(), op) and same_bits(meta.cpu(), om)
+    # the sequence the layer used to run: dense-shaped kernel, cast, mask-mode compression
+    s3, m3 = S.soft_threshold24_triton(x.to(DEV), scale=scale)
+    sp = S.to_sparse_semi_structured(s3.to(odt), mask=m3 != 0, dtype=odt)
+    assert same_bits(packed.cpu().contiguous(), sp.sparse_tensor_cutlass.cpu().contiguous())
+    assert same_bits(meta.cpu(), sp.meta_tensor_cutlass.cpu())
+    # and the tensor-core order written by the same pass equals the converted one
+    from sparse import spmm as _spmm
+    fused_tc = _spmm._tc_meta_cache[id(meta)][1]
+    _spmm.invalidate_meta(meta)
+    assert torch.equal(fused_tc, tc_metadata(meta, m, k))
