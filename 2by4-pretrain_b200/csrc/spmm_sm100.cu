@@ -172,7 +172,27 @@ struct SpmmParams {
     int k_splits;           // work units per tile along K (> 1 only for the accumulating fp32 output)
     int mblk_per_tile;      // 128-row blocks per tile: 2 (B staged once per 256 rows) or 1 (more, smaller tiles)
     float alpha;            // float32 outputs: D = alpha * (A * B) (+ bias); 16-bit and integer outputs ignore it
+    int bias_f32;           // bias holds float32 values instead of values of the output type
+    void *aux;              // fused MLP epilogues (CTA-pair kernel): second tensor shaped and pitched like out
+    int64_t ld_aux;
 };
+
+// Epilogue forms of the CTA-pair kernel.  PRE_GELU: aux = h = acc + bias rounded to the output type, out = gelu(h)
+// (tanh form, evaluated on the rounded h, so that out is exactly the activation of what aux holds).  DGELU: out =
+// acc * gelu'(aux): the input gradient of a layer whose input was gelu(aux), written as the gradient of aux.
+enum { EPI_PLAIN = 0, EPI_PRE_GELU = 1, EPI_DGELU = 2 };
+
+__device__ __forceinline__ float gelu_tanh(float v) {
+    const float u = 1.5957691216f * (v + 0.044715f * v * v * v);
+    return v / (1.f + __expf(-u));
+}
+// d/dv [v * sigmoid(u(v))], u = 1.5957691216 (v + 0.044715 v^3)
+__device__ __forceinline__ float gelu_tanh_grad(float v) {
+    const float v2 = v * v;
+    const float u = 1.5957691216f * (v + 0.044715f * v * v2);
+    const float sg = 1.f / (1.f + __expf(-u));
+    return sg + v * sg * (1.f - sg) * (1.5957691216f * (1.f + 0.134145f * v2));
+}
 
 template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
 template <> __device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
@@ -754,7 +774,7 @@ __device__ __forceinline__ void mma_sp_pair(uint32_t d_tmem, uint64_t adesc, uin
         : "memory");
 }
 
-template <bool A_MN, typename OutT>
+template <bool A_MN, typename OutT, int EPI>
 __global__ void __launch_bounds__(320, 1)
 spmm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_e, SpmmParams P) {
@@ -906,7 +926,7 @@ spmm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t held[NREG];
             if (run) {
                 float bias = 0.f;
-                if (P.bias) bias = from_out<OutT>(static_cast<const OutT *>(P.bias)[mrow]);
+                if (P.bias) bias = P.bias_f32 ? static_cast<const float *>(P.bias)[mrow] : from_out<OutT>(static_cast<const OutT *>(P.bias)[mrow]);
                 const uint32_t acc = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + half * HC;
 #pragma unroll
                 for (int c = 0; c < HC / 32; ++c) {
@@ -916,8 +936,13 @@ spmm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         Vec<OutT, 2> o;
-                        o.v[0] = to_out<OutT>(__uint_as_float(v[2 * i]) + bias);
-                        o.v[1] = to_out<OutT>(__uint_as_float(v[2 * i + 1]) + bias);
+                        if constexpr (EPI == EPI_DGELU) {   // no bias; the factor gelu'(aux) is applied at store time
+                            o.v[0] = to_out<OutT>(__uint_as_float(v[2 * i]));
+                            o.v[1] = to_out<OutT>(__uint_as_float(v[2 * i + 1]));
+                        } else {
+                            o.v[0] = to_out<OutT>(__uint_as_float(v[2 * i]) + bias);
+                            o.v[1] = to_out<OutT>(__uint_as_float(v[2 * i + 1]) + bias);
+                        }
                         held[c * 16 + i] = *reinterpret_cast<const uint32_t *>(&o);
                     }
                 }
@@ -928,22 +953,32 @@ spmm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 1);
             if (run) {
                 uint16_t *dst = reinterpret_cast<uint16_t *>(out) + tok0 * P.ld_out + mrow;
-                if (tok0 + HC <= P.n) {
-#pragma unroll
-                    for (int c2 = 0; c2 < NREG; ++c2) {
-                        dst[0] = (uint16_t)(held[c2] & 0xFFFFu);
-                        dst[P.ld_out] = (uint16_t)(held[c2] >> 16);
-                        dst += 2 * P.ld_out;
-                        asm volatile("" : "+l"(dst));   // one running pointer, not 96 precomputed addresses
+                uint16_t *aux = reinterpret_cast<uint16_t *>(P.aux) + tok0 * P.ld_aux + mrow;
+                // one 16-bit value: what goes to out; PRE_GELU also stores the value itself to aux first
+                auto put = [&](uint16_t h_bits) {
+                    if constexpr (EPI == EPI_PLAIN) {
+                        dst[0] = h_bits;
+                    } else if constexpr (EPI == EPI_PRE_GELU) {
+                        aux[0] = h_bits;
+                        const OutT g = to_out<OutT>(gelu_tanh(from_out<OutT>(*reinterpret_cast<const OutT *>(&h_bits))));
+                        dst[0] = *reinterpret_cast<const uint16_t *>(&g);
+                    } else {
+                        const uint16_t a_bits = aux[0];
+                        const OutT g = to_out<OutT>(from_out<OutT>(*reinterpret_cast<const OutT *>(&h_bits)) *
+                                                    gelu_tanh_grad(from_out<OutT>(*reinterpret_cast<const OutT *>(&a_bits))));
+                        dst[0] = *reinterpret_cast<const uint16_t *>(&g);
                     }
-                } else {
+                };
+                const bool full = tok0 + HC <= P.n;
 #pragma unroll
-                    for (int c2 = 0; c2 < NREG; ++c2) {
-                        if (tok0 + 2 * c2 < P.n) dst[0] = (uint16_t)(held[c2] & 0xFFFFu);
-                        if (tok0 + 2 * c2 + 1 < P.n) dst[P.ld_out] = (uint16_t)(held[c2] >> 16);
-                        dst += 2 * P.ld_out;
-                        asm volatile("" : "+l"(dst));
-                    }
+                for (int c2 = 0; c2 < NREG; ++c2) {
+                    if (full || tok0 + 2 * c2 < P.n) put((uint16_t)(held[c2] & 0xFFFFu));
+                    dst += P.ld_out;
+                    aux += P.ld_aux;
+                    if (full || tok0 + 2 * c2 + 1 < P.n) put((uint16_t)(held[c2] >> 16));
+                    dst += P.ld_out;
+                    aux += P.ld_aux;
+                    asm volatile("" : "+l"(dst), "+l"(aux));   // running pointers, not 96 precomputed addresses
                 }
             }
             if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 3);
@@ -1285,9 +1320,9 @@ int make_map_e(CUtensorMap *map, const void *e_tc, int64_t n_atoms) {
     return r == CUDA_SUCCESS ? SP24_OK : SP24_ERR_CUDA;
 }
 
-template <bool A_MN, typename OutT>
+template <bool A_MN, typename OutT, int EPI = EPI_PLAIN>
 int launch_spmm_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &me, SpmmParams P, cudaStream_t st) {
-    auto kern = spmm_pair_kernel<A_MN, OutT>;
+    auto kern = spmm_pair_kernel<A_MN, OutT, EPI>;
     static bool attr_set[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1437,7 +1472,8 @@ static int validate_spmm_args(const void *a_packed, int dtype, int a_mn_major, i
 
 static int spmm_impl(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms,
                      int64_t k, const void *b, int b_mn_major, int64_t ld_b, int64_t n, void *out, int out_dtype,
-                     int trans_out, int64_t ld_out, const void *bias, int activation, float alpha, int *status, void *stream) {
+                     int trans_out, int64_t ld_out, const void *bias, int activation, float alpha, int *status, void *stream,
+                     int bias_f32 = 0, int epi = EPI_PLAIN, void *aux = nullptr, int64_t ld_aux = 0) {
     if (!e_tc) return SP24_ERR_ARG;
     if (int rc = validate_spmm_args(a_packed, dtype, a_mn_major, ld_a, ms, k, b, b_mn_major, ld_b, n, out, out_dtype,
                                     trans_out, ld_out, bias, activation))
@@ -1459,6 +1495,9 @@ static int spmm_impl(const void *a_packed, int dtype, int a_mn_major, int64_t ld
     P.trace = nullptr;
     P.k_splits = 1;
     P.alpha = alpha;
+    P.bias_f32 = bias_f32;
+    P.aux = aux;
+    P.ld_aux = ld_aux;
 #ifdef SP24_TRACE_BUILD
     if (const char *env = getenv("SP24_SPMM_TRACE_PTR")) P.trace = reinterpret_cast<unsigned long long *>(strtoull(env, nullptr, 0));
 #endif
@@ -1471,19 +1510,34 @@ static int spmm_impl(const void *a_packed, int dtype, int a_mn_major, int64_t ld
               ((uint32_t)(b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BM >> 4) << 24);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // CTA-pair kernel: 16-bit types, token-major B and output, whole 256-row blocks, no activation
-    bool pair_form = !f8 && !b_mn_major && trans_out && ms % 256 == 0 && activation == 0 && n >= 1024;
-    pair_form = pair_form && pair_kernels_enabled();
+    const bool pair_ok = !f8 && !b_mn_major && trans_out && ms % 256 == 0 && activation == 0;
+    bool pair_form = pair_ok && n >= 1024 && pair_kernels_enabled();
+    if (epi != EPI_PLAIN) {
+        // the fused MLP epilogues exist in the pair kernel only
+        if (!pair_ok || !aux || ld_aux < ms || (ld_aux * 2) % 16 || !aligned16(aux)) return SP24_ERR_ARG;
+        pair_form = true;
+    } else if (bias_f32) {
+        if (!pair_ok) return SP24_ERR_ARG;          // a float32 bias is read by the pair kernel only
+        pair_form = true;
+    }
     if (pair_form) {
         CUtensorMap map_b, map_e;
         rc = make_map(&map_b, b, dtype, n, k, ld_b, 64, two::BN2 / 2);
         if (rc) return rc;
         rc = make_map_e(&map_e, e_tc, (ms / 128) * P.k_atoms);
         if (rc) return rc;
-        if (out_dtype == SP24_F16)
-            return a_mn_major ? launch_spmm_pair<true, __half>(map_a, map_b, map_e, P, st)
-                              : launch_spmm_pair<false, __half>(map_a, map_b, map_e, P, st);
-        return a_mn_major ? launch_spmm_pair<true, __nv_bfloat16>(map_a, map_b, map_e, P, st)
-                          : launch_spmm_pair<false, __nv_bfloat16>(map_a, map_b, map_e, P, st);
+#define SP24_PAIR(EPI_) \
+        do { \
+            if (out_dtype == SP24_F16) \
+                return a_mn_major ? launch_spmm_pair<true, __half, EPI_>(map_a, map_b, map_e, P, st) \
+                                  : launch_spmm_pair<false, __half, EPI_>(map_a, map_b, map_e, P, st); \
+            return a_mn_major ? launch_spmm_pair<true, __nv_bfloat16, EPI_>(map_a, map_b, map_e, P, st) \
+                              : launch_spmm_pair<false, __nv_bfloat16, EPI_>(map_a, map_b, map_e, P, st); \
+        } while (0)
+        if (epi == EPI_PRE_GELU) SP24_PAIR(EPI_PRE_GELU);
+        if (epi == EPI_DGELU) SP24_PAIR(EPI_DGELU);
+        SP24_PAIR(EPI_PLAIN);
+#undef SP24_PAIR
     }
     int bn = 128, mpt = 2;
     pick_tile(ms, n, sm_count_cached(), bn, mpt);
@@ -1518,6 +1572,17 @@ extern "C" int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_
                          int trans_out, int64_t ld_out, const void *bias, int activation, int *status, void *stream) {
     return spmm_impl(a_packed, dtype, a_mn_major, ld_a, e_tc, ms, k, b, b_mn_major, ld_b, n, out, out_dtype, trans_out, ld_out,
                      bias, activation, 1.f, status, stream);
+}
+
+// The 16-bit GEMM of a transformer MLP with its neighbours fused into the epilogue (CTA-pair kernel): see the header.
+extern "C" int sp24_spmm_mlp(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms,
+                             int64_t k, const void *b, int64_t ld_b, int64_t n, void *out, int64_t ld_out, const void *bias,
+                             int bias_is_f32, int epilogue, void *aux, int64_t ld_aux, int *status, void *stream) {
+    if (dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
+    if (epilogue < 0 || epilogue > 2) return SP24_ERR_ARG;
+    if (epilogue == EPI_DGELU && bias) return SP24_ERR_ARG;
+    return spmm_impl(a_packed, dtype, a_mn_major, ld_a, e_tc, ms, k, b, 0, ld_b, n, out, dtype, 1, ld_out, bias, 0, 1.f, status,
+                     stream, bias_is_f32 ? 1 : 0, epilogue, aux, ld_aux);
 }
 
 // The float8 GEMM with the dequantisation folded into the epilogue: D = alpha * (A_sparse * B) [+ bias] [activation],

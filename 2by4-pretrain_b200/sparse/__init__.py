@@ -10,7 +10,7 @@ from .decay import masked_add_, adamw_masked_decay_
 from .transposable_semi_structured import TransposableSparse, select_and_compress, select_and_compress_many
 from .semi_structured import to_sparse_semi_structured, SparseSemiStructuredTensor
 from .sparse_ops import (MyLinear, SparseLinear, SparseLinearTranspose, sparse_linear_transpose, sparse_state,
-                         load_sparse_state, refresh_sparse_layers)
+                         load_sparse_state, refresh_sparse_layers, fst_mlp)
 from .sste import SoftThreshold, SoftThresholdLinear
 from . import fp8  # noqa: F401  (float8 form of the FST layer: sparse.fp8.sparse_linear_transpose_fp8)
 
@@ -34,6 +34,7 @@ __all__ = [
     'select_and_compress',
     'select_and_compress_many',
     'refresh_sparse_layers',
+    'fst_mlp',
     'to_sparse_semi_structured',
     'SparseSemiStructuredTensor',
     'SoftThreshold',

@@ -18,7 +18,7 @@ from ._semi_structured_conversions import prune_compress
 from .semi_structured import SparseSemiStructuredTensor, to_sparse_semi_structured
 from .transposable_semi_structured import TransposableSparse, select_and_compress
 from .triton_ops import MVUE24_approx_triton
-from .spmm import sparse_linear as _spmm, sparse_mm_accumulate_ as _spmm_acc
+from .spmm import sparse_linear as _spmm, sparse_mm_accumulate_ as _spmm_acc, sparse_linear_mlp as _spmm_mlp, mlp_fusable
 
 
 def _dense_linear(name, dx_weight, doc):
@@ -117,6 +117,43 @@ def _mvue_compress_t(g, row_sums):
     return packed, meta
 
 
+def _fst_weight_grads(g, x, weight, bias, into_grad, need_w, need_b):
+    """dW = MVUE24(g^T) x and db = g.sum(0) of one FST layer; ``g`` (tokens, out_features) and ``x`` (tokens,
+    in_features) are 16-bit.  With ``into_grad`` (and an fp32 ``weight.grad`` already allocated) the GEMM adds dW
+    straight into ``weight.grad`` and the compression pass adds the column sums of ``g`` into ``bias.grad``; autograd
+    then receives None for both.  Returns (grad_weight, grad_bias)."""
+    grad_weight = grad_bias = None
+    bias_done = False
+    if need_w:
+        fp32_grad = weight.dtype == torch.float32 and x.shape[1] % 8 == 0
+        target = weight if (into_grad and fp32_grad) else None
+        into = target is not None and target.grad is not None and target.grad.dtype == torch.float32 \
+            and target.grad.is_contiguous()
+        bias_grad = None
+        if into and bias is not None and need_b and g.dtype in (torch.float16, torch.bfloat16):
+            bg = bias.grad
+            if bg is not None and bg.dtype == torch.float32 and bg.is_contiguous():
+                bias_grad = bg
+        if bias_grad is not None:
+            # the pass that compresses dY^T also adds its row sums (= grad_output.sum(0)) to bias.grad
+            gp, gm = _mvue_compress_t(g, bias_grad)
+            bias_done = True
+        else:
+            gs = to_sparse_semi_structured(g.t(), MVUE24=True, dtype=g.dtype)
+            gp, gm = gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass
+        if into:
+            _spmm_acc(target.grad, gp, gm, x)
+        elif fp32_grad:
+            # split-K GEMM with fp32 accumulation: the gradient arrives in the dtype of the master weight
+            grad_weight = torch.zeros((g.shape[1], x.shape[1]), dtype=torch.float32, device=g.device)
+            _spmm_acc(grad_weight, gp, gm, x)
+        else:
+            grad_weight = _spmm(x.t(), gp, gm).t()
+    if bias is not None and need_b and not bias_done:
+        grad_bias = g.sum(0)
+    return grad_weight, grad_bias
+
+
 class _fst_linear(autograd.Function):
     """What ``sparse_linear_transpose`` computes, on the raw compressed buffers: no tensor-subclass objects,
     no cast of the (unused) fp32 weight.  ``weight`` only routes the gradient.  With ``into_grad`` the weight
@@ -128,20 +165,20 @@ class _fst_linear(autograd.Function):
         x = input.reshape(-1, input.shape[-1])
         if x.dtype != pw.dtype:
             x = x.to(pw.dtype)
-        b = None if bias is None else (bias if bias.dtype == pw.dtype else bias.to(pw.dtype))
         ctx.save_for_backward(x, pt, mt)
         ctx.shape = input.shape
-        ctx.has_bias = bias is not None
-        ctx.fp32_grad = weight.dtype == torch.float32 and x.shape[1] % 8 == 0
-        ctx.grad_target = weight if (into_grad and ctx.fp32_grad) else None
-        ctx.bias_target = bias if (ctx.grad_target is not None and bias is not None) else None
-        output = _spmm(x, pw, mw, bias=b)     # bias added in the GEMM epilogue
+        ctx.weight, ctx.bias, ctx.into_grad = weight, bias, into_grad
+        if bias is not None and bias.dtype == torch.float32 and mlp_fusable(pw, x):
+            output = _spmm_mlp(x, pw, mw, bias=bias)      # float32 bias read by the epilogue: no cast launch
+        else:
+            b = None if bias is None else (bias if bias.dtype == pw.dtype else bias.to(pw.dtype))
+            output = _spmm(x, pw, mw, bias=b)             # bias added in the GEMM epilogue
         return output.view(*input.shape[:-1], -1)
 
     @staticmethod
     def backward(ctx, grad_output):
         x, pt, mt = ctx.saved_tensors
-        grad_input = grad_weight = grad_bias = None
+        grad_input = None
         if grad_output.dim() == 3 and grad_output.stride() == (0, 0, 0):
             grad_output = torch.ones_like(grad_output)
         g = grad_output.reshape(-1, grad_output.shape[-1])
@@ -149,34 +186,64 @@ class _fst_linear(autograd.Function):
             g = g.to(pt.dtype)
         if ctx.needs_input_grad[0]:
             grad_input = _spmm(g, pt, mt).view(ctx.shape)
-        bias_done = False
-        if ctx.needs_input_grad[1]:
-            target = ctx.grad_target
-            into = target is not None and target.grad is not None and target.grad.dtype == torch.float32 \
-                and target.grad.is_contiguous()
-            bias_grad = None
-            if into and ctx.has_bias and ctx.needs_input_grad[6] and g.dtype in (torch.float16, torch.bfloat16):
-                bg = ctx.bias_target.grad
-                if bg is not None and bg.dtype == torch.float32 and bg.is_contiguous():
-                    bias_grad = bg
-            if bias_grad is not None:
-                # the pass that compresses dY^T also adds its row sums (= grad_output.sum(0)) to bias.grad
-                gp, gm = _mvue_compress_t(g, bias_grad)
-                bias_done = True
-            else:
-                gs = to_sparse_semi_structured(g.t(), MVUE24=True, dtype=g.dtype)
-                gp, gm = gs.sparse_tensor_cutlass, gs.meta_tensor_cutlass
-            if into:
-                _spmm_acc(target.grad, gp, gm, x)
-            elif ctx.fp32_grad:
-                # split-K GEMM with fp32 accumulation: the gradient arrives in the dtype of the master weight
-                grad_weight = torch.zeros((g.shape[1], x.shape[1]), dtype=torch.float32, device=g.device)
-                _spmm_acc(grad_weight, gp, gm, x)
-            else:
-                grad_weight = _spmm(x.t(), gp, gm).t()
-        if ctx.has_bias and ctx.needs_input_grad[6] and not bias_done:
-            grad_bias = g.sum(0)
+        grad_weight, grad_bias = _fst_weight_grads(g, x, ctx.weight, ctx.bias, ctx.into_grad, ctx.needs_input_grad[1],
+                                                   ctx.needs_input_grad[6])
         return grad_input, grad_weight, None, None, None, None, grad_bias, None
+
+
+class _fst_mlp(autograd.Function):
+    """Transformer MLP, proj(gelu(fc(x))), on two FST layers with the element-wise work folded into the GEMM epilogues:
+    the up-projection writes both the pre-activation h and gelu(h); in the backward pass the down-projection's input
+    gradient is multiplied by gelu'(h) in its epilogue, so the gradient of h is written directly.  Saves four passes
+    over the (tokens, 4 d) activations per layer and step (GELU forward, its backward, and the tensors between them).
+    ``fc`` / ``proj`` are (weight, bias, (pw, mw, pt, mt), into_grad)."""
+
+    @staticmethod
+    def forward(ctx, input, w_fc, b_fc, w_proj, b_proj, comp_fc, comp_proj, into_grad):
+        pw1, mw1, pt1, mt1 = comp_fc
+        pw2, mw2, pt2, mt2 = comp_proj
+        x = input.reshape(-1, input.shape[-1])
+        if x.dtype != pw1.dtype:
+            x = x.to(pw1.dtype)
+        act, pre = _spmm_mlp(x, pw1, mw1, bias=b_fc, epilogue="gelu")
+        out = _spmm_mlp(act, pw2, mw2, bias=b_proj)
+        ctx.save_for_backward(x, act, pre, pt1, mt1, pt2, mt2)
+        ctx.shape = input.shape
+        ctx.params = (w_fc, b_fc, w_proj, b_proj, into_grad)
+        return out.view(*input.shape[:-1], -1)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, act, pre, pt1, mt1, pt2, mt2 = ctx.saved_tensors
+        w_fc, b_fc, w_proj, b_proj, into_grad = ctx.params
+        g = grad_output.reshape(-1, grad_output.shape[-1])
+        if g.dtype != pt2.dtype:
+            g = g.to(pt2.dtype)
+        g = g.contiguous()
+        need = ctx.needs_input_grad
+        d_pre = _spmm_mlp(g, pt2, mt2, epilogue="dgelu", aux=pre)           # gradient of fc's output, (tokens, 4 d)
+        gw2, gb2 = _fst_weight_grads(g, act, w_proj, b_proj, into_grad, need[3], need[4])
+        grad_input = _spmm(d_pre, pt1, mt1).view(ctx.shape) if need[0] else None
+        gw1, gb1 = _fst_weight_grads(d_pre, x, w_fc, b_fc, into_grad, need[1], need[2])
+        return grad_input, gw1, gb1, gw2, gb2, None, None, None
+
+
+def fst_mlp(x, fc, proj):
+    """proj(gelu(fc(x), approximate="tanh")) for two ``SparseLinearTranspose`` layers.  Runs the fused epilogues when
+    both layers are in sparse mode, their compressed copies are 16-bit and their shapes allow it; otherwise exactly
+    the three separate calls.  Counters of both layers advance as in their own ``forward``."""
+    w1, w2 = fc.weight, proj.weight
+    ok = w1.mode == 'sparse' and w2.mode == 'sparse' and w1.is_cuda and w1.shape[0] % 256 == 0 and w2.shape[0] % 256 == 0 \
+        and fc.bias is not None and proj.bias is not None
+    if not ok:
+        return proj(F.gelu(fc(x), approximate="tanh"))
+    fc._ensure_compressed()
+    proj._ensure_compressed()
+    y = _fst_mlp.apply(x, w1, fc.bias, w2, proj.bias, w1.compressed, w2.compressed,
+                       fc.accumulate_into_grad and proj.accumulate_into_grad)
+    fc._advance()
+    proj._advance()
+    return y
 
 
 class SparseLinearTranspose(nn.Linear):
@@ -242,28 +309,37 @@ class SparseLinearTranspose(nn.Linear):
             None, original_shape=torch.Size([in_f, out_f]), sparse_tensor_cutlass=pt, meta_tensor_cutlass=mt,
             dtype=dtype)
 
-    def forward(self, x):
+    def _ensure_compressed(self):
+        """Rebuild the mask and / or the compressed copies when this forward pass is due to (first micro-step after an
+        optimizer step; every ``freq`` optimizer steps with a new mask)."""
         w = self.weight
-        if w.mode == 'dense':
-            x = F.linear(x, w, self.bias)
-        else:
-            if w.mask.device != w.device:
-                w.mask = w.mask.to(device=w.device)
-            if w.cnt == 0:
-                if getattr(w, 'refreshed', False):
-                    w.refreshed = False      # refresh_sparse_layers has just rebuilt the copies of this step
-                else:
-                    self._refresh(reselect=(w.counter % w.freq == 0))
-            elif w.compressed is None:   # state restored in the middle of an accumulation window
-                self._refresh(reselect=False)
-            pw, mw, pt, mt = w.compressed
-            x = _fst_linear.apply(x, w, pw, mw, pt, mt, self.bias, self.accumulate_into_grad)
+        if w.mask.device != w.device:
+            w.mask = w.mask.to(device=w.device)
+        if w.cnt == 0:
+            if getattr(w, 'refreshed', False):
+                w.refreshed = False      # refresh_sparse_layers has just rebuilt the copies of this step
+            else:
+                self._refresh(reselect=(w.counter % w.freq == 0))
+        elif w.compressed is None:   # state restored in the middle of an accumulation window
+            self._refresh(reselect=False)
 
+    def _advance(self):
+        w = self.weight
         if self.training:
             if w.cnt == 0:
                 w.counter += 1
             w.step += 1
             w.cnt += 1
+
+    def forward(self, x):
+        w = self.weight
+        if w.mode == 'dense':
+            x = F.linear(x, w, self.bias)
+        else:
+            self._ensure_compressed()
+            pw, mw, pt, mt = w.compressed
+            x = _fst_linear.apply(x, w, pw, mw, pt, mt, self.bias, self.accumulate_into_grad)
+        self._advance()
         return x
 
 

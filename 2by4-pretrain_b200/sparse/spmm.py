@@ -24,6 +24,8 @@ _ext.register_signature("sp24_spmm_noalloc", [_vp, _i32, _i32, _i64, _vp, _i64, 
 
 _ext.register_signature("sp24_spmm_scaled", [_vp, _i32, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i32, _i64, _vp, _i32,
                                              ctypes.c_float, _vp, _vp])
+_ext.register_signature("sp24_spmm_mlp", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _i32, _i32, _vp,
+                                          _i64, _vp, _vp])
 _ext.register_signature("sp24_selftest_bounded_wait", [_vp, _i32, _vp])
 _ext.register_signature("sp24_spmm_accumulate_f32", [_vp, _i32, _i32, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64,
                                                      _i32, _vp, _vp])
@@ -165,6 +167,62 @@ def sparse_linear(input, weight, meta, bias=None, activation=None, alpha=None):
     res = out.t() if as_view else out
     sizes[-1] = ms
     return res.reshape(sizes) if len(sizes) != 2 else res
+
+
+_EPILOGUE = {"none": 0, "gelu": 1, "dgelu": 2}
+
+
+def mlp_fusable(weight: torch.Tensor, input: torch.Tensor) -> bool:
+    """Whether ``sparse_linear_mlp`` can take this GEMM: 16-bit operands, whole 256-row blocks of the sparse operand."""
+    return weight.dtype in (torch.float16, torch.bfloat16) and weight.shape[0] % 256 == 0 and input.dtype == weight.dtype
+
+
+def sparse_linear_mlp(input, weight, meta, bias=None, epilogue="none", aux=None):
+    """``sparse_linear`` with the neighbours of a transformer MLP's GEMMs fused into the epilogue (``sp24_spmm_mlp``).
+
+    ``epilogue``: "none"  -> returns input @ W_s^T + bias; ``bias`` may be float32 (no cast launch);
+                  "gelu"  -> returns (gelu(h), h) with h = input @ W_s^T + bias rounded to the operand dtype (tanh
+                             form of GELU, evaluated on the rounded h);
+                  "dgelu" -> returns (input @ W_s^T) * gelu'(aux), ``aux`` shaped like the result: the input
+                             gradient of a layer fed with gelu(aux), as the gradient with respect to aux.
+    ``input``: (tokens, k) contiguous, 16-bit; ``weight`` / ``meta``: the compressed (ms, k/2) operand, ms % 256 == 0."""
+    _ext.require_cuda(input, weight, meta, bias, aux)
+    if epilogue not in _EPILOGUE:
+        raise RuntimeError(f"sparse_linear_mlp: unknown epilogue {epilogue}")
+    if not mlp_fusable(weight, input):
+        raise RuntimeError("sparse_linear_mlp: 16-bit operands of one dtype and sparse rows % 256 == 0 required")
+    ms, kh = weight.shape
+    k = 2 * kh
+    x2 = input.reshape(-1, k)
+    if x2.stride(1) != 1 or x2.data_ptr() % 16 or (x2.stride(0) * x2.element_size()) % 16:
+        x2 = x2.contiguous()
+    n = x2.shape[0]
+    lay_a = _ext.layout_of(weight)
+    if lay_a is None:
+        raise RuntimeError("sparse_linear_mlp: invalid strides for the packed values")
+    a_mn, ld_a = lay_a
+    bias_f32 = 0
+    if bias is not None:
+        if bias.dim() != 1 or bias.shape[0] != ms or epilogue == "dgelu":
+            raise RuntimeError("sparse_linear_mlp: bias must have one value per output feature (none with dgelu)")
+        if bias.dtype == torch.float32:
+            bias_f32 = 1
+        elif bias.dtype != weight.dtype:
+            raise RuntimeError(f"sparse_linear_mlp: bias must be float32 or {weight.dtype}, got {bias.dtype}")
+        bias = bias.contiguous()
+    out = torch.empty((n, ms), dtype=weight.dtype, device=weight.device)
+    if epilogue == "gelu":
+        aux = torch.empty((n, ms), dtype=weight.dtype, device=weight.device)
+    elif epilogue == "dgelu":
+        if aux is None or tuple(aux.shape) != (n, ms) or aux.dtype != weight.dtype or not aux.is_contiguous():
+            raise RuntimeError("sparse_linear_mlp: dgelu needs a contiguous aux of the result's shape and dtype")
+    e_tc = tc_metadata(meta, ms, k)
+    status = _status_word(weight.device)
+    rc = _ext.lib().sp24_spmm_mlp(weight.data_ptr(), _ext.dt(weight.dtype), a_mn, ld_a, e_tc.data_ptr(), ms, k, x2.data_ptr(),
+                                  x2.stride(0), n, out.data_ptr(), ms, _ext.ptr(bias), bias_f32, _EPILOGUE[epilogue],
+                                  _ext.ptr(aux), ms, status.data_ptr(), _ext.stream())
+    _ext.check(rc, "sp24_spmm_mlp")
+    return (out, aux) if epilogue == "gelu" else out
 
 
 def sparse_mm_accumulate_(out: torch.Tensor, weight: torch.Tensor, meta: torch.Tensor, dense: torch.Tensor,

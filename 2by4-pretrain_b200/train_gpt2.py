@@ -36,6 +36,8 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
 class Block(nn.Module):
+    fused_mlp = True     # fc + GELU + proj through sparse.fst_mlp (GELU and its gradient in the GEMM epilogues)
+
     def __init__(self, d, heads, linear):
         super().__init__()
         self.heads = heads
@@ -52,7 +54,11 @@ class Block(nn.Module):
         q, k, v = (z.view(b, t, self.heads, d // self.heads).transpose(1, 2) for z in (q, k, v))
         y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = x + self.attn_proj(y.transpose(1, 2).reshape(b, t, d))
-        x = x + self.proj(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+        if self.fused_mlp:
+            import sparse
+            x = x + sparse.fst_mlp(self.ln2(x), self.fc, self.proj)
+        else:
+            x = x + self.proj(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
         return x
 
 

@@ -311,6 +311,24 @@ int sp24_spmm(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, con
               int64_t ld_out, const void *bias, int activation, int *status, void *stream);
 
 /*
+ * The GEMMs of a transformer MLP block with their element-wise neighbours fused into the epilogue.  16-bit operands,
+ * b stored (n, k) (tokens x features), out (n, ms) with pitch ld_out (what sp24_spmm calls trans_out = 1), ms % 256 == 0;
+ * runs on the CTA-pair kernel.  bias: ms values, of the output type or (bias_is_f32 != 0) float32, or NULL.
+ *   epilogue 0  out = acc + bias                                  (a float32 bias saves the cast launch per call)
+ *   epilogue 1  aux = h = acc + bias rounded to the output type;  out = gelu(h), tanh form, evaluated on the rounded h:
+ *               the up-projection of the MLP with its activation, keeping the pre-activation for the backward pass
+ *   epilogue 2  out = acc * gelu'(aux) (no bias): the input gradient of the down-projection, written as the gradient
+ *               of the up-projection's pre-activation aux
+ * aux is shaped and aligned like out, pitch ld_aux.  The reference fuses relu / silu into its GEMM epilogue
+ * (sparse/csrc/mySparseSemiStructuredLinear_cuda.cu:385-471) and has a fused tanh-GELU forward / backward pair as
+ * separate Triton kernels (sparse/GELUglu.py:7-243); its training layer runs bias, activation and their gradients as
+ * separate passes (README.md:169-200).
+ */
+int sp24_spmm_mlp(const void *a_packed, int dtype, int a_mn_major, int64_t ld_a, const void *e_tc, int64_t ms, int64_t k,
+                  const void *b, int64_t ld_b, int64_t n, void *out, int64_t ld_out, const void *bias, int bias_is_f32,
+                  int epilogue, void *aux, int64_t ld_aux, int *status, void *stream);
+
+/*
  * sp24_spmm for float8 operands with the dequantisation folded into the epilogue:
  *   D (float32) = alpha * (A_sparse * B) [+ bias[row]] [activation],  alpha = product of the per-tensor scales.
  * Both operands K-major (a_packed row-major (ms, k/2), b stored (n, k)), as for every 8-bit GEMM.  The reference's

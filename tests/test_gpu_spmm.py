@@ -748,3 +748,79 @@ def test_model_wide_refresh_equals_the_per_layer_refresh(S):
         assert torch.equal(ga, gb)
     assert outs[0][2] == outs[1][2]
     assert torch.equal(a[0].weight.mask, b[0].weight.mask) and torch.equal(a[2].weight.mask, b[2].weight.mask)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_mlp_epilogues_of_the_pair_kernel(S, dtype):
+    """sp24_spmm_mlp: float32 bias, GELU with the pre-activation kept, and the dGELU factor in the input-gradient
+    GEMM, against fp32 formulas (F.gelu(approximate="tanh") and autograd's derivative).  Tolerances as for the
+    plain GEMMs: 1e-3 (fp16) / 8e-3 (bf16) of the largest magnitude."""
+    from sparse.spmm import sparse_linear_mlp, sparse_linear, check_status
+    tol = TOL[dtype]
+    g = torch.Generator().manual_seed(31)
+    T, K, N = 1100, 256, 512                       # ragged token count, ms % 256 == 0
+    w = (torch.randn(N, K, generator=g) * 0.1).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)          # float32 bias
+    x = torch.randn(T, K, generator=g).to(dtype).to(DEV)
+    mask, (pw, mw), (pt, mt) = S.select_and_compress(w, dtype=dtype)
+    wd = torch.where(mask, w.to(dtype).float(), torch.zeros((), device=DEV))
+    h_ref = x.float() @ wd.t() + b
+    # float32 bias, no activation: equals the plain GEMM with the same bias, up to the bias rounding
+    y = sparse_linear_mlp(x, pw, mw, bias=b)
+    assert float((y.float() - h_ref).abs().max() / h_ref.abs().max()) <= tol
+    # GELU epilogue: aux holds the rounded pre-activation, out its activation
+    act, pre = sparse_linear_mlp(x, pw, mw, bias=b, epilogue="gelu")
+    assert pre.dtype == dtype and act.shape == pre.shape == (T, N)
+    assert float((pre.float() - h_ref).abs().max() / h_ref.abs().max()) <= tol
+    a_ref = F.gelu(pre.float(), approximate="tanh")
+    assert float((act.float() - a_ref).abs().max() / a_ref.abs().max()) <= tol
+    # dGELU epilogue: dA = G W (through the compressed W^T), times gelu'(pre)
+    gr = (torch.randn(T, N, generator=g) * 0.1).to(dtype).to(DEV)
+    mask2, (pw2, mw2), (pt2, mt2) = S.select_and_compress((torch.randn(K, N, generator=g) * 0.1).to(DEV), dtype=dtype)
+    gout = torch.randn(T, K, generator=g).to(dtype).to(DEV)
+    d_pre = sparse_linear_mlp(gout, pt2, mt2, epilogue="dgelu", aux=pre)              # (T, N)
+    dA = sparse_linear(gout, pt2, mt2).float()                                          # the unfused input gradient
+    p32 = pre.float().requires_grad_(True)
+    F.gelu(p32, approximate="tanh").backward(dA)
+    assert float((d_pre.float() - p32.grad).abs().max() / p32.grad.abs().max()) <= 2 * tol
+    check_status()
+    with pytest.raises(RuntimeError):
+        sparse_linear_mlp(gout, pt2, mt2, epilogue="dgelu")                            # aux missing
+    del gr
+
+
+def test_fused_mlp_equals_the_three_separate_layers(S):
+    """sparse.fst_mlp (GELU and its gradient in the GEMM epilogues) against proj(gelu(fc(x))) on the same two layers:
+    same output and input gradient within the bf16 tolerance of the chain, weight gradients equal up to the MVUE draws
+    that the slightly different roundings can flip."""
+    torch.manual_seed(13)
+    fc = S.SparseLinearTranspose(256, 1024).to(DEV)
+    proj = S.SparseLinearTranspose(1024, 256).to(DEV)
+    with torch.no_grad():
+        fc.bias.normal_(0, 0.5)
+        proj.bias.normal_(0, 0.5)
+    x0 = torch.randn(4, 320, 256, device=DEV)
+    dy = torch.randn(4, 320, 256, device=DEV) * 0.1
+    outs = {}
+    for fused in (False, True):
+        for lyr in (fc, proj):
+            lyr.weight.grad = lyr.bias.grad = None
+            lyr.weight.cnt, lyr.weight.counter = 0, 0
+        random.seed(99)
+        x = x0.clone().requires_grad_(True)
+        with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+            y = S.fst_mlp(x, fc, proj) if fused else proj(F.gelu(fc(x), approximate="tanh"))
+        y.backward(dy.to(y.dtype))
+        outs[fused] = (y.float().detach(), x.grad.clone(), fc.weight.grad.clone(), proj.weight.grad.clone(),
+                       fc.bias.grad.clone(), proj.bias.grad.clone())
+    rel = lambda a, b: float((a - b).norm() / b.norm())
+    assert rel(outs[True][0], outs[False][0]) < 1e-2
+    assert rel(outs[True][1], outs[False][1]) < 2e-2
+    assert rel(outs[True][4], outs[False][4]) < 2e-2 and rel(outs[True][5], outs[False][5]) < 1e-3
+    assert rel(outs[True][2], outs[False][2]) < 0.2 and rel(outs[True][3], outs[False][3]) < 0.05
+    assert fc.weight.cnt == 1 and proj.weight.counter == 1
+    # and against the fp32 masked reference
+    w1 = torch.where(fc.weight.mask, fc.weight.detach(), torch.zeros((), device=DEV))
+    w2 = torch.where(proj.weight.mask, proj.weight.detach(), torch.zeros((), device=DEV))
+    ref = F.linear(F.gelu(F.linear(x0, w1, fc.bias), approximate="tanh"), w2, proj.bias)
+    assert rel(outs[True][0], ref) < 2e-2
