@@ -182,16 +182,21 @@ struct SpmmParams {
 // acc * gelu'(aux): the input gradient of a layer whose input was gelu(aux), written as the gradient of aux.
 enum { EPI_PLAIN = 0, EPI_PRE_GELU = 1, EPI_DGELU = 2 };
 
-__device__ __forceinline__ float gelu_tanh(float v) {
-    const float u = 1.5957691216f * (v + 0.044715f * v * v * v);
-    return v / (1.f + __expf(-u));
+__device__ __forceinline__ float tanh_fast(float v) {
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
 }
-// d/dv [v * sigmoid(u(v))], u = 1.5957691216 (v + 0.044715 v^3)
+// GELU, tanh form: 0.5 v (1 + tanh(u)), u = sqrt(2 / pi) (v + 0.044715 v^3); one MUFU per value
+__device__ __forceinline__ float gelu_tanh(float v) {
+    const float t = tanh_fast(0.7978845608f * fmaf(0.044715f * v * v, v, v));
+    return 0.5f * v * (1.f + t);
+}
+// its derivative: 0.5 (1 + t) + 0.5 v (1 - t^2) sqrt(2 / pi) (1 + 3 * 0.044715 v^2)
 __device__ __forceinline__ float gelu_tanh_grad(float v) {
     const float v2 = v * v;
-    const float u = 1.5957691216f * (v + 0.044715f * v * v2);
-    const float sg = 1.f / (1.f + __expf(-u));
-    return sg + v * sg * (1.f - sg) * (1.5957691216f * (1.f + 0.134145f * v2));
+    const float t = tanh_fast(0.7978845608f * fmaf(0.044715f * v2, v, v));
+    return 0.5f * (1.f + t) + 0.5f * v * (1.f - t * t) * (0.7978845608f * fmaf(0.134145f, v2, 1.f));
 }
 
 template <typename OutT> __device__ __forceinline__ OutT to_out(float v);
@@ -954,31 +959,55 @@ spmm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (run) {
                 uint16_t *dst = reinterpret_cast<uint16_t *>(out) + tok0 * P.ld_out + mrow;
                 uint16_t *aux = reinterpret_cast<uint16_t *>(P.aux) + tok0 * P.ld_aux + mrow;
-                // one 16-bit value: what goes to out; PRE_GELU also stores the value itself to aux first
-                auto put = [&](uint16_t h_bits) {
-                    if constexpr (EPI == EPI_PLAIN) {
-                        dst[0] = h_bits;
-                    } else if constexpr (EPI == EPI_PRE_GELU) {
-                        aux[0] = h_bits;
-                        const OutT g = to_out<OutT>(gelu_tanh(from_out<OutT>(*reinterpret_cast<const OutT *>(&h_bits))));
-                        dst[0] = *reinterpret_cast<const uint16_t *>(&g);
-                    } else {
-                        const uint16_t a_bits = aux[0];
-                        const OutT g = to_out<OutT>(from_out<OutT>(*reinterpret_cast<const OutT *>(&h_bits)) *
-                                                    gelu_tanh_grad(from_out<OutT>(*reinterpret_cast<const OutT *>(&a_bits))));
-                        dst[0] = *reinterpret_cast<const uint16_t *>(&g);
-                    }
-                };
-                const bool full = tok0 + HC <= P.n;
+                if constexpr (EPI == EPI_PLAIN) {
+                    if (tok0 + HC <= P.n) {
 #pragma unroll
-                for (int c2 = 0; c2 < NREG; ++c2) {
-                    if (full || tok0 + 2 * c2 < P.n) put((uint16_t)(held[c2] & 0xFFFFu));
-                    dst += P.ld_out;
-                    aux += P.ld_aux;
-                    if (full || tok0 + 2 * c2 + 1 < P.n) put((uint16_t)(held[c2] >> 16));
-                    dst += P.ld_out;
-                    aux += P.ld_aux;
-                    asm volatile("" : "+l"(dst), "+l"(aux));   // running pointers, not 96 precomputed addresses
+                        for (int c2 = 0; c2 < NREG; ++c2) {
+                            dst[0] = (uint16_t)(held[c2] & 0xFFFFu);
+                            dst[P.ld_out] = (uint16_t)(held[c2] >> 16);
+                            dst += 2 * P.ld_out;
+                            asm volatile("" : "+l"(dst));   // one running pointer, not 96 precomputed addresses
+                        }
+                    } else {
+#pragma unroll
+                        for (int c2 = 0; c2 < NREG; ++c2) {
+                            if (tok0 + 2 * c2 < P.n) dst[0] = (uint16_t)(held[c2] & 0xFFFFu);
+                            if (tok0 + 2 * c2 + 1 < P.n) dst[P.ld_out] = (uint16_t)(held[c2] >> 16);
+                            dst += 2 * P.ld_out;
+                            asm volatile("" : "+l"(dst));
+                        }
+                    }
+                } else {
+                    const bool full = tok0 + HC <= P.n;
+                    auto as_f = [](uint16_t bits) { return from_out<OutT>(*reinterpret_cast<const OutT *>(&bits)); };
+                    auto as_b = [](float v) { const OutT o = to_out<OutT>(v); return *reinterpret_cast<const uint16_t *>(&o); };
+                    // chunks of 16 tokens: all loads of a chunk are issued before the first use, all its stores after
+                    constexpr int CHUNK = 8;
+#pragma unroll
+                    for (int c0 = 0; c0 < NREG; c0 += CHUNK) {
+                        uint16_t a[2 * CHUNK];
+                        if constexpr (EPI == EPI_DGELU) {
+#pragma unroll
+                            for (int j = 0; j < 2 * CHUNK; ++j)
+                                a[j] = (full || tok0 + 2 * c0 + j < P.n) ? aux[(int64_t)j * P.ld_aux] : (uint16_t)0;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 2 * CHUNK; ++j) {
+                            const uint32_t hw = held[c0 + (j >> 1)];
+                            const uint16_t h_bits = (j & 1) ? (uint16_t)(hw >> 16) : (uint16_t)(hw & 0xFFFFu);
+                            if (full || tok0 + 2 * c0 + j < P.n) {
+                                if constexpr (EPI == EPI_PRE_GELU) {
+                                    aux[(int64_t)j * P.ld_aux] = h_bits;
+                                    dst[(int64_t)j * P.ld_out] = as_b(gelu_tanh(as_f(h_bits)));
+                                } else {
+                                    dst[(int64_t)j * P.ld_out] = as_b(as_f(h_bits) * gelu_tanh_grad(as_f(a[j])));
+                                }
+                            }
+                        }
+                        dst += 2 * CHUNK * P.ld_out;
+                        aux += 2 * CHUNK * P.ld_aux;
+                        asm volatile("" : "+l"(dst), "+l"(aux));   // running pointers per chunk
+                    }
                 }
             }
             if (threadIdx.x == 64) SP24_TRACE(2, 4 * tl + 3);

@@ -36,7 +36,10 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
 class Block(nn.Module):
-    fused_mlp = True     # fc + GELU + proj through sparse.fst_mlp (GELU and its gradient in the GEMM epilogues)
+    # True: fc + GELU + proj through sparse.fst_mlp (GELU and its gradient in the GEMM epilogues).  Off by default:
+    # at d_model 768 the two GEMMs that would carry the extra epilogue work have K = 768, six K steps per tile, and
+    # their epilogue is already as long as the tile's tensor-core time; the separate GELU passes are faster.
+    fused_mlp = False
 
     def __init__(self, d, heads, linear):
         super().__init__()
