@@ -199,14 +199,31 @@ def run(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12,
     return res
 
 
+def synthetic_tokens(n, seq, vocab, gen, data="uniform"):
+    """(n, seq + 1) token ids.  "uniform": independent draws (nothing to learn: the loss stays near ln(vocab));
+    "affine": a random first token, then x[t + 1] = (5 x[t] + 7) mod vocab, a next-token rule a small model learns
+    within tens of steps (for tests that compare loss curves)."""
+    if data == "uniform":
+        return torch.randint(0, vocab, (n, seq + 1), generator=gen)
+    tok = torch.empty((n, seq + 1), dtype=torch.long)
+    tok[:, 0] = torch.randint(0, vocab, (n,), generator=gen)
+    for t in range(seq):
+        tok[:, t + 1] = (tok[:, t] * 5 + 7) % vocab
+    return tok
+
+
 def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12, d=768, heads=12, alpha=2e-4,
-               lr=6e-4, freq=40, verbose=False, return_losses=False, comm_groups=4):
+               lr=6e-4, freq=40, verbose=False, return_losses=False, comm_groups=4, data="uniform", global_stream=False):
     """The same step as ``run`` replayed from CUDA graphs.  Returns the same dict.
 
     With more than one rank and ``comm_groups`` > 1 the gradient all-reduce is split into that many groups of
     transformer blocks, last blocks first; each group's all-reduce starts on a second stream as soon as the
     backward pass (still running inside the graph) has left the group, signalled by an event-record node in the
-    graph.  ``comm_groups`` = 1 is one all-reduce of the whole flat gradient after the graph."""
+    graph.  ``comm_groups`` = 1 is one all-reduce of the whole flat gradient after the graph.
+
+    ``global_stream``: every rank draws the whole job's batch (world x batch sequences) from one common seed and keeps
+    its own slice, so that N ranks x batch B see exactly the sequences of one rank x batch N B; with ``return_losses``
+    the per-step losses are then averaged over the ranks."""
     import torch.distributed as dist
     import sparse
     from sparse._semi_structured_conversions import set_device_rng_offset
@@ -260,7 +277,7 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
     rng_counter = torch.zeros(1, dtype=torch.int64, device=dev)
     set_device_rng_offset(rng_counter if mode == "sparse" else None)
     static_tok = torch.zeros((batch, seq + 1), dtype=torch.long, device=dev)
-    gen = torch.Generator(device="cpu").manual_seed(10 + rank)
+    gen = torch.Generator(device="cpu").manual_seed(10 if global_stream else 10 + rank)
 
     def set_phase(reselect):
         # what SparseLinearTranspose.forward looks at: cnt == 0 -> rebuild the compressed copies,
@@ -290,8 +307,11 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
                                            alpha=alpha if use_mask else 0.0)
 
     def next_tokens():
-        tok = torch.randint(0, vocab, (batch, seq + 1), generator=gen).pin_memory()
-        static_tok.copy_(tok, non_blocking=True)
+        if global_stream:
+            tok = synthetic_tokens(batch * world, seq, vocab, gen, data)[rank * batch:(rank + 1) * batch].contiguous()
+        else:
+            tok = synthetic_tokens(batch, seq, vocab, gen, data)
+        static_tok.copy_(tok.pin_memory(), non_blocking=True)
 
     # Gradient exchange.  Group 0 = the last blocks (+ the final layer norm), ..., the last group = the first blocks
     # and the embeddings, whose gradients are complete only when the backward pass ends.  A group's slices of the
@@ -396,7 +416,10 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms.item())
-    loss_list = [float(v) for v in torch.stack(losses).float().cpu()]
+    loss_t = torch.stack(losses).float().reshape(-1)
+    if world > 1 and return_losses and global_stream:
+        dist.all_reduce(loss_t, op=dist.ReduceOp.AVG)     # mean over the ranks' slices = the loss of the whole batch
+    loss_list = [float(v) for v in loss_t.cpu()]
     res = {"tokens_per_s": batch * seq * world * steps / (ms * 1e-3), "ms_per_step": ms / steps, "world": world,
            "tokens_per_step": batch * seq * world, "last_loss": loss_list[-1], "mode": mode,
            "loss_finite": all(math.isfinite(v) for v in loss_list), "host_enqueue_ms_per_step": t_cpu * 1e3 / steps,
