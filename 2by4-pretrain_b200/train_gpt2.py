@@ -65,6 +65,30 @@ class Block(nn.Module):
         return x
 
 
+class _tied_head(torch.autograd.Function):
+    """logits = x W^T for the output head that shares W with the token embedding, with the head's share of dW written
+    (bf16, overwritten every step) into a buffer of its own instead of flowing into W.grad through autograd.  The head's
+    share is the first gradient a backward pass produces and the embedding's share the last; summed by autograd they
+    become available only at the very end, which keeps the largest tensor of the model out of every overlapped
+    gradient exchange.  ``on_ready`` is called once the buffer has been written."""
+
+    @staticmethod
+    def forward(ctx, x, weight, head_grad, on_ready):
+        xb, wb = x.to(head_grad.dtype), weight.to(head_grad.dtype)
+        ctx.save_for_backward(xb, wb)
+        ctx.head_grad, ctx.on_ready, ctx.x_dtype = head_grad, on_ready, x.dtype
+        return xb @ wb.t()
+
+    @staticmethod
+    def backward(ctx, g):
+        xb, wb = ctx.saved_tensors
+        g2, x2 = g.reshape(-1, g.shape[-1]), xb.reshape(-1, xb.shape[-1])
+        torch.mm(g2.t(), x2, out=ctx.head_grad)
+        if ctx.on_ready is not None:
+            ctx.on_ready()
+        return (g2 @ wb).view_as(xb).to(ctx.x_dtype), None, None, None
+
+
 class GPT2(nn.Module):
     def __init__(self, linear, layers=12, d=768, heads=12, seq=1024, vocab=50304):
         super().__init__()
@@ -76,6 +100,10 @@ class GPT2(nn.Module):
         # block index -> callable run when the gradient with respect to that block's input exists, i.e. when the
         # backward pass has left the block (used to start gradient all-reduces early)
         self.input_grad_hooks = {}
+        # set by a trainer that exchanges the head's share of the tied weight's gradient separately (see _tied_head)
+        self.head_grad = None
+        self.head_ready = None
+        self.first_block_hook = None
         self.apply(self._init)
 
     @staticmethod
@@ -88,11 +116,16 @@ class GPT2(nn.Module):
     def forward(self, idx, targets):
         b, t = idx.shape
         x = self.wte(idx) + self.wpe(torch.arange(t, device=idx.device))
+        if self.first_block_hook is not None and x.requires_grad:
+            x.register_hook(lambda g, f=self.first_block_hook: f())     # the backward pass has left block 0
         for i, blk in enumerate(self.blocks):
             if i in self.input_grad_hooks and x.requires_grad:
                 x.register_hook(lambda g, f=self.input_grad_hooks[i]: f())
             x = blk(x)
-        logits = F.linear(self.ln_f(x), self.wte.weight)  # tied output head
+        if self.head_grad is not None:
+            logits = _tied_head.apply(self.ln_f(x), self.wte.weight, self.head_grad, self.head_ready)
+        else:
+            logits = F.linear(self.ln_f(x), self.wte.weight)  # tied output head
         return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.reshape(-1))
 
 
@@ -213,13 +246,20 @@ def synthetic_tokens(n, seq, vocab, gen, data="uniform"):
 
 
 def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12, d=768, heads=12, alpha=2e-4,
-               lr=6e-4, freq=40, verbose=False, return_losses=False, comm_groups=4, data="uniform", global_stream=False):
+               lr=6e-4, freq=40, verbose=False, return_losses=False, comm_groups=4, data="uniform", global_stream=False,
+               split_head=True, reduce_dtype=torch.float32):
     """The same step as ``run`` replayed from CUDA graphs.  Returns the same dict.
 
     With more than one rank and ``comm_groups`` > 1 the gradient all-reduce is split into that many groups of
     transformer blocks, last blocks first; each group's all-reduce starts on a second stream as soon as the
     backward pass (still running inside the graph) has left the group, signalled by an event-record node in the
     graph.  ``comm_groups`` = 1 is one all-reduce of the whole flat gradient after the graph.
+
+    ``split_head``: the output head's share of the tied embedding's gradient goes to a bf16 buffer of its own, which is
+    all-reduced as soon as the backward pass has produced it (its first product) and added to the embedding's gradient
+    before the update; the embeddings' own (lookup) gradients, complete only when the backward pass ends, form the
+    last group alone.  ``reduce_dtype`` = torch.bfloat16 exchanges every group as bf16 (cast, all-reduce, cast back and
+    accumulate in fp32 locally): half the bytes on the wire.
 
     ``global_stream``: every rank draws the whole job's batch (world x batch sequences) from one common seed and keeps
     its own slice, so that N ranks x batch B see exactly the sequences of one rank x batch N B; with ``return_losses``
@@ -273,6 +313,10 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
                 p.mask = flat_mask[m_off:m_off + n_].view_as(p)     # the select kernel refreshes it in place
             off += pad(n_)
         bounds.append((start, off))
+    head_grad = None
+    if split_head:
+        head_grad = torch.zeros(model.wte.weight.shape, dtype=torch.bfloat16, device=dev)
+        model.head_grad = head_grad
     step_dev = torch.zeros(1, dtype=torch.float32, device=dev)
     rng_counter = torch.zeros(1, dtype=torch.int64, device=dev)
     set_device_rng_offset(rng_counter if mode == "sparse" else None)
@@ -299,6 +343,8 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
 
     def update():
         step_dev.add_(1)
+        if head_grad is not None:
+            model.wte.weight.grad.add_(head_grad)      # the (already averaged) head share joins the lookup share
         for (a, b), wd, use_mask in zip(bounds, (0.1, 0.0, 0.0), (False, True, False)):
             if b > a:
                 sparse.adamw_masked_decay_(flat_p[a:b], flat[a:b], flat_m[a:b], flat_v[a:b], step=step_dev, lr=lr,
@@ -316,12 +362,14 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
     # Gradient exchange.  Group 0 = the last blocks (+ the final layer norm), ..., the last group = the first blocks
     # and the embeddings, whose gradients are complete only when the backward pass ends.  A group's slices of the
     # flat buffer are contiguous inside each segment because parameters keep the model's order there.
-    n_groups = max(1, min(comm_groups, layers)) if world > 1 else 1
-    per = (layers + n_groups - 1) // n_groups
+    n_groups = max(1, min(comm_groups, layers + 1)) if world > 1 else 1
+    emb_alone = split_head and n_groups > 1        # blocks in the first n_groups - 1 groups, embeddings in the last
+    n_block_groups = n_groups - 1 if emb_alone else n_groups
+    per = (layers + n_block_groups - 1) // n_block_groups
     group_of = {}
     for i, blk in enumerate(model.blocks):
         for p in blk.parameters():
-            group_of[id(p)] = n_groups - 1 - min(i // per, n_groups - 1)
+            group_of[id(p)] = n_block_groups - 1 - min(i // per, n_block_groups - 1)
     for p in model.ln_f.parameters():
         group_of[id(p)] = 0
     slices = [[] for _ in range(n_groups)]
@@ -334,29 +382,49 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         else:
             slices[g_].append([a, b])
         o = b
-    comm = torch.cuda.Stream() if n_groups > 1 else None
-    ready = [torch.cuda.Event(external=True) for _ in range(n_groups - 1)]
+    comm = torch.cuda.Stream() if (n_groups > 1 or (world > 1 and split_head)) else None
+    n_ready = n_groups - 1      # groups released from inside the graph; the last one waits for the end of backward
+    ready = [torch.cuda.Event(external=True) for _ in range(max(n_ready, 0))]
+    head_ready = torch.cuda.Event(external=True) if (world > 1 and split_head) else None
     tail = torch.cuda.Event()
+    if world > 1 and split_head:
+        model.head_ready = head_ready.record
     if n_groups > 1:
-        for g_ in range(n_groups - 1):
-            # lowest block of group g_ is (n_groups - 1 - g_) * per; its gradients are all accumulated once the
-            # backward pass has also left the block below it
-            below = (n_groups - 1 - g_) * per - 1
-            model.input_grad_hooks[below] = ready[g_].record
+        for g_ in range(n_block_groups):
+            # the lowest block of group g_ is (n_block_groups - 1 - g_) * per; its gradients are all accumulated once the
+            # backward pass has also left the block below it (for block 0: once the embedding sum's gradient exists,
+            # which the hook on block 0's input reports)
+            below = (n_block_groups - 1 - g_) * per - 1
+            if below >= 0:
+                model.input_grad_hooks[below] = ready[g_].record
+            elif emb_alone:
+                model.first_block_hook = ready[g_].record
+    stage = torch.empty(total, dtype=reduce_dtype, device=dev) if (world > 1 and reduce_dtype != torch.float32) else None
+
+    def exchange(a, b):
+        if stage is None:
+            dist.all_reduce(flat[a:b], op=dist.ReduceOp.AVG)
+        else:
+            stage[a:b].copy_(flat[a:b])
+            dist.all_reduce(stage[a:b], op=dist.ReduceOp.AVG)
+            flat[a:b].copy_(stage[a:b])
 
     def reduce_grads():
         if world == 1:
             return
-        if n_groups == 1:
+        main = torch.cuda.current_stream()
+        if comm is None:
             dist.all_reduce(flat, op=dist.ReduceOp.AVG)
             return
-        main = torch.cuda.current_stream()
         tail.record(main)
         with torch.cuda.stream(comm):
+            if head_ready is not None:
+                comm.wait_event(head_ready)
+                dist.all_reduce(head_grad, op=dist.ReduceOp.AVG)
             for g_ in range(n_groups):
-                comm.wait_event(ready[g_] if g_ < n_groups - 1 else tail)
+                comm.wait_event(ready[g_] if g_ < n_ready else tail)
                 for a, b in slices[g_]:
-                    dist.all_reduce(flat[a:b], op=dist.ReduceOp.AVG)
+                    exchange(a, b)
         main.wait_stream(comm)
 
     # eager warm-up on a side stream (allocator, cuBLAS workspaces, optimizer state, kernel attributes)

@@ -157,6 +157,29 @@ def make_weights(n, device, seed0=2):
     return ws
 
 
+def make_device_batch(n, dev, seed0):
+    """n weight matrices drawn on the device, their output buffers and the descriptor array of the batched call
+    (mask + W + W^T copies, reference metadata order only).  Returns (descriptors, tensors to keep alive)."""
+    from sparse import _ext
+    ws, outs = [], []
+    descs = (_ext.DualDesc * n)()
+    for i in range(n):
+        g = torch.Generator(device=dev).manual_seed(seed0 + i)
+        w = (torch.randn(M, K, device=dev, generator=g) * 0.02).half()
+        mask = torch.empty(M, K, dtype=torch.bool, device=dev)
+        bw = torch.empty(M * K * 9 // 16, dtype=torch.float16, device=dev)
+        bt = torch.empty(M * K * 9 // 16, dtype=torch.float16, device=dev)
+        ws.append(w)
+        outs.append((mask, bw, bt))
+        d = descs[i]
+        d.w, d.m, d.k, d.ld_w = w.data_ptr(), M, K, K
+        d.mask, d.ld_mask = mask.data_ptr(), K
+        d.packed_w, d.ld_packed_w, d.meta_w = bw.data_ptr(), K // 2, bw.data_ptr() + M * K
+        d.packed_t, d.ld_packed_t, d.meta_t = bt.data_ptr(), K, bt.data_ptr() + M * K
+        d.tc_w = d.tc_t = None
+    return descs, (ws, outs)
+
+
 def cpu_arm(seconds_budget=12.0, max_reps=6):
     """Times the CPU restatement of the path (mask select in the reference's matmul form + both
     compressions) on full 4096 x 4096 matrices; returns (GB/s, cores, description)."""
@@ -248,24 +271,8 @@ def main():
 
     lib = _ext.lib()
     # device-resident inputs: 48 distinct matrices drawn on the device (seed 2 + matrix index, rank-disjoint)
-    ws = []
-    for i in range(BATCH):
-        g = torch.Generator(device=dev).manual_seed(2 + rank * BATCH + i)
-        ws.append((torch.randn(M, K, device=dev, generator=g) * 0.02).half())
+    descs, keep_alive = make_device_batch(BATCH, dev, 2 + rank * BATCH)
     ws_cpu = make_weights(E2E_BATCH, "cpu", seed0=2 + rank * E2E_BATCH)      # host copies for the end-to-end leg
-    descs = (_ext.DualDesc * BATCH)()
-    outs = []
-    for i in range(BATCH):
-        mask = torch.empty(M, K, dtype=torch.bool, device=dev)
-        bw = torch.empty(M * K * 9 // 16, dtype=torch.float16, device=dev)
-        bt = torch.empty(M * K * 9 // 16, dtype=torch.float16, device=dev)
-        outs.append((mask, bw, bt))
-        d = descs[i]
-        d.w, d.m, d.k, d.ld_w = ws[i].data_ptr(), M, K, K
-        d.mask, d.ld_mask = mask.data_ptr(), K
-        d.packed_w, d.ld_packed_w, d.meta_w = bw.data_ptr(), K // 2, bw.data_ptr() + M * K
-        d.packed_t, d.ld_packed_t, d.meta_t = bt.data_ptr(), K, bt.data_ptr() + M * K
-        d.tc_w = d.tc_t = None
     stream = torch.cuda.current_stream()
 
     def step_device():
@@ -302,7 +309,7 @@ def main():
     value = total_bytes / (ms * 1e-3) / 1e9
     per_launch_s = ms * 1e-3 / args.steps   # one GPU's launches: the roofline is per kernel launch, not per job
     achieved = ALG_BYTES_PER_MATRIX * BATCH / per_launch_s / 1e9
-    del ws, outs, descs
+    del keep_alive, descs
     torch.cuda.empty_cache()
 
     # end-to-end through the public API with host buffers
@@ -416,6 +423,13 @@ def run_case(name):
     if name == "dual":
         w = (torch.randn(8192, 8192, device=dev) * 0.02).half()
         fn = lambda: sparse.select_and_compress(w)
+    elif name == "dual_batch":        # the benchmark kernel on a sixth of its batch: 8 matrices of 4096 x 4096 in one launch
+        from sparse import _ext
+        descs, keep_alive = make_device_batch(8, dev, 2)
+        lib = _ext.lib()
+
+        def fn():
+            _ext.check(lib.sp24_select_dual_compress_batch(descs, 8, _ext.F16, _ext.F16, 1, _ext.stream()), "batch")
     elif name == "select":
         w = (torch.randn(8192, 8192, device=dev) * 0.02).half()
         fn = lambda: sparse.mask_select(w)

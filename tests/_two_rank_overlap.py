@@ -21,6 +21,14 @@ for groups in (1, 4):
                               comm_groups=groups)
     losses[groups] = r["losses"]
 ok = losses[1] == losses[4] and all(abs(v) < 20 for v in losses[1])
+# the same model with the head's share of the tied gradient inside autograd (one exchange group for the whole tail)
+r = train_gpt2.run_graphs(steps=5, warmup=2, mode="dense", batch=2, seq=256, layers=4, return_losses=True, comm_groups=4,
+                          split_head=False)
+ok = ok and all(abs(a - b) < 2e-2 for a, b in zip(r["losses"], losses[4]))     # bf16 head share: not bit-identical
+# and with every group exchanged as bf16
+r = train_gpt2.run_graphs(steps=5, warmup=2, mode="dense", batch=2, seq=256, layers=4, return_losses=True, comm_groups=4,
+                          reduce_dtype=torch.bfloat16)
+ok = ok and all(abs(a - b) < 2e-2 for a, b in zip(r["losses"], losses[4]))
 if dist.get_rank() == 0:
     print("OVERLAP_OK" if ok else f"OVERLAP_MISMATCH {losses}")
 dist.destroy_process_group()
