@@ -1510,6 +1510,11 @@ static int spmm_impl(const void *a_packed, int dtype, int a_mn_major, int64_t ld
     if (!aligned16(e_tc)) return SP24_ERR_ALIGN;
     const bool i8 = dtype == SP24_I8;
     const bool f8 = dtype == SP24_E4M3 || dtype == SP24_E5M2 || i8;   // 8-bit operand geometry
+    // CTA-pair kernel: 16-bit types, token-major B and output, whole 256-row blocks, no activation; the fused MLP
+    // epilogues and the float32 bias exist in that kernel only
+    const bool pair_ok = !f8 && !b_mn_major && trans_out && ms % 256 == 0 && activation == 0;
+    if (epi != EPI_PLAIN && (!pair_ok || !aux || ld_aux < ms || (ld_aux * 2) % 16 || !aligned16(aux))) return SP24_ERR_ARG;
+    if (bias_f32 && !pair_ok) return SP24_ERR_ARG;
     if (int rc = check_device()) return rc;
 
     CUtensorMap map_a;
@@ -1538,17 +1543,8 @@ static int spmm_impl(const void *a_packed, int dtype, int a_mn_major, int64_t ld
     P.idesc = (1u << 2) | ((i8 ? 2u : 1u) << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(a_mn_major ? 1 : 0) << 15) |
               ((uint32_t)(b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BM >> 4) << 24);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // CTA-pair kernel: 16-bit types, token-major B and output, whole 256-row blocks, no activation
-    const bool pair_ok = !f8 && !b_mn_major && trans_out && ms % 256 == 0 && activation == 0;
     bool pair_form = pair_ok && n >= 1024 && pair_kernels_enabled();
-    if (epi != EPI_PLAIN) {
-        // the fused MLP epilogues exist in the pair kernel only
-        if (!pair_ok || !aux || ld_aux < ms || (ld_aux * 2) % 16 || !aligned16(aux)) return SP24_ERR_ARG;
-        pair_form = true;
-    } else if (bias_f32) {
-        if (!pair_ok) return SP24_ERR_ARG;          // a float32 bias is read by the pair kernel only
-        pair_form = true;
-    }
+    if (epi != EPI_PLAIN || bias_f32) pair_form = true;      // checked above: these forms exist in the pair kernel only
     if (pair_form) {
         CUtensorMap map_b, map_e;
         rc = make_map(&map_b, b, dtype, n, k, ld_b, 64, two::BN2 / 2);

@@ -117,6 +117,26 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     descs[1].tc_w = descs[1].tc_t = None
     descs[1].m = 96
     assert lib.sp24_select_dual_compress_batch(descs, 2, F16, F16, 0, None) == -1
+    # entry points added for the float8 backward pass, the one-pass S-STE forward and the fused MLP epilogues
+    E4M3 = 3
+    # q8: float8 outputs only; a quantisation scale must be positive; k a multiple of 128
+    assert lib.sp24_prune_compress_q8(p, F16, 32, 128, 128, 0, q, F16, 64, r, 0, None, 0, 1.0, 0, 0, None) == -3
+    assert lib.sp24_prune_compress_q8(p, F16, 32, 128, 128, 0, q, E4M3, 64, r, 0, None, 0, 0.0, 0, 0, None) == -5
+    assert lib.sp24_prune_compress_q8(p, F16, 32, 64, 64, 1, q, E4M3, 32, r, 0, None, 0, 1.0, 0, 0, None) == -1
+    # the fast MVUE mode takes no uniforms; mode codes beyond the public enum are refused
+    assert lib.sp24_prune_compress(p, F16, 32, 64, 64, 0, q, F16, 32, r, 3, None, 0, r, 64, 0, 0, None) == -5
+    assert lib.sp24_prune_compress(p, F16, 32, 64, 64, 0, q, F16, 32, r, 4, None, 0, None, 0, 0, 0, None) == -5
+    assert lib.sp24_mvue24_dense_fast(p, F16, 32, 12, 12, 0, q, 12, 0, 0, None) == -1
+    # soft threshold + compress: 16-bit packed types only
+    assert lib.sp24_soft_threshold24_compress(p, F32, 32, 64, 64, 0, q, E4M3, 32, r, 0, 0.0, None, None) == -3
+    assert lib.sp24_soft_threshold24_compress(p, F32, 33, 64, 64, 0, q, F16, 32, r, 0, 0.0, None, None) == -1
+    # scaled float8 GEMM: 16-bit operands are refused; fused MLP epilogues: 16-bit only, dgelu takes no bias, and the
+    # second tensor is mandatory
+    assert lib.sp24_spmm_scaled(p, F16, 64, q, 128, 128, r, 128, 8, st, 1, 128, None, 0, 1.0, None, None) == -3
+    assert lib.sp24_spmm_mlp(p, E4M3, 0, 64, q, 256, 128, r, 128, 8, st, 256, None, 0, 0, None, 0, None, None) == -3
+    assert lib.sp24_spmm_mlp(p, F16, 0, 64, q, 256, 128, r, 128, 8, st, 256, r, 0, 2, st, 256, None, None) == -5
+    assert lib.sp24_spmm_mlp(p, F16, 0, 64, q, 256, 128, r, 128, 8, st, 256, None, 0, 1, None, 0, None, None) == -5
+    assert lib.sp24_spmm_mlp(p, F16, 0, 64, q, 128, 128, r, 128, 8, st, 128, None, 0, 1, st, 128, None, None) == -5
     # row sums exist for column-major storage only
     assert lib.sp24_prune_compress_ex(p, F16, 128, 64, 64, 0, q, F16, 32, r, 0, None, 0, None, 0, 0, 0, None, None, st, None) == -5
 
