@@ -64,14 +64,23 @@ class ColumnParallelSparseWeight:
             self.mask, (pw, mw), (pt, mt) = select_and_compress(local, mask=None, dtype=dtype)
             self.compressed = (pw, mw, pt, mt)
 
-    def forward_local(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Y[:, r0:r1] = x @ W_s[r0:r1].T (+ bias[r0:r1]); x is replicated (T x in_features)."""
-        from .spmm import sparse_linear
+    def forward_local(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, features_major: bool = False) -> torch.Tensor:
+        """Y[:, r0:r1] = x @ W_s[r0:r1].T (+ bias[r0:r1]); x is replicated (T x in_features).  With
+        ``features_major`` the block is computed as (r1 - r0, T) contiguous and returned as its transposed view: the
+        layout ``all_gather_columns`` can gather with one collective and no copy."""
+        from . import spmm as _spmm
         if self.compressed is None:
             return x.new_empty((x.shape[0], 0), dtype=self.dtype)
         pw, mw, _, _ = self.compressed
         b = None if bias is None else bias[self.r0:self.r1].to(self.dtype).contiguous()
-        return sparse_linear(x, pw, mw, bias=b)
+        if not features_major:
+            return _spmm.sparse_linear(x, pw, mw, bias=b)
+        keep = _spmm.RETURN_TRANSPOSED_VIEW
+        _spmm.RETURN_TRANSPOSED_VIEW = True
+        try:
+            return _spmm.sparse_linear(x, pw, mw, bias=b)
+        finally:
+            _spmm.RETURN_TRANSPOSED_VIEW = keep
 
     def grad_input_partial(self, grad_local: torch.Tensor) -> torch.Tensor:
         """This rank's term of dX = sum over ranks of dY[:, r0:r1] @ W_s[r0:r1]; the caller reduces."""
@@ -89,6 +98,12 @@ def all_gather_columns(y_local: torch.Tensor, out_features: int, world: Optional
     widths = [r1 - r0 for r0, r1 in (row_block(out_features, r, world) for r in range(world))]
     wmax = max(widths)
     t = y_local.shape[0]
+    if min(widths) == wmax and y_local.dim() == 2 and y_local.t().is_contiguous():
+        # equal blocks, each stored features-major (w, T): every rank's rows are one contiguous piece of the
+        # (out_features, T) result, so one all-gather into that tensor does it; Y is its transposed view
+        yt = y_local.new_empty((out_features, t))
+        dist.all_gather_into_tensor(yt, y_local.t(), group=group)
+        return yt.t()
     padded = y_local
     if y_local.shape[1] != wmax:
         padded = y_local.new_zeros((t, wmax))

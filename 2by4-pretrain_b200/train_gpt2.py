@@ -246,7 +246,7 @@ def synthetic_tokens(n, seq, vocab, gen, data="uniform"):
 
 
 def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12, d=768, heads=12, alpha=2e-4,
-               lr=6e-4, freq=40, verbose=False, return_losses=False, comm_groups=4, data="uniform", global_stream=False,
+               lr=6e-4, freq=40, verbose=False, return_losses=False, comm_groups=5, data="uniform", global_stream=False,
                split_head=True, reduce_dtype=torch.float32):
     """The same step as ``run`` replayed from CUDA graphs.  Returns the same dict.
 

@@ -409,6 +409,15 @@ def main():
             line["spmm_cfg4"] = spmm_extra
         if gpt2:
             line["gpt2_124m"] = gpt2
+        # the three quantities of the metric side by side (the first is `value`)
+        summary = {"prune_compress_GBps": value, "prune_compress_frac_of_hbm_peak": achieved / peak}
+        if spmm_extra and "fp16" in spmm_extra:
+            summary["spmm_fwd_bwd_TFLOPs_dense_equiv_fp16"] = spmm_extra["fp16"]["sparse_fwd_bwd_TFLOPs_dense_equiv"]
+            summary["spmm_fwd_bwd_speedup_vs_dense_fp16"] = spmm_extra["fp16"]["speedup_vs_dense"]
+        if gpt2 and "sparse_tokens_per_s" in gpt2:
+            summary["gpt2_124m_tokens_per_s"] = gpt2["sparse_tokens_per_s"]
+            summary["gpt2_124m_sparse_over_dense"] = gpt2["sparse_over_dense"]
+        line["north_star_summary"] = summary
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -578,8 +587,9 @@ def gpt2_measurements(world):
                "loss_finite": sp["loss_finite"], "n_gpus": world,
                "sparse_eager_ddp_tokens_per_s": sp_eager["tokens_per_s"],
                "sparse_eager_ddp_host_enqueue_ms_per_step": sp_eager["host_enqueue_ms_per_step"],
-               "note": "step replayed from CUDA graphs (forward+backward; the flat fp32 gradient all-reduced by NCCL "
-                       "in four block groups released by event nodes inside the backward graph; then masked "
+               "note": "step replayed from CUDA graphs (forward+backward; the flat fp32 gradient all-reduced by NCCL in "
+                       "groups released by event nodes inside the backward graph: the output head's share of the tied "
+                       "embedding gradient first, then four groups of blocks, the embeddings last; then masked "
                        "decay + AdamW); 50 timed sparse steps, mean, including the mask "
                        "refresh every 40 steps; eager = Python-launched step with DistributedDataParallel"}
     except Exception as exc:  # the headline line must still be printed
@@ -616,7 +626,7 @@ def sharded_spmm_measurements(dev, rank, world):
         return float(t.item())
 
     ms_local = timed(lambda i: sh.forward_local(xs[i % 3]))
-    ms_gather = timed(lambda i: all_gather_columns(sh.forward_local(xs[i % 3]), N, world))
+    ms_gather = timed(lambda i: all_gather_columns(sh.forward_local(xs[i % 3], features_major=True), N, world))
     flops = 2.0 * T * K * N
     return {"rows_of_W_per_rank": sh.r1 - sh.r0, "fwd_ms": ms_local, "fwd_TFLOPs_dense_equiv": flops / ms_local / 1e9,
             "fwd_plus_allgather_ms": ms_gather, "fwd_plus_allgather_TFLOPs_dense_equiv": flops / ms_gather / 1e9,

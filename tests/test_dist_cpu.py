@@ -109,8 +109,16 @@ def _gather_worker(rank, world, port, out):
         w = torch.arange(n_out * 8, dtype=torch.float32).reshape(n_out, 8)
         assert torch.equal(shard_rows(w), w[r0:r1])
         y = all_gather_columns(full[:, r0:r1].contiguous(), n_out)
+        ok = bool(torch.equal(y, full))
+        # equal blocks stored features-major (w, T): the single-collective path, result is a transposed view
+        n2 = 512
+        full2 = torch.arange(t * n2, dtype=torch.float32).reshape(t, n2)
+        a, b = row_block(n2, rank, world)
+        local = full2[:, a:b].t().contiguous().t()          # (T, w) view of a contiguous (w, T) block
+        y2 = all_gather_columns(local, n2)
+        ok = ok and bool(torch.equal(y2, full2)) and y2.t().is_contiguous()
         if rank == 0:
-            out.put(bool(torch.equal(y, full)))
+            out.put(ok)
     except Exception as exc:
         out.put(("error", repr(exc)))
         raise
