@@ -38,6 +38,10 @@ _SIGNATURES = {
                                _u64, _u64, _vp, _vp, _vp, _vp],
     "sp24_prune_compress_q8": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _i64, _vp, _i32, _vp, _i64, _f32, _u64, _u64, _vp],
     "sp24_soft_threshold24_compress": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _i64, _vp, _i32, _f32, _vp, _vp],
+    "sp24_layernorm_fwd": [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _f32, _vp],
+    "sp24_layernorm_bwd": [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp],
+    "sp24_cross_entropy_fwd": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i64, _vp],
+    "sp24_cross_entropy_bwd": [_vp, _i32, _vp, _vp, _vp, _f32, _vp, _i64, _i64, _i64, _i64, _vp],
     "sp24_adamw_masked_decay": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp],
     "sp24_to_dense": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _i64, _vp],
     "sp24_mvue24_dense": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _u64, _u64, _vp],

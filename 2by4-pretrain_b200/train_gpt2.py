@@ -35,6 +35,18 @@ import torch.nn.functional as F
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
+# True: layer norm and cross entropy run on the library's streaming kernels (sparse.train_ops) instead of the
+# framework's float32 layer norm + cast, gamma / beta gradient kernel and float32 log-softmax over the logits.
+FUSED_OPS = True
+
+
+def _layer_norm(d):
+    if FUSED_OPS:
+        from sparse.train_ops import LayerNorm
+        return LayerNorm(d)
+    return nn.LayerNorm(d)
+
+
 class Block(nn.Module):
     # True: fc + GELU + proj through sparse.fst_mlp (GELU and its gradient in the GEMM epilogues).  Off by default:
     # at d_model 768 the two GEMMs that would carry the extra epilogue work have K = 768, six K steps per tile, and
@@ -44,10 +56,10 @@ class Block(nn.Module):
     def __init__(self, d, heads, linear):
         super().__init__()
         self.heads = heads
-        self.ln1 = nn.LayerNorm(d)
+        self.ln1 = _layer_norm(d)
         self.attn_qkv = linear(d, 3 * d)
         self.attn_proj = linear(d, d)
-        self.ln2 = nn.LayerNorm(d)
+        self.ln2 = _layer_norm(d)
         self.fc = linear(d, 4 * d)
         self.proj = linear(4 * d, d)
 
@@ -96,7 +108,7 @@ class GPT2(nn.Module):
         self.wte = nn.Embedding(vocab, d)
         self.wpe = nn.Embedding(seq, d)
         self.blocks = nn.ModuleList(Block(d, heads, linear) for _ in range(layers))
-        self.ln_f = nn.LayerNorm(d)
+        self.ln_f = _layer_norm(d)
         # block index -> callable run when the gradient with respect to that block's input exists, i.e. when the
         # backward pass has left the block (used to start gradient all-reduces early)
         self.input_grad_hooks = {}
@@ -126,6 +138,9 @@ class GPT2(nn.Module):
             logits = _tied_head.apply(self.ln_f(x), self.wte.weight, self.head_grad, self.head_ready)
         else:
             logits = F.linear(self.ln_f(x), self.wte.weight)  # tied output head
+        if FUSED_OPS and logits.dtype in (torch.float16, torch.bfloat16):
+            from sparse.train_ops import cross_entropy
+            return cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1))
         return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.reshape(-1))
 
 

@@ -354,6 +354,36 @@ int sp24_spmm_accumulate_f32(const void *a_packed, int dtype, int a_mn_major, in
                              int64_t ld_out, int k_splits, int *status, void *stream);
 
 /*
+ * Two streaming kernels of the trainer around the sparse GEMMs.  No counterpart in the reference, whose model and
+ * training scripts live in another repository (README.md:18); they replace the framework's generic kernels where those
+ * dominate a training step of the GPT-2 configuration (float32 layer norm + cast, its gamma / beta gradient, float32
+ * copies of the logits around log-softmax).
+ *
+ * Layer normalisation over the last dimension, one warp per row: x float32 (rows, d) contiguous, d % 128 == 0,
+ * d <= 1024; out in out_dtype (F32 / F16 / BF16: the 16-bit operand of the next GEMM is written directly); mean and
+ * rstd (rows floats each) are kept for the backward pass, which takes dy in F32 / F16 / BF16, writes dx (float32) and
+ * ADDS the gamma / beta gradients into dgamma / dbeta (d floats each, float32 atomics: zero them or pass gradient
+ * buffers to accumulate into).
+ */
+int sp24_layernorm_fwd(const float *x, const float *gamma, const float *beta, void *out, int out_dtype, float *mean,
+                       float *rstd, int64_t rows, int64_t d, float eps, void *stream);
+int sp24_layernorm_bwd(const void *dy, int dy_dtype, const float *x, const float *gamma, const float *mean,
+                       const float *rstd, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t d, void *stream);
+
+/*
+ * Cross entropy over 16-bit logits (rows, v) with row pitch ld, v % 8 == 0, int64 class targets in [0, v); float32
+ * arithmetic, one block per row, each logit read once per pass.
+ *   forward:  lse[row] = log sum_c exp(logits[row, c]);  loss[row] = lse[row] - logits[row, target[row]]
+ *   backward: dlogits[row, c] = (exp(logits[row, c] - lse[row]) - [c == target[row]]) * scale * (*upstream),
+ *             upstream a device float (the gradient of the summed loss) or NULL for 1; scale e.g. 1 / rows for a mean.
+ *             dlogits has the logits' type and may alias logits.
+ */
+int sp24_cross_entropy_fwd(const void *logits, int dtype, const int64_t *targets, float *lse, float *loss, int64_t rows,
+                           int64_t v, int64_t ld, void *stream);
+int sp24_cross_entropy_bwd(const void *logits, int dtype, const int64_t *targets, const float *lse, const float *upstream,
+                           float scale, void *dlogits, int64_t rows, int64_t v, int64_t ld, int64_t ld_out, void *stream);
+
+/*
  * Self-test of the failure path of the GEMM kernels: launches one CTA that waits, with a limit of `polls`
  * polls (1 .. 2^20), on a barrier nothing signals.  The wait gives up, *status (a device int the caller
  * zeroed) becomes 9 and the kernel returns normally; the context stays usable.  No counterpart in the

@@ -5,6 +5,7 @@ masked decay."""
 import numpy as np
 import pytest
 import torch
+import torch.nn.functional as F
 
 from _golden import load, t, same_bits
 from oracle import sp24_oracle as O
@@ -659,3 +660,71 @@ def test_soft_threshold_compress_matches_the_three_pass_sequence(S, idt, odt, sc
     fused_tc = _spmm._tc_meta_cache[id(meta)][1]
     _spmm.invalidate_meta(meta)
     assert torch.equal(fused_tc, tc_metadata(meta, m, k))
+
+
+# ------------------------------------------------------------------------------------------------
+# trainer kernels around the GEMMs: layer norm and cross entropy (float arithmetic: torch fp32 references)
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("d", [128, 768, 1024])
+@pytest.mark.parametrize("odt", [torch.float32, torch.bfloat16, torch.float16])
+def test_layer_norm_kernels_match_torch_fp32(d, odt):
+    """sp24_layernorm_fwd / _bwd against F.layer_norm and autograd in float32.  Tolerances: output within one rounding
+    of the output type of the fp32 result (1e-5 relative for fp32 out, 2^-8 / 2^-11 for bf16 / fp16); dx, dgamma, dbeta
+    within 2e-5 of the largest magnitude for an fp32 dy, 1e-2 / 2e-3 when dy is first rounded to bf16 / fp16."""
+    from sparse.train_ops import _layer_norm
+    g = torch.Generator().manual_seed(d)
+    rows = 1000                                                    # not a multiple of the 8 rows per block
+    x = (torch.randn(rows, d, generator=g) * 2 + 0.5).to(DEV).requires_grad_(True)
+    w = (torch.randn(d, generator=g) * 0.5 + 1).to(DEV).requires_grad_(True)
+    b = torch.randn(d, generator=g).to(DEV).requires_grad_(True)
+    dy = torch.randn(rows, d, generator=g).to(DEV)
+    y = _layer_norm.apply(x, w, b, 1e-5, odt)
+    assert y.dtype == odt and y.shape == x.shape
+    y.backward(dy.to(odt))
+    got = (y.detach().float(), x.grad.clone(), w.grad.clone(), b.grad.clone())
+    x.grad = w.grad = b.grad = None
+    ref = F.layer_norm(x, (d,), w, b, 1e-5)
+    ref.backward(dy.to(odt).float())
+    tol_y = {torch.float32: 1e-5, torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11}[odt]
+    assert float((got[0] - ref.detach()).abs().max() / ref.detach().abs().max()) <= tol_y
+    tol_g = 2e-5
+    for a, r in zip(got[1:], (x.grad, w.grad, b.grad)):
+        assert float((a - r).abs().max() / r.abs().max()) <= tol_g, float((a - r).abs().max() / r.abs().max())
+
+
+def test_layer_norm_module_under_autocast_and_fallback():
+    from sparse.train_ops import LayerNorm
+    ln = LayerNorm(256).to(DEV)
+    x = torch.randn(4, 10, 256, device=DEV)
+    assert ln(x).dtype == torch.float32
+    with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+        y = ln(x)
+    assert y.dtype == torch.bfloat16 and y.shape == x.shape
+    assert float((y.float() - F.layer_norm(x, (256,), ln.weight, ln.bias)).abs().max()) < 0.05
+    odd = LayerNorm(100).to(DEV)                                   # not a multiple of 128: the parent's implementation
+    z = torch.randn(3, 100, device=DEV)
+    assert torch.allclose(odd(z), F.layer_norm(z, (100,), odd.weight, odd.bias), atol=1e-6)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,v", [(37, 512), (256, 50304)])
+def test_cross_entropy_kernels_match_torch_fp32(dt, rows, v):
+    """sp24_cross_entropy_fwd / _bwd against F.cross_entropy on the float32 copy of the same 16-bit logits: loss within
+    1e-5 relative (float32 summation order), gradient within one rounding of the logits' type of the fp32 gradient
+    (2^-8 / 2^-11 of the largest magnitude), including a scaled upstream gradient and a padded row pitch."""
+    from sparse.train_ops import cross_entropy
+    g = torch.Generator().manual_seed(rows + v)
+    buf = torch.zeros(rows, v + 16, dtype=dt, device=DEV)
+    logits = buf[:, :v]                                             # row pitch v + 16
+    logits.copy_((torch.randn(rows, v, generator=g) * 3).to(dt))
+    logits.requires_grad_(True)
+    tgt = torch.randint(0, v, (rows,), generator=g).to(DEV)
+    loss = cross_entropy(logits, tgt)
+    (loss * 0.37).backward()
+    l32 = logits.detach().float().contiguous().requires_grad_(True)
+    ref = F.cross_entropy(l32, tgt)
+    (ref * 0.37).backward()
+    assert abs(float(loss) - float(ref)) <= 1e-5 * abs(float(ref))
+    tol = {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11}[dt]
+    assert float((logits.grad.float() - l32.grad).abs().max() / l32.grad.abs().max()) <= tol
+    assert logits.grad.dtype == dt
