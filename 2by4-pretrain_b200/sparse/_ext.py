@@ -55,6 +55,7 @@ _SIGNATURES = {
                                      _vp, _vp, _vp, _vp],
     "sp24_select_dual_compress_batch": [ctypes.POINTER(DualDesc), _i32, _i32, _i32, _i32, _vp],
     "sp24_masked_add": [_vp, _vp, _vp, _i32, _i64, _f32, _vp],
+    "sp24_set_sm_budget": [_i32],
 }
 
 
@@ -80,6 +81,16 @@ def lib():
                 fn.argtypes = args
         _lib = h
     return _lib
+
+
+def set_sm_budget(sms: int) -> int:
+    """SMs the persistent GEMM kernels size their grids for (0 = all); returns the previous value.  Leave a
+    collective that runs beside the GEMMs its SMs (and cap its CTAs, ``NCCL_MAX_CTAS``): a GEMM grid sized for every
+    SM otherwise runs its last CTAs as a second wave behind the collective's.  Fixed at capture time in a CUDA graph."""
+    rc = lib().sp24_set_sm_budget(int(sms))
+    if rc < 0:
+        check(rc, "sp24_set_sm_budget")
+    return rc
 
 
 def register_signature(name, argtypes):

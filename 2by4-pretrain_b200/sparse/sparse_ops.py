@@ -117,11 +117,43 @@ def _mvue_compress_t(g, row_sums):
     return packed, meta
 
 
+def _mm_f32(a, b, acc=None):
+    """a @ b (16-bit operands) with a float32 result; added into ``acc`` in the GEMM's epilogue when given."""
+    try:
+        if acc is not None:
+            return torch.addmm(acc, a, b, out_dtype=torch.float32, out=acc)
+        return torch.mm(a, b, out_dtype=torch.float32)
+    except (TypeError, RuntimeError):             # a torch without the out_dtype argument on this overload
+        r = torch.mm(a, b).float()
+        return r if acc is None else acc.add_(r)
+
+
+def _dense_weight_grads(g, x, weight, bias, into_grad, need_w, need_b):
+    """The exact dW = g^T x as a dense GEMM with float32 output (the option ``weight_grad = "dense"`` of the layer).
+    Same contract as ``_fst_weight_grads``."""
+    grad_weight = grad_bias = None
+    into = into_grad and weight.grad is not None and weight.grad.dtype == torch.float32 and weight.grad.is_contiguous()
+    if need_w:
+        if into:
+            _mm_f32(g.t(), x, weight.grad)
+        else:
+            gw = _mm_f32(g.t(), x)
+            grad_weight = gw if weight.dtype == torch.float32 else gw.to(weight.dtype)
+    if bias is not None and need_b:
+        if into and need_w and bias.grad is not None and bias.grad.dtype == torch.float32:
+            bias.grad.add_(g.sum(0, dtype=torch.float32))
+        else:
+            grad_bias = g.sum(0)
+    return grad_weight, grad_bias
+
+
 def _fst_weight_grads(g, x, weight, bias, into_grad, need_w, need_b):
     """dW = MVUE24(g^T) x and db = g.sum(0) of one FST layer; ``g`` (tokens, out_features) and ``x`` (tokens,
     in_features) are 16-bit.  With ``into_grad`` (and an fp32 ``weight.grad`` already allocated) the GEMM adds dW
     straight into ``weight.grad`` and the compression pass adds the column sums of ``g`` into ``bias.grad``; autograd
     then receives None for both.  Returns (grad_weight, grad_bias)."""
+    if getattr(weight, 'weight_grad', 'mvue') == 'dense':
+        return _dense_weight_grads(g, x, weight, bias, into_grad, need_w, need_b)
     grad_weight = grad_bias = None
     bias_done = False
     if need_w:
@@ -263,6 +295,11 @@ class SparseLinearTranspose(nn.Linear):
     """
 
     materialize_sparse_tensors = False
+    # How the weight gradient is formed (``weight.weight_grad``, set per layer from this class attribute).  "mvue": the
+    # reference recipe, dW = MVUE24(dY^T) X on the sparse tensor cores (README.md:190-192 of the reference).  "dense":
+    # the exact dW = dY^T X as a dense GEMM: no estimator noise, and on B200 the faster of the two (the MVUE pass plus
+    # the sparse GEMM take longer than the dense GEMM they replace).
+    weight_grad = "mvue"
     # True: the weight-gradient GEMM adds straight into an existing fp32 ``weight.grad`` (a trainer that owns flat
     # gradient buffers and needs no autograd hook on the weight, e.g. the graph-replayed one); False: autograd gets it
     accumulate_into_grad = False
@@ -280,6 +317,7 @@ class SparseLinearTranspose(nn.Linear):
         self.weight.weight_sparse_T = None
         self.weight.compressed = None
         self.weight.mode = 'sparse'
+        self.weight.weight_grad = self.weight_grad
         self.func = func
 
         self.transposable_sparse = TransposableSparse(abs=True)

@@ -698,6 +698,28 @@ def test_weight_gradient_accumulates_into_an_existing_grad_buffer(S):
     assert float((a.weight.grad - b.weight.grad).abs().max() / a.weight.grad.abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("into", [False, True])
+def test_dense_weight_gradient_option_is_the_exact_gradient(S, into):
+    """weight_grad = "dense": dW is the exact dY^T X (no estimator), db the column sums; forward and dX unchanged.
+    Tolerance: fp16 operands, fp32 accumulation, 256 tokens: 2e-3 of the largest entry."""
+    torch.manual_seed(5)
+    layer = S.SparseLinearTranspose(256, 384, bias=True).to(DEV)
+    layer.weight.weight_grad = "dense"
+    layer.accumulate_into_grad = into
+    if into:
+        layer.weight.grad = torch.zeros_like(layer.weight)
+        layer.bias.grad = torch.zeros_like(layer.bias)
+    x = torch.randn(4, 64, 256, device=DEV, requires_grad=True)
+    y = layer(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    g16, x16 = g.reshape(-1, 384).half().float(), x.detach().reshape(-1, 256).half().float()
+    want_w, want_b = g16.t() @ x16, g16.sum(0)
+    assert float((layer.weight.grad - want_w).abs().max() / want_w.abs().max()) < 2e-3
+    assert float((layer.bias.grad.float() - want_b).abs().max() / want_b.abs().max()) < 2e-3
+    assert x.grad is not None and x.grad.shape == x.shape
+
+
 def test_spmm_random_shapes_agree_with_the_reference(S):
     """Thirty seeded random problems (rows, K, tokens, dtype, operand storage orders, bias): every one within the
     stated tolerance of the fp32 matmul of the pruned operands, whichever kernel the dispatcher picks."""
