@@ -54,10 +54,13 @@ template <> __device__ __forceinline__ float4 load4<__half>(const __half *p) {
     return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
 }
 
-// y = (x - mean) * rstd * gamma + beta, statistics in float32 (two passes over the registers)
+// y = (r - mean) * rstd * gamma + beta with r = x (+ delta, then also written to res_out as float32): statistics in
+// float32, two passes over the registers.  delta / res_out: both null, or the branch output that joins the residual
+// stream in front of this norm (same element type as the output) and the new residual stream.
 template <typename TOut, int NV>
-__global__ void __launch_bounds__(256) layernorm_fwd_kernel(const float *x, const float *gamma, const float *beta, TOut *out,
-                                                            float *mean_out, float *rstd_out, int64_t rows, float eps) {
+__global__ void __launch_bounds__(256) layernorm_fwd_kernel(const float *x, const TOut *delta, float *res_out, const float *gamma,
+                                                            const float *beta, TOut *out, float *mean_out, float *rstd_out,
+                                                            int64_t rows, float eps) {
     constexpr int d = NV * 128, nv = NV;
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -67,7 +70,13 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const float *x, cons
 #pragma unroll
     for (int i = 0; i < NV; ++i)
         if (i < nv) {
-            v[i] = load4<float>(x + row * d + (i * 32 + lane) * 4);
+            const int64_t at = row * d + (i * 32 + lane) * 4;
+            v[i] = load4<float>(x + at);
+            if (delta) {
+                const float4 dl = load4<TOut>(delta + at);
+                v[i] = make_float4(v[i].x + dl.x, v[i].y + dl.y, v[i].z + dl.z, v[i].w + dl.w);
+                store4<float>(res_out + at, v[i].x, v[i].y, v[i].z, v[i].w);
+            }
             s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
     const float mean = warp_sum(s) / (float)d;
@@ -93,49 +102,64 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const float *x, cons
     }
 }
 
-// dx = rstd * (g dy - mean(g dy) - xhat mean(g dy xhat));  dgamma += sum_rows dy xhat;  dbeta += sum_rows dy.
+// dx = rstd * (g dy - mean(g dy) - xhat mean(g dy xhat)) (+ dres);  dgamma += sum_rows dy xhat;  dbeta += sum_rows dy.
+// dres (optional): the gradient that reaches the norm's input along the residual stream, added before the store;
+// ddelta (optional): the same dx again in dy's element type, the gradient of the branch that was added in front.
 // Persistent warps: each walks rows warp, warp + nwarps, ... and keeps its column sums in registers; one reduction
 // over the block's eight warps in shared memory, then one atomic per column and block.
 template <typename TDy, int NV>
-__global__ void __launch_bounds__(256) layernorm_bwd_kernel(const TDy *dy, const float *x, const float *gamma, const float *mean,
-                                                            const float *rstd, float *dx, float *dgamma, float *dbeta,
-                                                            int64_t rows) {
+__global__ void __launch_bounds__(256, 2) layernorm_bwd_kernel(const TDy *dy, const float *x, const float *gamma, const float *mean,
+                                                               const float *rstd, const float *dres, float *dx, TDy *ddelta,
+                                                               float *dgamma, float *dbeta, int64_t rows) {
     extern __shared__ float red[];           // 2 x 8 x d floats
     constexpr int d = NV * 128, nv = NV;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float4 g[NV], ag[NV], ab[NV];
+    // Registers: only the two column sums (2 x NV float4) stay for the whole kernel.  A row is read twice: once for the
+    // two row-wide sums and the column sums, once more (from L1, where the first pass left it) together with the
+    // residual-stream gradient for the outputs.  Keeping the row in registers between the passes instead costs 155
+    // registers at d = 768, i.e. one resident block per SM and half the bandwidth.
+    float4 ag[NV], ab[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i)
         if (i < nv) {
-            g[i] = load4<float>(gamma + (i * 32 + lane) * 4);
             ag[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
+    const float4 *g4 = reinterpret_cast<const float4 *>(gamma) + lane;
     const int64_t nwarps = (int64_t)gridDim.x * 8;
     for (int64_t row = (int64_t)blockIdx.x * 8 + warp; row < rows; row += nwarps) {
         const float mu = mean[row], rs = rstd[row];
-        float4 xh[NV], gy[NV];
+        const int64_t base = row * d + lane * 4;
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
         for (int i = 0; i < NV; ++i)
             if (i < nv) {
-                const int c0 = (i * 32 + lane) * 4;
-                const float4 xv = load4<float>(x + row * d + c0);
-                const float4 dv = load4<TDy>(dy + row * d + c0);
-                xh[i] = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
-                gy[i] = make_float4(dv.x * g[i].x, dv.y * g[i].y, dv.z * g[i].z, dv.w * g[i].w);
-                s1 += (gy[i].x + gy[i].y) + (gy[i].z + gy[i].w);
-                s2 += (gy[i].x * xh[i].x + gy[i].y * xh[i].y) + (gy[i].z * xh[i].z + gy[i].w * xh[i].w);
-                ag[i].x += dv.x * xh[i].x; ag[i].y += dv.y * xh[i].y; ag[i].z += dv.z * xh[i].z; ag[i].w += dv.w * xh[i].w;
+                const float4 xv = load4<float>(x + base + i * 128);
+                const float4 dv = load4<TDy>(dy + base + i * 128);
+                const float4 g = __ldg(g4 + i * 32);
+                const float4 xh = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
+                const float4 gy = make_float4(dv.x * g.x, dv.y * g.y, dv.z * g.z, dv.w * g.w);
+                s1 += (gy.x + gy.y) + (gy.z + gy.w);
+                s2 += (gy.x * xh.x + gy.y * xh.y) + (gy.z * xh.z + gy.w * xh.w);
+                ag[i].x += dv.x * xh.x; ag[i].y += dv.y * xh.y; ag[i].z += dv.z * xh.z; ag[i].w += dv.w * xh.w;
                 ab[i].x += dv.x; ab[i].y += dv.y; ab[i].z += dv.z; ab[i].w += dv.w;
             }
         const float m1 = warp_sum(s1) / (float)d, m2 = warp_sum(s2) / (float)d;
 #pragma unroll
         for (int i = 0; i < NV; ++i)
             if (i < nv) {
-                const int c0 = (i * 32 + lane) * 4;
-                store4<float>(dx + row * d + c0, rs * (gy[i].x - m1 - xh[i].x * m2), rs * (gy[i].y - m1 - xh[i].y * m2),
-                              rs * (gy[i].z - m1 - xh[i].z * m2), rs * (gy[i].w - m1 - xh[i].w * m2));
+                const int64_t at = base + i * 128;
+                const float4 xv = load4<float>(x + at);
+                const float4 dv = load4<TDy>(dy + at);
+                const float4 g = __ldg(g4 + i * 32);
+                float4 o = make_float4(rs * (dv.x * g.x - m1 - (xv.x - mu) * rs * m2), rs * (dv.y * g.y - m1 - (xv.y - mu) * rs * m2),
+                                       rs * (dv.z * g.z - m1 - (xv.z - mu) * rs * m2), rs * (dv.w * g.w - m1 - (xv.w - mu) * rs * m2));
+                if (dres) {
+                    const float4 r = load4<float>(dres + at);
+                    o = make_float4(o.x + r.x, o.y + r.y, o.z + r.z, o.w + r.w);
+                }
+                store4<float>(dx + at, o.x, o.y, o.z, o.w);
+                if (ddelta) store4<TDy>(ddelta + at, o.x, o.y, o.z, o.w);
             }
     }
     float *rg = red, *rb = red + 8 * d;
@@ -238,23 +262,156 @@ __global__ void __launch_bounds__(256) ce_bwd_kernel(const T *logits, const int6
     }
 }
 
+// Forward and gradient in one kernel: the row is read from HBM once, kept in shared memory (STAGED; otherwise re-read,
+// mostly from L2), and the gradient for an upstream gradient of 1 is written in the same launch:
+// dlogits[row, c] = (exp(logits[row, c] - lse[row]) - [c == target[row]]) * scale.
+template <typename T, bool STAGED>
+__global__ void __launch_bounds__(512) ce_fused_kernel(const T *logits, const int64_t *targets, float *lse, float *loss,
+                                                       float scale, T *dlogits, int64_t v, int64_t ld, int64_t ld_out) {
+    extern __shared__ uint4 staged[];        // the row as 16-byte pieces (STAGED only)
+    __shared__ float scratch[16];
+    const int64_t row = blockIdx.x;
+    const T *p = logits + row * ld;
+    T *q = dlogits + row * ld_out;
+    const int64_t nvec = v / 8;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float m = -INFINITY, s = 0.f;
+    for (int64_t i0 = threadIdx.x; i0 < nvec; i0 += 4 * 512) {          // four 16-byte loads in flight per thread
+        uint4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t i = i0 + u * 512;
+            if (i < nvec) r[u] = *reinterpret_cast<const uint4 *>(p + i * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t i = i0 + u * 512;
+            if (i >= nvec) break;
+            if (STAGED) staged[i] = r[u];
+            float f[8];
+            unpack8<T>(r[u], f);
+            float vm = f[0];
+#pragma unroll
+            for (int j = 1; j < 8; ++j) vm = fmaxf(vm, f[j]);
+            const float nm = fmaxf(m, vm);
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc += __expf(f[j] - nm);
+            s = s * __expf(m - nm) + acc;
+            m = nm;
+        }
+    }
+    // block reductions over 16 warps
+    float wm = warp_max(m);
+    if (lane == 0) scratch[warp] = wm;
+    __syncthreads();
+    float gm = scratch[0];
+#pragma unroll
+    for (int w = 1; w < 16; ++w) gm = fmaxf(gm, scratch[w]);
+    __syncthreads();
+    const float ws = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - gm));
+    if (lane == 0) scratch[warp] = ws;
+    __syncthreads();
+    float gs = 0.f;
+#pragma unroll
+    for (int w = 0; w < 16; ++w) gs += scratch[w];
+    const float l = gm + logf(gs);
+    const int64_t tgt = targets[row];
+    if (threadIdx.x == 0) {
+        lse[row] = l;
+        loss[row] = l - Elem<T>::to_f32(p[tgt]);
+    }
+    for (int64_t i = threadIdx.x; i < nvec; i += 512) {
+        float f[8];
+        unpack8<T>(STAGED ? staged[i] : *reinterpret_cast<const uint4 *>(p + i * 8), f);
+        uint4 o;
+        uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t c = i * 8 + 2 * j;
+            const float a = (__expf(f[2 * j] - l) - (c == tgt ? 1.f : 0.f)) * scale;
+            const float b = (__expf(f[2 * j + 1] - l) - (c + 1 == tgt ? 1.f : 0.f)) * scale;
+            ow[j] = Elem<T>::pack2(a, b);
+        }
+        *reinterpret_cast<uint4 *>(q + i * 8) = o;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// token + position embedding: one warp per token
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void red_add_v4(float *addr, const float4 &v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+// out[row, :] = wte[ids[row], :] + wpe[row % t, :]; an id outside [0, vocab) contributes zeros
+__global__ void __launch_bounds__(256) embedding_fwd_kernel(const int64_t *ids, const float *wte, const float *wpe, float *out,
+                                                            int64_t rows, int64_t t, int64_t d, int64_t vocab) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int64_t id = ids[row];
+    const bool ok = id >= 0 && id < vocab;
+    const float *a = wte + (ok ? id : 0) * d, *b = wpe + (row % t) * d;
+    for (int64_t c = lane * 4; c < d; c += 128) {
+        const float4 u = ok ? load4<float>(a + c) : make_float4(0.f, 0.f, 0.f, 0.f), v = load4<float>(b + c);
+        store4<float>(out + row * d + c, u.x + v.x, u.y + v.y, u.z + v.z, u.w + v.w);
+    }
+}
+
+// dwte[ids[row], :] += dx[row, :];  dwpe[row % t, :] += dx[row, :]   (float32 vector reductions in L2; the order in
+// which rows that share a token or a position are added is not fixed)
+__global__ void __launch_bounds__(256) embedding_bwd_kernel(const float *dx, const int64_t *ids, float *dwte, float *dwpe,
+                                                            int64_t rows, int64_t t, int64_t d, int64_t vocab) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int64_t id = ids[row];
+    const bool ok = id >= 0 && id < vocab;
+    float *a = dwte + (ok ? id : 0) * d, *b = dwpe + (row % t) * d;
+    for (int64_t c = lane * 4; c < d; c += 128) {
+        const float4 v = load4<float>(dx + row * d + c);
+        if (ok) red_add_v4(a + c, v);
+        red_add_v4(b + c, v);
+    }
+}
+
+// g *= *factor unless *factor == 1 (the usual case: nothing is read or written then)
+template <typename T>
+__global__ void __launch_bounds__(256) scale_unless_one_kernel(T *g, const float *factor, int64_t nvec) {
+    const float f = *factor;
+    if (f == 1.f) return;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * 256) {
+        uint4 r = reinterpret_cast<uint4 *>(g)[i];
+        float x[8];
+        unpack8<T>(r, x);
+        uint32_t *w = reinterpret_cast<uint32_t *>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] = Elem<T>::pack2(x[2 * j] * f, x[2 * j + 1] * f);
+        reinterpret_cast<uint4 *>(g)[i] = r;
+    }
+}
+
 }  // namespace
 }  // namespace sp24
 
 using namespace sp24;
 
-extern "C" int sp24_layernorm_fwd(const float *x, const float *gamma, const float *beta, void *out, int out_dtype, float *mean,
-                                  float *rstd, int64_t rows, int64_t d, float eps, void *stream) {
+static int layernorm_fwd_impl(const float *x, const void *delta, float *res_out, const float *gamma, const float *beta, void *out,
+                              int out_dtype, float *mean, float *rstd, int64_t rows, int64_t d, float eps, void *stream) {
     if (!x || !gamma || !beta || !out || !mean || !rstd) return SP24_ERR_ARG;
+    if ((delta == nullptr) != (res_out == nullptr)) return SP24_ERR_ARG;
     if (out_dtype != SP24_F32 && out_dtype != SP24_F16 && out_dtype != SP24_BF16) return SP24_ERR_DTYPE;
     if (rows <= 0 || d <= 0 || d % 128 || d > 128 * MAXV) return SP24_ERR_SHAPE;
-    if (!aligned16(x) || !aligned16(gamma) || !aligned16(beta) || !aligned16(out)) return SP24_ERR_ALIGN;
+    if (!aligned16(x) || !aligned16(gamma) || !aligned16(beta) || !aligned16(out) || !aligned16(delta) || !aligned16(res_out))
+        return SP24_ERR_ALIGN;
     if (!(eps >= 0.f)) return SP24_ERR_ARG;
     if (int rc = check_device()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const unsigned blocks = (unsigned)((rows + 7) / 8);
 #define SP24_LN_FWD(T_, NV_) \
-    layernorm_fwd_kernel<T_, NV_><<<blocks, 256, 0, st>>>(x, gamma, beta, static_cast<T_ *>(out), mean, rstd, rows, eps)
+    layernorm_fwd_kernel<T_, NV_><<<blocks, 256, 0, st>>>(x, static_cast<const T_ *>(delta), res_out, gamma, beta, \
+                                                          static_cast<T_ *>(out), mean, rstd, rows, eps)
 #define SP24_LN_FWD_NV(T_) \
     switch (d / 128) { \
         case 1: SP24_LN_FWD(T_, 1); break; case 2: SP24_LN_FWD(T_, 2); break; case 3: SP24_LN_FWD(T_, 3); break; \
@@ -269,18 +426,28 @@ extern "C" int sp24_layernorm_fwd(const float *x, const float *gamma, const floa
     return launch_status();
 }
 
-extern "C" int sp24_layernorm_bwd(const void *dy, int dy_dtype, const float *x, const float *gamma, const float *mean,
-                                  const float *rstd, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t d,
-                                  void *stream) {
+extern "C" int sp24_layernorm_fwd(const float *x, const float *gamma, const float *beta, void *out, int out_dtype, float *mean,
+                                  float *rstd, int64_t rows, int64_t d, float eps, void *stream) {
+    return layernorm_fwd_impl(x, nullptr, nullptr, gamma, beta, out, out_dtype, mean, rstd, rows, d, eps, stream);
+}
+
+extern "C" int sp24_add_layernorm_fwd(const float *x, const void *delta, float *res_out, const float *gamma, const float *beta,
+                                      void *out, int out_dtype, float *mean, float *rstd, int64_t rows, int64_t d, float eps,
+                                      void *stream) {
+    if (!delta || !res_out) return SP24_ERR_ARG;
+    return layernorm_fwd_impl(x, delta, res_out, gamma, beta, out, out_dtype, mean, rstd, rows, d, eps, stream);
+}
+
+static int layernorm_bwd_impl(const void *dy, int dy_dtype, const float *dres, const float *x, const float *gamma, const float *mean,
+                              const float *rstd, float *dx, void *ddelta, float *dgamma, float *dbeta, int64_t rows, int64_t d,
+                              void *stream) {
     if (!dy || !x || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta) return SP24_ERR_ARG;
     if (dy_dtype != SP24_F32 && dy_dtype != SP24_F16 && dy_dtype != SP24_BF16) return SP24_ERR_DTYPE;
     if (rows <= 0 || d <= 0 || d % 128 || d > 128 * MAXV) return SP24_ERR_SHAPE;
-    if (!aligned16(dy) || !aligned16(x) || !aligned16(gamma) || !aligned16(dx)) return SP24_ERR_ALIGN;
+    if (!aligned16(dy) || !aligned16(x) || !aligned16(gamma) || !aligned16(dx) || !aligned16(dres) || !aligned16(ddelta))
+        return SP24_ERR_ALIGN;
     if (int rc = check_device()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int64_t blocks = (rows + 7) / 8;
-    const int64_t cap = (int64_t)sm_count() * 2;       // persistent: about one resident block per SM, each ends with 2 d atomics
-    if (blocks > cap) blocks = cap;
     const size_t smem = (size_t)2 * 8 * d * sizeof(float);       // at most 64 KB (d = 1024)
     static bool attr_set[3][8][64];
     int dev = 0;
@@ -294,7 +461,13 @@ extern "C" int sp24_layernorm_bwd(const void *dy, int dy_dtype, const float *x, 
                 return launch_status(); \
             attr_set[which][NV_ - 1][dev] = true; \
         } \
-        kern<<<(unsigned)blocks, 256, smem, st>>>(static_cast<const T_ *>(dy), x, gamma, mean, rstd, dx, dgamma, dbeta, rows); \
+        int resident = 0;                                                /* persistent grid: every block resident at once */ \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, 256, smem) != cudaSuccess || resident < 1) resident = 1; \
+        int64_t blocks = (rows + 7) / 8; \
+        const int64_t cap = (int64_t)sm_count() * resident; \
+        if (blocks > cap) blocks = cap; \
+        kern<<<(unsigned)blocks, 256, smem, st>>>(static_cast<const T_ *>(dy), x, gamma, mean, rstd, dres, dx, \
+                                                  static_cast<T_ *>(ddelta), dgamma, dbeta, rows); \
     } while (0)
 #define SP24_LN_BWD_NV(T_) \
     switch (d / 128) { \
@@ -308,6 +481,18 @@ extern "C" int sp24_layernorm_bwd(const void *dy, int dy_dtype, const float *x, 
 #undef SP24_LN_BWD_NV
 #undef SP24_LN_BWD
     return launch_status();
+}
+
+extern "C" int sp24_layernorm_bwd(const void *dy, int dy_dtype, const float *x, const float *gamma, const float *mean,
+                                  const float *rstd, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t d,
+                                  void *stream) {
+    return layernorm_bwd_impl(dy, dy_dtype, nullptr, x, gamma, mean, rstd, dx, nullptr, dgamma, dbeta, rows, d, stream);
+}
+
+extern "C" int sp24_add_layernorm_bwd(const void *dy, int dy_dtype, const float *dres, const float *x, const float *gamma,
+                                      const float *mean, const float *rstd, float *dx, void *ddelta, float *dgamma, float *dbeta,
+                                      int64_t rows, int64_t d, void *stream) {
+    return layernorm_bwd_impl(dy, dy_dtype, dres, x, gamma, mean, rstd, dx, ddelta, dgamma, dbeta, rows, d, stream);
 }
 
 extern "C" int sp24_cross_entropy_fwd(const void *logits, int dtype, const int64_t *targets, float *lse, float *loss, int64_t rows,
@@ -344,5 +529,85 @@ extern "C" int sp24_cross_entropy_bwd(const void *logits, int dtype, const int64
     else
         ce_bwd_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(logits), targets, lse, upstream,
                                                                     scale, static_cast<__nv_bfloat16 *>(dlogits), v, ld, ld_out);
+    return launch_status();
+}
+
+template <typename T>
+static int ce_fused_launch(const void *logits, const int64_t *targets, float *lse, float *loss, float scale, void *dlogits,
+                           int64_t rows, int64_t v, int64_t ld, int64_t ld_out, cudaStream_t st) {
+    const size_t row_bytes = (size_t)v * sizeof(T);
+    const bool staged = row_bytes <= 110 * 1024;           // two resident blocks per SM
+    if (staged) {
+        auto kern = ce_fused_kernel<T, true>;
+        static bool attr_set[64];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024) != cudaSuccess)
+                return launch_status();
+            attr_set[dev] = true;
+        }
+        kern<<<(unsigned)rows, 512, row_bytes, st>>>(static_cast<const T *>(logits), targets, lse, loss, scale,
+                                                     static_cast<T *>(dlogits), v, ld, ld_out);
+    } else {
+        ce_fused_kernel<T, false><<<(unsigned)rows, 512, 0, st>>>(static_cast<const T *>(logits), targets, lse, loss, scale,
+                                                                  static_cast<T *>(dlogits), v, ld, ld_out);
+    }
+    return launch_status();
+}
+
+extern "C" int sp24_cross_entropy_fused(const void *logits, int dtype, const int64_t *targets, float *lse, float *loss, float scale,
+                                        void *dlogits, int64_t rows, int64_t v, int64_t ld, int64_t ld_out, void *stream) {
+    if (!logits || !targets || !lse || !loss || !dlogits) return SP24_ERR_ARG;
+    if (dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
+    if (rows <= 0 || v <= 0 || v % 8) return SP24_ERR_SHAPE;
+    if (ld < v || ld % 8 || ld_out < v || ld_out % 8) return SP24_ERR_STRIDE;
+    if (!aligned16(logits) || !aligned16(dlogits)) return SP24_ERR_ALIGN;
+    if (rows > 0x7FFFFFFF) return SP24_ERR_TOO_LARGE;
+    if (int rc = check_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == SP24_F16 ? ce_fused_launch<__half>(logits, targets, lse, loss, scale, dlogits, rows, v, ld, ld_out, st)
+                             : ce_fused_launch<__nv_bfloat16>(logits, targets, lse, loss, scale, dlogits, rows, v, ld, ld_out, st);
+}
+
+extern "C" int sp24_scale_unless_one(void *g, int dtype, const float *factor, int64_t count, void *stream) {
+    if (!g || !factor) return SP24_ERR_ARG;
+    if (dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
+    if (count <= 0 || count % 8) return SP24_ERR_SHAPE;
+    if (!aligned16(g)) return SP24_ERR_ALIGN;
+    if (int rc = check_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t nvec = count / 8;
+    int64_t blocks = (nvec + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    if (dtype == SP24_F16)
+        scale_unless_one_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<__half *>(g), factor, nvec);
+    else
+        scale_unless_one_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(static_cast<__nv_bfloat16 *>(g), factor, nvec);
+    return launch_status();
+}
+
+extern "C" int sp24_embedding_fwd(const int64_t *ids, const float *wte, const float *wpe, float *out, int64_t rows, int64_t t,
+                                  int64_t d, int64_t vocab, void *stream) {
+    if (!ids || !wte || !wpe || !out) return SP24_ERR_ARG;
+    if (rows <= 0 || t <= 0 || d <= 0 || d % 4 || vocab <= 0) return SP24_ERR_SHAPE;
+    if (!aligned16(wte) || !aligned16(wpe) || !aligned16(out)) return SP24_ERR_ALIGN;
+    if ((rows + 7) / 8 > 0x7FFFFFFF) return SP24_ERR_TOO_LARGE;
+    if (int rc = check_device()) return rc;
+    embedding_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, wte, wpe, out, rows, t, d,
+                                                                                                     vocab);
+    return launch_status();
+}
+
+extern "C" int sp24_embedding_bwd(const float *dx, const int64_t *ids, float *dwte, float *dwpe, int64_t rows, int64_t t, int64_t d,
+                                  int64_t vocab, void *stream) {
+    if (!dx || !ids || !dwte || !dwpe) return SP24_ERR_ARG;
+    if (rows <= 0 || t <= 0 || d <= 0 || d % 4 || vocab <= 0) return SP24_ERR_SHAPE;
+    if (!aligned16(dx) || !aligned16(dwte) || !aligned16(dwpe)) return SP24_ERR_ALIGN;
+    if ((rows + 7) / 8 > 0x7FFFFFFF) return SP24_ERR_TOO_LARGE;
+    if (int rc = check_device()) return rc;
+    embedding_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(dx, ids, dwte, dwpe, rows, t, d,
+                                                                                                     vocab);
     return launch_status();
 }

@@ -40,6 +40,8 @@ _SIGNATURES = {
     "sp24_soft_threshold24_compress": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _i64, _vp, _i32, _f32, _vp, _vp],
     "sp24_layernorm_fwd": [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _f32, _vp],
     "sp24_layernorm_bwd": [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp],
+    "sp24_add_layernorm_fwd": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _f32, _vp],
+    "sp24_add_layernorm_bwd": [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp],
     "sp24_cross_entropy_fwd": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i64, _vp],
     "sp24_cross_entropy_bwd": [_vp, _i32, _vp, _vp, _vp, _f32, _vp, _i64, _i64, _i64, _i64, _vp],
     "sp24_adamw_masked_decay": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp],
@@ -55,6 +57,10 @@ _SIGNATURES = {
                                      _vp, _vp, _vp, _vp],
     "sp24_select_dual_compress_batch": [ctypes.POINTER(DualDesc), _i32, _i32, _i32, _i32, _vp],
     "sp24_masked_add": [_vp, _vp, _vp, _i32, _i64, _f32, _vp],
+    "sp24_cross_entropy_fused": [_vp, _i32, _vp, _vp, _vp, _f32, _vp, _i64, _i64, _i64, _i64, _vp],
+    "sp24_scale_unless_one": [_vp, _i32, _vp, _i64, _vp],
+    "sp24_embedding_fwd": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp],
+    "sp24_embedding_bwd": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp],
     "sp24_set_sm_budget": [_i32],
 }
 

@@ -47,6 +47,15 @@ def _layer_norm(d):
     return nn.LayerNorm(d)
 
 
+def _add_norm(x, delta, norm):
+    """(x + delta, norm(x + delta)): the residual connection and the following norm."""
+    if FUSED_OPS:
+        from sparse.train_ops import add_layer_norm
+        return add_layer_norm(x, delta, norm)
+    x = x + delta
+    return x, norm(x)
+
+
 class Block(nn.Module):
     # True: fc + GELU + proj through sparse.fst_mlp (GELU and its gradient in the GEMM epilogues).  Off by default:
     # at d_model 768 the two GEMMs that would carry the extra epilogue work have K = 768, six K steps per tile, and
@@ -63,18 +72,23 @@ class Block(nn.Module):
         self.fc = linear(d, 4 * d)
         self.proj = linear(4 * d, d)
 
-    def forward(self, x):
+    def forward(self, x, delta=None):
+        """``x``: the residual stream, ``delta``: the previous block's MLP output, not yet added to it (None in front
+        of the first block).  Returns the same pair for the next block: every residual add runs inside the kernel of
+        the norm that follows it."""
         b, t, d = x.shape
-        q, k, v = self.attn_qkv(self.ln1(x)).split(d, dim=2)
+        if delta is None:
+            h = self.ln1(x)
+        else:
+            x, h = _add_norm(x, delta, self.ln1)
+        q, k, v = self.attn_qkv(h).split(d, dim=2)
         q, k, v = (z.view(b, t, self.heads, d // self.heads).transpose(1, 2) for z in (q, k, v))
         y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        x = x + self.attn_proj(y.transpose(1, 2).reshape(b, t, d))
+        x, h = _add_norm(x, self.attn_proj(y.transpose(1, 2).reshape(b, t, d)), self.ln2)
         if self.fused_mlp:
             import sparse
-            x = x + sparse.fst_mlp(self.ln2(x), self.fc, self.proj)
-        else:
-            x = x + self.proj(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
-        return x
+            return x, sparse.fst_mlp(h, self.fc, self.proj)
+        return x, self.proj(F.gelu(self.fc(h), approximate="tanh"))
 
 
 class _tied_head(torch.autograd.Function):
@@ -116,6 +130,8 @@ class GPT2(nn.Module):
         self.head_grad = None
         self.head_ready = None
         self.first_block_hook = None
+        # True: the embedding gradients are added straight into existing float32 .grad buffers (flat-buffer trainers)
+        self.accumulate_into_grad = False
         self.apply(self._init)
 
     @staticmethod
@@ -127,17 +143,23 @@ class GPT2(nn.Module):
 
     def forward(self, idx, targets):
         b, t = idx.shape
-        x = self.wte(idx) + self.wpe(torch.arange(t, device=idx.device))
+        if FUSED_OPS and idx.is_cuda:
+            from sparse.train_ops import embed_tokens
+            x = embed_tokens(idx, self.wte.weight, self.wpe.weight, self.accumulate_into_grad)
+        else:
+            x = self.wte(idx) + self.wpe(torch.arange(t, device=idx.device))
         if self.first_block_hook is not None and x.requires_grad:
             x.register_hook(lambda g, f=self.first_block_hook: f())     # the backward pass has left block 0
+        delta = None
         for i, blk in enumerate(self.blocks):
             if i in self.input_grad_hooks and x.requires_grad:
                 x.register_hook(lambda g, f=self.input_grad_hooks[i]: f())
-            x = blk(x)
+            x, delta = blk(x, delta)
+        x, h = _add_norm(x, delta, self.ln_f)
         if self.head_grad is not None:
-            logits = _tied_head.apply(self.ln_f(x), self.wte.weight, self.head_grad, self.head_ready)
+            logits = _tied_head.apply(h, self.wte.weight, self.head_grad, self.head_ready)
         else:
-            logits = F.linear(self.ln_f(x), self.wte.weight)  # tied output head
+            logits = F.linear(h, self.wte.weight)  # tied output head
         if FUSED_OPS and logits.dtype in (torch.float16, torch.bfloat16):
             from sparse.train_ops import cross_entropy
             return cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1))

@@ -382,6 +382,21 @@ int sp24_layernorm_bwd(const void *dy, int dy_dtype, const float *x, const float
                        const float *rstd, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t d, void *stream);
 
 /*
+ * The same two kernels with the residual connection of a pre-norm transformer block folded in.
+ *   forward:  res_out = x + delta (float32; delta has the type of `out`: the branch output that joins the residual
+ *             stream), out = layer_norm(res_out); mean / rstd as above.  res_out may alias x.
+ *   backward: dx = layer-norm input gradient (from dy and x = the saved res_out) + dres, where dres (float32 or NULL)
+ *             is the gradient arriving along the residual stream; ddelta (dy's type, or NULL) receives the same
+ *             values: the gradient of the branch.  dx may alias dres.
+ * One pass over the residual stream per direction instead of three (add, norm, cast / accumulate).
+ */
+int sp24_add_layernorm_fwd(const float *x, const void *delta, float *res_out, const float *gamma, const float *beta, void *out,
+                           int out_dtype, float *mean, float *rstd, int64_t rows, int64_t d, float eps, void *stream);
+int sp24_add_layernorm_bwd(const void *dy, int dy_dtype, const float *dres, const float *x, const float *gamma,
+                           const float *mean, const float *rstd, float *dx, void *ddelta, float *dgamma, float *dbeta,
+                           int64_t rows, int64_t d, void *stream);
+
+/*
  * Cross entropy over 16-bit logits (rows, v) with row pitch ld, v % 8 == 0, int64 class targets in [0, v); float32
  * arithmetic, one block per row, each logit read once per pass.
  *   forward:  lse[row] = log sum_c exp(logits[row, c]);  loss[row] = lse[row] - logits[row, target[row]]
@@ -393,6 +408,31 @@ int sp24_cross_entropy_fwd(const void *logits, int dtype, const int64_t *targets
                            int64_t v, int64_t ld, void *stream);
 int sp24_cross_entropy_bwd(const void *logits, int dtype, const int64_t *targets, const float *lse, const float *upstream,
                            float scale, void *dlogits, int64_t rows, int64_t v, int64_t ld, int64_t ld_out, void *stream);
+
+/*
+ * Both passes in one launch, for a loss whose upstream gradient is 1 (a training loss that is differentiated directly):
+ * lse and loss as the forward above, and dlogits = (softmax - onehot) * scale written from the same read of the row
+ * (kept in shared memory when it fits: v * 2 bytes <= 110 KB; otherwise re-read).  dlogits may alias logits.
+ * sp24_scale_unless_one multiplies `count` 16-bit values (count % 8 == 0) by the device float *factor, and does
+ * nothing (no read, no write) when that is exactly 1: the backward pass of the fused form.
+ */
+int sp24_cross_entropy_fused(const void *logits, int dtype, const int64_t *targets, float *lse, float *loss, float scale,
+                             void *dlogits, int64_t rows, int64_t v, int64_t ld, int64_t ld_out, void *stream);
+int sp24_scale_unless_one(void *g, int dtype, const float *factor, int64_t count, void *stream);
+
+/*
+ * Token + learned position embedding of a decoder (float32 tables, d % 4 == 0), one warp per token:
+ *   forward:  out[row, :] = wte[ids[row], :] + wpe[row % t, :]          rows = batch * t tokens, ids int64
+ *   backward: dwte[ids[row], :] += dx[row, :];  dwpe[row % t, :] += dx[row, :]   (float32 vector reductions: the
+ *             gradient tables must hold what the sums are to be added to, e.g. zeros; rows that share a token or a
+ *             position are added in no fixed order, so sums can differ in the last bit from run to run)
+ * An id outside [0, vocab) reads as a zero row and receives no gradient.  Stands where the framework's sort-based
+ * embedding gradient (a dozen launches) sat in the GPT-2 step; no counterpart in the reference.
+ */
+int sp24_embedding_fwd(const int64_t *ids, const float *wte, const float *wpe, float *out, int64_t rows, int64_t t, int64_t d,
+                       int64_t vocab, void *stream);
+int sp24_embedding_bwd(const float *dx, const int64_t *ids, float *dwte, float *dwpe, int64_t rows, int64_t t, int64_t d,
+                       int64_t vocab, void *stream);
 
 /*
  * Self-test of the failure path of the GEMM kernels: launches one CTA that waits, with a limit of `polls`

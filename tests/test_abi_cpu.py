@@ -139,6 +139,29 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.sp24_spmm_mlp(p, F16, 0, 64, q, 128, 128, r, 128, 8, st, 128, None, 0, 1, st, 128, None, None) == -5
     # row sums exist for column-major storage only
     assert lib.sp24_prune_compress_ex(p, F16, 128, 64, 64, 0, q, F16, 32, r, 0, None, 0, None, 0, 0, 0, None, None, st, None) == -5
+    # trainer kernels: row length a multiple of 128 up to 1024; the residual forms want both extra tensors; cross
+    # entropy takes 16-bit logits with classes % 8 == 0 and a row pitch that covers them
+    assert lib.sp24_layernorm_fwd(p, q, r, st, BF16, st, st, 8, 100, 1e-5, None) == -1
+    assert lib.sp24_layernorm_fwd(p, q, r, st, BF16, st, st, 8, 2048, 1e-5, None) == -1
+    assert lib.sp24_layernorm_fwd(p, q, r, st, I8, st, st, 8, 128, 1e-5, None) == -3
+    assert lib.sp24_add_layernorm_fwd(p, None, st, q, r, st, BF16, st, st, 8, 128, 1e-5, None) == -5
+    assert lib.sp24_add_layernorm_fwd(p, q, None, q, r, st, BF16, st, st, 8, 128, 1e-5, None) == -5
+    assert lib.sp24_add_layernorm_fwd(p, ctypes.c_void_p(base + 2), st, q, r, st, BF16, st, st, 8, 128, 1e-5, None) == -4
+    assert lib.sp24_add_layernorm_bwd(p, BF16, None, q, r, st, st, None, None, st, st, 8, 128, None) == -5
+    assert lib.sp24_add_layernorm_bwd(p, BF16, None, q, r, st, st, st, None, st, st, 8, 96, None) == -1
+    assert lib.sp24_cross_entropy_fused(p, F32, q, r, st, 1.0, p, 4, 64, 64, 64, None) == -3
+    assert lib.sp24_cross_entropy_fused(p, BF16, q, r, st, 1.0, p, 4, 60, 64, 64, None) == -1
+    assert lib.sp24_cross_entropy_fused(p, BF16, q, r, st, 1.0, p, 4, 64, 32, 64, None) == -2
+    assert lib.sp24_cross_entropy_fused(p, BF16, q, r, st, 1.0, None, 4, 64, 64, 64, None) == -5
+    assert lib.sp24_scale_unless_one(p, BF16, None, 64, None) == -5
+    assert lib.sp24_scale_unless_one(p, BF16, q, 60, None) == -1
+    assert lib.sp24_embedding_fwd(p, q, r, st, 8, 4, 30, 100, None) == -1
+    assert lib.sp24_embedding_fwd(p, q, r, None, 8, 4, 32, 100, None) == -5
+    assert lib.sp24_embedding_bwd(p, q, ctypes.c_void_p(base + 4), st, 8, 4, 32, 100, None) == -4
+    # SM budget: negative refused; set / read back; odd values rounded down
+    assert lib.sp24_set_sm_budget(-1) == -5
+    assert lib.sp24_set_sm_budget(133) == 0
+    assert lib.sp24_set_sm_budget(0) == 132
 
 
 def test_missing_library_fails_loudly(monkeypatch):

@@ -706,12 +706,144 @@ def test_layer_norm_module_under_autocast_and_fallback():
     assert torch.allclose(odd(z), F.layer_norm(z, (100,), odd.weight, odd.bias), atol=1e-6)
 
 
+@pytest.mark.parametrize("d,dt", [(768, torch.bfloat16), (256, torch.float16), (1024, torch.float32)])
+def test_add_layer_norm_matches_the_separate_ops(d, dt):
+    """sp24_add_layernorm_fwd / _bwd: (x + delta, layer_norm(x + delta)) and its backward pass with a gradient arriving
+    along the residual stream, against torch in float32 on the same (rounded) inputs.  Tolerances: residual within
+    1e-6 relative; normalised output within one rounding of its type; dx within 2e-5 of the largest magnitude, the
+    branch gradient within one rounding of its type of dx; dgamma / dbeta within 2e-5."""
+    from sparse.train_ops import _add_layer_norm
+    g = torch.Generator().manual_seed(d)
+    rows = 1003
+    x = (torch.randn(rows, d, generator=g) * 2).to(DEV).requires_grad_(True)
+    delta = torch.randn(rows, d, generator=g).to(dt).to(DEV).requires_grad_(True)
+    w = (torch.randn(d, generator=g) * 0.5 + 1).to(DEV).requires_grad_(True)
+    b = torch.randn(d, generator=g).to(DEV).requires_grad_(True)
+    dy = torch.randn(rows, d, generator=g).to(dt).to(DEV)
+    dres = torch.randn(rows, d, generator=g).to(DEV)
+    res, y = _add_layer_norm.apply(x, delta, w, b, 1e-5)
+    assert res.dtype == torch.float32 and y.dtype == dt
+    torch.autograd.backward([res, y], [dres, dy])
+    got = (res.detach(), y.detach().float(), x.grad.clone(), delta.grad.clone(), w.grad.clone(), b.grad.clone())
+    assert got[3].dtype == dt
+    x.grad = delta.grad = w.grad = b.grad = None
+    d32 = delta.detach().float().requires_grad_(True)
+    r_ref = x + d32
+    y_ref = F.layer_norm(r_ref, (d,), w, b, 1e-5)
+    torch.autograd.backward([r_ref, y_ref], [dres, dy.float()])
+    tol = {torch.float32: 1e-5, torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11}[dt]
+    assert float((got[0] - r_ref.detach()).abs().max() / r_ref.detach().abs().max()) <= 1e-6
+    assert float((got[1] - y_ref.detach()).abs().max() / y_ref.detach().abs().max()) <= tol
+    assert float((got[2] - x.grad).abs().max() / x.grad.abs().max()) <= 2e-5
+    assert float((got[3].float() - d32.grad).abs().max() / d32.grad.abs().max()) <= max(tol, 2e-5)
+    for a, r in ((got[4], w.grad), (got[5], b.grad)):
+        assert float((a - r).abs().max() / r.abs().max()) <= 2e-5
+    # without a gradient along the residual stream (the last norm of a model)
+    x.grad = delta.grad = w.grad = b.grad = None
+    res, y = _add_layer_norm.apply(x, delta, w, b, 1e-5)
+    y.backward(dy)
+    want = torch.autograd.grad(F.layer_norm(x + delta.detach().float(), (d,), w, b, 1e-5), x, dy.float())[0]
+    assert float((x.grad - want).abs().max() / want.abs().max()) <= 2e-5
+
+
+def test_layer_norm_affine_gradients_added_into_existing_buffers():
+    """accumulate_into_grad: gamma / beta gradients are added by the kernel to the float32 .grad buffers in place (two
+    backward passes add up); autograd hands nothing over."""
+    from sparse.train_ops import LayerNorm, add_layer_norm
+    torch.manual_seed(2)
+    a, b = LayerNorm(384).to(DEV), LayerNorm(384).to(DEV)
+    b.accumulate_into_grad = True
+    b.weight.grad, b.bias.grad = torch.zeros_like(b.weight), torch.zeros_like(b.bias)
+    bufs = (b.weight.grad, b.bias.grad)
+    x = torch.randn(50, 384, device=DEV)
+    delta = torch.randn(50, 384, device=DEV)
+    for _ in range(2):
+        for ln in (a, b):
+            ln(x).square().sum().backward()
+            add_layer_norm(x, delta, ln)[1].square().sum().backward()
+    assert b.weight.grad is bufs[0] and b.bias.grad is bufs[1]
+    assert float((a.weight.grad - b.weight.grad).abs().max() / a.weight.grad.abs().max()) < 1e-5
+    assert float((a.bias.grad - b.bias.grad).abs().max() / a.bias.grad.abs().max()) < 1e-5
+
+
+def test_token_and_position_embedding_kernels():
+    """sp24_embedding_fwd / _bwd against nn.Embedding + autograd: the forward sum is exact; the gradient tables agree to
+    float32 summation order (1e-6 of the largest entry), repeated tokens included; into_grad adds into existing buffers."""
+    from sparse.train_ops import embed_tokens
+    g = torch.Generator().manual_seed(9)
+    vocab, t, d, batch = 1000, 48, 192, 6
+    wte = torch.randn(vocab, d, generator=g).to(DEV).requires_grad_(True)
+    wpe = torch.randn(64, d, generator=g).to(DEV).requires_grad_(True)          # more positions than t
+    ids = torch.randint(0, 40, (batch, t), generator=g).to(DEV)                  # few distinct tokens: many collisions
+    ids[0, 0] = vocab - 1
+    dy = torch.randn(batch, t, d, generator=g).to(DEV)
+    out = embed_tokens(ids, wte, wpe)
+    ref = F.embedding(ids, wte) + F.embedding(torch.arange(t, device=DEV), wpe)
+    assert torch.equal(out, ref)
+    out.backward(dy)
+    got = (wte.grad.clone(), wpe.grad.clone())
+    wte.grad = wpe.grad = None
+    ref.backward(dy)
+    for a, r in zip(got, (wte.grad, wpe.grad)):
+        assert float((a - r).abs().max() / r.abs().max()) < 1e-6
+    bufs = (wte.grad, wpe.grad)                                                  # now holding one gradient each
+    embed_tokens(ids, wte, wpe, into_grad=True).backward(dy)
+    assert wte.grad is bufs[0] and wpe.grad is bufs[1]
+    assert float((wte.grad - 2 * got[0]).abs().max() / got[0].abs().max()) < 2e-6
+    with pytest.raises(RuntimeError):
+        embed_tokens(ids.int(), wte, wpe)
+    with pytest.raises(RuntimeError):
+        embed_tokens(torch.zeros(2, 65, dtype=torch.long, device=DEV), wte, wpe)
+
+
+def test_add_layer_norm_wrapper_and_fallback():
+    from sparse.train_ops import add_layer_norm, LayerNorm
+    ln = LayerNorm(256).to(DEV)
+    x = torch.randn(2, 9, 256, device=DEV)
+    delta = torch.randn(2, 9, 256, device=DEV)
+    res, y = add_layer_norm(x, delta, ln)                          # float32 outside autocast: the kernel
+    assert torch.allclose(res, x + delta) and torch.allclose(y, F.layer_norm(x + delta, (256,), ln.weight, ln.bias), atol=1e-5)
+    with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+        res, y = add_layer_norm(x, delta.bfloat16(), ln)
+        assert res.dtype == torch.float32 and y.dtype == torch.bfloat16
+        res2, y2 = add_layer_norm(x, delta, ln)                    # float32 branch under autocast: the separate ops
+        assert torch.allclose(res2, x + delta)
+    odd = torch.nn.LayerNorm(100).to(DEV)
+    z = torch.randn(3, 100, device=DEV)
+    r, o = add_layer_norm(z, z, odd)
+    assert torch.allclose(r, 2 * z) and torch.allclose(o, odd(2 * z))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,v,fused", [(37, 512, True), (256, 50304, True), (64, 65536, True), (256, 50304, False),
+                                          (37, 512, False)])
+def test_cross_entropy_fused_gradient_for_unit_upstream(dt, rows, v, fused):
+    """loss.backward() directly on the loss (upstream gradient 1): the fused form writes the gradient in its forward
+    launch (row staged in shared memory up to 110 KB, re-read beyond: v = 65536); one rounding of the logits' type."""
+    from sparse.train_ops import cross_entropy
+    g = torch.Generator().manual_seed(rows + v + 1)
+    logits = (torch.randn(rows, v, generator=g) * 3).to(dt).to(DEV).requires_grad_(True)
+    tgt = torch.randint(0, v, (rows,), generator=g).to(DEV)
+    loss = cross_entropy(logits, tgt, fused=fused)
+    loss.backward()
+    l32 = logits.detach().float().requires_grad_(True)
+    ref = F.cross_entropy(l32, tgt)
+    ref.backward()
+    assert abs(float(loss) - float(ref)) <= 1e-5 * abs(float(ref))
+    tol = {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11}[dt]
+    assert float((logits.grad.float() - l32.grad).abs().max() / l32.grad.abs().max()) <= tol
+    with torch.no_grad():                                          # no gradient wanted: the forward-only kernel
+        assert abs(float(cross_entropy(logits, tgt)) - float(ref)) <= 1e-5 * abs(float(ref))
+
+
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows,v", [(37, 512), (256, 50304)])
 def test_cross_entropy_kernels_match_torch_fp32(dt, rows, v):
     """sp24_cross_entropy_fwd / _bwd against F.cross_entropy on the float32 copy of the same 16-bit logits: loss within
     1e-5 relative (float32 summation order), gradient within one rounding of the logits' type of the fp32 gradient
-    (2^-8 / 2^-11 of the largest magnitude), including a scaled upstream gradient and a padded row pitch."""
+    (2^-8 / 2^-11 of the largest magnitude), including a scaled upstream gradient and a padded row pitch.  The fused
+    form rounds twice when the upstream gradient is not 1 (once in the forward launch, once when rescaled): two
+    roundings, 2^-7 / 2^-10."""
     from sparse.train_ops import cross_entropy
     g = torch.Generator().manual_seed(rows + v)
     buf = torch.zeros(rows, v + 16, dtype=dt, device=DEV)
@@ -719,12 +851,14 @@ def test_cross_entropy_kernels_match_torch_fp32(dt, rows, v):
     logits.copy_((torch.randn(rows, v, generator=g) * 3).to(dt))
     logits.requires_grad_(True)
     tgt = torch.randint(0, v, (rows,), generator=g).to(DEV)
-    loss = cross_entropy(logits, tgt)
-    (loss * 0.37).backward()
     l32 = logits.detach().float().contiguous().requires_grad_(True)
     ref = F.cross_entropy(l32, tgt)
     (ref * 0.37).backward()
-    assert abs(float(loss) - float(ref)) <= 1e-5 * abs(float(ref))
-    tol = {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11}[dt]
-    assert float((logits.grad.float() - l32.grad).abs().max() / l32.grad.abs().max()) <= tol
-    assert logits.grad.dtype == dt
+    for fused, roundings in ((False, 1), (True, 2)):
+        logits.grad = None
+        loss = cross_entropy(logits, tgt, fused=fused)
+        (loss * 0.37).backward()
+        assert abs(float(loss) - float(ref)) <= 1e-5 * abs(float(ref))
+        tol = roundings * {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11}[dt]
+        assert float((logits.grad.float() - l32.grad).abs().max() / l32.grad.abs().max()) <= tol
+        assert logits.grad.dtype == dt
