@@ -105,76 +105,79 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const float *x, cons
 // dx = rstd * (g dy - mean(g dy) - xhat mean(g dy xhat)) (+ dres);  dgamma += sum_rows dy xhat;  dbeta += sum_rows dy.
 // dres (optional): the gradient that reaches the norm's input along the residual stream, added before the store;
 // ddelta (optional): the same dx again in dy's element type, the gradient of the branch that was added in front.
-// Persistent warps: each walks rows warp, warp + nwarps, ... and keeps its column sums in registers; one reduction
-// over the block's eight warps in shared memory, then one atomic per column and block.
+// Persistent warps: each walks rows warp, warp + nwarps, ... and keeps its column sums in its own slice of shared
+// memory; one reduction over the block's eight warps at the end, then one atomic per column and block.
+// The kernel is bound by the latency of a row's two dependent memory round trips (statistics, then outputs), so what
+// counts is the number of rows in flight: with the column sums in shared memory instead of registers a thread needs
+// under 64 registers and an SM holds 32 warps instead of 16; they form ONE block per SM (LnBwdWarps<NV> warps: 32 up
+// to d = 768, 16 beyond, by the shared memory their sums take), so that the closing atomics are one set per SM.
+// A row is read twice: once for the two row-wide sums and the column sums, once more (L1 / L2) together with the
+// residual-stream gradient.  (L2 prefetches of that gradient and of the warp's next row made it slower.)
+template <int NV> struct LnBwdWarps { static constexpr int value = NV <= 6 ? 32 : 16; };
+
 template <typename TDy, int NV>
-__global__ void __launch_bounds__(256, 2) layernorm_bwd_kernel(const TDy *dy, const float *x, const float *gamma, const float *mean,
-                                                               const float *rstd, const float *dres, float *dx, TDy *ddelta,
-                                                               float *dgamma, float *dbeta, int64_t rows) {
-    extern __shared__ float red[];           // 2 x 8 x d floats
-    constexpr int d = NV * 128, nv = NV;
+__global__ void __launch_bounds__(32 * LnBwdWarps<NV>::value, 1)
+    layernorm_bwd_kernel(const TDy *dy, const float *x, const float *gamma, const float *mean, const float *rstd, const float *dres,
+                         float *dx, TDy *ddelta, float *dgamma, float *dbeta, int64_t rows) {
+    extern __shared__ float red[];           // 2 x W x d floats: [gamma sums | beta sums] x warp x column
+    constexpr int d = NV * 128, W = LnBwdWarps<NV>::value;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // Registers: only the two column sums (2 x NV float4) stay for the whole kernel.  A row is read twice: once for the
-    // two row-wide sums and the column sums, once more (from L1, where the first pass left it) together with the
-    // residual-stream gradient for the outputs.  Keeping the row in registers between the passes instead costs 155
-    // registers at d = 768, i.e. one resident block per SM and half the bandwidth.
-    float4 ag[NV], ab[NV];
+    float4 *ag = reinterpret_cast<float4 *>(red + warp * d) + lane;
+    float4 *ab = reinterpret_cast<float4 *>(red + W * d + warp * d) + lane;
 #pragma unroll
-    for (int i = 0; i < NV; ++i)
-        if (i < nv) {
-            ag[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            ab[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    for (int i = 0; i < NV; ++i) {
+        ag[i * 32] = make_float4(0.f, 0.f, 0.f, 0.f);
+        ab[i * 32] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     const float4 *g4 = reinterpret_cast<const float4 *>(gamma) + lane;
-    const int64_t nwarps = (int64_t)gridDim.x * 8;
-    for (int64_t row = (int64_t)blockIdx.x * 8 + warp; row < rows; row += nwarps) {
+    const int64_t nwarps = (int64_t)gridDim.x * W;
+    for (int64_t row = (int64_t)blockIdx.x * W + warp; row < rows; row += nwarps) {
         const float mu = mean[row], rs = rstd[row];
+        const float shift = -mu * rs;
         const int64_t base = row * d + lane * 4;
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-        for (int i = 0; i < NV; ++i)
-            if (i < nv) {
-                const float4 xv = load4<float>(x + base + i * 128);
-                const float4 dv = load4<TDy>(dy + base + i * 128);
-                const float4 g = __ldg(g4 + i * 32);
-                const float4 xh = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
-                const float4 gy = make_float4(dv.x * g.x, dv.y * g.y, dv.z * g.z, dv.w * g.w);
-                s1 += (gy.x + gy.y) + (gy.z + gy.w);
-                s2 += (gy.x * xh.x + gy.y * xh.y) + (gy.z * xh.z + gy.w * xh.w);
-                ag[i].x += dv.x * xh.x; ag[i].y += dv.y * xh.y; ag[i].z += dv.z * xh.z; ag[i].w += dv.w * xh.w;
-                ab[i].x += dv.x; ab[i].y += dv.y; ab[i].z += dv.z; ab[i].w += dv.w;
-            }
-        const float m1 = warp_sum(s1) / (float)d, m2 = warp_sum(s2) / (float)d;
-#pragma unroll
-        for (int i = 0; i < NV; ++i)
-            if (i < nv) {
-                const int64_t at = base + i * 128;
-                const float4 xv = load4<float>(x + at);
-                const float4 dv = load4<TDy>(dy + at);
-                const float4 g = __ldg(g4 + i * 32);
-                float4 o = make_float4(rs * (dv.x * g.x - m1 - (xv.x - mu) * rs * m2), rs * (dv.y * g.y - m1 - (xv.y - mu) * rs * m2),
-                                       rs * (dv.z * g.z - m1 - (xv.z - mu) * rs * m2), rs * (dv.w * g.w - m1 - (xv.w - mu) * rs * m2));
-                if (dres) {
-                    const float4 r = load4<float>(dres + at);
-                    o = make_float4(o.x + r.x, o.y + r.y, o.z + r.z, o.w + r.w);
-                }
-                store4<float>(dx + at, o.x, o.y, o.z, o.w);
-                if (ddelta) store4<TDy>(ddelta + at, o.x, o.y, o.z, o.w);
-            }
-    }
-    float *rg = red, *rb = red + 8 * d;
-#pragma unroll
-    for (int i = 0; i < NV; ++i)
-        if (i < nv) {
-            const int c0 = (i * 32 + lane) * 4;
-            *reinterpret_cast<float4 *>(rg + warp * d + c0) = ag[i];
-            *reinterpret_cast<float4 *>(rb + warp * d + c0) = ab[i];
+        for (int i = 0; i < NV; ++i) {
+            const float4 xv = load4<float>(x + base + i * 128);
+            const float4 dv = load4<TDy>(dy + base + i * 128);
+            const float4 g = __ldg(g4 + i * 32);
+            const float4 xh = make_float4(fmaf(xv.x, rs, shift), fmaf(xv.y, rs, shift), fmaf(xv.z, rs, shift), fmaf(xv.w, rs, shift));
+            const float4 gy = make_float4(dv.x * g.x, dv.y * g.y, dv.z * g.z, dv.w * g.w);
+            s1 += (gy.x + gy.y) + (gy.z + gy.w);
+            s2 += (gy.x * xh.x + gy.y * xh.y) + (gy.z * xh.z + gy.w * xh.w);
+            float4 a = ag[i * 32], b = ab[i * 32];
+            a.x = fmaf(dv.x, xh.x, a.x); a.y = fmaf(dv.y, xh.y, a.y); a.z = fmaf(dv.z, xh.z, a.z); a.w = fmaf(dv.w, xh.w, a.w);
+            b.x += dv.x; b.y += dv.y; b.z += dv.z; b.w += dv.w;
+            ag[i * 32] = a;
+            ab[i * 32] = b;
         }
+        const float m1 = warp_sum(s1) / (float)d, m2 = warp_sum(s2) / (float)d;
+        const float c1 = -rs * m1, c2 = -rs * m2;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int64_t at = base + i * 128;
+            const float4 xv = load4<float>(x + at);
+            const float4 dv = load4<TDy>(dy + at);
+            const float4 g = __ldg(g4 + i * 32);
+            // rs (g dy - m1 - xhat m2) = (rs g) dy + c1 + c2 xhat
+            float4 o = make_float4(fmaf(c2, fmaf(xv.x, rs, shift), fmaf(rs * g.x, dv.x, c1)),
+                                   fmaf(c2, fmaf(xv.y, rs, shift), fmaf(rs * g.y, dv.y, c1)),
+                                   fmaf(c2, fmaf(xv.z, rs, shift), fmaf(rs * g.z, dv.z, c1)),
+                                   fmaf(c2, fmaf(xv.w, rs, shift), fmaf(rs * g.w, dv.w, c1)));
+            if (dres) {
+                const float4 r = load4<float>(dres + at);
+                o = make_float4(o.x + r.x, o.y + r.y, o.z + r.z, o.w + r.w);
+            }
+            store4<float>(dx + at, o.x, o.y, o.z, o.w);
+            if (ddelta) store4<TDy>(ddelta + at, o.x, o.y, o.z, o.w);
+        }
+    }
+    const float *rg = red, *rb = red + W * d;
     __syncthreads();
-    for (int c = threadIdx.x; c < d; c += 256) {
+    for (int c = threadIdx.x; c < d; c += 32 * W) {
         float sg = 0.f, sb = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
+        for (int w = 0; w < W; ++w) {
             sg += rg[w * d + c];
             sb += rb[w * d + c];
         }
@@ -231,7 +234,8 @@ __global__ void __launch_bounds__(256) ce_fwd_kernel(const T *logits, const int6
     if (threadIdx.x == 0) {
         const float l = gm + logf(gs);
         lse[row] = l;
-        loss[row] = l - Elem<T>::to_f32(p[targets[row]]);
+        const int64_t tgt = targets[row];
+        loss[row] = (tgt >= 0 && tgt < v) ? l - Elem<T>::to_f32(p[tgt]) : 0.f;     // a target outside [0, v) reads nothing
     }
 }
 
@@ -262,54 +266,90 @@ __global__ void __launch_bounds__(256) ce_bwd_kernel(const T *logits, const int6
     }
 }
 
-// Forward and gradient in one kernel: the row is read from HBM once, kept in shared memory (STAGED; otherwise re-read,
-// mostly from L2), and the gradient for an upstream gradient of 1 is written in the same launch:
-// dlogits[row, c] = (exp(logits[row, c] - lse[row]) - [c == target[row]]) * scale.
+// Forward and gradient in one kernel: the row is read from HBM once and the gradient for an upstream gradient of 1 is
+// written in the same launch: dlogits[row, c] = (exp(logits[row, c] - lse[row]) - [c == target[row]]) * scale.
+// STAGED: the whole row is brought into shared memory by asynchronous 16-byte copies, all issued before the first
+// wait (one memory round trip per row and block, two blocks per SM), and the three passes (maximum, sum, gradient)
+// read it from there; otherwise (rows beyond the shared-memory budget) the passes re-read the row, mostly from L2.
+// The kernel is bound by instruction issue and the exponential unit, not by memory, unless the passes are lean: the
+// maximum is taken on packed 16-bit pairs, an exponential is one multiply-add (log2 e and the offset folded) plus one
+// ex2, the gradient's scale rides in that offset, and the target's -1 is patched in by one thread afterwards instead
+// of being compared for in every element.
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+template <typename T> struct Pair16;
+template <> struct Pair16<__nv_bfloat16> {
+    typedef __nv_bfloat162 type;
+    static __device__ __forceinline__ void unpack(uint32_t w, float &lo, float &hi) {
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xFFFF0000u);
+    }
+    static __device__ __forceinline__ type lowest() { return __float2bfloat162_rn(-INFINITY); }
+};
+template <> struct Pair16<__half> {
+    typedef __half2 type;
+    static __device__ __forceinline__ void unpack(uint32_t w, float &lo, float &hi) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+        lo = f.x;
+        hi = f.y;
+    }
+    static __device__ __forceinline__ type lowest() { return __float2half2_rn(-INFINITY); }
+};
+
 template <typename T, bool STAGED>
 __global__ void __launch_bounds__(512) ce_fused_kernel(const T *logits, const int64_t *targets, float *lse, float *loss,
                                                        float scale, T *dlogits, int64_t v, int64_t ld, int64_t ld_out) {
     extern __shared__ uint4 staged[];        // the row as 16-byte pieces (STAGED only)
     __shared__ float scratch[16];
+    typedef typename Pair16<T>::type P2;
+    constexpr float L2E = 1.4426950408889634f;
     const int64_t row = blockIdx.x;
-    const T *p = logits + row * ld;
-    T *q = dlogits + row * ld_out;
-    const int64_t nvec = v / 8;
+    const uint4 *p = reinterpret_cast<const uint4 *>(logits + row * ld);
+    uint4 *q = reinterpret_cast<uint4 *>(dlogits + row * ld_out);
+    const int nvec = (int)(v / 8);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float m = -INFINITY, s = 0.f;
-    for (int64_t i0 = threadIdx.x; i0 < nvec; i0 += 4 * 512) {          // four 16-byte loads in flight per thread
-        uint4 r[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int64_t i = i0 + u * 512;
-            if (i < nvec) r[u] = *reinterpret_cast<const uint4 *>(p + i * 8);
+    if (STAGED) {
+        for (int i = threadIdx.x; i < nvec; i += 512) {
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(staged + i);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(p + i) : "memory");
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int64_t i = i0 + u * 512;
-            if (i >= nvec) break;
-            if (STAGED) staged[i] = r[u];
-            float f[8];
-            unpack8<T>(r[u], f);
-            float vm = f[0];
-#pragma unroll
-            for (int j = 1; j < 8; ++j) vm = fmaxf(vm, f[j]);
-            const float nm = fmaxf(m, vm);
-            float acc = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc += __expf(f[j] - nm);
-            s = s * __expf(m - nm) + acc;
-            m = nm;
-        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        // every pass below gives a thread the pieces it copied itself: no barrier needed before reading them
     }
-    // block reductions over 16 warps
-    float wm = warp_max(m);
+    // pass 1: maximum, on packed pairs (exact)
+    P2 m2 = Pair16<T>::lowest();
+    for (int i = threadIdx.x; i < nvec; i += 512) {
+        const uint4 r = STAGED ? staged[i] : p[i];
+        const P2 *h = reinterpret_cast<const P2 *>(&r);
+        m2 = __hmax2(__hmax2(m2, h[0]), __hmax2(h[1], __hmax2(h[2], h[3])));
+    }
+    float lo, hi;
+    Pair16<T>::unpack(*reinterpret_cast<const uint32_t *>(&m2), lo, hi);
+    const float wm = warp_max(fmaxf(lo, hi));
     if (lane == 0) scratch[warp] = wm;
     __syncthreads();
     float gm = scratch[0];
 #pragma unroll
     for (int w = 1; w < 16; ++w) gm = fmaxf(gm, scratch[w]);
     __syncthreads();
-    const float ws = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - gm));
+    // pass 2: sum of exp(x - max)
+    const float off1 = -gm * L2E;
+    float s0 = 0.f, s1 = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += 512) {
+        const uint4 r = STAGED ? staged[i] : p[i];
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            Pair16<T>::unpack(w[j], lo, hi);
+            s0 += ex2_fast(fmaf(lo, L2E, off1));
+            s1 += ex2_fast(fmaf(hi, L2E, off1));
+        }
+    }
+    const float ws = warp_sum(s0 + s1);
     if (lane == 0) scratch[warp] = ws;
     __syncthreads();
     float gs = 0.f;
@@ -317,23 +357,33 @@ __global__ void __launch_bounds__(512) ce_fused_kernel(const T *logits, const in
     for (int w = 0; w < 16; ++w) gs += scratch[w];
     const float l = gm + logf(gs);
     const int64_t tgt = targets[row];
+    const bool tgt_ok = tgt >= 0 && tgt < v;
+    const T *pe = reinterpret_cast<const T *>(p);
     if (threadIdx.x == 0) {
         lse[row] = l;
-        loss[row] = l - Elem<T>::to_f32(p[tgt]);
+        loss[row] = tgt_ok ? l - Elem<T>::to_f32(pe[tgt]) : 0.f;      // a target outside [0, v) reads nothing
     }
-    for (int64_t i = threadIdx.x; i < nvec; i += 512) {
-        float f[8];
-        unpack8<T>(STAGED ? staged[i] : *reinterpret_cast<const uint4 *>(p + i * 8), f);
+    // pass 3: scale * exp(x - lse) = ex2(x log2 e - lse log2 e + log2 scale)   (scale = 0 gives ex2(-inf) = 0)
+    const float off2 = fmaf(-l, L2E, log2f(scale));
+    for (int i = threadIdx.x; i < nvec; i += 512) {
+        const uint4 r = STAGED ? staged[i] : p[i];
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(&r);
         uint4 o;
         uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int64_t c = i * 8 + 2 * j;
-            const float a = (__expf(f[2 * j] - l) - (c == tgt ? 1.f : 0.f)) * scale;
-            const float b = (__expf(f[2 * j + 1] - l) - (c + 1 == tgt ? 1.f : 0.f)) * scale;
-            ow[j] = Elem<T>::pack2(a, b);
+            Pair16<T>::unpack(w[j], lo, hi);
+            ow[j] = Elem<T>::pack2(ex2_fast(fmaf(lo, L2E, off2)), ex2_fast(fmaf(hi, L2E, off2)));
         }
-        *reinterpret_cast<uint4 *>(q + i * 8) = o;
+        q[i] = o;
+    }
+    if (tgt_ok) {
+        __syncthreads();                                            // the vector holding the target's entry is written
+        if (threadIdx.x == 0) {
+            const float x = Elem<T>::to_f32(STAGED ? reinterpret_cast<const T *>(staged)[tgt] : pe[tgt]);
+            const uint16_t one = (uint16_t)(Elem<T>::pack2(ex2_fast(fmaf(x, L2E, off2)) - scale, 0.f) & 0xFFFFu);
+            reinterpret_cast<uint16_t *>(q)[tgt] = one;
+        }
     }
 }
 
@@ -448,13 +498,14 @@ static int layernorm_bwd_impl(const void *dy, int dy_dtype, const float *dres, c
         return SP24_ERR_ALIGN;
     if (int rc = check_device()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const size_t smem = (size_t)2 * 8 * d * sizeof(float);       // at most 64 KB (d = 1024)
     static bool attr_set[3][8][64];
     int dev = 0;
     cudaGetDevice(&dev);
     const int which = dy_dtype == SP24_F32 ? 0 : (dy_dtype == SP24_F16 ? 1 : 2);
 #define SP24_LN_BWD(T_, NV_) \
     do { \
+        constexpr int W = LnBwdWarps<NV_>::value; \
+        const size_t smem = (size_t)2 * W * d * sizeof(float);           /* 32 warps x 6 KB = 192 KB at d = 768 */ \
         auto kern = layernorm_bwd_kernel<T_, NV_>; \
         if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !attr_set[which][NV_ - 1][dev]) { \
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
@@ -462,11 +513,11 @@ static int layernorm_bwd_impl(const void *dy, int dy_dtype, const float *dres, c
             attr_set[which][NV_ - 1][dev] = true; \
         } \
         int resident = 0;                                                /* persistent grid: every block resident at once */ \
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, 256, smem) != cudaSuccess || resident < 1) resident = 1; \
-        int64_t blocks = (rows + 7) / 8; \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, 32 * W, smem) != cudaSuccess || resident < 1) resident = 1; \
+        int64_t blocks = (rows + W - 1) / W; \
         const int64_t cap = (int64_t)sm_count() * resident; \
         if (blocks > cap) blocks = cap; \
-        kern<<<(unsigned)blocks, 256, smem, st>>>(static_cast<const T_ *>(dy), x, gamma, mean, rstd, dres, dx, \
+        kern<<<(unsigned)blocks, 32 * W, smem, st>>>(static_cast<const T_ *>(dy), x, gamma, mean, rstd, dres, dx, \
                                                   static_cast<T_ *>(ddelta), dgamma, dbeta, rows); \
     } while (0)
 #define SP24_LN_BWD_NV(T_) \
@@ -563,7 +614,8 @@ extern "C" int sp24_cross_entropy_fused(const void *logits, int dtype, const int
     if (rows <= 0 || v <= 0 || v % 8) return SP24_ERR_SHAPE;
     if (ld < v || ld % 8 || ld_out < v || ld_out % 8) return SP24_ERR_STRIDE;
     if (!aligned16(logits) || !aligned16(dlogits)) return SP24_ERR_ALIGN;
-    if (rows > 0x7FFFFFFF) return SP24_ERR_TOO_LARGE;
+    if (!(scale >= 0.f) || !(scale < INFINITY)) return SP24_ERR_ARG;
+    if (rows > 0x7FFFFFFF || v / 8 > 0x7FFFFFFF) return SP24_ERR_TOO_LARGE;
     if (int rc = check_device()) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return dtype == SP24_F16 ? ce_fused_launch<__half>(logits, targets, lse, loss, scale, dlogits, rows, v, ld, ld_out, st)

@@ -378,16 +378,30 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         loss.backward()
         return loss.detach()
 
-    def update():
+    seg_args = list(zip(bounds, (0.1, 0.0, 0.0), (False, True, False)))     # embeddings, sparse weights, everything else
+
+    def update_segment(which):
+        (a, b), wd, use_mask = seg_args[which]
+        if b > a:
+            sparse.adamw_masked_decay_(flat_p[a:b], flat[a:b], flat_m[a:b], flat_v[a:b], step=step_dev, lr=lr,
+                                       betas=(0.9, 0.95), eps=1e-8, weight_decay=wd,
+                                       mask=flat_mask if (use_mask and mode == "sparse") else None,
+                                       alpha=alpha if use_mask else 0.0)
+
+    def update_blocks():
+        # everything but the embeddings: needs only the block groups' exchanges
         step_dev.add_(1)
+        update_segment(1)
+        update_segment(2)
+
+    def update_embeddings():
         if head_grad is not None:
             model.wte.weight.grad.add_(head_grad)      # the (already averaged) head share joins the lookup share
-        for (a, b), wd, use_mask in zip(bounds, (0.1, 0.0, 0.0), (False, True, False)):
-            if b > a:
-                sparse.adamw_masked_decay_(flat_p[a:b], flat[a:b], flat_m[a:b], flat_v[a:b], step=step_dev, lr=lr,
-                                           betas=(0.9, 0.95), eps=1e-8, weight_decay=wd,
-                                           mask=flat_mask if (use_mask and mode == "sparse") else None,
-                                           alpha=alpha if use_mask else 0.0)
+        update_segment(0)
+
+    def update():
+        update_blocks()
+        update_embeddings()
 
     def next_tokens():
         if global_stream:
@@ -424,6 +438,7 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
     ready = [torch.cuda.Event(external=True) for _ in range(max(n_ready, 0))]
     head_ready = torch.cuda.Event(external=True) if (world > 1 and split_head) else None
     tail = torch.cuda.Event()
+    blocks_done = torch.cuda.Event()     # recorded on the exchange stream before the last (embeddings-only) group
     if world > 1 and split_head:
         model.head_ready = head_ready.record
     if n_groups > 1:
@@ -446,7 +461,16 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
             dist.all_reduce(stage[a:b], op=dist.ReduceOp.AVG)
             flat[a:b].copy_(stage[a:b])
 
-    def reduce_grads():
+    def reduce_grads(before_embeddings=None):
+        """Issues the exchanges.  ``before_embeddings`` (a callable) is run on the main stream once every group but the
+        last, embeddings-only one has been exchanged, i.e. beside that last exchange: the update of all other
+        parameters hides the one exchange that cannot overlap the backward pass."""
+        overlap_update = before_embeddings is not None and world > 1 and comm is not None and emb_alone
+        if not overlap_update and before_embeddings is not None:
+            if world > 1:
+                reduce_grads()
+            before_embeddings()
+            return
         if world == 1:
             return
         main = torch.cuda.current_stream()
@@ -459,9 +483,14 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
                 comm.wait_event(head_ready)
                 dist.all_reduce(head_grad, op=dist.ReduceOp.AVG)
             for g_ in range(n_groups):
+                if overlap_update and g_ == n_groups - 1:
+                    blocks_done.record(comm)
                 comm.wait_event(ready[g_] if g_ < n_ready else tail)
                 for a, b in slices[g_]:
                     exchange(a, b)
+        if overlap_update:
+            main.wait_event(blocks_done)
+            before_embeddings()
         main.wait_stream(comm)
 
     # eager warm-up on a side stream (allocator, cuBLAS workspaces, optimizer state, kernel attributes)
@@ -486,16 +515,18 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         with torch.cuda.graph(g, pool=pool):
             losses_static[key] = fwd_bwd()
         graphs[key] = g
-    g_upd = torch.cuda.CUDAGraph()
+    g_upd, g_upd_emb = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
     with torch.cuda.graph(g_upd, pool=pool):
-        update()
+        update_blocks()
+    with torch.cuda.graph(g_upd_emb, pool=pool):
+        update_embeddings()
 
     def one_step(i):
         next_tokens()
         key = (mode == "sparse") and (i % freq == 0)
         graphs[key].replay()
-        reduce_grads()
-        g_upd.replay()
+        reduce_grads(g_upd.replay)
+        g_upd_emb.replay()
         return losses_static[key]
 
     it = 0
@@ -535,7 +566,7 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         from sparse.spmm import check_status
         check_status()
     set_device_rng_offset(None)
-    del graphs, g_upd, model, flat, flat_p, flat_m, flat_v
+    del graphs, g_upd, g_upd_emb, model, flat, flat_p, flat_m, flat_v
     torch.cuda.empty_cache()
     if own_group:
         dist.destroy_process_group()

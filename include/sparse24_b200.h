@@ -403,6 +403,7 @@ int sp24_add_layernorm_bwd(const void *dy, int dy_dtype, const float *dres, cons
  *   backward: dlogits[row, c] = (exp(logits[row, c] - lse[row]) - [c == target[row]]) * scale * (*upstream),
  *             upstream a device float (the gradient of the summed loss) or NULL for 1; scale e.g. 1 / rows for a mean.
  *             dlogits has the logits' type and may alias logits.
+ * A target outside [0, v) reads no logit: its row's loss is 0 and no entry of its gradient row has the 1 subtracted.
  */
 int sp24_cross_entropy_fwd(const void *logits, int dtype, const int64_t *targets, float *lse, float *loss, int64_t rows,
                            int64_t v, int64_t ld, void *stream);
@@ -412,7 +413,8 @@ int sp24_cross_entropy_bwd(const void *logits, int dtype, const int64_t *targets
 /*
  * Both passes in one launch, for a loss whose upstream gradient is 1 (a training loss that is differentiated directly):
  * lse and loss as the forward above, and dlogits = (softmax - onehot) * scale written from the same read of the row
- * (kept in shared memory when it fits: v * 2 bytes <= 110 KB; otherwise re-read).  dlogits may alias logits.
+ * (kept in shared memory when it fits: v * 2 bytes <= 110 KB; otherwise re-read).  dlogits may alias logits;
+ * scale >= 0 and finite.
  * sp24_scale_unless_one multiplies `count` 16-bit values (count % 8 == 0) by the device float *factor, and does
  * nothing (no read, no write) when that is exactly 1: the backward pass of the fused form.
  */
