@@ -1,5 +1,4 @@
 // Library-wide pieces of the C ABI: error strings, version, device check.
-#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 
@@ -21,10 +20,7 @@ int check_device() {
     return ok ? SP24_OK : SP24_ERR_DEVICE;
 }
 
-// SMs the persistent kernels may size their grids for (0 = all of the device); see sp24_set_sm_budget.
-static std::atomic<int> g_sm_budget{0};
-
-// Number of SMs of the current device (cached per device ordinal; 148 if the query fails), capped by the budget.
+// Number of SMs of the current device (cached per device ordinal; 148 if the query fails).
 int sm_count() {
     static int cached[64];
     int dev = 0;
@@ -34,8 +30,7 @@ int sm_count() {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
         cached[dev] = n;
     }
-    const int budget = g_sm_budget.load(std::memory_order_relaxed);
-    return budget > 0 && budget < cached[dev] ? budget : cached[dev];
+    return cached[dev];
 }
 
 int launch_status() {
@@ -63,8 +58,3 @@ extern "C" const char *sp24_strerror(int code) {
 }
 
 extern "C" int sp24_abi_version(void) { return 2; }
-
-extern "C" int sp24_set_sm_budget(int sms) {
-    if (sms < 0) return SP24_ERR_ARG;
-    return sp24::g_sm_budget.exchange(sms & ~1);
-}

@@ -61,7 +61,6 @@ _SIGNATURES = {
     "sp24_scale_unless_one": [_vp, _i32, _vp, _i64, _vp],
     "sp24_embedding_fwd": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp],
     "sp24_embedding_bwd": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp],
-    "sp24_set_sm_budget": [_i32],
 }
 
 
@@ -87,16 +86,6 @@ def lib():
                 fn.argtypes = args
         _lib = h
     return _lib
-
-
-def set_sm_budget(sms: int) -> int:
-    """SMs the persistent GEMM kernels size their grids for (0 = all); returns the previous value.  Leave a
-    collective that runs beside the GEMMs its SMs (and cap its CTAs, ``NCCL_MAX_CTAS``): a GEMM grid sized for every
-    SM otherwise runs its last CTAs as a second wave behind the collective's.  Fixed at capture time in a CUDA graph."""
-    rc = lib().sp24_set_sm_budget(int(sms))
-    if rc < 0:
-        check(rc, "sp24_set_sm_budget")
-    return rc
 
 
 def register_signature(name, argtypes):

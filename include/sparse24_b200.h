@@ -66,17 +66,6 @@ const char *sp24_strerror(int code);
 int sp24_abi_version(void);
 
 /*
- * Number of SMs the persistent kernels (the sparse GEMMs: one CTA, or one CTA of a pair, per SM) size their grids
- * for; 0 (the default) = every SM of the device, odd values are rounded down.  For processes that run a
- * collective beside the GEMMs: a collective's CTAs hold SMs for milliseconds, a GEMM CTA (over 200 KB of shared
- * memory) cannot share an SM with them, and a persistent grid sized for all SMs then runs its last CTAs as a
- * second wave, i.e. takes twice as long.  Leaving the collective its SMs (this call) and capping the collective's
- * CTA count (NCCL_MAX_CTAS) removes that wave.  Process-wide, read at launch (so fixed at capture time inside a
- * CUDA graph); returns the previous value, SP24_ERR_ARG for a negative one.  No counterpart in the reference.
- */
-int sp24_set_sm_budget(int sms);
-
-/*
  * Dense -> 2:4 compressed (values + reordered metadata), fused prune + compress + metadata.
  * Replaces sparse_semi_structured_from_dense_triton and the Triton kernels
  * _sparse_semi_structured_from_dense_triton_16 / _8

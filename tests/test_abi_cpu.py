@@ -158,10 +158,6 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.sp24_embedding_fwd(p, q, r, st, 8, 4, 30, 100, None) == -1
     assert lib.sp24_embedding_fwd(p, q, r, None, 8, 4, 32, 100, None) == -5
     assert lib.sp24_embedding_bwd(p, q, ctypes.c_void_p(base + 4), st, 8, 4, 32, 100, None) == -4
-    # SM budget: negative refused; set / read back; odd values rounded down
-    assert lib.sp24_set_sm_budget(-1) == -5
-    assert lib.sp24_set_sm_budget(133) == 0
-    assert lib.sp24_set_sm_budget(0) == 132
 
 
 def test_missing_library_fails_loudly(monkeypatch):
