@@ -426,6 +426,63 @@ __global__ void __launch_bounds__(256) embedding_bwd_kernel(const float *dx, con
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// GELU (tanh form) over 16-bit tensors: 16-byte accesses, float32 arithmetic, tanh.approx
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float gelu_f(float x) {
+    const float u = x * fmaf(0.0356774081f, x * x, 0.7978845608f);          // sqrt(2/pi) (x + 0.044715 x^3)
+    return 0.5f * x * (1.f + tanh_fast(u));
+}
+__device__ __forceinline__ float dgelu_f(float x) {
+    const float x2 = x * x;
+    const float t = tanh_fast(x * fmaf(0.0356774081f, x2, 0.7978845608f));
+    // 0.5 (1 + t) + 0.5 x (1 - t^2) sqrt(2/pi) (1 + 3 * 0.044715 x^2)
+    return fmaf(0.5f * x * (1.f - t * t), fmaf(0.1070322243f, x2, 0.7978845608f), 0.5f * (1.f + t));
+}
+
+// BWD: out = dy * gelu'(x); otherwise out = gelu(x).  Two 16-byte pieces per thread and trip.
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(256) gelu_kernel(const uint4 *x, const uint4 *dy, uint4 *out, int64_t nvec) {
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nvec; i += 2 * stride) {
+        const int64_t i2 = i + stride;
+        const bool two = i2 < nvec;
+        uint4 a0 = x[i], a1, g0, g1;
+        if (two) a1 = x[i2];
+        if (BWD) {
+            g0 = dy[i];
+            if (two) g1 = dy[i2];
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (h == 1 && !two) break;
+            const uint4 &a = h ? a1 : a0;
+            const uint4 &g = h ? g1 : g0;
+            const uint32_t *aw = reinterpret_cast<const uint32_t *>(&a), *gw = reinterpret_cast<const uint32_t *>(&g);
+            uint4 o;
+            uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float lo, hi;
+                Pair16<T>::unpack(aw[j], lo, hi);
+                if (BWD) {
+                    float glo, ghi;
+                    Pair16<T>::unpack(gw[j], glo, ghi);
+                    ow[j] = Elem<T>::pack2(glo * dgelu_f(lo), ghi * dgelu_f(hi));
+                } else {
+                    ow[j] = Elem<T>::pack2(gelu_f(lo), gelu_f(hi));
+                }
+            }
+            out[h ? i2 : i] = o;
+        }
+    }
+}
+
 // g *= *factor unless *factor == 1 (the usual case: nothing is read or written then)
 template <typename T>
 __global__ void __launch_bounds__(256) scale_unless_one_kernel(T *g, const float *factor, int64_t nvec) {
@@ -661,5 +718,28 @@ extern "C" int sp24_embedding_bwd(const float *dx, const int64_t *ids, float *dw
     if (int rc = check_device()) return rc;
     embedding_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(dx, ids, dwte, dwpe, rows, t, d,
                                                                                                      vocab);
+    return launch_status();
+}
+
+extern "C" int sp24_gelu(const void *x, const void *dy, void *out, int dtype, int64_t count, void *stream) {
+    if (!x || !out) return SP24_ERR_ARG;
+    if (dtype != SP24_F16 && dtype != SP24_BF16) return SP24_ERR_DTYPE;
+    if (count <= 0 || count % 8) return SP24_ERR_SHAPE;
+    if (!aligned16(x) || !aligned16(dy) || !aligned16(out)) return SP24_ERR_ALIGN;
+    if (int rc = check_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t nvec = count / 8;
+    int64_t blocks = (nvec + 511) / 512;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    const uint4 *xv = static_cast<const uint4 *>(x), *gv = static_cast<const uint4 *>(dy);
+    uint4 *ov = static_cast<uint4 *>(out);
+    if (dtype == SP24_F16) {
+        if (dy) gelu_kernel<__half, true><<<(unsigned)blocks, 256, 0, st>>>(xv, gv, ov, nvec);
+        else gelu_kernel<__half, false><<<(unsigned)blocks, 256, 0, st>>>(xv, gv, ov, nvec);
+    } else {
+        if (dy) gelu_kernel<__nv_bfloat16, true><<<(unsigned)blocks, 256, 0, st>>>(xv, gv, ov, nvec);
+        else gelu_kernel<__nv_bfloat16, false><<<(unsigned)blocks, 256, 0, st>>>(xv, gv, ov, nvec);
+    }
     return launch_status();
 }

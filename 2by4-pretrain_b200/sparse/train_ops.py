@@ -277,3 +277,34 @@ def embed_tokens(ids: torch.Tensor, wte: torch.Tensor, wpe: torch.Tensor, into_g
     if ids.shape[1] > wpe.shape[0]:
         raise RuntimeError(f"embed_tokens: {ids.shape[1]} positions, the position table holds {wpe.shape[0]}")
     return _embed_tokens.apply(ids, wte, wpe, into_grad)
+
+
+class _gelu(autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        rc = _ext.lib().sp24_gelu(x.data_ptr(), None, out.data_ptr(), _ext.dt(x.dtype), x.numel(), _ext.stream())
+        _ext.check(rc, "sp24_gelu")
+        ctx.save_for_backward(x)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (x,) = ctx.saved_tensors
+        dy = grad_output.contiguous()
+        if dy.dtype != x.dtype:
+            dy = dy.to(x.dtype)
+        out = torch.empty_like(x)
+        rc = _ext.lib().sp24_gelu(x.data_ptr(), dy.data_ptr(), out.data_ptr(), _ext.dt(x.dtype), x.numel(), _ext.stream())
+        _ext.check(rc, "sp24_gelu")
+        return out
+
+
+def gelu(x: torch.Tensor) -> torch.Tensor:
+    """``F.gelu(x, approximate="tanh")`` for 16-bit CUDA tensors with a multiple of 8 elements on the library's streaming
+    kernel (float32 arithmetic, ``tanh.approx``: the formula of the GEMM epilogues); anything else goes to torch."""
+    if not (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and x.numel() % 8 == 0 and x.numel() > 0):
+        return torch.nn.functional.gelu(x, approximate="tanh")
+    _ext.require_cuda(x)
+    return _gelu.apply(x)

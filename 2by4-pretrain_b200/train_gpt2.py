@@ -56,6 +56,13 @@ def _add_norm(x, delta, norm):
     return x, norm(x)
 
 
+def _gelu(x):
+    if FUSED_OPS:
+        from sparse.train_ops import gelu
+        return gelu(x)
+    return F.gelu(x, approximate="tanh")
+
+
 class Block(nn.Module):
     # True: fc + GELU + proj through sparse.fst_mlp (GELU and its gradient in the GEMM epilogues).  Off by default:
     # at d_model 768 the two GEMMs that would carry the extra epilogue work have K = 768, six K steps per tile, and
@@ -88,7 +95,7 @@ class Block(nn.Module):
         if self.fused_mlp:
             import sparse
             return x, sparse.fst_mlp(h, self.fc, self.proj)
-        return x, self.proj(F.gelu(self.fc(h), approximate="tanh"))
+        return x, self.proj(_gelu(self.fc(h)))
 
 
 class _tied_head(torch.autograd.Function):

@@ -412,6 +412,13 @@ int sp24_cross_entropy_fused(const void *logits, int dtype, const int64_t *targe
 int sp24_scale_unless_one(void *g, int dtype, const float *factor, int64_t count, void *stream);
 
 /*
+ * GELU, tanh form, over `count` contiguous 16-bit values (count % 8 == 0), float32 arithmetic:
+ *   dy == NULL: out = gelu(x);   dy != NULL: out = dy * gelu'(x)   (out may alias x or dy).
+ * The same formula as the GEMM epilogues of sp24_spmm / sp24_spmm_mlp (tanh.approx).
+ */
+int sp24_gelu(const void *x, const void *dy, void *out, int dtype, int64_t count, void *stream);
+
+/*
  * Token + learned position embedding of a decoder (float32 tables, d % 4 == 0), one warp per token:
  *   forward:  out[row, :] = wte[ids[row], :] + wpe[row % t, :]          rows = batch * t tokens, ids int64
  *   backward: dwte[ids[row], :] += dx[row, :];  dwpe[row % t, :] += dx[row, :]   (float32 vector reductions: the

@@ -155,6 +155,9 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.sp24_cross_entropy_fused(p, BF16, q, r, st, 1.0, None, 4, 64, 64, 64, None) == -5
     assert lib.sp24_scale_unless_one(p, BF16, None, 64, None) == -5
     assert lib.sp24_scale_unless_one(p, BF16, q, 60, None) == -1
+    assert lib.sp24_gelu(p, None, q, F32, 64, None) == -3
+    assert lib.sp24_gelu(p, None, q, BF16, 60, None) == -1
+    assert lib.sp24_gelu(p, None, None, BF16, 64, None) == -5
     assert lib.sp24_embedding_fwd(p, q, r, st, 8, 4, 30, 100, None) == -1
     assert lib.sp24_embedding_fwd(p, q, r, None, 8, 4, 32, 100, None) == -5
     assert lib.sp24_embedding_bwd(p, q, ctypes.c_void_p(base + 4), st, 8, 4, 32, 100, None) == -4

@@ -766,6 +766,27 @@ def test_layer_norm_affine_gradients_added_into_existing_buffers():
     assert float((a.bias.grad - b.bias.grad).abs().max() / a.bias.grad.abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_gelu_kernel_matches_torch_fp32(dt):
+    """sp24_gelu forward and backward against F.gelu(approximate="tanh") and autograd in float32 on the same 16-bit
+    inputs: within one rounding of the output type plus the 2^-11 of tanh.approx (bf16 2^-8, fp16 2^-10 of the largest
+    magnitude); an odd element count goes to torch."""
+    from sparse.train_ops import gelu
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randn(257, 3072, generator=g) * 2).to(dt).to(DEV).requires_grad_(True)
+    dy = torch.randn(257, 3072, generator=g).to(dt).to(DEV)
+    y = gelu(x)
+    y.backward(dy)
+    x32 = x.detach().float().requires_grad_(True)
+    ref = F.gelu(x32, approximate="tanh")
+    ref.backward(dy.float())
+    tol = {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -10}[dt]
+    assert y.dtype == dt and float((y.float() - ref).abs().max() / ref.abs().max()) <= tol
+    assert float((x.grad.float() - x32.grad).abs().max() / x32.grad.abs().max()) <= tol
+    odd = torch.randn(7, device=DEV).to(dt)
+    assert torch.equal(gelu(odd), F.gelu(odd, approximate="tanh"))
+
+
 def test_token_and_position_embedding_kernels():
     """sp24_embedding_fwd / _bwd against nn.Embedding + autograd: the forward sum is exact; the gradient tables agree to
     float32 summation order (1e-6 of the largest entry), repeated tokens included; into_grad adds into existing buffers."""
