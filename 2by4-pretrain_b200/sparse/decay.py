@@ -4,6 +4,20 @@ import torch
 from . import _ext
 
 
+def _storage_order(t: torch.Tensor):
+    """``t`` as a flat view over its elements in storage order, or None when its storage is not dense (gaps or
+    overlaps).  Tensors with equal sizes and strides keep their element correspondence under this view."""
+    if t.is_contiguous():
+        return t.view(-1)
+    dims = sorted((st, sz) for sz, st in zip(t.shape, t.stride()) if sz != 1)
+    expect = 1
+    for st, sz in dims:
+        if st != expect:
+            return None
+        expect *= sz
+    return t.as_strided((t.numel(),), (1,), t.storage_offset())
+
+
 def masked_add_(grad: torch.Tensor, p_data: torch.Tensor, p_mask: torch.Tensor, alpha: float = 0):
     '''
     equivalent to
@@ -13,23 +27,31 @@ def masked_add_(grad: torch.Tensor, p_data: torch.Tensor, p_mask: torch.Tensor, 
     _ext.require_cuda(grad, p_data, p_mask)
     assert (grad.layout, p_data.layout, p_mask.layout) == (torch.strided, torch.strided, torch.strided)
     assert grad.stride() == p_data.stride() == p_mask.stride()
-    if grad.dtype != torch.float32 or p_data.dtype != torch.float32:
-        raise RuntimeError("masked_add_: grad and p_data must be float32 (cast the gradient with .float() first)")
-    if not grad.is_contiguous():
-        # the reference indexes flat storage; only dense storage makes that well defined
-        raise RuntimeError("masked_add_: tensors must be contiguous")
-    if p_mask.dtype in (torch.bool, torch.uint8, torch.int8):
+    # like the reference kernel, work on flat storage: any dense layout shared by the three tensors will do
+    g, q, m = _storage_order(grad), _storage_order(p_data), _storage_order(p_mask)
+    if g is None or q is None or m is None or g.shape != q.shape or g.shape != m.shape:
+        raise RuntimeError("masked_add_: tensors must share one dense layout (no gaps, no overlaps)")
+    if m.dtype in (torch.bool, torch.uint8, torch.int8):
         itemsize = 1
-    elif p_mask.dtype in (torch.float16, torch.bfloat16):
+    elif m.dtype in (torch.float16, torch.bfloat16):
         itemsize = 2
-    elif p_mask.dtype == torch.float32:
+    elif m.dtype == torch.float32:
         itemsize = 4
     else:
-        p_mask = p_mask != 0
+        m = m != 0
         itemsize = 1
-    rc = _ext.lib().sp24_masked_add(grad.data_ptr(), p_data.data_ptr(), p_mask.data_ptr(), itemsize, grad.numel(),
-                                    float(alpha), _ext.stream())
+    # the kernel computes in float32 on float32 tensors; other floating types go through float32 copies and are
+    # rounded once on the way back
+    g32 = g if g.dtype == torch.float32 else g.float()
+    q32 = q if q.dtype == torch.float32 else q.float()
+    if g32.data_ptr() % 16 or q32.data_ptr() % 16 or m.data_ptr() % (4 * itemsize):
+        g32 = g32.clone() if g32 is g else g32
+        q32, m = q32.clone(), m.clone()
+    rc = _ext.lib().sp24_masked_add(g32.data_ptr(), q32.data_ptr(), m.data_ptr(), itemsize, g32.numel(), float(alpha),
+                                    _ext.stream())
     _ext.check(rc, "sp24_masked_add")
+    if g32 is not g:
+        g.copy_(g32)
 
 
 def adamw_masked_decay_(p, grad, exp_avg, exp_avg_sq, *, step, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,

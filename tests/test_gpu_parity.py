@@ -304,12 +304,27 @@ def test_masked_add_matches_oracle(S, n, mdt):
     assert same_bits(gg.cpu(), O.masked_add(grad, p, mask != 0, 2e-4))
 
 
-def test_masked_add_rejects_mismatch(S):
+def test_masked_add_layouts_and_types(S):
+    """Strides must agree (as in the reference); any dense layout the three tensors share works (flat storage
+    order); 16-bit gradients and weights go through float32 and are rounded once; gapped storage is refused."""
     a = torch.zeros(8, 8, device=DEV)
     with pytest.raises(AssertionError):
         S.masked_add_(a, a.t(), a.bool(), alpha=0.1)
-    with pytest.raises(RuntimeError, match="float32"):
-        S.masked_add_(a.half(), a.half(), a.bool(), alpha=0.1)
+    g = torch.Generator().manual_seed(12)
+    grad, p = torch.randn(48, 80, generator=g).to(DEV), torch.randn(48, 80, generator=g).to(DEV)
+    mask = (torch.rand(48, 80, generator=g) < 0.5).to(DEV)
+    want = grad + 0.3 * p * (~mask)
+    gt = grad.t().contiguous().t()                                   # column-major storage, shared by all three
+    S.masked_add_(gt, p.t().contiguous().t(), mask.t().contiguous().t(), alpha=0.3)
+    assert torch.allclose(gt, want, atol=1e-6)
+    for dt in (torch.float16, torch.bfloat16):
+        g16 = grad.to(dt)
+        S.masked_add_(g16, p.to(dt), mask, alpha=0.3)
+        ref = (grad.to(dt).float() + 0.3 * p.to(dt).float() * (~mask)).to(dt)
+        assert g16.dtype == dt and float((g16.float() - ref.float()).abs().max()) <= float(ref.abs().max()) * 2 ** -8
+    wide = torch.zeros(8, 16, device=DEV)
+    with pytest.raises(RuntimeError, match="dense layout"):
+        S.masked_add_(wide[:, ::2], wide[:, ::2], wide[:, ::2].bool(), alpha=0.1)
 
 
 # ------------------------------------------------------------------------------------------------
