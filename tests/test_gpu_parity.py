@@ -322,9 +322,9 @@ def test_masked_add_layouts_and_types(S):
         S.masked_add_(g16, p.to(dt), mask, alpha=0.3)
         ref = (grad.to(dt).float() + 0.3 * p.to(dt).float() * (~mask)).to(dt)
         assert g16.dtype == dt and float((g16.float() - ref.float()).abs().max()) <= float(ref.abs().max()) * 2 ** -8
-    wide = torch.zeros(8, 16, device=DEV)
+    wide, wide_mask = torch.zeros(8, 16, device=DEV), torch.zeros(8, 16, dtype=torch.bool, device=DEV)
     with pytest.raises(RuntimeError, match="dense layout"):
-        S.masked_add_(wide[:, ::2], wide[:, ::2], wide[:, ::2].bool(), alpha=0.1)
+        S.masked_add_(wide[:, ::2], wide[:, ::2], wide_mask[:, ::2], alpha=0.1)
 
 
 # ------------------------------------------------------------------------------------------------
