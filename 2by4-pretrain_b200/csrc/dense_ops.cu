@@ -421,7 +421,20 @@ struct AdamParams {
     float lr, beta1, beta2, eps, weight_decay, alpha;
     float step;                // optimizer step number (1, 2, ...) when step_dev is null
     const float *step_dev;     // optional: step number read on the device (replayed launches)
+    const void *g2;            // optional second gradient, added to g on the first n2 elements (n2 % 4 == 0)
+    int g2_dtype;              // SP24_F32 / SP24_F16 / SP24_BF16
+    int64_t n2;
 };
+
+__device__ __forceinline__ float4 load_extra4(const void *g2, int dtype, int64_t i) {
+    if (dtype == SP24_F32) return reinterpret_cast<const float4 *>(g2)[i];
+    const uint2 r = reinterpret_cast<const uint2 *>(g2)[i];
+    if (dtype == SP24_BF16)
+        return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xFFFF0000u), __uint_as_float(r.y << 16),
+                           __uint_as_float(r.y & 0xFFFF0000u));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&r.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
 
 __device__ __forceinline__ void adam_one(float &p, float g, float &m, float &v, bool keep, const AdamParams &P, float inv_bc1,
                                          float inv_sqrt_bc2) {
@@ -441,7 +454,11 @@ __global__ void __launch_bounds__(256) adamw_masked_decay_kernel(AdamParams P) {
     const int64_t n4 = P.n / 4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
         float4 p = reinterpret_cast<const float4 *>(P.p)[i];
-        const float4 g = reinterpret_cast<const float4 *>(P.g)[i];
+        float4 g = reinterpret_cast<const float4 *>(P.g)[i];
+        if (P.g2 && i * 4 < P.n2) {
+            const float4 e = load_extra4(P.g2, P.g2_dtype, i);
+            g = make_float4(g.x + e.x, g.y + e.y, g.z + e.z, g.w + e.w);
+        }
         float4 m = reinterpret_cast<const float4 *>(P.m)[i];
         float4 v = reinterpret_cast<const float4 *>(P.v)[i];
         uint32_t mk = 0x01010101u;
@@ -465,25 +482,37 @@ __global__ void __launch_bounds__(256) adamw_masked_decay_kernel(AdamParams P) {
 }  // namespace
 }  // namespace sp24
 
-extern "C" int sp24_adamw_masked_decay(void *p, const void *grad, const void *mask, void *exp_avg, void *exp_avg_sq, int64_t n,
-                                       float lr, float beta1, float beta2, float eps, float weight_decay, float alpha,
-                                       float step, const float *step_dev, void *stream) {
+extern "C" int sp24_adamw_masked_decay_ex(void *p, const void *grad, const void *mask, void *exp_avg, void *exp_avg_sq, int64_t n,
+                                          float lr, float beta1, float beta2, float eps, float weight_decay, float alpha,
+                                          float step, const float *step_dev, const void *grad2, int grad2_dtype,
+                                          int64_t grad2_count, void *stream) {
     using namespace sp24;
     if (!p || !grad || !exp_avg || !exp_avg_sq) return SP24_ERR_ARG;
     if (n < 0) return SP24_ERR_SHAPE;
     if (n == 0) return SP24_OK;
     if (!step_dev && !(step >= 1.f)) return SP24_ERR_ARG;
-    if (!aligned16(p) || !aligned16(grad) || !aligned16(exp_avg) || !aligned16(exp_avg_sq) ||
+    if (grad2) {
+        if (grad2_dtype != SP24_F32 && grad2_dtype != SP24_F16 && grad2_dtype != SP24_BF16) return SP24_ERR_DTYPE;
+        if (grad2_count <= 0 || grad2_count > n || grad2_count % 4) return SP24_ERR_SHAPE;
+    }
+    if (!aligned16(p) || !aligned16(grad) || !aligned16(exp_avg) || !aligned16(exp_avg_sq) || !aligned16(grad2) ||
         (mask && (reinterpret_cast<uintptr_t>(mask) & 3u)))
         return SP24_ERR_ALIGN;
     if (int rc = check_device()) return rc;
     AdamParams P{static_cast<float *>(p), const_cast<float *>(static_cast<const float *>(grad)), static_cast<float *>(exp_avg),
                  static_cast<float *>(exp_avg_sq), static_cast<const uint8_t *>(mask), n, lr, beta1, beta2, eps, weight_decay,
-                 alpha, step, step_dev};
+                 alpha, step, step_dev, grad2, grad2_dtype, grad2 ? grad2_count : 0};
     const int64_t n4 = n / 4;
     int64_t blocks = (n4 + 255) / 256;
     if (blocks < 1) blocks = 1;
     if (blocks > 148 * 16) blocks = 148 * 16;
     adamw_masked_decay_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(P);
     return launch_status();
+}
+
+extern "C" int sp24_adamw_masked_decay(void *p, const void *grad, const void *mask, void *exp_avg, void *exp_avg_sq, int64_t n,
+                                       float lr, float beta1, float beta2, float eps, float weight_decay, float alpha,
+                                       float step, const float *step_dev, void *stream) {
+    return sp24_adamw_masked_decay_ex(p, grad, mask, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, alpha, step,
+                                      step_dev, nullptr, 0, 0, stream);
 }

@@ -55,12 +55,13 @@ def masked_add_(grad: torch.Tensor, p_data: torch.Tensor, p_mask: torch.Tensor, 
 
 
 def adamw_masked_decay_(p, grad, exp_avg, exp_avg_sq, *, step, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
-                        mask=None, alpha=0.0):
+                        mask=None, alpha=0.0, extra_grad=None):
     """Masked decay (``masked_add_``) and the AdamW update of ``p`` in one pass.  All tensors float32, contiguous,
     same number of elements; ``mask`` bool / uint8 or None.  ``step``: the optimizer step number (int, from 1),
     or a one-element float32 CUDA tensor holding it (read on the device, for CUDA-graph replay).  ``grad`` is
-    left unchanged."""
-    _ext.require_cuda(p, grad, exp_avg, exp_avg_sq, mask)
+    left unchanged.  ``extra_grad``: a second gradient (float32 / float16 / bfloat16, contiguous, a multiple of four
+    elements, at most as many as ``p``) added to ``grad`` on the leading elements it covers, inside the same pass."""
+    _ext.require_cuda(p, grad, exp_avg, exp_avg_sq, mask, extra_grad)
     n = p.numel()
     for t in (p, grad, exp_avg, exp_avg_sq):
         if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
@@ -71,8 +72,15 @@ def adamw_masked_decay_(p, grad, exp_avg, exp_avg_sq, *, step, lr, betas=(0.9, 0
     step_dev, step_host = (step, 1.0) if isinstance(step, torch.Tensor) else (None, float(step))
     if step_dev is not None and (step_dev.dtype != torch.float32 or step_dev.numel() != 1 or not step_dev.is_cuda):
         raise RuntimeError("adamw_masked_decay_: a device step must be a one-element float32 CUDA tensor")
-    rc = _ext.lib().sp24_adamw_masked_decay(p.data_ptr(), grad.data_ptr(), _ext.ptr(mask), exp_avg.data_ptr(),
-                                            exp_avg_sq.data_ptr(), n, lr, betas[0], betas[1], eps, weight_decay, alpha,
-                                            step_host, _ext.ptr(step_dev), _ext.stream())
-    _ext.check(rc, "sp24_adamw_masked_decay")
+    n2, dt2 = 0, 0
+    if extra_grad is not None:
+        n2 = extra_grad.numel()
+        if extra_grad.dtype not in (torch.float32, torch.float16, torch.bfloat16) or not extra_grad.is_contiguous() \
+                or n2 == 0 or n2 > n or n2 % 4:
+            raise RuntimeError("adamw_masked_decay_: extra_grad must be a contiguous float tensor of 4 k <= numel(p) elements")
+        dt2 = _ext.dt(extra_grad.dtype)
+    rc = _ext.lib().sp24_adamw_masked_decay_ex(p.data_ptr(), grad.data_ptr(), _ext.ptr(mask), exp_avg.data_ptr(),
+                                               exp_avg_sq.data_ptr(), n, lr, betas[0], betas[1], eps, weight_decay, alpha,
+                                               step_host, _ext.ptr(step_dev), _ext.ptr(extra_grad), dt2, n2, _ext.stream())
+    _ext.check(rc, "sp24_adamw_masked_decay_ex")
     return p

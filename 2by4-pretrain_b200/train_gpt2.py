@@ -387,13 +387,13 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
 
     seg_args = list(zip(bounds, (0.1, 0.0, 0.0), (False, True, False)))     # embeddings, sparse weights, everything else
 
-    def update_segment(which):
+    def update_segment(which, extra_grad=None):
         (a, b), wd, use_mask = seg_args[which]
         if b > a:
             sparse.adamw_masked_decay_(flat_p[a:b], flat[a:b], flat_m[a:b], flat_v[a:b], step=step_dev, lr=lr,
                                        betas=(0.9, 0.95), eps=1e-8, weight_decay=wd,
                                        mask=flat_mask if (use_mask and mode == "sparse") else None,
-                                       alpha=alpha if use_mask else 0.0)
+                                       alpha=alpha if use_mask else 0.0, extra_grad=extra_grad)
 
     def update_blocks():
         # everything but the embeddings: needs only the block groups' exchanges
@@ -402,9 +402,10 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         update_segment(2)
 
     def update_embeddings():
-        if head_grad is not None:
-            model.wte.weight.grad.add_(head_grad)      # the (already averaged) head share joins the lookup share
-        update_segment(0)
+        # the (already averaged) head share of the tied embedding's gradient joins the lookup share inside the update
+        # kernel: the token embedding is the first tensor of this segment
+        assert seg_decay and seg_decay[0] is model.wte.weight
+        update_segment(0, head_grad)
 
     def update():
         update_blocks()
@@ -468,6 +469,17 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
             dist.all_reduce(stage[a:b], op=dist.ReduceOp.AVG)
             flat[a:b].copy_(stage[a:b])
 
+    # verbose runs time every exchange of the last step on the exchange stream (when it started after the step's first
+    # kernel, how long it took): trace[name] = [start event, end event]
+    trace = {} if verbose else None
+    step_start = torch.cuda.Event(enable_timing=True) if verbose else None
+
+    def mark(name, which):
+        if trace is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            trace.setdefault(name, [None, None])[which] = ev
+
     def reduce_grads(before_embeddings=None):
         """Issues the exchanges.  ``before_embeddings`` (a callable) is run on the main stream once every group but the
         last, embeddings-only one has been exchanged, i.e. beside that last exchange: the update of all other
@@ -488,13 +500,17 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         with torch.cuda.stream(comm):
             if head_ready is not None:
                 comm.wait_event(head_ready)
+                mark("head", 0)
                 dist.all_reduce(head_grad, op=dist.ReduceOp.AVG)
+                mark("head", 1)
             for g_ in range(n_groups):
                 if overlap_update and g_ == n_groups - 1:
                     blocks_done.record(comm)
                 comm.wait_event(ready[g_] if g_ < n_ready else tail)
+                mark(f"group {g_}", 0)
                 for a, b in slices[g_]:
                     exchange(a, b)
+                mark(f"group {g_}", 1)
         if overlap_update:
             main.wait_event(blocks_done)
             before_embeddings()
@@ -531,6 +547,8 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
     def one_step(i):
         next_tokens()
         key = (mode == "sparse") and (i % freq == 0)
+        if step_start is not None:
+            step_start.record()
         graphs[key].replay()
         reduce_grads(g_upd.replay)
         g_upd_emb.replay()
@@ -579,6 +597,9 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         dist.destroy_process_group()
     if verbose and rank == 0:
         print({k: v for k, v in res.items() if k != "losses"})
+        for name, (ev0, ev1) in (trace or {}).items():
+            print(f"  exchange {name}: starts {step_start.elapsed_time(ev0):.2f} ms into the step, takes "
+                  f"{ev0.elapsed_time(ev1):.2f} ms")
     return res
 
 

@@ -270,6 +270,15 @@ int sp24_adamw_masked_decay(void *p, const void *grad, const void *mask, void *e
                             const float *step_dev, void *stream);
 
 /*
+ * The same update with a second gradient added to the first grad2_count elements (grad2_count % 4 == 0, <= n):
+ * g = grad + grad2 there, grad2 in float32 / float16 / bfloat16.  For a gradient that arrives in two parts, e.g. a tied
+ * embedding whose output-head share is exchanged on its own as 16-bit values: no separate pass adds the parts.
+ */
+int sp24_adamw_masked_decay_ex(void *p, const void *grad, const void *mask, void *exp_avg, void *exp_avg_sq, int64_t n,
+                               float lr, float beta1, float beta2, float eps, float weight_decay, float alpha, float step,
+                               const float *step_dev, const void *grad2, int grad2_dtype, int64_t grad2_count, void *stream);
+
+/*
  * Metadata re-layout for the tensor cores: the reference's reordered metadata (m*k/16 int16 or m*k/32
  * int32) -> the order tcgen05.mma.sp consumes from tensor memory.  The result is a sequence of 2048-byte
  * atoms, one per (128-row block, 128-column block), row blocks outermost; 16-bit types: atom byte

@@ -582,6 +582,28 @@ def test_fused_masked_decay_adamw_matches_the_two_pass_recipe(S, n):
     assert torch.allclose(p, pr2.data, rtol=2e-5, atol=1e-8)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+def test_adamw_second_gradient_equals_adding_it_first(S, dt):
+    """extra_grad: the update with a second gradient on the leading elements is bit-identical to adding that gradient
+    (converted to float32) to the first one beforehand."""
+    g = torch.Generator().manual_seed(31)
+    n, n2 = 4099, 2048
+    p0 = (torch.randn(n, generator=g) * 0.02).to(DEV)
+    grad = (torch.randn(n, generator=g) * 1e-3).to(DEV)
+    extra = (torch.randn(n2, generator=g) * 1e-3).to(dt).to(DEV)
+    mask = (torch.rand(n, generator=g) < 0.5).to(DEV)
+    kw = dict(step=3, lr=6e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, mask=mask, alpha=2e-4)
+    pa, ma, va = p0.clone(), torch.full_like(p0, 1e-4), torch.full_like(p0, 1e-7)
+    pb, mb, vb = p0.clone(), ma.clone(), va.clone()
+    S.adamw_masked_decay_(pa, grad, ma, va, extra_grad=extra, **kw)
+    summed = grad.clone()
+    summed[:n2] += extra.float()
+    S.adamw_masked_decay_(pb, summed, mb, vb, **kw)
+    assert torch.equal(pa, pb) and torch.equal(ma, mb) and torch.equal(va, vb)
+    with pytest.raises(RuntimeError):
+        S.adamw_masked_decay_(pa, grad, ma, va, extra_grad=extra[:6], **kw)
+
+
 def test_prune_compress_random_shapes_match_the_oracle(S):
     """Twenty-four seeded random conversions (shape, dtype pair, storage order, pruning rule): packed values and
     reordered metadata equal the oracle's bit for bit."""
