@@ -415,7 +415,9 @@ namespace sp24 {
 namespace {
 
 struct AdamParams {
-    float *p, *g, *m, *v;
+    float *p;
+    const void *g;             // gradient, float32 or 16-bit (g_dtype)
+    float *m, *v;
     const uint8_t *mask;       // may be null: no masked decay
     int64_t n;
     float lr, beta1, beta2, eps, weight_decay, alpha;
@@ -424,6 +426,7 @@ struct AdamParams {
     const void *g2;            // optional second gradient, added to g on the first n2 elements (n2 % 4 == 0)
     int g2_dtype;              // SP24_F32 / SP24_F16 / SP24_BF16
     int64_t n2;
+    int g_dtype;               // SP24_F32 / SP24_F16 / SP24_BF16
 };
 
 __device__ __forceinline__ float4 load_extra4(const void *g2, int dtype, int64_t i) {
@@ -454,7 +457,7 @@ __global__ void __launch_bounds__(256) adamw_masked_decay_kernel(AdamParams P) {
     const int64_t n4 = P.n / 4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
         float4 p = reinterpret_cast<const float4 *>(P.p)[i];
-        float4 g = reinterpret_cast<const float4 *>(P.g)[i];
+        float4 g = load_extra4(P.g, P.g_dtype, i);
         if (P.g2 && i * 4 < P.n2) {
             const float4 e = load_extra4(P.g2, P.g2_dtype, i);
             g = make_float4(g.x + e.x, g.y + e.y, g.z + e.z, g.w + e.w);
@@ -475,19 +478,24 @@ __global__ void __launch_bounds__(256) adamw_masked_decay_kernel(AdamParams P) {
     const int64_t i = n4 * 4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < P.n) {
         const bool keep = P.mask ? P.mask[i] != 0 : true;
-        adam_one(P.p[i], P.g[i], P.m[i], P.v[i], keep, P, inv_bc1, inv_sqrt_bc2);
+        float g;
+        if (P.g_dtype == SP24_F32) g = static_cast<const float *>(P.g)[i];
+        else if (P.g_dtype == SP24_BF16) g = __bfloat162float(static_cast<const __nv_bfloat16 *>(P.g)[i]);
+        else g = __half2float(static_cast<const __half *>(P.g)[i]);
+        adam_one(P.p[i], g, P.m[i], P.v[i], keep, P, inv_bc1, inv_sqrt_bc2);
     }
 }
 
 }  // namespace
 }  // namespace sp24
 
-extern "C" int sp24_adamw_masked_decay_ex(void *p, const void *grad, const void *mask, void *exp_avg, void *exp_avg_sq, int64_t n,
-                                          float lr, float beta1, float beta2, float eps, float weight_decay, float alpha,
-                                          float step, const float *step_dev, const void *grad2, int grad2_dtype,
-                                          int64_t grad2_count, void *stream) {
+extern "C" int sp24_adamw_masked_decay_ex(void *p, const void *grad, int grad_dtype, const void *mask, void *exp_avg,
+                                          void *exp_avg_sq, int64_t n, float lr, float beta1, float beta2, float eps,
+                                          float weight_decay, float alpha, float step, const float *step_dev,
+                                          const void *grad2, int grad2_dtype, int64_t grad2_count, void *stream) {
     using namespace sp24;
     if (!p || !grad || !exp_avg || !exp_avg_sq) return SP24_ERR_ARG;
+    if (grad_dtype != SP24_F32 && grad_dtype != SP24_F16 && grad_dtype != SP24_BF16) return SP24_ERR_DTYPE;
     if (n < 0) return SP24_ERR_SHAPE;
     if (n == 0) return SP24_OK;
     if (!step_dev && !(step >= 1.f)) return SP24_ERR_ARG;
@@ -499,9 +507,9 @@ extern "C" int sp24_adamw_masked_decay_ex(void *p, const void *grad, const void 
         (mask && (reinterpret_cast<uintptr_t>(mask) & 3u)))
         return SP24_ERR_ALIGN;
     if (int rc = check_device()) return rc;
-    AdamParams P{static_cast<float *>(p), const_cast<float *>(static_cast<const float *>(grad)), static_cast<float *>(exp_avg),
+    AdamParams P{static_cast<float *>(p), grad, static_cast<float *>(exp_avg),
                  static_cast<float *>(exp_avg_sq), static_cast<const uint8_t *>(mask), n, lr, beta1, beta2, eps, weight_decay,
-                 alpha, step, step_dev, grad2, grad2_dtype, grad2 ? grad2_count : 0};
+                 alpha, step, step_dev, grad2, grad2_dtype, grad2 ? grad2_count : 0, grad_dtype};
     const int64_t n4 = n / 4;
     int64_t blocks = (n4 + 255) / 256;
     if (blocks < 1) blocks = 1;
@@ -513,6 +521,6 @@ extern "C" int sp24_adamw_masked_decay_ex(void *p, const void *grad, const void 
 extern "C" int sp24_adamw_masked_decay(void *p, const void *grad, const void *mask, void *exp_avg, void *exp_avg_sq, int64_t n,
                                        float lr, float beta1, float beta2, float eps, float weight_decay, float alpha,
                                        float step, const float *step_dev, void *stream) {
-    return sp24_adamw_masked_decay_ex(p, grad, mask, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, alpha, step,
-                                      step_dev, nullptr, 0, 0, stream);
+    return sp24_adamw_masked_decay_ex(p, grad, SP24_F32, mask, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, alpha,
+                                      step, step_dev, nullptr, 0, 0, stream);
 }

@@ -45,8 +45,8 @@ _SIGNATURES = {
     "sp24_cross_entropy_fwd": [_vp, _i32, _vp, _vp, _vp, _i64, _i64, _i64, _vp],
     "sp24_cross_entropy_bwd": [_vp, _i32, _vp, _vp, _vp, _f32, _vp, _i64, _i64, _i64, _i64, _vp],
     "sp24_adamw_masked_decay": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp],
-    "sp24_adamw_masked_decay_ex": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp, _i32, _i64,
-                                   _vp],
+    "sp24_adamw_masked_decay_ex": [_vp, _vp, _i32, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp, _i32,
+                                   _i64, _vp],
     "sp24_to_dense": [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _i64, _vp],
     "sp24_mvue24_dense": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _u64, _u64, _vp],
     "sp24_mvue24_dense_fast": [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _i64, _u64, _u64, _vp],

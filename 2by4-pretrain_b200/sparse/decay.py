@@ -57,14 +57,16 @@ def masked_add_(grad: torch.Tensor, p_data: torch.Tensor, p_mask: torch.Tensor, 
 def adamw_masked_decay_(p, grad, exp_avg, exp_avg_sq, *, step, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
                         mask=None, alpha=0.0, extra_grad=None):
     """Masked decay (``masked_add_``) and the AdamW update of ``p`` in one pass.  All tensors float32, contiguous,
-    same number of elements; ``mask`` bool / uint8 or None.  ``step``: the optimizer step number (int, from 1),
+    same number of elements (``grad`` may also be float16 / bfloat16: what a 16-bit gradient exchange leaves behind);
+    ``mask`` bool / uint8 or None.  ``step``: the optimizer step number (int, from 1),
     or a one-element float32 CUDA tensor holding it (read on the device, for CUDA-graph replay).  ``grad`` is
     left unchanged.  ``extra_grad``: a second gradient (float32 / float16 / bfloat16, contiguous, a multiple of four
     elements, at most as many as ``p``) added to ``grad`` on the leading elements it covers, inside the same pass."""
     _ext.require_cuda(p, grad, exp_avg, exp_avg_sq, mask, extra_grad)
     n = p.numel()
     for t in (p, grad, exp_avg, exp_avg_sq):
-        if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
+        ok_dtype = t.dtype == torch.float32 or (t is grad and t.dtype in (torch.float16, torch.bfloat16))
+        if not ok_dtype or not t.is_contiguous() or t.numel() != n:
             raise RuntimeError("adamw_masked_decay_: expected contiguous float32 tensors of equal size")
     if mask is not None:
         if mask.dtype not in (torch.bool, torch.uint8) or not mask.is_contiguous() or mask.numel() != n:
@@ -79,7 +81,7 @@ def adamw_masked_decay_(p, grad, exp_avg, exp_avg_sq, *, step, lr, betas=(0.9, 0
                 or n2 == 0 or n2 > n or n2 % 4:
             raise RuntimeError("adamw_masked_decay_: extra_grad must be a contiguous float tensor of 4 k <= numel(p) elements")
         dt2 = _ext.dt(extra_grad.dtype)
-    rc = _ext.lib().sp24_adamw_masked_decay_ex(p.data_ptr(), grad.data_ptr(), _ext.ptr(mask), exp_avg.data_ptr(),
+    rc = _ext.lib().sp24_adamw_masked_decay_ex(p.data_ptr(), grad.data_ptr(), _ext.dt(grad.dtype), _ext.ptr(mask), exp_avg.data_ptr(),
                                                exp_avg_sq.data_ptr(), n, lr, betas[0], betas[1], eps, weight_decay, alpha,
                                                step_host, _ext.ptr(step_dev), _ext.ptr(extra_grad), dt2, n2, _ext.stream())
     _ext.check(rc, "sp24_adamw_masked_decay_ex")

@@ -302,8 +302,8 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
     ``split_head``: the output head's share of the tied embedding's gradient goes to a bf16 buffer of its own, which is
     all-reduced as soon as the backward pass has produced it (its first product) and added to the embedding's gradient
     before the update; the embeddings' own (lookup) gradients, complete only when the backward pass ends, form the
-    last group alone.  ``reduce_dtype`` = torch.bfloat16 exchanges every group as bf16 (cast, all-reduce, cast back and
-    accumulate in fp32 locally): half the bytes on the wire.
+    last group alone.  ``reduce_dtype`` = torch.bfloat16 exchanges every group as bf16 (cast, all-reduce; the optimizer
+    kernel reads the averaged 16-bit gradient, no cast back): half the bytes on the wire.
 
     ``global_stream``: every rank draws the whole job's batch (world x batch sequences) from one common seed and keeps
     its own slice, so that N ranks x batch B see exactly the sequences of one rank x batch N B; with ``return_losses``
@@ -386,11 +386,15 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         return loss.detach()
 
     seg_args = list(zip(bounds, (0.1, 0.0, 0.0), (False, True, False)))     # embeddings, sparse weights, everything else
+    # 16-bit exchange: every group is cast into this buffer, all-reduced there, and read from there by the update
+    stage = torch.empty(total, dtype=reduce_dtype, device=dev) if (world > 1 and reduce_dtype != torch.float32) else None
 
     def update_segment(which, extra_grad=None):
         (a, b), wd, use_mask = seg_args[which]
         if b > a:
-            sparse.adamw_masked_decay_(flat_p[a:b], flat[a:b], flat_m[a:b], flat_v[a:b], step=step_dev, lr=lr,
+            # after a 16-bit exchange the averaged gradient sits in the 16-bit staging buffer: the update reads it there
+            grads = flat if stage is None else stage
+            sparse.adamw_masked_decay_(flat_p[a:b], grads[a:b], flat_m[a:b], flat_v[a:b], step=step_dev, lr=lr,
                                        betas=(0.9, 0.95), eps=1e-8, weight_decay=wd,
                                        mask=flat_mask if (use_mask and mode == "sparse") else None,
                                        alpha=alpha if use_mask else 0.0, extra_grad=extra_grad)
@@ -459,15 +463,13 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
                 model.input_grad_hooks[below] = ready[g_].record
             elif emb_alone:
                 model.first_block_hook = ready[g_].record
-    stage = torch.empty(total, dtype=reduce_dtype, device=dev) if (world > 1 and reduce_dtype != torch.float32) else None
 
     def exchange(a, b):
         if stage is None:
             dist.all_reduce(flat[a:b], op=dist.ReduceOp.AVG)
         else:
-            stage[a:b].copy_(flat[a:b])
+            stage[a:b].copy_(flat[a:b])                        # cast; no cast back: the optimizer kernel reads 16 bits
             dist.all_reduce(stage[a:b], op=dist.ReduceOp.AVG)
-            flat[a:b].copy_(stage[a:b])
 
     # verbose runs time every exchange of the last step on the exchange stream (when it started after the step's first
     # kernel, how long it took): trace[name] = [start event, end event]
@@ -494,7 +496,7 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
             return
         main = torch.cuda.current_stream()
         if comm is None:
-            dist.all_reduce(flat, op=dist.ReduceOp.AVG)
+            exchange(0, total)
             return
         tail.record(main)
         with torch.cuda.stream(comm):

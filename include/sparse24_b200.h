@@ -270,13 +270,16 @@ int sp24_adamw_masked_decay(void *p, const void *grad, const void *mask, void *e
                             const float *step_dev, void *stream);
 
 /*
- * The same update with a second gradient added to the first grad2_count elements (grad2_count % 4 == 0, <= n):
- * g = grad + grad2 there, grad2 in float32 / float16 / bfloat16.  For a gradient that arrives in two parts, e.g. a tied
- * embedding whose output-head share is exchanged on its own as 16-bit values: no separate pass adds the parts.
+ * The same update with the gradient in float32, float16 or bfloat16 (grad_dtype; a 16-bit gradient is what a 16-bit
+ * gradient exchange leaves behind: no cast back to float32) and, optionally, a second gradient added to the first
+ * grad2_count elements (grad2_count % 4 == 0, <= n): g = grad + grad2 there, grad2 in any of the three types.  For a
+ * gradient that arrives in two parts, e.g. a tied embedding whose output-head share is exchanged on its own: no
+ * separate pass adds the parts.
  */
-int sp24_adamw_masked_decay_ex(void *p, const void *grad, const void *mask, void *exp_avg, void *exp_avg_sq, int64_t n,
-                               float lr, float beta1, float beta2, float eps, float weight_decay, float alpha, float step,
-                               const float *step_dev, const void *grad2, int grad2_dtype, int64_t grad2_count, void *stream);
+int sp24_adamw_masked_decay_ex(void *p, const void *grad, int grad_dtype, const void *mask, void *exp_avg, void *exp_avg_sq,
+                               int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay, float alpha,
+                               float step, const float *step_dev, const void *grad2, int grad2_dtype, int64_t grad2_count,
+                               void *stream);
 
 /*
  * Metadata re-layout for the tensor cores: the reference's reordered metadata (m*k/16 int16 or m*k/32

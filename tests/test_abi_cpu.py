@@ -103,9 +103,10 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
                                        None) == -4
     assert lib.sp24_adamw_masked_decay(p, q, None, r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 0.0, None, None) == -5
     # second gradient: 16- or 32-bit floats, a multiple of four elements, no longer than the range
-    assert lib.sp24_adamw_masked_decay_ex(p, q, None, r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 1.0, None, q, 5, 8, None) == -3
-    assert lib.sp24_adamw_masked_decay_ex(p, q, None, r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 1.0, None, q, 2, 6, None) == -1
-    assert lib.sp24_adamw_masked_decay_ex(p, q, None, r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 1.0, None, q, 2, 32, None) == -1
+    assert lib.sp24_adamw_masked_decay_ex(p, q, F32, None, r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 1.0, None, q, 5, 8, None) == -3
+    assert lib.sp24_adamw_masked_decay_ex(p, q, F32, None, r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 1.0, None, q, 2, 6, None) == -1
+    assert lib.sp24_adamw_masked_decay_ex(p, q, F32, None, r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 1.0, None, q, 2, 32, None) == -1
+    assert lib.sp24_adamw_masked_decay_ex(p, q, I8, None, r, st, 16, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0.0, 1.0, None, None, 0, 0, None) == -3
     # tensor-core metadata copies need whole 128-row / 128-column blocks
     assert lib.sp24_select_dual_compress_tc(p, F16, 64, 128, 128, 1, q, 128, q, F16, 64, r, q, 128, r, st, st, None) == -1
     assert lib.sp24_prune_compress_ex(p, F16, 64, 64, 64, 0, q, F16, 32, r, 0, None, 0, None, 0, 0, 0, None, st, None, None) == -5
