@@ -572,8 +572,9 @@ def side_measurements(dev):
 
 def gpt2_measurements(world):
     """cfg5: GPT-2-124M-shaped model, 8 x 1024 synthetic tokens per GPU and step, data-parallel over the
-    ranks of this job (NCCL all-reduce through DistributedDataParallel).  Tokens/s of the sparse recipe
-    (SparseLinearTranspose in every block, masked decay, AdamW) and of the same model with dense linears."""
+    ranks of this job (graph-replayed step, grouped NCCL all-reduce of the flat gradient; the eager figure uses
+    DistributedDataParallel).  Tokens/s of the sparse recipe (SparseLinearTranspose in every block, masked decay,
+    AdamW) and of the same model with dense linears."""
     sys.path.insert(0, os.path.join(ROOT, "2by4-pretrain_b200"))
     import train_gpt2
     out = {}
@@ -581,16 +582,22 @@ def gpt2_measurements(world):
         sp = train_gpt2.run_graphs(steps=50, warmup=3, mode="sparse")
         de = train_gpt2.run_graphs(steps=20, warmup=3, mode="dense")
         sp_eager = train_gpt2.run(steps=10, warmup=3, mode="sparse")
+        bf16_exchange = {}
+        if world > 1:   # the option that halves the exchanged bytes (the optimizer kernel reads the bf16 average)
+            sp16 = train_gpt2.run_graphs(steps=30, warmup=3, mode="sparse", reduce_dtype=torch.bfloat16)
+            bf16_exchange = {"sparse_tokens_per_s_bf16_gradient_exchange": sp16["tokens_per_s"],
+                             "sparse_ms_per_step_bf16_gradient_exchange": sp16["ms_per_step"]}
         out = {"sparse_tokens_per_s": sp["tokens_per_s"], "sparse_ms_per_step": sp["ms_per_step"],
                "dense_tokens_per_s": de["tokens_per_s"], "dense_ms_per_step": de["ms_per_step"],
                "sparse_over_dense": sp["tokens_per_s"] / de["tokens_per_s"], "tokens_per_step": sp["tokens_per_step"],
                "loss_finite": sp["loss_finite"], "n_gpus": world,
                "sparse_eager_ddp_tokens_per_s": sp_eager["tokens_per_s"],
                "sparse_eager_ddp_host_enqueue_ms_per_step": sp_eager["host_enqueue_ms_per_step"],
+               **bf16_exchange,
                "note": "step replayed from CUDA graphs (forward+backward; the flat fp32 gradient all-reduced by NCCL in "
                        "groups released by event nodes inside the backward graph: the output head's share of the tied "
-                       "embedding gradient first, then four groups of blocks, the embeddings last; then masked "
-                       "decay + AdamW); 50 timed sparse steps, mean, including the mask "
+                       "embedding gradient first, then four groups of blocks, the embeddings last, beside the masked "
+                       "decay + AdamW of the other parameters); 50 timed sparse steps, mean, including the mask "
                        "refresh every 40 steps; eager = Python-launched step with DistributedDataParallel"}
     except Exception as exc:  # the headline line must still be printed
         out = {"error": repr(exc)[:300]}

@@ -602,6 +602,13 @@ def test_adamw_second_gradient_equals_adding_it_first(S, dt):
     assert torch.equal(pa, pb) and torch.equal(ma, mb) and torch.equal(va, vb)
     with pytest.raises(RuntimeError):
         S.adamw_masked_decay_(pa, grad, ma, va, extra_grad=extra[:6], **kw)
+    if dt != torch.float32:
+        # a 16-bit main gradient (what a 16-bit exchange leaves behind) = the same values handed over as float32
+        pc, mc, vc = p0.clone(), torch.full_like(p0, 1e-4), torch.full_like(p0, 1e-7)
+        pd, md, vd = p0.clone(), mc.clone(), vc.clone()
+        S.adamw_masked_decay_(pc, grad.to(dt), mc, vc, extra_grad=extra, **kw)
+        S.adamw_masked_decay_(pd, grad.to(dt).float(), md, vd, extra_grad=extra, **kw)
+        assert torch.equal(pc, pd) and torch.equal(mc, md) and torch.equal(vc, vd)
 
 
 def test_prune_compress_random_shapes_match_the_oracle(S):
