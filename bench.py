@@ -486,6 +486,32 @@ def run_case(name):
         gr = torch.randn(8192, 4096, device=dev)
         mk = torch.rand(8192, 4096, device=dev) < 0.5
         fn = lambda: sparse.masked_add_(gr, p, mk, alpha=2e-4)
+    elif name in ("ce_fused", "add_ln_fwd", "add_ln_bwd", "gelu_bwd"):
+        # the trainer's streaming kernels at the GPT-2-124M shapes (8192 tokens; 50304 classes, d = 768, 4 d = 3072)
+        from sparse import train_ops
+        rows = 8192
+        if name == "ce_fused":
+            logits = (torch.randn(rows, 50304, device=dev) * 2).bfloat16().requires_grad_(True)
+            tgt = torch.randint(0, 50304, (rows,), device=dev)
+            fn = lambda: train_ops.cross_entropy(logits, tgt)
+        elif name == "gelu_bwd":
+            xs = [torch.randn(rows, 3072, device=dev).bfloat16().requires_grad_(True) for _ in range(3)]
+            dy = torch.randn(rows, 3072, device=dev).bfloat16()
+            it = iter(range(1 << 30))
+            fn = lambda: train_ops.gelu(xs[next(it) % 3]).backward(dy)
+        else:
+            ln = train_ops.LayerNorm(768).to(dev)
+            xs = [torch.randn(rows, 768, device=dev).requires_grad_(True) for _ in range(6)]
+            ds = [torch.randn(rows, 768, device=dev).bfloat16().requires_grad_(True) for _ in range(6)]
+            dres, dy = torch.randn(rows, 768, device=dev), torch.randn(rows, 768, device=dev).bfloat16()
+            it = iter(range(1 << 30))
+
+            def fn():
+                i = next(it) % 6
+                with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+                    res, y = train_ops.add_layer_norm(xs[i], ds[i], ln)
+                if name == "add_ln_bwd":
+                    torch.autograd.backward([res, y], [dres, dy])
     else:
         raise SystemExit(f"unknown case {name}")
     for _ in range(4):
