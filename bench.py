@@ -781,6 +781,9 @@ def spmm_measurements(dev):
             "sparse_fwd_bwd_TFLOPs_dense_equiv": 3 * flops / sp_total / 1e12,
             "dense_fwd_bwd_TFLOPs": 3 * flops / de_total / 1e12,
             "speedup_vs_dense": de_total / sp_total,
+            # the layer's option weight_grad = "dense": sparse forward and input gradient, exact dense weight gradient
+            # (no MVUE estimate); not the reference recipe, reported beside it
+            "speedup_vs_dense_with_dense_weight_gradient": de_total / (t_fwd + t_dx + d_dw),
             "per_gemm_TFLOPs": {"fwd": flops / t_fwd / 1e12, "dx": flops / t_dx / 1e12,
                                 "dw_gemm_only": flops / t_dw_gemm_only / 1e12,
                                 "dw_splitk_fp32_gemm_and_memset_only": flops / t_dw_splitk_gemm / 1e12},
