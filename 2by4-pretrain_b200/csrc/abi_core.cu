@@ -1,6 +1,7 @@
 // Library-wide pieces of the C ABI: error strings, version, device check.
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 #include "sp24_common.cuh"
 
@@ -58,3 +59,24 @@ extern "C" const char *sp24_strerror(int code) {
 }
 
 extern "C" int sp24_abi_version(void) { return 2; }
+
+// Peer memory for exchanges that run on the copy engines: a buffer exported by its owner (cudaIpcGetMemHandle, or a
+// framework's equivalent) is mapped into this process; copies from the returned address are ordinary device-to-device
+// copies on a stream of the current device.
+extern "C" int sp24_ipc_open(const void *handle, int handle_bytes, void **ptr) {
+    if (!handle || !ptr || handle_bytes != (int)sizeof(cudaIpcMemHandle_t)) return SP24_ERR_ARG;
+    if (int rc = sp24::check_device()) return rc;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    *ptr = nullptr;
+    if (cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        sp24::launch_status();     // clears (and with SP24_DEBUG prints) the runtime's error
+        return SP24_ERR_CUDA;
+    }
+    return SP24_OK;
+}
+
+extern "C" int sp24_ipc_close(void *ptr) {
+    if (!ptr) return SP24_ERR_ARG;
+    return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? SP24_OK : SP24_ERR_CUDA;
+}

@@ -62,6 +62,8 @@ _SIGNATURES = {
     "sp24_cross_entropy_fused": [_vp, _i32, _vp, _vp, _vp, _f32, _vp, _i64, _i64, _i64, _i64, _vp],
     "sp24_scale_unless_one": [_vp, _i32, _vp, _i64, _vp],
     "sp24_gelu": [_vp, _vp, _vp, _i32, _i64, _vp],
+    "sp24_ipc_open": [_vp, _i32, ctypes.POINTER(ctypes.c_void_p)],
+    "sp24_ipc_close": [_vp],
     "sp24_embedding_fwd": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp],
     "sp24_embedding_bwd": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp],
 }

@@ -291,7 +291,7 @@ def synthetic_tokens(n, seq, vocab, gen, data="uniform"):
 
 def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, layers=12, d=768, heads=12, alpha=2e-4,
                lr=6e-4, freq=40, verbose=False, return_losses=False, comm_groups=5, data="uniform", global_stream=False,
-               split_head=True, reduce_dtype=torch.float32):
+               split_head=True, reduce_dtype=torch.float32, exchange="nccl"):
     """The same step as ``run`` replayed from CUDA graphs.  Returns the same dict.
 
     With more than one rank and ``comm_groups`` > 1 the gradient all-reduce is split into that many groups of
@@ -304,6 +304,9 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
     before the update; the embeddings' own (lookup) gradients, complete only when the backward pass ends, form the
     last group alone.  ``reduce_dtype`` = torch.bfloat16 exchanges every group as bf16 (cast, all-reduce; the optimizer
     kernel reads the averaged 16-bit gradient, no cast back): half the bytes on the wire.
+
+    ``exchange``: "nccl" (all-reduce kernels, which hold SMs beside the backward pass) or "copy" (``sparse.peer``: the
+    same average from peer-to-peer copies on the DMA engines plus small element-wise kernels; one node, float32).
 
     ``global_stream``: every rank draws the whole job's batch (world x batch sequences) from one common seed and keeps
     its own slice, so that N ranks x batch B see exactly the sequences of one rank x batch N B; with ``return_losses``
@@ -464,8 +467,20 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
             elif emb_alone:
                 model.first_block_hook = ready[g_].record
 
+    averager = None
+    if world > 1 and exchange == "copy":
+        from sparse.peer import CopyEngineAverage
+        if stage is not None:
+            raise RuntimeError("run_graphs: the copy-engine exchange works on the float32 gradient buffer")
+        averager = CopyEngineAverage()
+        averager.add_buffer("flat", flat)
+        if head_grad is not None:
+            averager.add_buffer("head", head_grad)
+
     def exchange(a, b):
-        if stage is None:
+        if averager is not None:
+            averager.average("flat", a, b)
+        elif stage is None:
             dist.all_reduce(flat[a:b], op=dist.ReduceOp.AVG)
         else:
             stage[a:b].copy_(flat[a:b])                        # cast; no cast back: the optimizer kernel reads 16 bits
@@ -497,13 +512,18 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         main = torch.cuda.current_stream()
         if comm is None:
             exchange(0, total)
+            if averager is not None:
+                averager.finish()
             return
         tail.record(main)
         with torch.cuda.stream(comm):
             if head_ready is not None:
                 comm.wait_event(head_ready)
                 mark("head", 0)
-                dist.all_reduce(head_grad, op=dist.ReduceOp.AVG)
+                if averager is not None:
+                    averager.average("head", 0, head_grad.numel())
+                else:
+                    dist.all_reduce(head_grad, op=dist.ReduceOp.AVG)
                 mark("head", 1)
             for g_ in range(n_groups):
                 if overlap_update and g_ == n_groups - 1:
@@ -513,6 +533,8 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
                 for a, b in slices[g_]:
                     exchange(a, b)
                 mark(f"group {g_}", 1)
+            if averager is not None:
+                averager.finish()
         if overlap_update:
             main.wait_event(blocks_done)
             before_embeddings()
@@ -552,6 +574,7 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         if step_start is not None:
             step_start.record()
         graphs[key].replay()
+        mark("forward + backward graph", 1)
         reduce_grads(g_upd.replay)
         g_upd_emb.replay()
         return losses_static[key]
@@ -593,6 +616,10 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
         from sparse.spmm import check_status
         check_status()
     set_device_rng_offset(None)
+    if averager is not None:        # peers unmap this rank's buffers before they are freed
+        torch.cuda.synchronize()
+        averager.close()
+        dist.barrier()
     del graphs, g_upd, g_upd_emb, model, flat, flat_p, flat_m, flat_v
     torch.cuda.empty_cache()
     if own_group:
@@ -600,8 +627,11 @@ def run_graphs(steps, warmup, mode="sparse", batch=8, seq=1024, vocab=50304, lay
     if verbose and rank == 0:
         print({k: v for k, v in res.items() if k != "losses"})
         for name, (ev0, ev1) in (trace or {}).items():
-            print(f"  exchange {name}: starts {step_start.elapsed_time(ev0):.2f} ms into the step, takes "
-                  f"{ev0.elapsed_time(ev1):.2f} ms")
+            if ev0 is None:
+                print(f"  {name}: ends {step_start.elapsed_time(ev1):.2f} ms into the step")
+            else:
+                print(f"  exchange {name}: starts {step_start.elapsed_time(ev0):.2f} ms into the step, takes "
+                      f"{ev0.elapsed_time(ev1):.2f} ms")
     return res
 
 

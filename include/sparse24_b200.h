@@ -66,6 +66,16 @@ const char *sp24_strerror(int code);
 int sp24_abi_version(void);
 
 /*
+ * Peer memory for a gradient exchange that runs on the copy engines instead of on SMs (no counterpart in the
+ * reference): map a buffer another process of this node exported (a 64-byte cudaIpcMemHandle_t, e.g. from
+ * cudaIpcGetMemHandle or the framework's storage-sharing call) into this process; *ptr is then the base address of
+ * the exporter's allocation, valid on the current device, and copies from it are ordinary asynchronous
+ * device-to-device copies.  One open per handle and process; close before the exporter frees the buffer.
+ */
+int sp24_ipc_open(const void *handle, int handle_bytes, void **ptr);
+int sp24_ipc_close(void *ptr);
+
+/*
  * Dense -> 2:4 compressed (values + reordered metadata), fused prune + compress + metadata.
  * Replaces sparse_semi_structured_from_dense_triton and the Triton kernels
  * _sparse_semi_structured_from_dense_triton_16 / _8

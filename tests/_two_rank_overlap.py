@@ -32,6 +32,11 @@ ok = ok and all(abs(a - b) < 2e-2 for a, b in zip(r["losses"], losses[4]))     #
 r = train_gpt2.run_graphs(steps=5, warmup=2, mode="dense", batch=2, seq=256, layers=4, return_losses=True, comm_groups=4,
                           reduce_dtype=torch.bfloat16)
 ok = ok and all(abs(a - b) < 2e-2 for a, b in zip(r["losses"], losses[4]))
+# the same average from peer-to-peer copies on the DMA engines (sparse.peer) instead of NCCL's all-reduce kernels: with
+# two ranks both compute (a + b) / 2, bit for bit
+r = train_gpt2.run_graphs(steps=5, warmup=2, mode="dense", batch=2, seq=256, layers=4, return_losses=True, comm_groups=4,
+                          exchange="copy")
+ok = ok and r["losses"] == losses[4]
 # the library's trainer kernels (atomics: last-bit differences between runs), one group against four
 train_gpt2.FUSED_OPS = True
 fused = {}

@@ -160,6 +160,11 @@ def test_bad_arguments_are_rejected_without_a_gpu(lib):
     assert lib.sp24_cross_entropy_fused(p, BF16, q, r, st, 1.0, None, 4, 64, 64, 64, None) == -5
     assert lib.sp24_scale_unless_one(p, BF16, None, 64, None) == -5
     assert lib.sp24_scale_unless_one(p, BF16, q, 60, None) == -1
+    # peer memory: a handle is the 64 bytes of a cudaIpcMemHandle_t
+    out_ptr = ctypes.c_void_p()
+    assert lib.sp24_ipc_open(None, 64, ctypes.byref(out_ptr)) == -5
+    assert lib.sp24_ipc_open(p, 63, ctypes.byref(out_ptr)) == -5
+    assert lib.sp24_ipc_close(None) == -5
     assert lib.sp24_gelu(p, None, q, F32, 64, None) == -3
     assert lib.sp24_gelu(p, None, q, BF16, 60, None) == -1
     assert lib.sp24_gelu(p, None, None, BF16, 64, None) == -5
