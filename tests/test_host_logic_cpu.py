@@ -77,3 +77,34 @@ def test_tensor_core_metadata_cache_notices_in_place_writes():
     assert spmm._tc_meta_cache[id(meta)][2] != spmm._stamp(meta)
     spmm.invalidate_meta(meta)
     assert id(meta) not in spmm._tc_meta_cache
+
+
+def test_masked_add_storage_order_view():
+    """The flat view over a tensor's elements in storage order: identity for contiguous tensors, the underlying
+    buffer for transposed / permuted ones, None when the storage has gaps."""
+    from sparse.decay import _storage_order
+    a = torch.arange(24.).reshape(4, 6)
+    assert torch.equal(_storage_order(a), a.reshape(-1))
+    assert torch.equal(_storage_order(a.t()), a.reshape(-1))            # same storage, same order
+    b = torch.arange(120.).reshape(2, 3, 4, 5).permute(2, 0, 3, 1)
+    assert torch.equal(_storage_order(b), torch.arange(120.))
+    assert _storage_order(a[:, ::2]) is None                            # gaps
+    assert _storage_order(a[1:3, :]).numel() == 12                      # a contiguous slab keeps its offset
+    assert torch.equal(_storage_order(a[1:3, :]), a.reshape(-1)[6:18])
+    assert _storage_order(a.expand(2, 4, 6)) is None                    # overlapping (stride 0)
+
+
+def test_copy_engine_average_shards_partition_every_range():
+    """The shards of a range, one per rank, are disjoint, in order, cover the range exactly and start on multiples of
+    eight elements from its beginning (16-byte pieces for 16-bit values)."""
+    from sparse.peer import CopyEngineAverage
+    for world in (2, 3, 4, 8):
+        avg = CopyEngineAverage.__new__(CopyEngineAverage)
+        avg.world = world
+        for a, b in ((0, 8), (16, 16 + 85_000_004), (4, 4 + 7), (0, 38_633_472), (8, 8 + 63)):
+            pos = a
+            for p in range(world):
+                lo, hi = avg._shard(a, b, p)
+                assert lo == pos and hi >= lo and (lo - a) % 8 == 0 or lo == b
+                pos = hi
+            assert pos == b
