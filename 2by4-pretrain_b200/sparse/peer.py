@@ -36,8 +36,16 @@ class PeerBuffers:
             raise RuntimeError("PeerBuffers: contiguous tensors only")
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.local = tensor
-        shared = tensor.untyped_storage()._share_cuda_()
+        storage = tensor.untyped_storage()
+        shared = storage._share_cuda_()
         handle, offset = bytes(shared[1]), int(shared[3])
+        # The framework counts references of a shared block on behalf of consumers that rebuild it through its own
+        # machinery; the peers here map the block themselves and are held off by close() + a barrier instead, so the
+        # count taken by the call above is handed straight back (otherwise the block would stay parked until exit).
+        try:
+            type(storage)._release_ipc_counter(shared[4], shared[5], device=shared[0])
+        except Exception:    # a torch without this hook: the block is released at process exit
+            pass
         # newer torch puts a version byte and a type byte ('c': plain cudaMalloc block, 'e': expandable segment) in
         # front of the 64 bytes of the cudaIpcMemHandle_t
         if len(handle) == 66 and handle[1:2] == b"c":
