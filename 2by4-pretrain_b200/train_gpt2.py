@@ -643,9 +643,15 @@ if __name__ == "__main__":
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--graphs", action="store_true", help="replay the step from CUDA graphs")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "copy"],
+                    help="with --graphs and several ranks: NCCL all-reduce kernels, or peer copies on the DMA engines")
+    ap.add_argument("--bf16-exchange", action="store_true", help="with --graphs: exchange the gradients as bf16")
     a = ap.parse_args()
     t0 = time.time()
-    fn = run_graphs if a.graphs else run
-    r = fn(a.steps, a.warmup, a.mode, batch=a.batch, layers=a.layers, verbose=True)
+    if a.graphs:
+        r = run_graphs(a.steps, a.warmup, a.mode, batch=a.batch, layers=a.layers, verbose=True, exchange=a.exchange,
+                       reduce_dtype=torch.bfloat16 if a.bf16_exchange else torch.float32)
+    else:
+        r = run(a.steps, a.warmup, a.mode, batch=a.batch, layers=a.layers, verbose=True)
     if int(os.environ.get("RANK", "0")) == 0:
         print(f"wall {time.time() - t0:.1f}s")
